@@ -1,0 +1,229 @@
+/*
+ * kcg_kernels.h — C ABI of the B200 (sm_100a) operator kernels.
+ *
+ * The reference project (KernelCodeGen) never executes a kernel itself: its
+ * Optimizer + Backend print CUDA C source, one `__global__ kernelN(T* arg0, ...)`
+ * per operator, whose parameters are flat row-major device pointers in
+ * function-argument order followed by the outputs, with the static shape baked
+ * into the text (src/Backend/CUDA.cc:1019-1064) and the launch geometry passed
+ * out of band as a comment.  An external harness compiled and launched that
+ * text.  This header is the replacement for that boundary: one entry point per
+ * operator family, taking the same flat device pointers plus the shape the
+ * reference baked in, and launching a hand-written sm_100a kernel.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer owned by the caller; nothing here
+ *     synchronises the stream or copies to the host unless stated;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - every function returns a kcg_status (0 = success) and never aborts;
+ *   - tensors are dense row-major unless a leading dimension / stride is given;
+ *   - element counts and strides are in ELEMENTS, not bytes;
+ *   - functions are re-entrant; kernels launched on different streams do not
+ *     share state, except the per-device scratch buffer documented at
+ *     kcg_layernorm().
+ */
+#ifndef KCG_KERNELS_H_
+#define KCG_KERNELS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define KCG_API
+#else
+#define KCG_API __attribute__((visibility("default")))
+#endif
+
+/* dtype strings of the reference Frontend (src/Frontend/Operators.cc:5-15)
+ * plus the two storage types the B200 configs add. */
+typedef enum kcg_dtype {
+  KCG_F32 = 0,    /* "float32"      */
+  KCG_F16 = 1,    /* "float16"      */
+  KCG_BF16 = 2,   /* "bfloat16"     (extension) */
+  KCG_F8E4M3 = 3, /* "float8_e4m3"  (extension) */
+  KCG_I32 = 4,    /* "int32"        (ElementWise "Cast" target) */
+  KCG_F64 = 5,    /* "float64"      (accepted by the graph builder only) */
+  KCG_I64 = 6,    /* "int64"        (accepted by the graph builder only) */
+  KCG_I16 = 7,    /* "int16"        (accepted by the graph builder only) */
+  KCG_BOOL = 8    /* "bool"         (accepted by the graph builder only) */
+} kcg_dtype;
+
+typedef enum kcg_status {
+  KCG_OK = 0,
+  KCG_ERR_INVALID_ARG = 1,  /* null pointer, non-positive size, bad enum      */
+  KCG_ERR_UNSUPPORTED = 2,  /* legal request this build has no kernel for     */
+  KCG_ERR_ALIGNMENT = 3,    /* pointer / leading dimension not 16-byte aligned */
+  KCG_ERR_CUDA = 4,         /* a CUDA runtime / driver call failed            */
+  KCG_ERR_TIMEOUT = 5,      /* a bounded device-side wait gave up             */
+  KCG_ERR_NO_DEVICE = 6     /* no sm_100 device is current                    */
+} kcg_status;
+
+/* ElementWise::operationMap keys (src/Frontend/Operators.cc:997-1000). */
+typedef enum kcg_unary_op {
+  KCG_UNARY_TANH = 0,
+  KCG_UNARY_SQRT = 1,
+  KCG_UNARY_LOG = 2,
+  KCG_UNARY_RELU = 3,
+  KCG_UNARY_CAST = 4,
+  KCG_UNARY_GELU = 5
+} kcg_unary_op;
+
+/* Binary::operationMap keys (src/Frontend/Operators.cc:609-612). */
+typedef enum kcg_binary_op {
+  KCG_BINARY_ADD = 0,
+  KCG_BINARY_MUL = 1,
+  KCG_BINARY_DIV = 2,
+  KCG_BINARY_SUB = 3,
+  KCG_BINARY_POW = 4,
+  KCG_BINARY_EQUAL = 5,
+  KCG_BINARY_GREATER = 6
+} kcg_binary_op;
+
+#define KCG_MAX_RANK 8
+
+KCG_API const char* kcg_status_string(int status);
+/* Text of the most recent failure on the calling thread ("" if none). */
+KCG_API const char* kcg_last_error(void);
+KCG_API int kcg_version(void);
+/*
+ * Kernels that wait on hardware barriers bound every wait; one that gives up stores a
+ * kcg_status in a host-mapped word instead of hanging.  Call this after the stream has
+ * been synchronised: it returns that word (KCG_OK if no kernel reported anything) and
+ * clears it.
+ */
+KCG_API int kcg_device_status(void);
+KCG_API size_t kcg_dtype_size(int dtype);
+
+/*
+ * LayerNorm — replaces the kernel emitted for `LayerNorm_{dims}_axis_{a}`
+ * (builder: src/Frontend/Operators.cc:1076-1251; schedule:
+ * src/Optimizer/Optimizer.cc:1802-1930).
+ *
+ *   rows = product of the dims before `axis`, cols = product of the dims from
+ *   `axis` on.  For each row: mean = sum(x)/cols; d = x - mean;
+ *   var = sum(d*d)/cols (biased); y = gamma * (d / sqrt(var + eps)) + beta.
+ *   gamma and beta hold `cols` elements of the same dtype as x.  Statistics are
+ *   accumulated in fp32 whatever the storage dtype.  y may alias x (the
+ *   reference's MemorySpace::inplace).
+ *
+ *   dtype: KCG_F32, KCG_BF16 or KCG_F16.
+ *
+ *   Rows too long to be held on chip by one thread block are split over several
+ *   blocks; that path keeps per-chunk statistics in a per-device scratch buffer
+ *   that the library allocates (cudaMalloc) on first use and re-uses afterwards.
+ *   Two such calls running concurrently on one device from different streams
+ *   would share it: serialise them.
+ */
+KCG_API int kcg_layernorm(int dtype, int64_t rows, int64_t cols, const void* x,
+                          const void* gamma, const void* beta, float eps, void* y,
+                          void* stream);
+
+/*
+ * Unary elementwise map — replaces `{Op}_Elementwise_{dims}` and
+ * `Relu_Elementwise_{dims}` (builders: src/Frontend/Operators.cc:222-289 and
+ * :1003-1074; schedule: src/Optimizer/Optimizer.cc:1080-1175).
+ *
+ *   Gelu is the tanh form with the reference's literal constants:
+ *   0.5*x*(1 + tanh(0.797884*(x + 0.044715*x^3))).  Cast is a value conversion
+ *   (the generated code prints static_cast, src/Backend/CUDA.cc:537-548);
+ *   float -> int32 truncates toward zero.  For every op other than Cast
+ *   dtype_out must equal dtype_in.  y may alias x when the dtypes have equal size.
+ *
+ *   dtype_in: KCG_F32, KCG_BF16, KCG_F16 (and KCG_I32 for Cast).
+ */
+KCG_API int kcg_eltwise(int op, int dtype_in, int dtype_out, int64_t n, const void* x,
+                        void* y, void* stream);
+
+/*
+ * Binary elementwise map with numpy-style broadcasting — replaces
+ * `{Op}_Binary_{dimsA}_{Op}_{dimsB}` (builder:
+ * src/Frontend/Operators.cc:772-889; schedule: src/Optimizer/Optimizer.cc:928-991).
+ *
+ *   Shapes are aligned at the trailing dimension; where they differ one of the
+ *   two extents must be 1.  The output has the broadcast shape and the dtype of
+ *   the inputs.  Equal / Greater write 1 or 0 in that dtype.
+ *   rank_a, rank_b <= KCG_MAX_RANK.  c may alias a when a has the output shape.
+ */
+KCG_API int kcg_binary(int op, int dtype, int rank_a, const int64_t* shape_a, int rank_b,
+                       const int64_t* shape_b, const void* a, const void* b, void* c,
+                       void* stream);
+
+/*
+ * Row softmax over the last dimension — replaces `Softmax_{dims}_axis{a}`
+ * (builder: src/Frontend/Operators.cc:462-578):  y = exp(s*x) / sum(exp(s*x)),
+ * evaluated in the max-subtracted form.  `scale` (s) and `causal` are extensions
+ * with neutral defaults 1.0f / 0: with causal != 0 the row index within the
+ * trailing [q_len, cols] matrix masks columns j > i + (cols - q_len).
+ * y may alias x (the reference's Softmax is always in place).
+ */
+KCG_API int kcg_softmax(int dtype, int64_t rows, int64_t cols, float scale, int causal,
+                        int64_t q_len, const void* x, void* y, void* stream);
+
+/*
+ * GEMM — replaces `Matmul_m{m}n{n}k{k}` and
+ * `BatchMatmul_{b..}_m{m}_n{n}_k{k}_{N|T}{N|T}` (builders:
+ * src/Frontend/Operators.cc:120-220 and :291-457; schedules:
+ * src/Optimizer/Optimizer.cc:406-570 and :3290-3445).
+ *
+ *   For each batch index g in [0, batch):
+ *     C_g[m, n] = alpha * sum_k opA(A_g)[m, k] * opB(B_g)[k, n]
+ *   trans_a == 0: A_g is [M, K] row-major with leading dimension lda (Layout::rowMajor);
+ *   trans_a != 0: A_g is [K, M] row-major with leading dimension lda (Layout::colMajor);
+ *   trans_b == 0: B_g is [K, N] row-major, ldb (Layout::rowMajor);
+ *   trans_b != 0: B_g is [N, K] row-major, ldb (Layout::colMajor).
+ *   X_g = X + g * stride_x (elements).  C_g is [M, N] row-major, ldc.
+ *   alpha = (scale_a ? *scale_a : 1) * (scale_b ? *scale_b : 1), read on the
+ *   device (per-tensor FP8 de-quantisation scales); pass NULL for 1.
+ *
+ *   dtype_in / dtype_out combinations:
+ *     KCG_BF16 -> KCG_BF16 | KCG_F32, KCG_F16 -> KCG_F16 | KCG_F32
+ *         tcgen05 tensor-core kernel, fp32 accumulation in tensor memory;
+ *     KCG_F8E4M3 -> KCG_BF16 | KCG_F32   tcgen05 kind::f8f6f4, fp32 accumulation;
+ *     KCG_F32 -> KCG_F32   CUDA-core FFMA kernel, sequential-k fp32 accumulation
+ *         (the reference's own arithmetic; tensor cores cannot hold 1e-5).
+ *   Tensor-core paths need 16-byte aligned base pointers and leading dimensions
+ *   / batch strides that are multiples of 16 bytes; M, N, K are arbitrary.
+ */
+KCG_API int kcg_gemm(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K,
+                     int64_t batch, int trans_a, int trans_b, const void* A, int64_t lda,
+                     int64_t stride_a, const void* B, int64_t ldb, int64_t stride_b, void* C,
+                     int64_t ldc, int64_t stride_c, const float* scale_a,
+                     const float* scale_b, void* stream);
+
+/*
+ * Fused multi-head attention forward — replaces
+ * `Fused_Multi_Head_Attention_{batch..}_SL{S}_HD{D}`, the kernel the reference
+ * builds when it finds BatchMatmul(NT) -> Softmax -> BatchMatmul(NN)
+ * (match: src/Optimizer/Optimizer.cc:2113-2199; build: :2606-2860).
+ *
+ *   O[b,h,i,:] = sum_j softmax_j(softmax_scale * Q[b,h,i,:].K[b,h,j,:]) * V[b,h,j,:]
+ *   causal != 0 masks j > i + (Skv - Sq).  The reference has neither scale nor
+ *   mask: pass 1.0f and 0 for its semantics.
+ *   Each tensor is addressed as base + b*stride[0] + h*stride[1] + s*stride[2] + d
+ *   (elements; the head dimension is contiguous), so [B,H,S,D] and [B,S,H,D]
+ *   layouts are both expressible.  dtype: KCG_BF16 or KCG_F16; D in {64, 128}.
+ *   Softmax statistics are kept in fp32.
+ */
+KCG_API int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int64_t D,
+                         float softmax_scale, int causal, const void* Q,
+                         const int64_t q_strides[3], const void* K, const int64_t k_strides[3],
+                         const void* V, const int64_t v_strides[3], void* O,
+                         const int64_t o_strides[3], void* stream);
+
+/*
+ * Row-range owned by one rank when `total` independent units (GEMM rows of A/C,
+ * attention batch*head slices, LayerNorm / elementwise rows) are split over
+ * `world` GPUs in contiguous blocks rounded to `granule` units.  The reference
+ * has no multi-GPU code; this is the only sharding rule the library uses.
+ */
+KCG_API int kcg_shard_range(int64_t total, int world, int rank, int64_t granule,
+                            int64_t* begin, int64_t* count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KCG_KERNELS_H_ */

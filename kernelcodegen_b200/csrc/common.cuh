@@ -1,0 +1,125 @@
+// Shared host/device helpers for the sm_100a operator kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "kcg_kernels.h"
+
+namespace kcg {
+
+// Records a human-readable message for kcg_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+void clear_error();
+
+#define KCG_CUDA_OK(expr)                                                               \
+  do {                                                                                  \
+    cudaError_t _e = (expr);                                                            \
+    if (_e != cudaSuccess)                                                              \
+      return ::kcg::fail(KCG_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                  \
+                         cudaGetErrorString(_e), __FILE__, __LINE__);                   \
+  } while (0)
+
+// Returns KCG_OK if the launch that just happened was accepted by the runtime.
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(KCG_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+  return KCG_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// ---- storage <-> fp32 conversion -------------------------------------------------
+template <typename T> struct Conv;
+template <> struct Conv<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <> struct Conv<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+template <> struct Conv<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Conv<int32_t> {
+  static __device__ __forceinline__ float to_f(int32_t v) { return static_cast<float>(v); }
+  static __device__ __forceinline__ int32_t from_f(float v) { return static_cast<int32_t>(v); }
+};
+
+// A 16-byte vector of T, loaded and stored with one 128-bit access.
+template <typename T> struct alignas(16) Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  T v[N];
+};
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> ld_vec(const T* p) {
+  Vec16<T> r;
+  *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(p);
+  return r;
+}
+// Streaming variants: data that is touched once should not displace reusable lines.
+template <typename T>
+__device__ __forceinline__ Vec16<T> ld_vec_stream(const T* p) {
+  Vec16<T> r;
+  *reinterpret_cast<uint4*>(&r) = __ldcs(reinterpret_cast<const uint4*>(p));
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void st_vec(T* p, const Vec16<T>& r) {
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&r);
+}
+template <typename T>
+__device__ __forceinline__ void st_vec_stream(T* p, const Vec16<T>& r) {
+  __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&r));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the whole thread block; every thread receives the result.
+// `scratch` holds at least 33 floats of shared memory.  Safe to call repeatedly.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  if (nwarps == 1) return v;
+  __syncthreads();  // protect scratch from the previous call's readers
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  if (nwarps == 1) return v;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+}  // namespace kcg

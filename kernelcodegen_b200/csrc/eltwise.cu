@@ -1,0 +1,449 @@
+// Unary maps, binary maps with broadcasting, and the row softmax.
+//
+// Definitions follow the reference Frontend: unary ops
+// src/Frontend/Operators.cc:960-1000 (Gelu with the literal constants 0.797884 and
+// 0.044715), Relu :222-289, binary ops and the broadcast rule :581-612 and :772-889,
+// softmax :462-578.  The reference schedules (src/Optimizer/Optimizer.cc:928-1175)
+// tile a near-square 2-D view 64x64 with 4x4 elements per thread; here every map is a
+// flat stream of 128-bit accesses, because the ops are HBM-bound and have no reuse.
+#include "common.cuh"
+
+namespace kcg {
+namespace {
+
+// ---------------------------------------------------------------- unary functors
+// kFast selects hardware approximations whose error is below the rounding of a
+// 16-bit result; fp32 results use the accurate library routines.
+template <bool kFast> __device__ __forceinline__ float tanh_f(float v) {
+  if constexpr (kFast) {
+    float r;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+  } else {
+    return tanhf(v);
+  }
+}
+
+struct OpTanh { template <bool F> static __device__ __forceinline__ float f(float v) { return tanh_f<F>(v); } };
+struct OpSqrt { template <bool F> static __device__ __forceinline__ float f(float v) { return sqrtf(v); } };
+struct OpLog  { template <bool F> static __device__ __forceinline__ float f(float v) { return F ? __logf(v) : logf(v); } };
+struct OpRelu { template <bool F> static __device__ __forceinline__ float f(float v) { return fmaxf(0.f, v); } };
+struct OpCast { template <bool F> static __device__ __forceinline__ float f(float v) { return v; } };
+struct OpGelu {
+  template <bool F> static __device__ __forceinline__ float f(float v) {
+    const float inner = 0.797884f * (0.044715f * (v * (v * v)) + v);
+    return (v * 0.5f) * (tanh_f<F>(inner) + 1.0f);
+  }
+};
+
+template <typename TI, typename TO, typename Op, int UNROLL>
+__global__ void __launch_bounds__(256)
+unary_vec(const TI* __restrict__ x, TO* __restrict__ y, int64_t ngroups) {
+  // One group = EPT elements = whole 16-byte vectors on both sides.
+  constexpr int EPT = 16 / (sizeof(TI) < sizeof(TO) ? sizeof(TI) : sizeof(TO));
+  constexpr int NI = EPT * sizeof(TI) / 16, NO = EPT * sizeof(TO) / 16;
+  constexpr bool kFast = sizeof(TO) < 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int64_t g0 = static_cast<int64_t>(blockIdx.x) * blockDim.x * UNROLL + threadIdx.x;
+  for (; g0 < ngroups; g0 += stride * UNROLL) {
+    Vec16<TI> in[UNROLL][NI];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t g = g0 + static_cast<int64_t>(u) * blockDim.x;
+      if (g < ngroups) {
+#pragma unroll
+        for (int k = 0; k < NI; ++k) in[u][k] = ld_vec_stream(x + g * EPT + k * Vec16<TI>::N);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t g = g0 + static_cast<int64_t>(u) * blockDim.x;
+      if (g < ngroups) {
+        Vec16<TO> out[NO];
+#pragma unroll
+        for (int e = 0; e < EPT; ++e) {
+          const float v = Conv<TI>::to_f(in[u][e / Vec16<TI>::N].v[e % Vec16<TI>::N]);
+          out[e / Vec16<TO>::N].v[e % Vec16<TO>::N] = Conv<TO>::from_f(Op::template f<kFast>(v));
+        }
+#pragma unroll
+        for (int k = 0; k < NO; ++k) st_vec_stream(y + g * EPT + k * Vec16<TO>::N, out[k]);
+      }
+    }
+  }
+}
+
+template <typename TI, typename TO, typename Op>
+__global__ void __launch_bounds__(256)
+unary_scalar(const TI* __restrict__ x, TO* __restrict__ y, int64_t begin, int64_t n) {
+  constexpr bool kFast = sizeof(TO) < 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = begin + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = Conv<TO>::from_f(Op::template f<kFast>(Conv<TI>::to_f(x[i])));
+}
+
+template <typename TI, typename TO, typename Op>
+int launch_unary(int64_t n, const void* xv, void* yv, cudaStream_t stream) {
+  const TI* x = static_cast<const TI*>(xv);
+  TO* y = static_cast<TO*>(yv);
+  constexpr int EPT = 16 / (sizeof(TI) < sizeof(TO) ? sizeof(TI) : sizeof(TO));
+  constexpr int UNROLL = 4;
+  const int sms = sm_count();
+  int64_t done = 0;
+  if (aligned16(x) && aligned16(y) && n >= EPT) {
+    const int64_t ngroups = n / EPT;
+    const int64_t want = (ngroups + 256 * UNROLL - 1) / (256 * UNROLL);
+    const int64_t cap = static_cast<int64_t>(sms) * 8;
+    unary_vec<TI, TO, Op, UNROLL><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(x, y, ngroups);
+    int rc = check_launch("unary_vec");
+    if (rc) return rc;
+    done = ngroups * EPT;
+  }
+  if (done < n) {
+    const int64_t rest = n - done;
+    const int64_t want = (rest + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(sms) * 8;
+    unary_scalar<TI, TO, Op><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(x, y, done, n);
+    return check_launch("unary_scalar");
+  }
+  return KCG_OK;
+}
+
+template <typename T, typename Op>
+int unary_same(int dtype, int64_t n, const void* x, void* y, cudaStream_t s);
+
+template <typename Op>
+int dispatch_unary_same(int dtype, int64_t n, const void* x, void* y, cudaStream_t s) {
+  switch (dtype) {
+    case KCG_F32: return launch_unary<float, float, Op>(n, x, y, s);
+    case KCG_BF16: return launch_unary<__nv_bfloat16, __nv_bfloat16, Op>(n, x, y, s);
+    case KCG_F16: return launch_unary<__half, __half, Op>(n, x, y, s);
+    default: return fail(KCG_ERR_UNSUPPORTED, "eltwise: dtype %d has no kernel (float32, bfloat16, float16)", dtype);
+  }
+}
+
+template <typename TI>
+int dispatch_cast_out(int dtype_out, int64_t n, const void* x, void* y, cudaStream_t s) {
+  switch (dtype_out) {
+    case KCG_F32: return launch_unary<TI, float, OpCast>(n, x, y, s);
+    case KCG_BF16: return launch_unary<TI, __nv_bfloat16, OpCast>(n, x, y, s);
+    case KCG_F16: return launch_unary<TI, __half, OpCast>(n, x, y, s);
+    case KCG_I32: return launch_unary<TI, int32_t, OpCast>(n, x, y, s);
+    default: return fail(KCG_ERR_UNSUPPORTED, "eltwise Cast: target dtype %d has no kernel", dtype_out);
+  }
+}
+
+// ---------------------------------------------------------------- binary functors
+struct BAdd { static __device__ __forceinline__ float f(float a, float b) { return a + b; } };
+struct BMul { static __device__ __forceinline__ float f(float a, float b) { return a * b; } };
+struct BDiv { static __device__ __forceinline__ float f(float a, float b) { return a / b; } };
+struct BSub { static __device__ __forceinline__ float f(float a, float b) { return a - b; } };
+struct BPow { static __device__ __forceinline__ float f(float a, float b) { return powf(a, b); } };
+struct BEq  { static __device__ __forceinline__ float f(float a, float b) { return a == b ? 1.f : 0.f; } };
+struct BGt  { static __device__ __forceinline__ float f(float a, float b) { return a > b ? 1.f : 0.f; } };
+
+// Both operands have the output shape.
+template <typename T, typename Op, int UNROLL>
+__global__ void __launch_bounds__(256)
+binary_same_vec(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ c, int64_t nvec) {
+  constexpr int VW = Vec16<T>::N;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int64_t g0 = static_cast<int64_t>(blockIdx.x) * blockDim.x * UNROLL + threadIdx.x;
+  for (; g0 < nvec; g0 += stride * UNROLL) {
+    Vec16<T> va[UNROLL], vb[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t g = g0 + static_cast<int64_t>(u) * blockDim.x;
+      if (g < nvec) {
+        va[u] = ld_vec_stream(a + g * VW);
+        vb[u] = ld_vec_stream(b + g * VW);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t g = g0 + static_cast<int64_t>(u) * blockDim.x;
+      if (g < nvec) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < VW; ++j)
+          o.v[j] = Conv<T>::from_f(Op::f(Conv<T>::to_f(va[u].v[j]), Conv<T>::to_f(vb[u].v[j])));
+        st_vec_stream(c + g * VW, o);
+      }
+    }
+  }
+}
+
+// General broadcast.  Dimensions are collapsed on the host; dim 0 is innermost.
+struct BcastDims {
+  int rank;
+  int64_t extent[KCG_MAX_RANK];
+  int64_t stride_a[KCG_MAX_RANK];  // 0 where a is broadcast
+  int64_t stride_b[KCG_MAX_RANK];
+};
+
+// Each thread produces VEC consecutive outputs along the innermost dimension
+// (extent[0] % VEC == 0).  An operand whose inner stride is 1 is read as a vector
+// when VEC is a whole 16-byte vector; one whose inner stride is 0 is read once.
+template <typename T, typename Op, int VEC>
+__global__ void __launch_bounds__(256)
+binary_bcast(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ c,
+             const BcastDims d, int64_t ngroups) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t inner_groups = d.extent[0] / VEC;
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < ngroups; g += stride) {
+    int64_t rem = g / inner_groups;
+    const int64_t i0 = (g % inner_groups) * VEC;
+    int64_t oa = i0 * d.stride_a[0], ob = i0 * d.stride_b[0];
+#pragma unroll 1
+    for (int k = 1; k < d.rank; ++k) {
+      const int64_t idx = rem % d.extent[k];
+      rem /= d.extent[k];
+      oa += idx * d.stride_a[k];
+      ob += idx * d.stride_b[k];
+    }
+    float fa[VEC], fb[VEC];
+    if constexpr (VEC == Vec16<T>::N) {
+      if (d.stride_a[0] == 1) {
+        Vec16<T> t = ld_vec(a + oa);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) fa[j] = Conv<T>::to_f(t.v[j]);
+      } else {
+        const float s = Conv<T>::to_f(a[oa]);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) fa[j] = s;
+      }
+      if (d.stride_b[0] == 1) {
+        Vec16<T> t = ld_vec(b + ob);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) fb[j] = Conv<T>::to_f(t.v[j]);
+      } else {
+        const float s = Conv<T>::to_f(b[ob]);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) fb[j] = s;
+      }
+      Vec16<T> o;
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) o.v[j] = Conv<T>::from_f(Op::f(fa[j], fb[j]));
+      st_vec(c + g * VEC, o);
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        fa[j] = Conv<T>::to_f(a[oa + j * d.stride_a[0]]);
+        fb[j] = Conv<T>::to_f(b[ob + j * d.stride_b[0]]);
+        c[g * VEC + j] = Conv<T>::from_f(Op::f(fa[j], fb[j]));
+      }
+    }
+  }
+}
+
+template <typename T, typename Op>
+int launch_binary(const BcastDims& d, bool same_shape, int64_t total, const void* av,
+                  const void* bv, void* cv, cudaStream_t stream) {
+  const T* a = static_cast<const T*>(av);
+  const T* b = static_cast<const T*>(bv);
+  T* c = static_cast<T*>(cv);
+  constexpr int VW = Vec16<T>::N;
+  const int sms = sm_count();
+  const int64_t cap = static_cast<int64_t>(sms) * 8;
+  const bool al = aligned16(a) && aligned16(b) && aligned16(c);
+  if (same_shape && al && total % VW == 0) {
+    constexpr int UNROLL = 4;
+    const int64_t nvec = total / VW;
+    const int64_t want = (nvec + 256 * UNROLL - 1) / (256 * UNROLL);
+    binary_same_vec<T, Op, UNROLL><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(a, b, c, nvec);
+    return check_launch("binary_same_vec");
+  }
+  // Vector accesses along the innermost dimension need every outer stride to keep
+  // 16-byte alignment, which holds when the inner extent is a multiple of VW.
+  bool vec_ok = al && d.extent[0] % VW == 0;
+  for (int k = 1; k < d.rank && vec_ok; ++k)
+    vec_ok = (d.stride_a[k] % VW == 0) && (d.stride_b[k] % VW == 0);
+  if (vec_ok) {
+    const int64_t ngroups = total / VW;
+    const int64_t want = (ngroups + 255) / 256;
+    binary_bcast<T, Op, VW><<<static_cast<int>(want < cap * 4 ? want : cap * 4), 256, 0, stream>>>(a, b, c, d, ngroups);
+  } else {
+    const int64_t want = (total + 255) / 256;
+    binary_bcast<T, Op, 1><<<static_cast<int>(want < cap * 4 ? want : cap * 4), 256, 0, stream>>>(a, b, c, d, total);
+  }
+  return check_launch("binary_bcast");
+}
+
+template <typename Op>
+int dispatch_binary_dtype(int dtype, const BcastDims& d, bool same, int64_t total, const void* a,
+                          const void* b, void* c, cudaStream_t s) {
+  switch (dtype) {
+    case KCG_F32: return launch_binary<float, Op>(d, same, total, a, b, c, s);
+    case KCG_BF16: return launch_binary<__nv_bfloat16, Op>(d, same, total, a, b, c, s);
+    case KCG_F16: return launch_binary<__half, Op>(d, same, total, a, b, c, s);
+    default: return fail(KCG_ERR_UNSUPPORTED, "binary: dtype %d has no kernel (float32, bfloat16, float16)", dtype);
+  }
+}
+
+// ---------------------------------------------------------------- softmax
+// One thread block per row, the row is read twice (max+sum online, then normalise);
+// the second read of a row that was just streamed is served from L2.
+template <typename T>
+__global__ void __launch_bounds__(256)
+softmax_rows(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int64_t cols, float scale,
+             int causal, int64_t q_len) {
+  __shared__ float red[33];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + row * cols;
+    T* yr = y + row * cols;
+    int64_t valid = cols;
+    if (causal) {
+      const int64_t i = row % q_len;
+      valid = i + (cols - q_len) + 1;
+      if (valid > cols) valid = cols;
+      if (valid < 0) valid = 0;
+    }
+    float m = -INFINITY, s = 0.f;
+    for (int64_t j = threadIdx.x; j < valid; j += blockDim.x) {
+      const float v = Conv<T>::to_f(xr[j]) * scale;
+      const float nm = fmaxf(m, v);
+      s = s * __expf(m - nm) + __expf(v - nm);
+      m = nm;
+    }
+    const float gm = block_max(m, red);
+    s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+    const float gs = block_sum(s, red);
+    const float inv = gs > 0.f ? 1.0f / gs : 0.f;
+    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) {
+      float o = 0.f;
+      if (j < valid) o = __expf(Conv<T>::to_f(xr[j]) * scale - gm) * inv;
+      yr[j] = Conv<T>::from_f(o);
+    }
+  }
+}
+
+template <typename T>
+int launch_softmax(int64_t rows, int64_t cols, float scale, int causal, int64_t q_len,
+                   const void* x, void* y, cudaStream_t stream) {
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  softmax_rows<T><<<static_cast<int>(rows < cap ? rows : cap), 256, 0, stream>>>(
+      static_cast<const T*>(x), static_cast<T*>(y), rows, cols, scale, causal, q_len);
+  return check_launch("softmax_rows");
+}
+
+}  // namespace
+}  // namespace kcg
+
+extern "C" int kcg_eltwise(int op, int dtype_in, int dtype_out, int64_t n, const void* x, void* y,
+                           void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (n < 0) return fail(KCG_ERR_INVALID_ARG, "eltwise: negative element count");
+  if (n == 0) return KCG_OK;
+  if (!x || !y) return fail(KCG_ERR_INVALID_ARG, "eltwise: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (op != KCG_UNARY_CAST && dtype_in != dtype_out)
+    return fail(KCG_ERR_INVALID_ARG, "eltwise: op %d needs dtype_out == dtype_in (got %d -> %d)", op,
+                dtype_in, dtype_out);
+  switch (op) {
+    case KCG_UNARY_TANH: return dispatch_unary_same<OpTanh>(dtype_in, n, x, y, s);
+    case KCG_UNARY_SQRT: return dispatch_unary_same<OpSqrt>(dtype_in, n, x, y, s);
+    case KCG_UNARY_LOG: return dispatch_unary_same<OpLog>(dtype_in, n, x, y, s);
+    case KCG_UNARY_RELU: return dispatch_unary_same<OpRelu>(dtype_in, n, x, y, s);
+    case KCG_UNARY_GELU: return dispatch_unary_same<OpGelu>(dtype_in, n, x, y, s);
+    case KCG_UNARY_CAST:
+      switch (dtype_in) {
+        case KCG_F32: return dispatch_cast_out<float>(dtype_out, n, x, y, s);
+        case KCG_BF16: return dispatch_cast_out<__nv_bfloat16>(dtype_out, n, x, y, s);
+        case KCG_F16: return dispatch_cast_out<__half>(dtype_out, n, x, y, s);
+        case KCG_I32: return dispatch_cast_out<int32_t>(dtype_out, n, x, y, s);
+        default: return fail(KCG_ERR_UNSUPPORTED, "eltwise Cast: source dtype %d has no kernel", dtype_in);
+      }
+    default: return fail(KCG_ERR_INVALID_ARG, "eltwise: unknown op %d", op);
+  }
+}
+
+extern "C" int kcg_binary(int op, int dtype, int rank_a, const int64_t* shape_a, int rank_b,
+                          const int64_t* shape_b, const void* a, const void* b, void* c,
+                          void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (rank_a < 0 || rank_b < 0 || rank_a > KCG_MAX_RANK || rank_b > KCG_MAX_RANK)
+    return fail(KCG_ERR_INVALID_ARG, "binary: rank out of range (%d, %d; max %d)", rank_a, rank_b, KCG_MAX_RANK);
+  if ((rank_a && !shape_a) || (rank_b && !shape_b)) return fail(KCG_ERR_INVALID_ARG, "binary: null shape");
+  const int rank = rank_a > rank_b ? rank_a : rank_b;
+  // Trailing-aligned extents, innermost first; missing leading dims count as 1.
+  int64_t ea[KCG_MAX_RANK], eb[KCG_MAX_RANK], eo[KCG_MAX_RANK];
+  int64_t total = 1;
+  bool same = true;
+  for (int k = 0; k < rank; ++k) {
+    ea[k] = k < rank_a ? shape_a[rank_a - 1 - k] : 1;
+    eb[k] = k < rank_b ? shape_b[rank_b - 1 - k] : 1;
+    if (ea[k] < 0 || eb[k] < 0) return fail(KCG_ERR_INVALID_ARG, "binary: negative extent");
+    if (ea[k] != eb[k] && ea[k] != 1 && eb[k] != 1)
+      return fail(KCG_ERR_INVALID_ARG, "binary: dim not equal (%lld vs %lld at trailing dim %d)",
+                  static_cast<long long>(ea[k]), static_cast<long long>(eb[k]), k);
+    eo[k] = ea[k] == 1 ? eb[k] : ea[k];
+    if (ea[k] != eb[k]) same = false;
+    total *= eo[k];
+  }
+  if (total == 0) return KCG_OK;
+  if (!a || !b || !c) return fail(KCG_ERR_INVALID_ARG, "binary: null pointer");
+  // Dense strides of each operand; 0 where it is broadcast.
+  int64_t sa[KCG_MAX_RANK], sb[KCG_MAX_RANK];
+  int64_t ra = 1, rb = 1;
+  for (int k = 0; k < rank; ++k) {
+    sa[k] = (ea[k] == 1 && eo[k] != 1) ? 0 : ra;
+    sb[k] = (eb[k] == 1 && eo[k] != 1) ? 0 : rb;
+    ra *= ea[k];
+    rb *= eb[k];
+  }
+  // Collapse neighbours that both operands traverse contiguously (or both broadcast).
+  BcastDims d;
+  d.rank = 0;
+  for (int k = 0; k < rank; ++k) {
+    if (eo[k] == 1) continue;
+    if (d.rank > 0) {
+      const int p = d.rank - 1;
+      if (sa[k] == d.stride_a[p] * d.extent[p] && sb[k] == d.stride_b[p] * d.extent[p]) {
+        d.extent[p] *= eo[k];
+        continue;
+      }
+    }
+    d.extent[d.rank] = eo[k];
+    d.stride_a[d.rank] = sa[k];
+    d.stride_b[d.rank] = sb[k];
+    ++d.rank;
+  }
+  if (d.rank == 0) {
+    d.rank = 1;
+    d.extent[0] = 1;
+    d.stride_a[0] = 0;
+    d.stride_b[0] = 0;
+  }
+  for (int k = d.rank; k < KCG_MAX_RANK; ++k) { d.extent[k] = 1; d.stride_a[k] = 0; d.stride_b[k] = 0; }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (op) {
+    case KCG_BINARY_ADD: return dispatch_binary_dtype<BAdd>(dtype, d, same, total, a, b, c, s);
+    case KCG_BINARY_MUL: return dispatch_binary_dtype<BMul>(dtype, d, same, total, a, b, c, s);
+    case KCG_BINARY_DIV: return dispatch_binary_dtype<BDiv>(dtype, d, same, total, a, b, c, s);
+    case KCG_BINARY_SUB: return dispatch_binary_dtype<BSub>(dtype, d, same, total, a, b, c, s);
+    case KCG_BINARY_POW: return dispatch_binary_dtype<BPow>(dtype, d, same, total, a, b, c, s);
+    case KCG_BINARY_EQUAL: return dispatch_binary_dtype<BEq>(dtype, d, same, total, a, b, c, s);
+    case KCG_BINARY_GREATER: return dispatch_binary_dtype<BGt>(dtype, d, same, total, a, b, c, s);
+    default: return fail(KCG_ERR_INVALID_ARG, "binary: unknown op %d", op);
+  }
+}
+
+extern "C" int kcg_softmax(int dtype, int64_t rows, int64_t cols, float scale, int causal,
+                           int64_t q_len, const void* x, void* y, void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (rows < 0 || cols < 0) return fail(KCG_ERR_INVALID_ARG, "softmax: negative size");
+  if (rows == 0 || cols == 0) return KCG_OK;
+  if (!x || !y) return fail(KCG_ERR_INVALID_ARG, "softmax: null pointer");
+  if (causal && (q_len <= 0 || rows % q_len != 0))
+    return fail(KCG_ERR_INVALID_ARG, "softmax: causal needs q_len > 0 dividing rows (rows=%lld q_len=%lld)",
+                static_cast<long long>(rows), static_cast<long long>(q_len));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case KCG_F32: return launch_softmax<float>(rows, cols, scale, causal, q_len, x, y, s);
+    case KCG_BF16: return launch_softmax<__nv_bfloat16>(rows, cols, scale, causal, q_len, x, y, s);
+    case KCG_F16: return launch_softmax<__half>(rows, cols, scale, causal, q_len, x, y, s);
+    default: return fail(KCG_ERR_UNSUPPORTED, "softmax: dtype %d has no kernel", dtype);
+  }
+}

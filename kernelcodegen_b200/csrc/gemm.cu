@@ -1,0 +1,42 @@
+// kcg_gemm: argument checking and the choice between the tensor-core kernel
+// (gemm_tcgen05.cu) and the fp32 CUDA-core kernel (sgemm.cu).
+#include "common.cuh"
+
+namespace kcg {
+int sgemm_f32(int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a, int trans_b, const float* A,
+              int64_t lda, int64_t stride_a, const float* B, int64_t ldb, int64_t stride_b, float* C,
+              int64_t ldc, int64_t stride_c, const float* scale_a, const float* scale_b, cudaStream_t stream);
+int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
+                 int trans_b, const void* A, int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
+                 int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
+                 const float* scale_b, cudaStream_t stream);
+}  // namespace kcg
+
+extern "C" int kcg_gemm(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch,
+                        int trans_a, int trans_b, const void* A, int64_t lda, int64_t stride_a,
+                        const void* B, int64_t ldb, int64_t stride_b, void* C, int64_t ldc,
+                        int64_t stride_c, const float* scale_a, const float* scale_b, void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (M < 0 || N < 0 || K < 0 || batch < 0) return fail(KCG_ERR_INVALID_ARG, "gemm: negative extent");
+  if (M == 0 || N == 0 || batch == 0) return KCG_OK;
+  if (K == 0) return fail(KCG_ERR_INVALID_ARG, "gemm: K must be positive");
+  if (!A || !B || !C) return fail(KCG_ERR_INVALID_ARG, "gemm: null pointer");
+  const int64_t a_cols = trans_a ? M : K, b_cols = trans_b ? K : N;
+  if (lda < a_cols || ldb < b_cols || ldc < N)
+    return fail(KCG_ERR_INVALID_ARG,
+                "gemm: leading dimension shorter than a row (lda=%lld need %lld, ldb=%lld need %lld, ldc=%lld need %lld)",
+                static_cast<long long>(lda), static_cast<long long>(a_cols), static_cast<long long>(ldb),
+                static_cast<long long>(b_cols), static_cast<long long>(ldc), static_cast<long long>(N));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype_in == KCG_F32) {
+    if (dtype_out != KCG_F32) return fail(KCG_ERR_UNSUPPORTED, "gemm: float32 inputs produce float32");
+    return sgemm_f32(M, N, K, batch, trans_a, trans_b, static_cast<const float*>(A), lda, stride_a,
+                     static_cast<const float*>(B), ldb, stride_b, static_cast<float*>(C), ldc, stride_c,
+                     scale_a, scale_b, s);
+  }
+  if (dtype_in == KCG_BF16 || dtype_in == KCG_F16 || dtype_in == KCG_F8E4M3)
+    return gemm_tcgen05(dtype_in, dtype_out, M, N, K, batch, trans_a, trans_b, A, lda, stride_a, B, ldb,
+                        stride_b, C, ldc, stride_c, scale_a, scale_b, s);
+  return fail(KCG_ERR_UNSUPPORTED, "gemm: input dtype %d has no kernel", dtype_in);
+}

@@ -1,0 +1,409 @@
+// Tensor-core GEMM for sm_100a: C = alpha * op(A) * op(B), 16-bit and FP8 inputs, fp32
+// accumulation in tensor memory.
+//
+// This replaces the kernel the reference emits for Matmul / BatchMatmul
+// (src/Optimizer/Optimizer.cc:406-570, :3290-3445): a 128x128x8 CUDA-core tile with a
+// register/shared double buffer.  The Blackwell design keeps the same roles — stage
+// operand tiles in shared memory, accumulate a C tile on chip, write it once — but maps
+// them to the hardware units that exist for it:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of 128-byte-swizzled A and B
+//               tiles into a 4-stage ring, completion counted on mbarriers;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=32 bytes) from
+//               shared-memory descriptors into one of two 128x256 fp32 accumulators in
+//               tensor memory, and releases ring stages with tcgen05.commit;
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (one TMEM lane quarter per
+//               warp), scale, convert and store, while the MMA warp already fills the
+//               other accumulator with the next tile.
+// CTAs are persistent (one per SM) and walk the tile list in an M-grouped order so that
+// the tiles in flight share A row-blocks and B column-blocks in L2 (the reference's
+// unused GROUP_SIZE_M, include/KernelCodeGen.h:36).
+//
+// Both operand layouts of the reference API are handled without a transpose pass: a
+// row-major [M,K] A or [N,K] B tile is "K-major" for the MMA, a row-major [K,M] A or
+// [K,N] B tile (the plain Matmul's B) is "MN-major"; only the TMA box shape and two
+// descriptor fields differ.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+#include <mutex>
+
+namespace kcg {
+
+int* device_status_word();  // runtime.cu: host-mapped word the kernels report faults into
+
+namespace {
+using namespace sm100;
+
+constexpr int BM = 128, BN = 256, STAGES = 4;
+constexpr int A_BYTES = BM * 128;
+constexpr int B_BYTES = BN * 128;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr int GROUP_M = 8;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+struct GemmParams {
+  void* C;
+  int64_t M, N, K;
+  int64_t ldc, stride_c;
+  int m_tiles, n_tiles;
+  int64_t total_tiles;
+  int k_blocks;
+  const float* scale_a;
+  const float* scale_b;
+  int* status;
+  int c_vec_ok;
+};
+
+__device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, int& b, int& mt, int& nt) {
+  const int64_t per_batch = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+  b = static_cast<int>(tile / per_batch);
+  const int r = static_cast<int>(tile % per_batch);
+  const int group_span = GROUP_M * p.n_tiles;
+  const int group = r / group_span;
+  const int first_m = group * GROUP_M;
+  const int gsize = min(p.m_tiles - first_m, GROUP_M);
+  const int in_group = r % group_span;
+  mt = first_m + in_group % gsize;
+  nt = in_group / gsize;
+}
+
+template <Kind kKind, int kElemBytes, bool kAMn, bool kBMn, typename TOut>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmParams p, const uint32_t idesc) {
+  constexpr int BK = 128 / kElemBytes;             // elements per k-block (128 bytes of K)
+  constexpr int UMMA_K = 32 / kElemBytes;          // elements per MMA (32 bytes of K)
+  constexpr int MN_BOX = 128 / kElemBytes;         // inner extent of an MN-major TMA box
+  constexpr int MN_BOX_BYTES = BK * 128;           // one MN-major box: BK k-rows of 128 bytes
+  constexpr int MN_KSTEP = UMMA_K * 128;           // bytes between MMA k-steps, MN-major
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                 // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;       // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]
+  uint64_t* drain_bar = bars + 2 * STAGES + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        int b, mt, nt;
+        tile_coords(tile, p, b, mt, nt);
+        const int m0 = mt * BM, n0 = nt * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* a_dst = smem + s * STAGE_BYTES;
+          uint8_t* b_dst = a_dst + A_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if constexpr (!kAMn) {
+            tma_load_3d(a_dst, &tmA, &full_bar[s], k0, m0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < A_BYTES / MN_BOX_BYTES; ++j)
+              tma_load_3d(a_dst + j * MN_BOX_BYTES, &tmA, &full_bar[s], m0 + j * MN_BOX, k0, b);
+          }
+          if constexpr (!kBMn) {
+            tma_load_3d(b_dst, &tmB, &full_bar[s], k0, n0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < B_BYTES / MN_BOX_BYTES; ++j)
+              tma_load_3d(b_dst + j * MN_BOX_BYTES, &tmB, &full_bar[s], n0 + j * MN_BOX, k0, b);
+          }
+        }
+      }
+      if (!ok) {
+        if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
+        // Let the copies that were already issued land before the CTA goes away.
+        int zero = 0;
+        const uint32_t first = it > STAGES ? it - STAGES : 0;
+        for (uint32_t j = first; j < it; ++j)
+          mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1u, &zero, 1u << 16);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    uint32_t it = 0, tile_iter = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tile_iter) {
+      const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
+      if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = kAMn ? make_smem_desc(a_addr + k * MN_KSTEP, MN_BOX_BYTES, 1024)
+                                        : make_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = kBMn ? make_smem_desc(b_addr + k * MN_KSTEP, MN_BOX_BYTES, 1024)
+                                        : make_smem_desc(b_addr + k * 32, 16, 1024);
+            mma_ss<kKind>(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          mma_commit(&empty_bar[s]);
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) mma_commit(&tfull_bar[acc]);
+      __syncwarp();
+    }
+    if (!ok) {
+      if (lane == 0) {
+        if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
+        int zero = 0;
+        mma_commit(drain_bar);
+        mbar_wait(drain_bar, 0, &zero, 1u << 20);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    float alpha = 1.f;
+    if (p.scale_a) alpha *= *p.scale_a;
+    if (p.scale_b) alpha *= *p.scale_b;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tile_iter) {
+      int b, mt, nt;
+      tile_coords(tile, p, b, mt, nt);
+      const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
+      if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t row = static_cast<int64_t>(mt) * BM + quarter * 32 + lane;
+      const int64_t col0 = static_cast<int64_t>(nt) * BN;
+      TOut* crow = static_cast<TOut*>(p.C) + b * p.stride_c + row * p.ldc;
+      const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      constexpr int VW = Vec16<TOut>::N;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_base + c * 32, r);
+        tmem_wait_ld();
+        if (row < p.M) {
+          const int64_t cbase = col0 + c * 32;
+#pragma unroll
+          for (int g = 0; g < 32 / VW; ++g) {
+            const int64_t col = cbase + g * VW;
+            if (p.c_vec_ok && col + VW <= p.N) {
+              Vec16<TOut> o;
+#pragma unroll
+              for (int j = 0; j < VW; ++j) o.v[j] = Conv<TOut>::from_f(alpha * __uint_as_float(r[g * VW + j]));
+              st_vec(crow + col, o);
+            } else {
+#pragma unroll
+              for (int j = 0; j < VW; ++j)
+                if (col + j < p.N) crow[col + j] = Conv<TOut>::from_f(alpha * __uint_as_float(r[g * VW + j]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+    if (!ok && lane == 0 && !*abort_flag) {
+      *abort_flag = 1;
+      *p.status = KCG_ERR_TIMEOUT;
+      __threadfence_system();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+}  // namespace
+
+// Encodes a rank-`rank` tensor map with 128-byte swizzle.  dims/strides are innermost
+// first; strides (bytes) are given for dims 1..rank-1.
+int encode_tmap_sw128(CUtensorMap* out, int dtype, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(KCG_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  CUtensorMapDataType dt;
+  switch (dtype) {
+    case KCG_BF16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
+    case KCG_F16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+    case KCG_F8E4M3: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    case KCG_F32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
+    default: return fail(KCG_ERR_UNSUPPORTED, "tensor map: dtype %d", dtype);
+  }
+  cuuint64_t gd[5], gs[5];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) { gd[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) gs[i] = strides_bytes[i];
+  CUresult r = fn(out, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gd, gs, bx, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(KCG_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu)",
+                static_cast<int>(r), rank, static_cast<unsigned long long>(dims[0]),
+                static_cast<unsigned long long>(rank > 1 ? dims[1] : 1));
+  return KCG_OK;
+}
+
+namespace {
+
+template <Kind kKind, int kElemBytes, bool kAMn, bool kBMn, typename TOut>
+int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, uint32_t idesc,
+                   cudaStream_t stream) {
+  auto kern = gemm_tcgen05_kernel<kKind, kElemBytes, kAMn, kBMn, TOut>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  const int sms = sm_count();
+  const int grid = static_cast<int>(p.total_tiles < sms ? p.total_tiles : sms);
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p, idesc);
+  return check_launch("gemm_tcgen05_kernel");
+}
+
+template <Kind kKind, int kElemBytes, typename TOut>
+int launch_layout(int trans_a, int trans_b, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                  uint32_t idesc, cudaStream_t s) {
+  // trans_a != 0: A is [K, M] row-major -> MN-major operand; trans_b == 0: B is [K, N] -> MN-major.
+  if (!trans_a && trans_b) return launch_variant<kKind, kElemBytes, false, false, TOut>(tmA, tmB, p, idesc, s);
+  if (!trans_a && !trans_b) return launch_variant<kKind, kElemBytes, false, true, TOut>(tmA, tmB, p, idesc, s);
+  if (trans_a && trans_b) return launch_variant<kKind, kElemBytes, true, false, TOut>(tmA, tmB, p, idesc, s);
+  return launch_variant<kKind, kElemBytes, true, true, TOut>(tmA, tmB, p, idesc, s);
+}
+
+}  // namespace
+
+int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
+                 int trans_b, const void* A, int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
+                 int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
+                 const float* scale_b, cudaStream_t stream) {
+  const int es = dtype_in == KCG_F8E4M3 ? 1 : 2;
+  if (!aligned16(A) || !aligned16(B))
+    return fail(KCG_ERR_ALIGNMENT, "gemm: A and B must be 16-byte aligned for the tensor-core path");
+  if ((lda * es) % 16 || (ldb * es) % 16 || (batch > 1 && ((stride_a * es) % 16 || (stride_b * es) % 16)))
+    return fail(KCG_ERR_ALIGNMENT,
+                "gemm: leading dimensions and batch strides must be multiples of 16 bytes (lda=%lld ldb=%lld)",
+                static_cast<long long>(lda), static_cast<long long>(ldb));
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || batch > INT32_MAX)
+    return fail(KCG_ERR_UNSUPPORTED, "gemm: extents above 2^31-1 are not supported");
+
+  const int BK = 128 / es;
+  const uint32_t mn_box = 128 / es;
+  CUtensorMap tmA, tmB;
+  {
+    const uint64_t a_rows = trans_a ? K : M, a_cols = trans_a ? M : K;
+    uint64_t dims[3] = {a_cols, a_rows, static_cast<uint64_t>(batch)};
+    uint64_t strides[2] = {static_cast<uint64_t>(lda) * es,
+                           batch > 1 ? static_cast<uint64_t>(stride_a) * es : a_rows * static_cast<uint64_t>(lda) * es};
+    uint32_t box[3];
+    if (!trans_a) { box[0] = BK; box[1] = BM; } else { box[0] = mn_box; box[1] = BK; }
+    box[2] = 1;
+    int rc = encode_tmap_sw128(&tmA, dtype_in, A, 3, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t b_rows = trans_b ? N : K, b_cols = trans_b ? K : N;
+    uint64_t dims[3] = {b_cols, b_rows, static_cast<uint64_t>(batch)};
+    uint64_t strides[2] = {static_cast<uint64_t>(ldb) * es,
+                           batch > 1 ? static_cast<uint64_t>(stride_b) * es : b_rows * static_cast<uint64_t>(ldb) * es};
+    uint32_t box[3];
+    if (trans_b) { box[0] = BK; box[1] = BN; } else { box[0] = mn_box; box[1] = BK; }
+    box[2] = 1;
+    int rc = encode_tmap_sw128(&tmB, dtype_in, B, 3, dims, strides, box);
+    if (rc) return rc;
+  }
+
+  GemmParams p;
+  p.C = C; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.stride_c = stride_c;
+  p.m_tiles = static_cast<int>((M + BM - 1) / BM);
+  p.n_tiles = static_cast<int>((N + BN - 1) / BN);
+  p.total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * batch;
+  p.k_blocks = static_cast<int>((K + BK - 1) / BK);
+  p.scale_a = scale_a; p.scale_b = scale_b;
+  p.status = device_status_word();
+  if (!p.status) return fail(KCG_ERR_CUDA, "gemm: could not allocate the host-mapped status word");
+  const size_t out_es = kcg_dtype_size(dtype_out);
+  p.c_vec_ok = aligned16(C) && (ldc * out_es) % 16 == 0 && (stride_c * out_es) % 16 == 0;
+
+  const uint32_t a_mn = trans_a ? 1u : 0u, b_mn = trans_b ? 0u : 1u;
+  if (dtype_in == KCG_F8E4M3) {
+    const uint32_t idesc = make_idesc(0, 0, a_mn, b_mn, BM, BN);
+    if (dtype_out == KCG_BF16)
+      return launch_layout<Kind::F8F6F4, 1, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, p, idesc, stream);
+    if (dtype_out == KCG_F32)
+      return launch_layout<Kind::F8F6F4, 1, float>(trans_a, trans_b, tmA, tmB, p, idesc, stream);
+    return fail(KCG_ERR_UNSUPPORTED, "gemm: float8_e4m3 inputs produce bfloat16 or float32 (got dtype %d)", dtype_out);
+  }
+  const uint32_t fmt = dtype_in == KCG_BF16 ? 1u : 0u;
+  const uint32_t idesc = make_idesc(fmt, fmt, a_mn, b_mn, BM, BN);
+  if (dtype_out == KCG_F32) return launch_layout<Kind::F16, 2, float>(trans_a, trans_b, tmA, tmB, p, idesc, stream);
+  if (dtype_in == KCG_BF16 && dtype_out == KCG_BF16)
+    return launch_layout<Kind::F16, 2, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, p, idesc, stream);
+  if (dtype_in == KCG_F16 && dtype_out == KCG_F16)
+    return launch_layout<Kind::F16, 2, __half>(trans_a, trans_b, tmA, tmB, p, idesc, stream);
+  return fail(KCG_ERR_UNSUPPORTED, "gemm: dtype combination %d -> %d has no kernel", dtype_in, dtype_out);
+}
+
+}  // namespace kcg

@@ -1,0 +1,148 @@
+// Library-wide runtime state: error text, device properties, the per-device scratch
+// buffer, and the small entry points that launch nothing.
+#include "common.cuh"
+
+#include <cstring>
+#include <mutex>
+
+namespace kcg {
+
+namespace {
+thread_local char g_error[512] = {0};
+
+struct DeviceState {
+  int sms = 0;
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+};
+constexpr int kMaxDevices = 64;
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mutex;
+
+int current_device() {
+  int d = -1;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) return -1;
+  return d;
+}
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+void clear_error() { g_error[0] = 0; }
+
+int sm_count() {
+  const int d = current_device();
+  if (d < 0) return 1;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_dev[d].sms == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) n = 148;
+    g_dev[d].sms = n;
+  }
+  return g_dev[d].sms;
+}
+
+// Returns a device buffer of at least `bytes` bytes that stays valid until a larger
+// request replaces it (cudaFree of the old buffer waits for work in flight).
+void* device_scratch(size_t bytes) {
+  const int d = current_device();
+  if (d < 0) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState& st = g_dev[d];
+  if (st.scratch_bytes >= bytes && st.scratch) return st.scratch;
+  if (st.scratch) {
+    cudaFree(st.scratch);
+    st.scratch = nullptr;
+    st.scratch_bytes = 0;
+  }
+  size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
+  void* p = nullptr;
+  if (cudaMalloc(&p, want) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  st.scratch = p;
+  st.scratch_bytes = want;
+  return p;
+}
+
+// One host-mapped word per process that kernels write a kcg_status into when a bounded
+// device-side wait gives up.  Host memory, so reading it needs no device synchronisation
+// beyond the caller's own wait for the stream.
+int* device_status_word() {
+  static int* word = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, 64, cudaHostAllocPortable | cudaHostAllocMapped) == cudaSuccess) {
+      word = static_cast<int*>(p);
+      *word = 0;
+    } else {
+      cudaGetLastError();
+    }
+  });
+  return word;
+}
+
+}  // namespace kcg
+
+extern "C" int kcg_device_status(void) {
+  int* w = kcg::device_status_word();
+  if (!w) return KCG_OK;
+  const int v = *reinterpret_cast<volatile int*>(w);
+  *reinterpret_cast<volatile int*>(w) = 0;
+  return v;
+}
+
+extern "C" const char* kcg_status_string(int status) {
+  switch (status) {
+    case KCG_OK: return "ok";
+    case KCG_ERR_INVALID_ARG: return "invalid argument";
+    case KCG_ERR_UNSUPPORTED: return "unsupported configuration";
+    case KCG_ERR_ALIGNMENT: return "pointer or stride not 16-byte aligned";
+    case KCG_ERR_CUDA: return "CUDA call failed";
+    case KCG_ERR_TIMEOUT: return "device-side wait timed out";
+    case KCG_ERR_NO_DEVICE: return "no sm_100 device";
+    default: return "unknown status";
+  }
+}
+
+extern "C" const char* kcg_last_error(void) { return kcg::g_error; }
+
+extern "C" int kcg_version(void) { return 100; }
+
+extern "C" size_t kcg_dtype_size(int dtype) {
+  switch (dtype) {
+    case KCG_F32: case KCG_I32: return 4;
+    case KCG_F16: case KCG_BF16: case KCG_I16: return 2;
+    case KCG_F8E4M3: case KCG_BOOL: return 1;
+    case KCG_F64: case KCG_I64: return 8;
+    default: return 0;
+  }
+}
+
+extern "C" int kcg_shard_range(int64_t total, int world, int rank, int64_t granule,
+                               int64_t* begin, int64_t* count) {
+  using namespace kcg;
+  clear_error();
+  if (total < 0 || world <= 0 || rank < 0 || rank >= world || granule <= 0 || !begin || !count)
+    return fail(KCG_ERR_INVALID_ARG, "shard_range: total=%lld world=%d rank=%d granule=%lld",
+                static_cast<long long>(total), world, rank, static_cast<long long>(granule));
+  // Split the granules as evenly as possible; earlier ranks take the remainder.
+  const int64_t granules = (total + granule - 1) / granule;
+  const int64_t base = granules / world, extra = granules % world;
+  const int64_t g0 = base * rank + (rank < extra ? rank : extra);
+  const int64_t gn = base + (rank < extra ? 1 : 0);
+  int64_t b = g0 * granule, e = (g0 + gn) * granule;
+  if (b > total) b = total;
+  if (e > total) e = total;
+  *begin = b;
+  *count = e - b;
+  return KCG_OK;
+}

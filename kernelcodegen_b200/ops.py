@@ -1,0 +1,202 @@
+"""Operator calls on torch CUDA tensors, one per reference Frontend operator.
+
+Names and argument meaning follow the reference's operator builders
+(include/Frontend/Operators.h:75-133): ``matmul`` (Matmul), ``batched_matmul``
+(BatchedMatmul with Layout flags), ``softmax``, ``layernorm`` (axis, eps), ``elementwise``
+("Tanh" | "Sqrt" | "Log" | "Relu" | "Cast" | "Gelu"), ``relu``, ``binary`` ("Add" | "Mul" |
+"Div" | "Sub" | "Pow" | "Equal" | "Greater") and ``fmha`` for the fused
+BatchedMatmul -> Softmax -> BatchedMatmul chain.  torch only supplies device memory and
+the current stream; every computation is a call through the C ABI into the sm_100a
+kernels, and there is no fallback path.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from ._lib import KcgError, check  # noqa: F401  (re-exported)
+
+_DT = {
+    torch.float32: _lib.F32,
+    torch.float16: _lib.F16,
+    torch.bfloat16: _lib.BF16,
+    torch.int32: _lib.I32,
+}
+if hasattr(torch, "float8_e4m3fn"):
+    _DT[torch.float8_e4m3fn] = _lib.F8E4M3
+
+DTYPE_NAMES = {
+    "float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16, "int32": torch.int32,
+    "float8_e4m3": getattr(torch, "float8_e4m3fn", None),
+}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"dtype {t.dtype} has no kernel") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if not t.is_cuda:
+            raise ValueError("operands must be CUDA tensors (there is no CPU path)")
+        if not t.is_contiguous():
+            raise ValueError("operands must be contiguous")
+
+
+def _i64arr(v):
+    return (ctypes.c_int64 * len(v))(*[int(x) for x in v])
+
+
+def layernorm(x, scale, bias, axis: int, eps: float = 1e-5, inplace: bool = False, out=None):
+    """LayerNorm over dims [axis..] (reference: LayerNorm::build, Operators.h:125-128)."""
+    _need_cuda(x, scale, bias)
+    nd = x.dim()
+    if axis >= nd or axis <= -nd:
+        raise ValueError("axis is out of bounds for array of dimension.")
+    if axis < 0:
+        axis += nd
+    norm_shape = tuple(x.shape[axis:])
+    cols = math.prod(norm_shape)
+    rows = x.numel() // cols if cols else 0
+    if tuple(scale.shape) != norm_shape or tuple(bias.shape) != norm_shape:
+        # trailing-aligned broadcast with 1-dims (Operators.cc:1102-1123)
+        scale = scale.expand(norm_shape).contiguous()
+        bias = bias.expand(norm_shape).contiguous()
+    y = x if inplace else (out if out is not None else torch.empty_like(x))
+    check(_lib.load().kcg_layernorm(_dt(x), rows, cols, x.data_ptr(), scale.data_ptr(), bias.data_ptr(),
+                                    float(eps), y.data_ptr(), _stream()), "kcg_layernorm")
+    return y
+
+
+def elementwise(x, operation: str, dtype=None, inplace: bool = False, out=None):
+    """Unary map (reference: ElementWise::build, Operators.h:114-123)."""
+    _need_cuda(x)
+    if operation not in _lib.UNARY_OPS:
+        raise KeyError(operation)
+    out_dtype = x.dtype if dtype is None else (DTYPE_NAMES[dtype] if isinstance(dtype, str) else dtype)
+    if inplace:
+        y = x
+    else:
+        y = out if out is not None else torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    check(_lib.load().kcg_eltwise(_lib.UNARY_OPS[operation], _dt(x), _dt(y), x.numel(), x.data_ptr(),
+                                  y.data_ptr(), _stream()), "kcg_eltwise")
+    return y
+
+
+def relu(x, inplace: bool = False):
+    """Reference: Relu::build (Operators.h:83-85)."""
+    return elementwise(x, "Relu", inplace=inplace)
+
+
+def binary(a, b, operation: str, inplace: bool = False, out=None):
+    """Broadcasting binary map (reference: Binary::build, Operators.h:101-112)."""
+    _need_cuda(a, b)
+    if operation not in _lib.BINARY_OPS:
+        raise KeyError(operation)
+    if a.dtype != b.dtype:
+        raise TypeError("binary: operands must share a dtype")
+    try:
+        oshape = torch.broadcast_shapes(a.shape, b.shape)
+    except RuntimeError:
+        raise ValueError("dim not equal") from None
+    if inplace:
+        if tuple(a.shape) != tuple(oshape):
+            raise ValueError("inplace needs the left operand to have the output shape")
+        c = a
+    else:
+        c = out if out is not None else torch.empty(oshape, dtype=a.dtype, device=a.device)
+    check(_lib.load().kcg_binary(_lib.BINARY_OPS[operation], _dt(a), a.dim(), _i64arr(a.shape), b.dim(),
+                                 _i64arr(b.shape), a.data_ptr(), b.data_ptr(), c.data_ptr(), _stream()),
+          "kcg_binary")
+    return c
+
+
+def softmax(x, axis: int = -1, scale: float = 1.0, causal: bool = False, inplace: bool = True):
+    """Softmax over the last dim, in place like the reference (Softmax::build, Operators.h:93-95)."""
+    _need_cuda(x)
+    if axis not in (-1, x.dim() - 1):
+        raise ValueError("At present, only support reduction on the last dim.")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    q_len = x.shape[-2] if x.dim() >= 2 else 1
+    y = x if inplace else torch.empty_like(x)
+    check(_lib.load().kcg_softmax(_dt(x), rows, cols, float(scale), int(causal), q_len, x.data_ptr(),
+                                  y.data_ptr(), _stream()), "kcg_softmax")
+    return y
+
+
+def _scale_ptr(s):
+    if s is None:
+        return None
+    if not (s.is_cuda and s.dtype == torch.float32 and s.numel() == 1):
+        raise ValueError("per-tensor scales are one float32 on the device")
+    return s.data_ptr()
+
+
+def batched_matmul(A, B, trans_a: bool = False, trans_b: bool = False, out_dtype=None, scale_a=None,
+                   scale_b=None, out=None):
+    """C = op(A) op(B) over leading batch dims (reference: BatchedMatmul::build with
+    Layout::rowMajor / Layout::colMajor, Operators.h:87-89; trans_x=True is colMajor)."""
+    _need_cuda(A, B)
+    if A.dim() < 2 or A.dim() != B.dim():
+        raise ValueError("BatchedMatmul: A, B dim not matched.")
+    m, k1 = (A.shape[-1], A.shape[-2]) if trans_a else (A.shape[-2], A.shape[-1])
+    n, k2 = (B.shape[-2], B.shape[-1]) if trans_b else (B.shape[-1], B.shape[-2])
+    if k1 != k2:
+        raise ValueError("Can't apply BatchedMatmul Operation due to imcompatible K-dim.")
+    if tuple(A.shape[:-2]) != tuple(B.shape[:-2]):
+        raise ValueError("BatchedMatmul: batch dims differ")
+    batch = math.prod(A.shape[:-2])
+    if out_dtype is None:
+        out_dtype = torch.bfloat16 if A.dtype == getattr(torch, "float8_e4m3fn", None) else A.dtype
+    C = out if out is not None else torch.empty(tuple(A.shape[:-2]) + (m, n), dtype=out_dtype, device=A.device)
+    check(_lib.load().kcg_gemm(_dt(A), _DT[C.dtype], m, n, k1, batch, int(trans_a), int(trans_b),
+                               A.data_ptr(), A.shape[-1], A.shape[-1] * A.shape[-2],
+                               B.data_ptr(), B.shape[-1], B.shape[-1] * B.shape[-2],
+                               C.data_ptr(), n, m * n, _scale_ptr(scale_a), _scale_ptr(scale_b), _stream()),
+          "kcg_gemm")
+    return C
+
+
+def matmul(A, B, out_dtype=None, scale_a=None, scale_b=None, out=None):
+    """C[M,N] = A[M,K] B[K,N], both row-major (reference: Matmul::build, Operators.h:79-81)."""
+    if A.dim() != 2 or B.dim() != 2:
+        raise ValueError("Matmul takes rank-2 operands")
+    if A.shape[1] != B.shape[0]:
+        raise ValueError("Can't apply Matmul Operation due to imcompatible K-dim.")
+    return batched_matmul(A, B, False, False, out_dtype, scale_a, scale_b, out)
+
+
+def fmha(Q, K, V, softmax_scale: float = 1.0, causal: bool = False, out_layout: str = "bhsd", out=None):
+    """Fused attention forward on [B,H,S,D] tensors: softmax(scale * Q K^T [+ causal mask]) V,
+    the chain BatchedMatmul(NT) -> Softmax -> BatchedMatmul(NN) the reference fuses
+    (test/test.cc:128-130).  ``out_layout`` "bshd" returns O as [B,S,H,D]."""
+    for t in (Q, K, V):
+        if not t.is_cuda:
+            raise ValueError("operands must be CUDA tensors (there is no CPU path)")
+        if t.dim() != 4 or t.stride(-1) != 1:
+            raise ValueError("fmha takes [B,H,S,D] tensors with a contiguous head dimension")
+    B, H, Sq, D = Q.shape
+    Skv = K.shape[2]
+    if out is None:
+        if out_layout == "bhsd":
+            out = torch.empty((B, H, Sq, D), dtype=Q.dtype, device=Q.device)
+        elif out_layout == "bshd":
+            out = torch.empty((B, Sq, H, D), dtype=Q.dtype, device=Q.device).permute(0, 2, 1, 3)
+        else:
+            raise ValueError(out_layout)
+    st = lambda t: _i64arr([t.stride(0), t.stride(1), t.stride(2)])
+    check(_lib.load().kcg_fmha_fwd(_dt(Q), B, H, Sq, Skv, D, float(softmax_scale), int(causal),
+                                   Q.data_ptr(), st(Q), K.data_ptr(), st(K), V.data_ptr(), st(V),
+                                   out.data_ptr(), st(out), _stream()), "kcg_fmha_fwd")
+    return out
