@@ -215,6 +215,14 @@ KCG_API int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Sk
                          const int64_t o_strides[3], void* stream);
 
 /*
+ * Tuning switch with no counterpart in the reference: the probability tile P is handed
+ * to the second MMA through tensor memory (1, the default) or through a swizzled
+ * shared-memory tile (0).  Both give identical results; kept so the two data paths can
+ * be compared on the same build.  Process-wide, not thread-safe.
+ */
+KCG_API void kcg_fmha_set_p_in_tmem(int enabled);
+
+/*
  * Row-range owned by one rank when `total` independent units (GEMM rows of A/C,
  * attention batch*head slices, LayerNorm / elementwise rows) are split over
  * `world` GPUs in contiguous blocks rounded to `granule` units.  The reference

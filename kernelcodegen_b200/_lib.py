@@ -39,6 +39,7 @@ SIGNATURES = {
                   _vp, _vp, _vp], _ci),
     "kcg_fmha_fwd": ([_ci, _i64, _i64, _i64, _i64, _i64, _fp, _ci, _vp, _i64p, _vp, _i64p, _vp, _i64p, _vp, _i64p,
                       _vp], _ci),
+    "kcg_fmha_set_p_in_tmem": ([_ci], None),
     "kcg_shard_range": ([_i64, _ci, _ci, _i64, _i64p, _i64p], _ci),
 }
 

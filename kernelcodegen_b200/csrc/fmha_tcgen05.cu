@@ -1,5 +1,409 @@
-// Fused multi-head attention forward (placeholder until the tcgen05 kernel lands).
+// Fused multi-head attention forward for sm_100a.
+//
+// The reference fuses BatchedMatmul(Q,K^T) -> Softmax -> BatchedMatmul(P,V) into one
+// flash-attention style kernel (src/Optimizer/Optimizer.cc:2606-2860): a CTA owns Br query
+// rows, walks the keys in blocks of Bc, keeps running row max / row sum, and rescales the
+// output accumulator, all in fp32 FFMA with the score tile staged through shared memory.
+// This kernel keeps that blockwise online-softmax algorithm and moves both contractions to
+// the tensor cores:
+//   warp 0      TMA loads of the 128-row Q tile (once) and of 128-key K and V tiles into
+//               2-stage rings;
+//   warp 1      one thread issues tcgen05.mma: S = Q K^T into one of two score buffers in
+//               tensor memory, then O += P V with V consumed straight from its row-major
+//               [key, d] tile (an "MN-major" B operand), so no transpose is needed;
+//   warps 2-5   softmax: one thread per query row reads its 128 scores from tensor memory
+//               (a row never spans lanes, so the row max / row sum need no shuffles),
+//               computes exp2 of the scaled scores, writes P as the 16-bit A operand of the
+//               second MMA and, when the running max moved, rescales O in tensor memory.
+// The score MMA of key block j+1 is issued before the PV MMA of block j, so tensor-core
+// work overlaps the softmax of the previous block.
+//
+// Extensions over the reference (which has neither): a softmax scale folded into the
+// exp2 argument, and a causal mask that also skips key blocks above the diagonal.
 #include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace kcg {
+
+int* device_status_word();
+int encode_tmap_sw128(CUtensorMap* out, int dtype, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box);
+
+namespace {
+using namespace sm100;
+
+constexpr int BM = 128;          // query rows per CTA
+constexpr int BN = 128;          // keys per block
+constexpr int KV_STAGES = 2;
+constexpr int TILE16K = 16384;   // one 128-row x 128-byte swizzled block
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr float kRescaleThreshold = 8.0f;  // in log2 units: rescale O only when the max grew by > 2^8
+
+struct FmhaParams {
+  void* O;
+  int64_t o_sb, o_sh, o_ss;  // element strides of O
+  int B, H, Sq, Skv;
+  float scale_log2;          // softmax_scale * log2(e)
+  int causal;
+  int q_tiles;
+  int* status;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// kPTmem: P is written to tensor memory and the PV MMA reads its A operand from there;
+// otherwise P goes through a swizzled shared-memory tile.
+template <typename T, int D, bool kPTmem>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const FmhaParams p, const uint32_t idesc_qk,
+                const uint32_t idesc_pv) {
+  constexpr int DB = D / 64;                 // 128-byte blocks along the head dimension
+  constexpr int QK_TILE = DB * TILE16K;      // bytes of a Q, K or V tile
+  constexpr int P_BYTES = 2 * TILE16K;
+  constexpr uint32_t S_COL0 = 0, O_COL = 256, P_COL = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint8_t* q_smem = smem;
+  uint8_t* k_smem = q_smem + QK_TILE;
+  uint8_t* v_smem = k_smem + KV_STAGES * QK_TILE;
+  uint8_t* p_smem = v_smem + KV_STAGES * QK_TILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2]
+  uint64_t* s_empty = bars + 11;  // [2]
+  uint64_t* p_full = bars + 13;
+  uint64_t* pv_done = bars + 14;
+  uint64_t* drain_bar = bars + 15;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Causal: the last query tiles have the most key blocks; start them first.
+  const int qt = p.causal ? (p.q_tiles - 1 - static_cast<int>(blockIdx.x)) : static_cast<int>(blockIdx.x);
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int q0 = qt * BM;
+  const int off = p.Skv - p.Sq;  // key index of the diagonal for query 0
+  int kv_end = p.Skv;
+  if (p.causal) kv_end = min(p.Skv, q0 + BM + off);
+  const int n_tiles = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA loader
+    if (lane == 0 && n_tiles > 0) {
+      bool ok = true;
+      mbar_expect_tx(q_full, QK_TILE);
+#pragma unroll
+      for (int d = 0; d < DB; ++d) tma_load_4d(q_smem + d * TILE16K, &tmQ, q_full, d * 64, q0, h, b);
+      int issued = 0;
+      for (int j = 0; j < n_tiles; ++j) {
+        const uint32_t s = j % KV_STAGES, ph = (j / KV_STAGES) & 1u;
+        if (!mbar_wait(&k_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(&k_full[s], QK_TILE);
+#pragma unroll
+        for (int d = 0; d < DB; ++d)
+          tma_load_4d(k_smem + s * QK_TILE + d * TILE16K, &tmK, &k_full[s], d * 64, j * BN, h, b);
+        if (!mbar_wait(&v_empty[s], ph ^ 1u, abort_flag)) { ok = false; issued = j; break; }
+        mbar_expect_tx(&v_full[s], QK_TILE);
+#pragma unroll
+        for (int d = 0; d < DB; ++d)
+          tma_load_4d(v_smem + s * QK_TILE + d * TILE16K, &tmV, &v_full[s], d * 64, j * BN, h, b);
+        issued = j + 1;
+      }
+      if (!ok) {
+        if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
+        int zero = 0;
+        mbar_wait(q_full, 0, &zero, 2000000ull);
+        for (int j = issued > KV_STAGES ? issued - KV_STAGES : 0; j < issued; ++j) {
+          mbar_wait(&k_full[j % KV_STAGES], (j / KV_STAGES) & 1u, &zero, 2000000ull);
+          mbar_wait(&v_full[j % KV_STAGES], (j / KV_STAGES) & 1u, &zero, 2000000ull);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    bool ok = n_tiles > 0;
+    const uint32_t q_addr = smem_u32(q_smem);
+    const uint32_t p_addr = smem_u32(p_smem);
+    auto issue_s = [&](int j) -> bool {
+      const uint32_t s = j % KV_STAGES, ph = (j / KV_STAGES) & 1u;
+      const uint32_t sb = j & 1u, sph = (j >> 1) & 1u;
+      if (!mbar_wait(&k_full[s], ph, abort_flag)) return false;
+      if (!mbar_wait(&s_empty[sb], sph ^ 1u, abort_flag)) return false;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t k_addr = smem_u32(k_smem + s * QK_TILE);
+#pragma unroll
+        for (int d = 0; d < DB; ++d)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_ss<Kind::F16>(tmem_base + S_COL0 + sb * BN,
+                              make_smem_desc(q_addr + d * TILE16K + k * 32, 16, 1024),
+                              make_smem_desc(k_addr + d * TILE16K + k * 32, 16, 1024), idesc_qk,
+                              (d | k) != 0 ? 1u : 0u);
+        mma_commit(&k_empty[s]);
+        mma_commit(&s_full[sb]);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok) ok = mbar_wait(q_full, 0, abort_flag);
+    if (ok) ok = issue_s(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
+      const uint32_t s = j % KV_STAGES, ph = (j / KV_STAGES) & 1u;
+      if (!mbar_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(p_full, j & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t v_addr = smem_u32(v_smem + s * QK_TILE);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t bdesc = make_smem_desc(v_addr + kk * 2048, TILE16K, 1024);
+          const uint32_t accumulate = (j | kk) != 0 ? 1u : 0u;
+          if constexpr (kPTmem) {
+            mma_ts_f16(tmem_base + O_COL, tmem_base + P_COL + kk * 8, bdesc, idesc_pv, accumulate);
+          } else {
+            const uint64_t adesc = make_smem_desc(p_addr + (kk >> 2) * TILE16K + (kk & 3) * 32, 16, 1024);
+            mma_ss<Kind::F16>(tmem_base + O_COL, adesc, bdesc, idesc_pv, accumulate);
+          }
+        }
+        mma_commit(&v_empty[s]);
+        mma_commit(pv_done);
+      }
+      __syncwarp();
+    }
+    if (!ok && n_tiles > 0) {
+      if (lane == 0) {
+        if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
+        int zero = 0;
+        mma_commit(drain_bar);
+        mbar_wait(drain_bar, 0, &zero, 20000000ull);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / epilogue
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;            // row within the tile == TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const int qi = q0 + r;                        // global query index
+    const float c = p.scale_log2;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const uint32_t sb = j & 1u, sph = (j >> 1) & 1u;
+      if (!mbar_wait(&s_full[sb], sph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_addr = tmem_base + lane_base + S_COL0 + sb * BN;
+      const int kv0 = j * BN;
+      // Columns >= limit are masked: beyond the keys, or above the causal diagonal.
+      int limit = p.Skv - kv0;
+      if (p.causal) limit = min(limit, qi + off + 1 - kv0);
+      const bool need_mask = limit < BN;
+      // pass 1: row max
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        uint32_t sreg[32];
+        tmem_ld32(s_addr + cc * 32, sreg);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (cc * 32 + i < limit) mx = fmaxf(mx, __uint_as_float(sreg[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sreg[i]));
+        }
+      }
+      const float mt = mx * c;
+      float alpha = 1.f;
+      bool rescale = false;
+      if (mt > m + kRescaleThreshold || m == -INFINITY) {
+        if (mt > m) {
+          alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - mt);
+          rescale = (j > 0);
+          m = mt;
+        }
+      }
+      const float m_eff = (m == -INFINITY) ? 0.f : m;
+      // pass 2: p = exp2(s*c - m), packed to 16 bits, row sum in fp32
+      uint32_t pk[BN / 2];
+      float lsum = 0.f;
+#pragma unroll
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        uint32_t sreg[32];
+        tmem_ld32(s_addr + cc * 32, sreg);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = fast_exp2(fmaf(__uint_as_float(sreg[i]), c, -m_eff));
+          float p1 = fast_exp2(fmaf(__uint_as_float(sreg[i + 1]), c, -m_eff));
+          if (need_mask) {
+            if (cc * 32 + i >= limit) p0 = 0.f;
+            if (cc * 32 + i + 1 >= limit) p1 = 0.f;
+          }
+          lsum += p0 + p1;
+          pk[cc * 16 + i / 2] = pack2<T>(p0, p1);
+        }
+      }
+      // S(j) is fully read: hand the score buffer back to the MMA warp.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      // P buffer and O are free once the PV MMA of the previous block has finished.
+      if (j > 0) {
+        if (!mbar_wait(pv_done, (j - 1) & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, rescale)) {
+          const float a = rescale ? alpha : 1.f;
+#pragma unroll 1
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t oreg[32];
+            tmem_ld32(tmem_base + lane_base + O_COL + cc * 32, oreg);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * a);
+            tmem_st32(tmem_base + lane_base + O_COL + cc * 32, oreg);
+          }
+          tmem_wait_st();
+        }
+      }
+      l = l * alpha + lsum;
+      if constexpr (kPTmem) {
+        tmem_st32(tmem_base + lane_base + P_COL, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
+        tmem_st32(tmem_base + lane_base + P_COL + 32, reinterpret_cast<uint32_t(&)[32]>(pk[32]));
+        tmem_wait_st();
+      } else {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          uint8_t* dst = p_smem + (q >> 3) * TILE16K + r * 128 + (((q & 7) ^ (r & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
+        }
+        fence_proxy_async_smem();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // epilogue: O / l -> global
+    if (ok && n_tiles > 0) ok = mbar_wait(pv_done, (n_tiles - 1) & 1u, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+      T* orow = static_cast<T*>(p.O) + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh +
+                static_cast<int64_t>(qi) * p.o_ss;
+#pragma unroll 1
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t oreg[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tmem_base + lane_base + O_COL + cc * 32, oreg);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) oreg[i] = 0u;
+        }
+        if (qi < p.Sq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack2<T>(__uint_as_float(oreg[g * 8 + 0]) * inv_l, __uint_as_float(oreg[g * 8 + 1]) * inv_l);
+            o.y = pack2<T>(__uint_as_float(oreg[g * 8 + 2]) * inv_l, __uint_as_float(oreg[g * 8 + 3]) * inv_l);
+            o.z = pack2<T>(__uint_as_float(oreg[g * 8 + 4]) * inv_l, __uint_as_float(oreg[g * 8 + 5]) * inv_l);
+            o.w = pack2<T>(__uint_as_float(oreg[g * 8 + 6]) * inv_l, __uint_as_float(oreg[g * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) = o;
+          }
+        }
+      }
+    } else if (lane == 0 && !*abort_flag) {
+      *abort_flag = 1;
+      *p.status = KCG_ERR_TIMEOUT;
+      __threadfence_system();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <typename T, int D, bool kPTmem>
+int launch_fmha(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FmhaParams& p,
+                uint32_t fmt, cudaStream_t stream) {
+  constexpr int DB = D / 64;
+  constexpr int SMEM = DB * TILE16K * (1 + 2 * KV_STAGES) + 2 * TILE16K + 1024 + 256;
+  auto kern = fmha_fwd_kernel<T, D, kPTmem>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "fmha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  const uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, BM, BN);
+  const uint32_t idesc_pv = make_idesc(fmt, fmt, 0, 1, BM, D);
+  dim3 grid(p.q_tiles, p.B * p.H);
+  kern<<<grid, NUM_THREADS, SMEM, stream>>>(tmQ, tmK, tmV, p, idesc_qk, idesc_pv);
+  return check_launch("fmha_fwd_kernel");
+}
+
+int g_p_in_tmem = 1;
+
+}  // namespace
+
+// Chooses whether P travels through tensor memory (1, default) or shared memory (0).
+extern "C" __attribute__((visibility("default"))) void kcg_fmha_set_p_in_tmem(int v) { g_p_in_tmem = v; }
+
+}  // namespace kcg
 
 extern "C" int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int64_t D,
                             float softmax_scale, int causal, const void* Q, const int64_t q_strides[3],
@@ -7,5 +411,50 @@ extern "C" int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t
                             const int64_t v_strides[3], void* O, const int64_t o_strides[3], void* stream) {
   using namespace kcg;
   clear_error();
-  return fail(KCG_ERR_UNSUPPORTED, "fmha: kernel not built");
+  if (B < 0 || H < 0 || Sq < 0 || Skv < 0) return fail(KCG_ERR_INVALID_ARG, "fmha: negative extent");
+  if (dtype != KCG_BF16 && dtype != KCG_F16)
+    return fail(KCG_ERR_UNSUPPORTED, "fmha: dtype %d has no kernel (bfloat16, float16)", dtype);
+  if (D != 64 && D != 128) return fail(KCG_ERR_UNSUPPORTED, "fmha: head dimension %lld (64 or 128)", static_cast<long long>(D));
+  if (B == 0 || H == 0 || Sq == 0) return KCG_OK;
+  if (!Q || !K || !V || !O || !q_strides || !k_strides || !v_strides || !o_strides)
+    return fail(KCG_ERR_INVALID_ARG, "fmha: null pointer");
+  if (Skv == 0) return fail(KCG_ERR_INVALID_ARG, "fmha: Skv must be positive");
+  if (B * H > 65535 || Sq > INT32_MAX || Skv > INT32_MAX)
+    return fail(KCG_ERR_UNSUPPORTED, "fmha: batch*heads above 65535 is not supported");
+  const void* ptrs[4] = {Q, K, V, O};
+  const int64_t* strides[4] = {q_strides, k_strides, v_strides, o_strides};
+  for (int t = 0; t < 4; ++t) {
+    if (!aligned16(ptrs[t])) return fail(KCG_ERR_ALIGNMENT, "fmha: tensor %d is not 16-byte aligned", t);
+    for (int i = 0; i < 3; ++i)
+      if (strides[t][i] % 8 != 0 || strides[t][i] <= 0)
+        return fail(KCG_ERR_ALIGNMENT, "fmha: strides must be positive multiples of 8 elements (tensor %d stride %d = %lld)",
+                    t, i, static_cast<long long>(strides[t][i]));
+  }
+  CUtensorMap tm[3];
+  const int64_t seq[3] = {Sq, Skv, Skv};
+  for (int t = 0; t < 3; ++t) {
+    uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(seq[t]), static_cast<uint64_t>(H),
+                        static_cast<uint64_t>(B)};
+    uint64_t st[3] = {static_cast<uint64_t>(strides[t][2]) * 2, static_cast<uint64_t>(strides[t][1]) * 2,
+                      static_cast<uint64_t>(strides[t][0]) * 2};
+    uint32_t box[4] = {64, 128, 1, 1};
+    int rc = encode_tmap_sw128(&tm[t], dtype, ptrs[t], 4, dims, st, box);
+    if (rc) return rc;
+  }
+  FmhaParams p;
+  p.O = O; p.o_sb = o_strides[0]; p.o_sh = o_strides[1]; p.o_ss = o_strides[2];
+  p.B = static_cast<int>(B); p.H = static_cast<int>(H); p.Sq = static_cast<int>(Sq); p.Skv = static_cast<int>(Skv);
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.causal = causal ? 1 : 0;
+  p.q_tiles = static_cast<int>((Sq + BM - 1) / BM);
+  p.status = device_status_word();
+  if (!p.status) return fail(KCG_ERR_CUDA, "fmha: could not allocate the host-mapped status word");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint32_t fmt = dtype == KCG_BF16 ? 1u : 0u;
+#define KCG_FMHA(TT, DD)                                                                      \
+  (g_p_in_tmem ? launch_fmha<TT, DD, true>(tm[0], tm[1], tm[2], p, fmt, s)                    \
+               : launch_fmha<TT, DD, false>(tm[0], tm[1], tm[2], p, fmt, s))
+  if (dtype == KCG_BF16) return D == 128 ? KCG_FMHA(__nv_bfloat16, 128) : KCG_FMHA(__nv_bfloat16, 64);
+  return D == 128 ? KCG_FMHA(__half, 128) : KCG_FMHA(__half, 64);
+#undef KCG_FMHA
 }

@@ -155,7 +155,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         int zero = 0;
         const uint32_t first = it > STAGES ? it - STAGES : 0;
         for (uint32_t j = first; j < it; ++j)
-          mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1u, &zero, 1u << 16);
+          mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1u, &zero, 2000000ull);
       }
     }
   } else if (warp == 1) {
@@ -194,7 +194,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
         int zero = 0;
         mma_commit(drain_bar);
-        mbar_wait(drain_bar, 0, &zero, 1u << 20);
+        mbar_wait(drain_bar, 0, &zero, 20000000ull);
       }
       __syncwarp();
     }

@@ -55,17 +55,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
 // Polls until the barrier phase with the given parity has completed.  Returns false if
-// `*abort_flag` becomes non-zero or the budget of polls runs out (each poll may itself
-// block for a hardware-defined interval, so the budget corresponds to seconds).
-constexpr uint32_t kWaitBudget = 1u << 24;
+// `*abort_flag` becomes non-zero or `budget_ns` nanoseconds of wall time pass first; no
+// legitimate wait in these kernels lasts longer than a few hundred microseconds.
+constexpr uint64_t kWaitBudgetNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          uint32_t budget = kWaitBudget) {
-  for (uint32_t i = 0; i < budget; ++i) {
+                                          uint64_t budget_ns = kWaitBudgetNs) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u && *abort_flag) return false;
+    if ((i & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > budget_ns) return false;
+    }
   }
-  return false;
 }
 
 // ---- TMA -------------------------------------------------------------------------
