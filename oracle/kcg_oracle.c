@@ -228,6 +228,14 @@ int64_t oracle_binary_f32(int op, int rank_a, const int64_t* shape_a, int rank_b
   return total;
 }
 
+/* Binary with equal shapes — the same nest as above without broadcast (every index maps to
+ * itself), with the outer loop optionally run in parallel for the timed CPU baseline. */
+void oracle_binary_same_f32(int op, const float* a, const float* b, float* c, int64_t n, int threads) {
+  threads = clamp_threads(threads);
+#pragma omp parallel for num_threads(threads) schedule(static)
+  for (int64_t i = 0; i < n; ++i) c[i] = binary_apply(op, a[i], b[i]);
+}
+
 /* Attention as the reference composes it — test/test.cc:128-130:
  *   S = BatchedMatmul(Q, rowMajor, K, colMajor); P = Softmax(S, -1); O = BatchedMatmul(P, V)
  * on [B,H,S,D] tensors, the chain FMHAOptimizer::applicable recognises

@@ -61,6 +61,7 @@ def _c():
         _lib.oracle_unary_f32.argtypes = [ci, f32p, f32p, i64, ci]
         _lib.oracle_binary_f32.argtypes = [ci, ci, i64p, ci, i64p, f32p, f32p, f32p]
         _lib.oracle_binary_f32.restype = i64
+        _lib.oracle_binary_same_f32.argtypes = [ci, f32p, f32p, f32p, i64, ci]
         _lib.oracle_attention_f32.argtypes = [f32p, f32p, f32p, f32p, i64, i64, i64, i64, i64, ctypes.c_float, ci,
                                               i64p, i64p, i64p, i64p, i64, i64, ci]
     return _lib
@@ -148,6 +149,15 @@ class ref32:
         c = np.empty(out_shape, np.float32)
         assert c.size == total
         _c().oracle_binary_f32(BINARY_OPS[op], a.ndim, sa, b.ndim, sb, _p(a), _p(b), _p(c))
+        return c
+
+    @staticmethod
+    def binary_same(op, a, b, threads=1):
+        """Equal-shape case of the binary nest, optionally multi-threaded (CPU baseline)."""
+        a = np.ascontiguousarray(a, np.float32); b = np.ascontiguousarray(b, np.float32)
+        assert a.shape == b.shape
+        c = np.empty_like(a)
+        _c().oracle_binary_same_f32(BINARY_OPS[op], _p(a), _p(b), _p(c), a.size, threads)
         return c
 
     @staticmethod
