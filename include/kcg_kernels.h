@@ -123,6 +123,13 @@ KCG_API int kcg_layernorm(int dtype, int64_t rows, int64_t cols, const void* x,
                           void* stream);
 
 /*
+ * Tuning switch with no counterpart in the reference: rows of up to 32 * vecs_per_lane
+ * 16-byte vectors are normalised by one warp each (no block barrier); longer rows get one
+ * thread block each.  Range 0..16, default 8.  Process-wide, not thread-safe.
+ */
+KCG_API void kcg_layernorm_set_warp_row_limit(int vecs_per_lane);
+
+/*
  * Unary elementwise map — replaces `{Op}_Elementwise_{dims}` and
  * `Relu_Elementwise_{dims}` (builders: src/Frontend/Operators.cc:222-289 and
  * :1003-1074; schedule: src/Optimizer/Optimizer.cc:1080-1175).

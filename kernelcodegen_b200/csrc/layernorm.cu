@@ -8,8 +8,8 @@
 // between the two reductions), which is what an HBM-bound op should cost.
 //
 // Three kernels:
-//   ln_warp_rows   one warp per row, rows of up to 32*8 16-byte vectors, no barriers
-//   ln_block_rows  one thread block per row, rows of up to 512*VPT vectors
+//   ln_warp_rows   one warp per row, rows of up to 32*16 16-byte vectors, no barriers
+//   ln_block_rows  one thread block per row, rows of up to 512*8 vectors
 //   ln_chunk_*     rows too long (or too ragged) for the above: each row is cut
 //                  into chunks, per-chunk (mean, M2) go to a scratch buffer, and a
 //                  second kernel merges them (Chan's formula) and normalises.
@@ -21,166 +21,141 @@ void* device_scratch(size_t bytes);  // runtime.cu
 
 namespace {
 
-template <typename T, int VPT>
-__global__ void __launch_bounds__(256)
-ln_warp_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
-             T* __restrict__ y, int64_t rows, int cols, float eps) {
-  constexpr int VW = Vec16<T>::N;
-  const int lane = threadIdx.x & 31;
-  const int warps = blockDim.x >> 5;
-  const int nvec = cols / VW;
-  const float inv_n = 1.0f / static_cast<float>(cols);
+// Longest row (in 16-byte vectors per lane) that is given to the warp-per-row kernel.
+int g_warp_row_max_vecs = 8;
 
-  // gamma / beta are the same for every row: keep them in registers across the row loop
-  // while they fit, otherwise re-read them (L1/L2 hits) when a row is written.
-  constexpr bool kCache = VPT * (8 + VW) <= 64;
-  Vec16<T> g[kCache ? VPT : 1], b[kCache ? VPT : 1];
-  if constexpr (kCache) {
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = i * 32 + lane;
-      if (vi < nvec) {
-        g[i] = ld_vec(gamma + vi * VW);
-        b[i] = ld_vec(beta + vi * VW);
-      }
-    }
+// A row sits in registers as raw 32-bit words (two 16-bit elements or one fp32 per word)
+// and is unpacked three times: for the sum, for the centred sum of squares and for the
+// output.  Keeping the packed form (a bf16 row of 4096 is 64 registers per lane at one warp
+// per row) is what lets enough warps be resident to cover HBM latency; `opaque` stops the
+// compiler from keeping an unpacked fp32 copy alive across the three passes instead.
+template <typename T> struct Words;
+template <> struct Words<float> {
+  static constexpr int EPW = 1;
+  static __device__ __forceinline__ void unpack(uint32_t w, float (&f)[1]) { f[0] = __uint_as_float(w); }
+  static __device__ __forceinline__ uint32_t pack(const float (&f)[1]) { return __float_as_uint(f[0]); }
+};
+template <> struct Words<__nv_bfloat16> {
+  static constexpr int EPW = 2;
+  static __device__ __forceinline__ void unpack(uint32_t w, float (&f)[2]) {
+    f[0] = __uint_as_float(w << 16);
+    f[1] = __uint_as_float(w & 0xffff0000u);
   }
+  static __device__ __forceinline__ uint32_t pack(const float (&f)[2]) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(f[0], f[1]);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+template <> struct Words<__half> {
+  static constexpr int EPW = 2;
+  static __device__ __forceinline__ void unpack(uint32_t w, float (&f)[2]) {
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    f[0] = v.x;
+    f[1] = v.y;
+  }
+  static __device__ __forceinline__ uint32_t pack(const float (&f)[2]) {
+    __half2 v = __floats2half2_rn(f[0], f[1]);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+__device__ __forceinline__ uint32_t opaque(uint32_t w) {
+  asm volatile("" : "+r"(w));
+  return w;
+}
 
-  int64_t row = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5);
-  const int64_t step = static_cast<int64_t>(gridDim.x) * warps;
-  for (; row < rows; row += step) {
-    const T* xr = x + row * cols;
-    T* yr = y + row * cols;
-    float v[VPT][VW];
-    float s = 0.f;
+// Loads, normalises and stores one row held by `nthr` cooperating threads (a warp or a
+// block); `reduce` sums a float over those threads.  kExact: the row is exactly
+// nthr * VPT vectors long, so no bounds checks are needed.
+template <typename T, int VPT, bool kExact, typename Reduce>
+__device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __restrict__ gamma,
+                                       const T* __restrict__ beta, T* __restrict__ yr, int tid, int nthr,
+                                       int nvec, float inv_n, float eps, Reduce reduce) {
+  using W = Words<T>;
+  constexpr int EPW = W::EPW;
+  uint4 v[VPT];
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = i * 32 + lane;
-      if (vi < nvec) {
-        Vec16<T> t = ld_vec_stream(xr + vi * VW);
+  for (int i = 0; i < VPT; ++i)
+    if (kExact || i * nthr + tid < nvec) v[i] = __ldcs(reinterpret_cast<const uint4*>(xr) + i * nthr + tid);
+  float s = 0.f;
 #pragma unroll
-        for (int j = 0; j < VW; ++j) {
-          v[i][j] = Conv<T>::to_f(t.v[j]);
-          s += v[i][j];
-        }
-      } else {
+  for (int i = 0; i < VPT; ++i)
+    if (kExact || i * nthr + tid < nvec) {
+      const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
 #pragma unroll
-        for (int j = 0; j < VW; ++j) v[i][j] = 0.f;
+      for (int k = 0; k < 4; ++k) {
+        float f[EPW];
+        W::unpack(w[k], f);
+#pragma unroll
+        for (int e = 0; e < EPW; ++e) s += f[e];
       }
     }
-    const float mean = warp_sum(s) * inv_n;
-    float q = 0.f;
+  const float mean = reduce(s) * inv_n;
+  float q = 0.f;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = i * 32 + lane;
-      if (vi < nvec) {
+  for (int i = 0; i < VPT; ++i)
+    if (kExact || i * nthr + tid < nvec) {
+      const uint32_t w[4] = {opaque(v[i].x), opaque(v[i].y), opaque(v[i].z), opaque(v[i].w)};
 #pragma unroll
-        for (int j = 0; j < VW; ++j) {
-          v[i][j] -= mean;
-          q += v[i][j] * v[i][j];
+      for (int k = 0; k < 4; ++k) {
+        float f[EPW];
+        W::unpack(w[k], f);
+#pragma unroll
+        for (int e = 0; e < EPW; ++e) {
+          const float d = f[e] - mean;
+          q = fmaf(d, d, q);
         }
       }
     }
-    const float rstd = 1.0f / sqrtf(warp_sum(q) * inv_n + eps);
+  const float rstd = 1.0f / sqrtf(reduce(q) * inv_n + eps);
+  const float shift = -mean * rstd;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = i * 32 + lane;
-      if (vi < nvec) {
-        Vec16<T> o, gg, bb;
-        if constexpr (kCache) {
-          gg = g[i];
-          bb = b[i];
-        } else {
-          gg = ld_vec(gamma + vi * VW);
-          bb = ld_vec(beta + vi * VW);
-        }
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = i * nthr + tid;
+    if (kExact || vi < nvec) {
+      const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
+      const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(beta) + vi);
+      const uint32_t w[4] = {opaque(v[i].x), opaque(v[i].y), opaque(v[i].z), opaque(v[i].w)};
+      const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+      const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
+      uint32_t o[4];
 #pragma unroll
-        for (int j = 0; j < VW; ++j)
-          o.v[j] = Conv<T>::from_f(Conv<T>::to_f(gg.v[j]) * (v[i][j] * rstd) + Conv<T>::to_f(bb.v[j]));
-        st_vec_stream(yr + vi * VW, o);
+      for (int k = 0; k < 4; ++k) {
+        float f[EPW], g[EPW], b[EPW], r[EPW];
+        W::unpack(w[k], f);
+        W::unpack(gw[k], g);
+        W::unpack(bw[k], b);
+#pragma unroll
+        for (int e = 0; e < EPW; ++e) r[e] = fmaf(g[e], fmaf(f[e], rstd, shift), b[e]);
+        o[k] = W::pack(r);
       }
+      __stcs(reinterpret_cast<uint4*>(yr) + vi, make_uint4(o[0], o[1], o[2], o[3]));
     }
   }
 }
 
-template <typename T, int VPT>
+// One warp per row, four rows per block, no shared memory and no block barrier; rows of
+// up to 32*VPT vectors.
+template <typename T, int VPT, bool kExact>
+__global__ void __launch_bounds__(128, 5)
+ln_warp_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+             T* __restrict__ y, int64_t rows, int cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  ln_row<T, VPT, kExact>(x + row * cols, gamma, beta, y + row * cols, lane, 32, cols / Vec16<T>::N,
+                         1.0f / static_cast<float>(cols), eps, [](float v) { return warp_sum(v); });
+}
+
+// One thread block per row for longer rows: blockDim.x threads hold up to VPT vectors each.
+template <typename T, int VPT, bool kExact>
 __global__ void __launch_bounds__(512)
 ln_block_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
               T* __restrict__ y, int64_t rows, int cols, float eps) {
-  constexpr int VW = Vec16<T>::N;
   __shared__ float red[33];
-  const int tid = threadIdx.x, nthr = blockDim.x;
-  const int nvec = cols / VW;
-  const float inv_n = 1.0f / static_cast<float>(cols);
-
-  // gamma / beta are the same for every row: keep them in registers across the row loop
-  // while they fit, otherwise re-read them (L1/L2 hits) when a row is written.
-  constexpr bool kCache = VPT * (8 + VW) <= 64;
-  Vec16<T> g[kCache ? VPT : 1], b[kCache ? VPT : 1];
-  if constexpr (kCache) {
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = i * nthr + tid;
-      if (vi < nvec) {
-        g[i] = ld_vec(gamma + vi * VW);
-        b[i] = ld_vec(beta + vi * VW);
-      }
-    }
-  }
-
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const T* xr = x + row * cols;
-    T* yr = y + row * cols;
-    float v[VPT][VW];
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = i * nthr + tid;
-      if (vi < nvec) {
-        Vec16<T> t = ld_vec_stream(xr + vi * VW);
-#pragma unroll
-        for (int j = 0; j < VW; ++j) {
-          v[i][j] = Conv<T>::to_f(t.v[j]);
-          s += v[i][j];
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < VW; ++j) v[i][j] = 0.f;
-      }
-    }
-    const float mean = block_sum(s, red) * inv_n;
-    float q = 0.f;
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = i * nthr + tid;
-      if (vi < nvec) {
-#pragma unroll
-        for (int j = 0; j < VW; ++j) {
-          v[i][j] -= mean;
-          q += v[i][j] * v[i][j];
-        }
-      }
-    }
-    const float rstd = 1.0f / sqrtf(block_sum(q, red) * inv_n + eps);
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int vi = i * nthr + tid;
-      if (vi < nvec) {
-        Vec16<T> o, gg, bb;
-        if constexpr (kCache) {
-          gg = g[i];
-          bb = b[i];
-        } else {
-          gg = ld_vec(gamma + vi * VW);
-          bb = ld_vec(beta + vi * VW);
-        }
-#pragma unroll
-        for (int j = 0; j < VW; ++j)
-          o.v[j] = Conv<T>::from_f(Conv<T>::to_f(gg.v[j]) * (v[i][j] * rstd) + Conv<T>::to_f(bb.v[j]));
-        st_vec_stream(yr + vi * VW, o);
-      }
-    }
-  }
+  const int64_t row = blockIdx.x;
+  ln_row<T, VPT, kExact>(x + row * cols, gamma, beta, y + row * cols, threadIdx.x, blockDim.x,
+                         cols / Vec16<T>::N, 1.0f / static_cast<float>(cols), eps,
+                         [&](float v) { return block_sum(v, red); });
 }
 
 // ---- split-row path ----------------------------------------------------------------
@@ -274,44 +249,41 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
   const bool vec_ok = (cols % VW == 0) && aligned16(x) && aligned16(y) && aligned16(gamma) &&
                       aligned16(beta);
   const int64_t nvec = cols / VW;
-  const int sms = sm_count();
-  if (vec_ok && nvec <= 32 * 8) {
-    const int warps = 8;
-    const int64_t want = (rows + warps - 1) / warps;
-    const int grid = static_cast<int>(want < static_cast<int64_t>(sms) * 8 ? want : static_cast<int64_t>(sms) * 8);
+  if (rows > 0x7fffffffll * 4) return fail(KCG_ERR_UNSUPPORTED, "layernorm: more than 2^33 rows");
+  if (vec_ok && nvec <= 32 * g_warp_row_max_vecs) {
+    const unsigned grid = static_cast<unsigned>((rows + 3) / 4);
     const int vpt = static_cast<int>((nvec + 31) / 32);
-#define KCG_LN_WARP(V)                                                                   \
-  ln_warp_rows<T, V><<<grid, warps * 32, 0, stream>>>(x, gamma, beta, y, rows,           \
-                                                      static_cast<int>(cols), eps)
+#define KCG_LN_WARP(V)                                                                             \
+  do {                                                                                             \
+    if (nvec == 32 * V)                                                                            \
+      ln_warp_rows<T, V, true><<<grid, 128, 0, stream>>>(x, gamma, beta, y, rows, static_cast<int>(cols), eps);  \
+    else                                                                                           \
+      ln_warp_rows<T, V, false><<<grid, 128, 0, stream>>>(x, gamma, beta, y, rows, static_cast<int>(cols), eps); \
+  } while (0)
     if (vpt <= 1) KCG_LN_WARP(1);
     else if (vpt <= 2) KCG_LN_WARP(2);
     else if (vpt <= 4) KCG_LN_WARP(4);
-    else KCG_LN_WARP(8);
+    else if (vpt <= 8) KCG_LN_WARP(8);
+    else KCG_LN_WARP(16);
 #undef KCG_LN_WARP
     return check_launch("ln_warp_rows");
   }
-  // Block per row while a row fits 512 threads x (64 fp32 values per thread).
-  constexpr int kMaxVpt = 64 / VW;
-  if (vec_ok && nvec <= 512 * kMaxVpt) {
-    // Aim for at most 256 threads; widen per-thread work first, then the block.
-    int vpt = 1;
-    while (vpt < kMaxVpt && nvec > 256 * vpt) vpt *= 2;
-    int threads = static_cast<int>((nvec + vpt - 1) / vpt);
+  // Block per row: at most 8 vectors per thread and at most 512 threads.
+  if (vec_ok && nvec <= 512 * 8 && rows <= 0x7fffffffll) {
+    int threads = static_cast<int>((nvec + 7) / 8);
     threads = (threads + 31) / 32 * 32;
-    const int ctas_per_sm = 2048 / threads > 8 ? 8 : 2048 / threads;
-    const int64_t cap = static_cast<int64_t>(sms) * (ctas_per_sm > 0 ? ctas_per_sm : 1);
-    const int grid = static_cast<int>(rows < cap ? rows : cap);
-#define KCG_LN_BLOCK(V)                                                                  \
-  ln_block_rows<T, V><<<grid, threads, 0, stream>>>(x, gamma, beta, y, rows,             \
-                                                    static_cast<int>(cols), eps)
-    switch (vpt) {
-      case 1: KCG_LN_BLOCK(1); break;
-      case 2: KCG_LN_BLOCK(2); break;
-      case 4: KCG_LN_BLOCK(4); break;
-      case 8: if constexpr (kMaxVpt >= 8) { KCG_LN_BLOCK(8); } break;
-      case 16: if constexpr (kMaxVpt >= 16) { KCG_LN_BLOCK(16); } break;
-      default: return fail(KCG_ERR_UNSUPPORTED, "layernorm: unexpected vectors per thread %d", vpt);
-    }
+    const int vpt = static_cast<int>((nvec + threads - 1) / threads);
+    const unsigned grid = static_cast<unsigned>(rows);
+#define KCG_LN_BLOCK(V)                                                                            \
+  do {                                                                                             \
+    if (nvec == static_cast<int64_t>(threads) * V)                                                 \
+      ln_block_rows<T, V, true><<<grid, threads, 0, stream>>>(x, gamma, beta, y, rows, static_cast<int>(cols), eps);  \
+    else                                                                                           \
+      ln_block_rows<T, V, false><<<grid, threads, 0, stream>>>(x, gamma, beta, y, rows, static_cast<int>(cols), eps); \
+  } while (0)
+    if (vpt <= 2) KCG_LN_BLOCK(2);
+    else if (vpt <= 4) KCG_LN_BLOCK(4);
+    else KCG_LN_BLOCK(8);
 #undef KCG_LN_BLOCK
     return check_launch("ln_block_rows");
   }
@@ -336,6 +308,10 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
 
 }  // namespace
 }  // namespace kcg
+
+extern "C" void kcg_layernorm_set_warp_row_limit(int vecs_per_lane) {
+  kcg::g_warp_row_max_vecs = vecs_per_lane < 0 ? 0 : (vecs_per_lane > 16 ? 16 : vecs_per_lane);
+}
 
 extern "C" int kcg_layernorm(int dtype, int64_t rows, int64_t cols, const void* x,
                              const void* gamma, const void* beta, float eps, void* y,

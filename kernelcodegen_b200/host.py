@@ -54,7 +54,7 @@ def elementwise(x, operation, out=None):
 
 def binary(a, b, operation, out=None):
     da, db = _up("bin_a", a), _up("bin_b", b)
-    shape = torch.broadcast_shapes(a.shape, b.shape)
+    shape = ops._broadcast_shape(a.shape, b.shape)
     c = ops.binary(da, db, operation, out=_dev("bin_c", torch.empty(shape, dtype=a.dtype, device="meta")))
     return _down(c, out)
 

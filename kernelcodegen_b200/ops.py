@@ -57,6 +57,18 @@ def _i64arr(v):
     return (ctypes.c_int64 * len(v))(*[int(x) for x in v])
 
 
+def _broadcast_shape(sa, sb):
+    """Trailing-aligned broadcast of two shapes (the rule of Binary::build, Operators.cc:797-821)."""
+    out = []
+    for i in range(1, max(len(sa), len(sb)) + 1):
+        da = sa[-i] if i <= len(sa) else 1
+        db = sb[-i] if i <= len(sb) else 1
+        if da != db and da != 1 and db != 1:
+            raise ValueError("dim not equal")
+        out.append(db if da == 1 else da)
+    return tuple(reversed(out))
+
+
 def layernorm(x, scale, bias, axis: int, eps: float = 1e-5, inplace: bool = False, out=None):
     """LayerNorm over dims [axis..] (reference: LayerNorm::build, Operators.h:125-128)."""
     _need_cuda(x, scale, bias)
@@ -105,10 +117,7 @@ def binary(a, b, operation: str, inplace: bool = False, out=None):
         raise KeyError(operation)
     if a.dtype != b.dtype:
         raise TypeError("binary: operands must share a dtype")
-    try:
-        oshape = torch.broadcast_shapes(a.shape, b.shape)
-    except RuntimeError:
-        raise ValueError("dim not equal") from None
+    oshape = _broadcast_shape(a.shape, b.shape)
     if inplace:
         if tuple(a.shape) != tuple(oshape):
             raise ValueError("inplace needs the left operand to have the output shape")
