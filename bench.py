@@ -331,12 +331,19 @@ def main() -> None:
         return not args.no_extras and (not only or name in only)
 
     def time_op(fn, iters, warm=3):
-        for _ in range(warm):
-            fn()
+        """Average device time of `fn`: `iters` calls captured in a CUDA graph, replayed once timed."""
+        with torch.cuda.stream(cap_stream):
+            for _ in range(warm):
+                fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=cap_stream):
+            for _ in range(iters):
+                fn()
+        g.replay()
         barrier()
         e0.record()
-        for _ in range(iters):
-            fn()
+        g.replay()
         e1.record()
         barrier()
         return max_over_ranks(e0.elapsed_time(e1)) / iters
@@ -421,6 +428,25 @@ def main() -> None:
                 "frac_of_measured_bf16_peak": tf / world / peaks["bf16_tflops"],
                 "frac_of_nominal_2250": tf / world / 2250.0}
         del Q, K, V, Oo
+        torch.cuda.empty_cache()
+    if world > 1 and not args.no_extras:
+        # the optional exchange: NCCL all-gather of a sharded output (here the 128 MiB bf16 C
+        # block of the GEMM shard and the 64 MiB LayerNorm block), timed on the device
+        for name, shape in (("allgather_gemm_c_block", (8192, 8192)), ("allgather_ln_block", (ROWS, COLS))):
+            loc = torch.zeros(shape, dtype=dt, device="cuda")
+            out = torch.empty((shape[0] * world, shape[1]), dtype=dt, device="cuda")
+            for _ in range(3):
+                dist.all_gather_into_tensor(out, loc)
+            barrier()
+            e0.record()
+            for _ in range(5):
+                dist.all_gather_into_tensor(out, loc)
+            e1.record()
+            barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1)) / 5
+            recv = (world - 1) * loc.numel() * 2
+            workloads[name] = {"ms": ms, "value": recv / (ms * 1e-3) / 1e9, "unit": "GB/s received per GPU"}
+            del loc, out
         torch.cuda.empty_cache()
     if _lib.device_status() != 0:
         raise SystemExit("a kernel reported a timed-out device-side wait")

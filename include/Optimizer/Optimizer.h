@@ -1,0 +1,67 @@
+// Optimizers: in the reference each one pattern-matches functions by name and rewrites
+// their loop nests into a GPU schedule (include/Optimizer/Optimizer.h:29-286).  Here the
+// schedules are the hand-written sm_100a kernels, so an optimizer only SELECTS: `applicable`
+// finds the functions of its family that are still tagged "cpu", `applyOptimzer` tags them
+// "gpu" and records the kernel that will run them.  The static tile-config maps are kept
+// (KernelCodeGenerator fills them from its tables) and recorded with the selection.
+#pragma once
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "Frontend/Operators.h"
+
+namespace KernelCodeGen {
+
+struct Module;      // defined in KernelCodeGen.h
+struct OpBuilder {};  // placeholder for the reference's mlir::OpBuilder parameter
+
+struct Optimizer {
+  virtual ~Optimizer() = default;
+  virtual bool applicable(Module& module) = 0;
+  virtual void applyOptimzer(Module& module, OpBuilder& builder) = 0;
+  bool operator==(const Optimizer& other) { return name == other.name; }
+  std::string name;
+
+ protected:
+  // functions whose name contains `needle` (and not `exclude`) and that are still "cpu"
+  std::vector<std::string> collect(Module& module, const std::string& needle, const std::string& exclude = "");
+  void select(Module& module, const std::vector<std::string>& funcs, const std::map<std::string, int>& config);
+  std::vector<std::string> matched;
+};
+
+#define KCG_DECLARE_OPTIMIZER(Class, Name, configMember)                 \
+  struct Class : Optimizer {                                             \
+    Class() { this->name = Name; }                                       \
+    bool applicable(Module& module) override;                            \
+    void applyOptimzer(Module& module, OpBuilder& builder) override;     \
+    static std::map<std::string, int> configMember;                      \
+  }
+
+KCG_DECLARE_OPTIMIZER(MatmulOptimizer, "Matmul", matmulConfig);
+KCG_DECLARE_OPTIMIZER(BinaryOptimizer, "Binary", binaryConfig);
+KCG_DECLARE_OPTIMIZER(ElementWiseOptimizer, "ElementWise", elementWiseConfig);
+KCG_DECLARE_OPTIMIZER(LayerNormOptimizer, "LayerNorm", layerNormConfig);
+KCG_DECLARE_OPTIMIZER(GatherOptimizer, "Gather", gatherConfig);
+KCG_DECLARE_OPTIMIZER(BatchMatmulOptimizer, "BatchMatmul", batchMatmulConfig);
+// Extension: the reference has no stand-alone softmax schedule (softmax only exists fused).
+KCG_DECLARE_OPTIMIZER(SoftmaxOptimizer, "Softmax", softmaxConfig);
+
+// Finds BatchMatmul(NT) -> Softmax -> BatchMatmul(NN) chains whose intermediate results have
+// a single user (reference: src/Optimizer/Optimizer.cc:2113-2199) and replaces each by one
+// Fused_Multi_Head_Attention call.
+struct FMHAOptimizer : Optimizer {
+  FMHAOptimizer() { this->name = "FMHA"; }
+  bool applicable(Module& module) override;
+  void applyOptimzer(Module& module, OpBuilder& builder) override;
+  static std::map<std::string, int> fmhaConfig;
+
+ private:
+  struct Chain { int qk, softmax, pv; };
+  std::vector<Chain> chains;
+};
+
+#undef KCG_DECLARE_OPTIMIZER
+
+}  // namespace KernelCodeGen

@@ -1,0 +1,318 @@
+// KernelCodeGenerator: config tables, the optimize() sweep, the textual plan and run().
+#include "KernelCodeGen.h"
+
+#include <fstream>
+#include <iostream>
+#include <sstream>
+
+#include "kcg_kernels.h"
+
+namespace KernelCodeGen {
+
+namespace {
+
+std::shared_ptr<GraphData> clone(const std::shared_ptr<GraphData>& g) {
+  return g ? std::make_shared<GraphData>(*g) : nullptr;
+}
+
+const char* entry_for(OpKind k) {
+  switch (k) {
+    case OpKind::Matmul: case OpKind::BatchedMatmul: return "kcg_gemm";
+    case OpKind::Softmax: return "kcg_softmax";
+    case OpKind::LayerNorm: return "kcg_layernorm";
+    case OpKind::ElementWise: return "kcg_eltwise";
+    case OpKind::Binary: return "kcg_binary";
+    case OpKind::FusedAttention: return "kcg_fmha_fwd";
+  }
+  return "?";
+}
+
+void rebuild_calls(Module& m) {
+  m.calls.clear();
+  if (!m.graph) return;
+  for (int i = 0; i < static_cast<int>(m.graph->ops.size()); ++i) {
+    const auto& op = m.graph->ops[i];
+    if (op.erased) continue;
+    m.calls.push_back({op.kind, op.func, entry_for(op.kind), i});
+  }
+}
+
+std::string shape_str(const std::vector<int64_t>& s) {
+  std::string r = "[";
+  for (size_t i = 0; i < s.size(); ++i) r += (i ? "," : "") + std::to_string(s[i]);
+  return r + "]";
+}
+
+int index_of(const std::vector<std::string>& v, const std::string& s) {
+  for (size_t i = 0; i < v.size(); ++i)
+    if (v[i] == s) return static_cast<int>(i);
+  return -1;
+}
+
+}  // namespace
+
+void Module::dump() const {
+  if (!graph) return;
+  std::cerr << "module @" << graph->name << " {\n";
+  for (const auto& f : graph->func_order) {
+    const auto& info = graph->funcs.at(f);
+    std::cerr << "  func @" << f << " {func.state = \"" << info.state << "\"";
+    if (!info.optimizer.empty()) std::cerr << ", optimizer = \"" << info.optimizer << "\"";
+    std::cerr << "}\n";
+  }
+  for (const auto& c : calls) std::cerr << "  launch " << c.entry << " for @" << c.func << "\n";
+  std::cerr << "}\n";
+}
+
+KernelCodeGenerator::KernelCodeGenerator(const std::string& platform_) : platform(platform_) {
+  // Default tile-config tables with the reference's keys (include/KernelCodeGen.h:35-58).  The
+  // matmul / fmha entries describe the sm_100a kernels: CTA tile, k-block, ring depth.
+  matmulConfigs = {{{"BLOCK_SIZE_M", 128}, {"BLOCK_SIZE_N", 256}, {"BLOCK_SIZE_K", 64}, {"GROUP_SIZE_M", 8},
+                    {"STAGES", 4}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}}};
+  batchMatmulConfigs = matmulConfigs;
+  binaryConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
+  elementWiseConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
+  layerNormConfigs = {{{"WARP_ROW_VECS", 8}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}}};
+  gatherConfigs = {};
+  softmaxConfigs = {{{"BLOCK_SIZE", 256}}};
+  fmhaConfigs = {{{"BLOCK_SIZE", 192}, {"Br", 128}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}}};
+}
+
+ComputeDAG& KernelCodeGenerator::createGraph(const std::string& graphName) {
+  minLatency = FLT_MAX;
+  graph.data = std::make_shared<GraphData>();
+  graph.data->name = graphName;
+  return graph;
+}
+
+void KernelCodeGenerator::dump(Module& module, const std::string& info) {
+  if (KCGLog::level == Log::Release) return;
+  std::cerr << "----------------------------------------------------------\n";
+  std::cerr << "           " << info << "\n";
+  std::cerr << "----------------------------------------------------------\n";
+  module.dump();
+}
+
+void KernelCodeGenerator::save(const std::string& str, const std::string& file) {
+  if (file == "terminal") {
+    std::cout << str;
+    return;
+  }
+  std::ofstream w(file.c_str());
+  if (!w.is_open()) {
+    std::cerr << "Can't open file \"" << file << "\"\n";
+    return;
+  }
+  w << str;
+}
+
+void KernelCodeGenerator::resetModule(Module& module) { module.graph = clone(backupModule_.graph); }
+void KernelCodeGenerator::backupModule(Module& module) { backupModule_.graph = clone(module.graph); }
+void KernelCodeGenerator::saveBestModule(Module& module) {
+  bestModule.graph = clone(module.graph);
+  rebuild_calls(bestModule);
+}
+
+Module& KernelCodeGenerator::optimize(ComputeDAG& graph_) {
+  graph = graph_;
+  Module module;
+  module.graph = clone(graph.data);
+  saveBestModule(module);
+  OpBuilder builder;
+  for (auto& opt : opts) {
+    backupModule(module);
+    std::vector<std::map<std::string, int>>* table = nullptr;
+    std::map<std::string, int>* slot = nullptr;
+    if (*opt == FMHAOptimizer()) { table = &fmhaConfigs; slot = &FMHAOptimizer::fmhaConfig; }
+    else if (*opt == MatmulOptimizer()) { table = &matmulConfigs; slot = &MatmulOptimizer::matmulConfig; }
+    else if (*opt == BinaryOptimizer()) { table = &binaryConfigs; slot = &BinaryOptimizer::binaryConfig; }
+    else if (*opt == ElementWiseOptimizer()) { table = &elementWiseConfigs; slot = &ElementWiseOptimizer::elementWiseConfig; }
+    else if (*opt == LayerNormOptimizer()) { table = &layerNormConfigs; slot = &LayerNormOptimizer::layerNormConfig; }
+    else if (*opt == GatherOptimizer()) { table = &gatherConfigs; slot = &GatherOptimizer::gatherConfig; }
+    else if (*opt == BatchMatmulOptimizer()) { table = &batchMatmulConfigs; slot = &BatchMatmulOptimizer::batchMatmulConfig; }
+    else if (*opt == SoftmaxOptimizer()) { table = &softmaxConfigs; slot = &SoftmaxOptimizer::softmaxConfig; }
+    bool applied = false;
+    if (table) {
+      for (auto& cfg : *table) {
+        *slot = cfg;
+        resetModule(module);
+        if (opt->applicable(module)) {
+          opt->applyOptimzer(module, builder);
+          const float latency = evaluate(module);
+          // The reference compares with `<` against a minimum that evaluate()==0 reaches at
+          // once, so later optimizers would never update the best module; every selection is
+          // kept here (`<=`), which is what its one-optimizer-per-run tests observe anyway.
+          if (latency <= minLatency) {
+            minLatency = latency;
+            saveBestModule(module);
+            applied = true;
+          }
+        }
+      }
+      if (!applied) resetModule(module);
+      else module.graph = clone(bestModule.graph);
+    } else if (opt->applicable(module)) {
+      opt->applyOptimzer(module, builder);
+      const float latency = evaluate(module);
+      if (latency <= minLatency) {
+        minLatency = latency;
+        saveBestModule(module);
+      }
+    }
+  }
+  return bestModule;
+}
+
+std::string CUDAGen(Module& module) {
+  std::ostringstream os;
+  if (!module.graph) return "";
+  const auto& g = *module.graph;
+  os << "// dispatch plan for graph \"" << g.name << "\": one line per sm_100a kernel launch\n";
+  for (const auto& c : module.calls) {
+    const auto& op = g.ops[c.op];
+    const auto& info = g.funcs.at(op.func);
+    os << (info.state == "gpu" ? "launch " : "// no optimizer selected @");
+    if (info.state == "gpu") os << c.entry << "  // @";
+    os << op.func << " (";
+    for (size_t i = 0; i < op.inputs.size(); ++i) {
+      const auto& t = g.tensors[op.inputs[i]];
+      os << (i ? ", " : "") << "%" << op.inputs[i] << ":" << toStr(t.dtype) << shape_str(t.shape);
+    }
+    const auto& o = g.tensors[op.output];
+    os << ") -> %" << op.output << ":" << toStr(o.dtype) << shape_str(o.shape);
+    if (o.alias_of >= 0) os << " inplace(%" << g.root(op.output) << ")";
+    if (!info.optimizer.empty()) {
+      os << "  [" << info.optimizer;
+      for (const auto& kv : info.config) os << " " << kv.first << "=" << kv.second;
+      os << "]";
+    }
+    os << "\n";
+  }
+  return os.str();
+}
+
+std::string KernelCodeGenerator::codegen(Module module) {
+  if (platform == "CUDA") {
+    std::string text = CUDAGen(module);
+    if (KCGLog::level == Log::Debug) std::cerr << text;
+    return text;
+  }
+  std::cerr << "Platform \"" << platform << "\" has no back end (only \"CUDA\").\n";
+  return "";
+}
+
+int KernelCodeGenerator::run(Module& module, const Bindings& bindings, void* stream) {
+  if (!module.graph) return KCG_ERR_INVALID_ARG;
+  const auto& g = *module.graph;
+  auto ptr = [&](int id) -> void* {
+    for (int t = id; t >= 0; t = g.tensors[t].alias_of)
+      if (void* p = bindings.get(t)) return p;
+    return nullptr;
+  };
+  auto numel = [&](int id) {
+    int64_t n = 1;
+    for (auto d : g.tensors[id].shape) n *= d;
+    return n;
+  };
+  for (const auto& c : module.calls) {
+    const auto& op = g.ops[c.op];
+    const auto& info = g.funcs.at(op.func);
+    if (info.state != "gpu") {
+      std::cerr << "run: no optimizer selected a kernel for @" << op.func
+                << " (push the matching Optimizer into opts); there is no CPU execution path.\n";
+      return KCG_ERR_UNSUPPORTED;
+    }
+    std::vector<void*> in;
+    for (int id : op.inputs) {
+      void* p = ptr(id);
+      if (!p) {
+        std::cerr << "run: tensor %" << id << " of @" << op.func << " has no device pointer bound.\n";
+        return KCG_ERR_INVALID_ARG;
+      }
+      in.push_back(p);
+    }
+    void* out = ptr(op.output);
+    if (!out) {
+      std::cerr << "run: result %" << op.output << " of @" << op.func << " has no device pointer bound.\n";
+      return KCG_ERR_INVALID_ARG;
+    }
+    const auto& t0 = g.tensors[op.inputs[0]];
+    const auto& to = g.tensors[op.output];
+    int rc = KCG_OK;
+    switch (op.kind) {
+      case OpKind::Matmul: {
+        const int64_t m = t0.shape[0], k = t0.shape[1], n = g.tensors[op.inputs[1]].shape[1];
+        const float* sa = op.scale_a >= 0 ? static_cast<const float*>(ptr(op.scale_a)) : nullptr;
+        const float* sb = op.scale_b >= 0 ? static_cast<const float*>(ptr(op.scale_b)) : nullptr;
+        rc = kcg_gemm(static_cast<int>(t0.dtype), static_cast<int>(to.dtype), m, n, k, 1, 0, 0, in[0], k, 0, in[1], n, 0,
+                      out, n, 0, sa, sb, stream);
+        break;
+      }
+      case OpKind::BatchedMatmul: {
+        const auto& sa = t0.shape;
+        const auto& sb = g.tensors[op.inputs[1]].shape;
+        const size_t r = sa.size();
+        const bool ta = op.layoutA == Layout::colMajor, tb = op.layoutB == Layout::colMajor;
+        const int64_t m = ta ? sa[r - 1] : sa[r - 2], k = ta ? sa[r - 2] : sa[r - 1];
+        const int64_t n = tb ? sb[r - 2] : sb[r - 1];
+        int64_t batch = 1;
+        for (size_t d = 0; d + 2 < r; ++d) batch *= sa[d];
+        rc = kcg_gemm(static_cast<int>(t0.dtype), static_cast<int>(to.dtype), m, n, k, batch, ta, tb, in[0], sa[r - 1],
+                      sa[r - 1] * sa[r - 2], in[1], sb[r - 1], sb[r - 1] * sb[r - 2], out, n, m * n, nullptr, nullptr,
+                      stream);
+        break;
+      }
+      case OpKind::Softmax: {
+        const int64_t cols = t0.shape.back();
+        const int64_t rows = cols ? numel(op.inputs[0]) / cols : 0;
+        const int64_t q_len = t0.shape.size() >= 2 ? t0.shape[t0.shape.size() - 2] : 1;
+        rc = kcg_softmax(static_cast<int>(t0.dtype), rows, cols, op.scale, op.causal, q_len, in[0], out, stream);
+        break;
+      }
+      case OpKind::LayerNorm: {
+        int64_t cols = 1;
+        for (size_t d = static_cast<size_t>(op.axis); d < t0.shape.size(); ++d) cols *= t0.shape[d];
+        const int64_t rows = cols ? numel(op.inputs[0]) / cols : 0;
+        if (numel(op.inputs[1]) != cols || numel(op.inputs[2]) != cols) {
+          std::cerr << "run: LayerNorm scale/bias with broadcast (1) dims must be bound pre-expanded to the "
+                       "normalised shape.\n";
+          return KCG_ERR_UNSUPPORTED;
+        }
+        rc = kcg_layernorm(static_cast<int>(t0.dtype), rows, cols, in[0], in[1], in[2], op.eps, out, stream);
+        break;
+      }
+      case OpKind::ElementWise: {
+        const int opi = index_of(ElementWise::operations(), op.operation);
+        rc = kcg_eltwise(opi, static_cast<int>(t0.dtype), static_cast<int>(to.dtype), numel(op.inputs[0]), in[0], out,
+                         stream);
+        break;
+      }
+      case OpKind::Binary: {
+        const auto& sa = t0.shape;
+        const auto& sb = g.tensors[op.inputs[1]].shape;
+        rc = kcg_binary(index_of(Binary::operations(), op.operation), static_cast<int>(t0.dtype),
+                        static_cast<int>(sa.size()), sa.data(), static_cast<int>(sb.size()), sb.data(), in[0], in[1], out,
+                        stream);
+        break;
+      }
+      case OpKind::FusedAttention: {
+        const auto& q = t0.shape;
+        const auto& k = g.tensors[op.inputs[1]].shape;
+        const size_t r = q.size();
+        const int64_t D = q[r - 1], Sq = q[r - 2], Skv = k[r - 2];
+        const int64_t H = r == 4 ? q[1] : 1, B = q[0];
+        const int64_t qs[3] = {H * Sq * D, Sq * D, D}, ks[3] = {H * Skv * D, Skv * D, D};
+        rc = kcg_fmha_fwd(static_cast<int>(t0.dtype), B, H, Sq, Skv, D, op.scale, op.causal, in[0], qs, in[1], ks, in[2],
+                          ks, out, qs, stream);
+        break;
+      }
+    }
+    if (rc != KCG_OK) {
+      std::cerr << "run: " << c.entry << " for @" << op.func << " failed: " << kcg_last_error() << "\n";
+      return rc;
+    }
+  }
+  return KCG_OK;
+}
+
+}  // namespace KernelCodeGen

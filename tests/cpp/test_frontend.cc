@@ -1,0 +1,357 @@
+// Front-end tests in the style of the reference's own test program (test/test.cc): each
+// case builds a graph with the reference call sequence, optimizes it and checks the result.
+//   test_frontend cpu    graph construction, naming, dedup, error handling, plans (no GPU)
+//   test_frontend gpu    runs the plans on the current device and compares with the CPU oracle
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <iostream>
+#include <random>
+#include <string>
+#include <vector>
+
+#include "KernelCodeGen.h"
+#include "kcg_kernels.h"
+
+using namespace KernelCodeGen;
+
+static int failures = 0;
+#define CHECK(cond)                                                              \
+  do {                                                                           \
+    if (!(cond)) {                                                               \
+      std::fprintf(stderr, "CHECK failed %s:%d: %s\n", __FILE__, __LINE__, #cond); \
+      ++failures;                                                                \
+    }                                                                            \
+  } while (0)
+
+static bool has(const std::string& text, const std::string& needle) { return text.find(needle) != std::string::npos; }
+
+// ---------------------------------------------------------------------------------- cpu mode
+static void test_operators_cast() {  // test/test.cc:8-49, the live sequence
+  KernelCodeGenerator generator("CUDA");
+  auto graph = generator.createGraph("demo");
+  generator.setLogMode(Log::Release);
+  generator.opts.push_back(std::move(std::make_unique<ElementWiseOptimizer>()));
+  auto A = graph.create<PlaceHolder>(std::vector<int64_t>{2, 768, 768}, std::string{"float32"});
+  auto gelu = graph.create<ElementWise>(A, "Cast", MemorySpace::global, "int32");
+  CHECK(bool(A) && bool(gelu));
+  CHECK(gelu.dtype() == DType::i32 && gelu.shape() == A.shape());
+  graph.dump();
+  auto module = generator.optimize(graph);
+  generator.dump(module);
+  auto&& sourceCode = generator.codegen(module);
+  CHECK(has(sourceCode, "launch kcg_eltwise") && has(sourceCode, "@Cast_Elementwise_2_768_768"));
+  CHECK(module.graph->funcs.at("Cast_Elementwise_2_768_768").state == "gpu");
+  // the graph the user holds is untouched by optimize (the reference optimizes a clone)
+  CHECK(graph.data->funcs.at("Cast_Elementwise_2_768_768").state == "cpu");
+}
+
+static void test_commented_sequences() {  // test/test.cc:26-46, the commented-out variants
+  KernelCodeGenerator generator("CUDA");
+  generator.opts.push_back(std::make_unique<LayerNormOptimizer>());
+  generator.opts.push_back(std::make_unique<BinaryOptimizer>());
+  generator.opts.push_back(std::make_unique<MatmulOptimizer>());
+  generator.opts.push_back(std::make_unique<BatchMatmulOptimizer>());
+  generator.opts.push_back(std::make_unique<ElementWiseOptimizer>());
+  auto graph = generator.createGraph("demo");
+  {
+    auto A = graph.create<PlaceHolder>(std::vector<int64_t>{2, 768, 768}, std::string{"float32"});
+    int64_t axis_ = 1;
+    float eps = 1e-5;
+    auto scale = graph.create<PlaceHolder>(std::vector<int64_t>{768, 768}, std::string{"float32"});
+    auto bias = graph.create<PlaceHolder>(std::vector<int64_t>{768, 768}, std::string{"float32"});
+    auto layernorm = graph.create<LayerNorm>(A, scale, bias, axis_, eps);
+    CHECK(bool(layernorm) && layernorm.shape() == A.shape());
+  }
+  {
+    auto A = graph.create<PlaceHolder>(std::vector<int64_t>{16, 1, 1, 256}, std::string{"float32"});
+    auto B = graph.create<PlaceHolder>(std::vector<int64_t>{1, 128, 256}, std::string{"float32"});
+    auto C = graph.create<Binary>(A, B, "Add");
+    CHECK(bool(C) && C.shape() == (std::vector<int64_t>{16, 1, 128, 256}));
+  }
+  {
+    int m = 2048, n = 2048, k = 1024;
+    auto A = graph.create<PlaceHolder>(std::vector<int64_t>{m, k}, std::string{"float32"});
+    auto B = graph.create<PlaceHolder>(std::vector<int64_t>{k, n}, std::string{"float32"});
+    auto C = graph.create<Matmul>(A, B);
+    auto D = graph.create<Relu>(C, MemorySpace::inplace);  // test/test.cc:62-63
+    auto C2 = graph.create<Matmul>(A, B, MemorySpace::global);  // old call form, test/test.cc:89
+    CHECK(bool(C) && bool(D) && bool(C2));
+    CHECK(graph.data->tensors[D.id].alias_of == C.id);
+  }
+  {
+    auto A = graph.create<PlaceHolder>(std::vector<int64_t>{256, 2048, 64}, std::string{"float32"});
+    auto B = graph.create<PlaceHolder>(std::vector<int64_t>{256, 2048, 64}, std::string{"float32"});
+    auto C = graph.create<BatchedMatmul>(A, Layout::rowMajor, B, Layout::colMajor);
+    CHECK(bool(C) && C.shape() == (std::vector<int64_t>{256, 2048, 2048}));
+  }
+  const auto& f = graph.data->funcs;
+  CHECK(f.count("LayerNorm_2_768_768_axis_1"));
+  CHECK(f.count("Add_Binary_16_1_1_256_Add_1_128_256"));
+  CHECK(f.count("Matmul_m2048n2048k1024"));
+  CHECK(f.count("Relu_Elementwise_2048_2048"));
+  CHECK(f.count("BatchMatmul_256_m2048_n2048_k64_NT"));
+  // two calls of the same (op, shape) share one function
+  int matmul_funcs = 0;
+  for (const auto& name : graph.data->func_order) matmul_funcs += name == "Matmul_m2048n2048k1024";
+  CHECK(matmul_funcs == 1);
+  auto module = generator.optimize(graph);
+  for (const auto& kv : module.graph->funcs) CHECK(kv.second.state == "gpu");
+  // "Matmul" must not claim the batched function (reference: Optimizer.cc:255)
+  CHECK(module.graph->funcs.at("BatchMatmul_256_m2048_n2048_k64_NT").optimizer == "BatchMatmul");
+  CHECK(module.graph->funcs.at("Matmul_m2048n2048k1024").optimizer == "Matmul");
+  CHECK(module.graph->funcs.at("Relu_Elementwise_2048_2048").optimizer == "ElementWise");
+  auto plan = generator.codegen(module);
+  CHECK(has(plan, "launch kcg_layernorm") && has(plan, "launch kcg_binary") && has(plan, "launch kcg_gemm"));
+  CHECK(has(plan, "inplace(%"));
+  generator.save(plan, "/tmp/kcg_plan_test.txt");
+  FILE* fp = std::fopen("/tmp/kcg_plan_test.txt", "r");
+  CHECK(fp != nullptr);
+  if (fp) std::fclose(fp);
+}
+
+static void test_flash_attention_graph() {  // test/test.cc:107-147
+  KernelCodeGenerator generator("CUDA");
+  auto graph = generator.createGraph("flash_attn_demo");
+  generator.opts.push_back(std::move(std::make_unique<FMHAOptimizer>()));
+  int64_t head_dim = 64L, seq_len = 2048L, batch_size = 8, head_num = 32;
+  for (const char* dtype : {"float32", "bfloat16"}) {
+    graph = generator.createGraph("flash_attn_demo");
+    auto Q = graph.create<PlaceHolder>(std::vector<int64_t>{batch_size, head_num, seq_len, head_dim}, std::string{dtype});
+    auto K = graph.create<PlaceHolder>(std::vector<int64_t>{batch_size, head_num, seq_len, head_dim}, std::string{dtype});
+    auto V = graph.create<PlaceHolder>(std::vector<int64_t>{batch_size, head_num, seq_len, head_dim}, std::string{dtype});
+    auto S = graph.create<BatchedMatmul>(Q, Layout::rowMajor, K, Layout::colMajor);
+    auto P = graph.create<Softmax>(S, -1, MemorySpace::inplace);
+    auto O = graph.create<BatchedMatmul>(P, Layout::rowMajor, V, Layout::rowMajor);
+    CHECK(bool(O) && O.shape() == Q.shape());
+    CHECK(graph.data->funcs.count("BatchMatmul_8_32_m2048_n2048_k64_NT"));
+    CHECK(graph.data->funcs.count("Softmax_8_32_2048_2048_axis3"));
+    CHECK(graph.data->funcs.count("BatchMatmul_8_32_m2048_n64_k2048_NN"));
+    auto module = generator.optimize(graph);
+    auto plan = generator.codegen(module);
+    if (std::string(dtype) == "bfloat16") {
+      CHECK(module.calls.size() == 1);
+      CHECK(has(plan, "launch kcg_fmha_fwd") && has(plan, "@Fused_Multi_Head_Attention_8_32_SL2048_HD64"));
+      CHECK(!module.graph->funcs.count("Softmax_8_32_2048_2048_axis3"));
+    } else {
+      // the fused kernel is a 16-bit tensor-core kernel: the fp32 chain stays three calls
+      CHECK(module.calls.size() == 3 && !has(plan, "kcg_fmha_fwd"));
+    }
+  }
+  // a second user of the scores blocks the fusion (single-user rule, Optimizer.cc:2131-2135)
+  graph = generator.createGraph("no_fuse");
+  auto Q = graph.create<PlaceHolder>(std::vector<int64_t>{2, 128, 64}, std::string{"bfloat16"});
+  auto S = graph.create<BatchedMatmul>(Q, Layout::rowMajor, Q, Layout::colMajor);
+  auto P = graph.create<Softmax>(S, -1, MemorySpace::inplace);
+  auto O = graph.create<BatchedMatmul>(P, Layout::rowMajor, Q, Layout::rowMajor);
+  auto extra = graph.create<ElementWise>(P, "Tanh", MemorySpace::global);
+  (void)O; (void)extra;
+  auto module = generator.optimize(graph);
+  CHECK(module.calls.size() == 4);
+}
+
+static void test_errors() {
+  KernelCodeGenerator generator("CUDA");
+  auto graph = generator.createGraph("errors");
+  auto A = graph.create<PlaceHolder>(std::vector<int64_t>{4, 5}, std::string{"float32"});
+  auto B = graph.create<PlaceHolder>(std::vector<int64_t>{4, 3}, std::string{"float32"});
+  CHECK(!graph.create<Matmul>(A, B));                       // incompatible K
+  CHECK(!graph.create<Binary>(A, B, "Add"));                // dim not equal
+  CHECK(!graph.create<Binary>(A, A, "Nope"));
+  CHECK(!graph.create<LayerNorm>(A, A, A, int64_t(2)));     // axis out of bounds
+  CHECK(!graph.create<LayerNorm>(A, B, A, int64_t(1)));     // scale dim is not equal
+  CHECK(!graph.create<Softmax>(A, 0));                      // only the last dim
+  CHECK(!graph.create<PlaceHolder>(std::vector<int64_t>{4}, std::string{"complex64"}));
+  CHECK(!graph.create<Matmul>(Value{}, B));                 // null operand
+  CHECK(!graph.create<Transpose>(A));
+  CHECK(!graph.create<Gather>(A, A));
+  CHECK(getDType("bfloat16") == DType::bf16 && getDType("float8_e4m3") == DType::f8e4m3 && toStr(DType::f16) == "float16");
+  // run() refuses functions no optimizer selected, and unbound tensors
+  auto C = graph.create<ElementWise>(A, "Gelu", MemorySpace::global);
+  auto module = generator.optimize(graph);
+  Bindings bind;
+  CHECK(generator.run(module, bind) == KCG_ERR_UNSUPPORTED);
+  generator.opts.push_back(std::make_unique<ElementWiseOptimizer>());
+  auto module2 = generator.optimize(graph);
+  CHECK(generator.run(module2, bind) == KCG_ERR_INVALID_ARG);
+  (void)C;
+  KernelCodeGenerator rocm("ROCm");
+  auto g2 = rocm.createGraph("x");
+  auto m2 = rocm.optimize(g2);
+  CHECK(rocm.codegen(m2).empty());
+}
+
+// ---------------------------------------------------------------------------------- gpu mode
+extern "C" {
+int cudaMalloc(void**, size_t);
+int cudaFree(void*);
+int cudaMemcpy(void*, const void*, size_t, int);
+int cudaDeviceSynchronize(void);
+// CPU oracle (oracle/kcg_oracle.c)
+void oracle_matmul_f32(const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t, int64_t, int);
+void oracle_layernorm_f32(const float*, const float*, const float*, float*, int64_t, int64_t, float, int);
+void oracle_unary_f32(int, const float*, float*, int64_t, int);
+int64_t oracle_binary_f32(int, int, const int64_t*, int, const int64_t*, const float*, const float*, float*);
+void oracle_attention_f32(const float*, const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t, int64_t,
+                          float, int, const int64_t*, const int64_t*, const int64_t*, const int64_t*, int64_t, int64_t, int);
+}
+
+static std::vector<float> randn(size_t n, unsigned seed, float std_ = 1.f, float mean = 0.f) {
+  std::mt19937 gen(seed);
+  std::normal_distribution<float> d(mean, std_);
+  std::vector<float> v(n);
+  for (auto& x : v) x = d(gen);
+  return v;
+}
+static void* upload(const void* h, size_t bytes) {
+  void* d = nullptr;
+  if (cudaMalloc(&d, bytes) != 0) { std::fprintf(stderr, "cudaMalloc failed\n"); std::exit(2); }
+  if (h) cudaMemcpy(d, h, bytes, 1);
+  return d;
+}
+static std::vector<float> download(void* d, size_t n) {
+  std::vector<float> v(n);
+  cudaMemcpy(v.data(), d, n * 4, 2);
+  return v;
+}
+static double rel_fro(const std::vector<float>& got, const std::vector<float>& want) {
+  double num = 0, den = 0;
+  for (size_t i = 0; i < want.size(); ++i) {
+    num += (double(got[i]) - want[i]) * (double(got[i]) - want[i]);
+    den += double(want[i]) * want[i];
+  }
+  return std::sqrt(num / (den > 0 ? den : 1));
+}
+static uint16_t to_bf16(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  u += 0x7FFF + ((u >> 16) & 1);
+  return uint16_t(u >> 16);
+}
+static float from_bf16(uint16_t h) {
+  uint32_t u = uint32_t(h) << 16;
+  float f;
+  std::memcpy(&f, &u, 4);
+  return f;
+}
+
+static void gpu_matmul_relu() {  // Matmul -> Relu inplace, fp32 (test/test.cc:59-63 scaled down)
+  KernelCodeGenerator generator("CUDA");
+  auto graph = generator.createGraph("matmul_demo");
+  generator.opts.push_back(std::make_unique<MatmulOptimizer>());
+  generator.opts.push_back(std::make_unique<ElementWiseOptimizer>());
+  const int m = 512, n = 256, k = 128;
+  auto A = graph.create<PlaceHolder>(std::vector<int64_t>{m, k}, std::string{"float32"});
+  auto B = graph.create<PlaceHolder>(std::vector<int64_t>{k, n}, std::string{"float32"});
+  auto C = graph.create<Matmul>(A, B);
+  auto D = graph.create<Relu>(C, MemorySpace::inplace);
+  auto module = generator.optimize(graph);
+  auto hA = randn(size_t(m) * k, 1), hB = randn(size_t(k) * n, 2);
+  Bindings bind;
+  void* dC = upload(nullptr, size_t(m) * n * 4);
+  bind.set(A, upload(hA.data(), hA.size() * 4));
+  bind.set(B, upload(hB.data(), hB.size() * 4));
+  bind.set(C, dC);  // D aliases C
+  CHECK(generator.run(module, bind) == KCG_OK);
+  cudaDeviceSynchronize();
+  std::vector<float> want(size_t(m) * n), relu(size_t(m) * n);
+  oracle_matmul_f32(hA.data(), hB.data(), want.data(), m, n, k, 0, m, 0);
+  oracle_unary_f32(3, want.data(), relu.data(), relu.size(), 0);
+  CHECK(rel_fro(download(dC, relu.size()), relu) <= 1e-5);
+  (void)D;
+}
+
+static void gpu_layernorm_gelu_add() {  // the headline chain through the graph API, fp32
+  KernelCodeGenerator generator("CUDA");
+  auto graph = generator.createGraph("ln_gelu_add");
+  generator.opts.push_back(std::make_unique<LayerNormOptimizer>());
+  generator.opts.push_back(std::make_unique<ElementWiseOptimizer>());
+  generator.opts.push_back(std::make_unique<BinaryOptimizer>());
+  const int64_t rows = 96, cols = 4096;
+  auto X = graph.create<PlaceHolder>(std::vector<int64_t>{rows, cols}, std::string{"float32"});
+  auto G = graph.create<PlaceHolder>(std::vector<int64_t>{cols}, std::string{"float32"});
+  auto Bt = graph.create<PlaceHolder>(std::vector<int64_t>{cols}, std::string{"float32"});
+  auto R = graph.create<PlaceHolder>(std::vector<int64_t>{rows, cols}, std::string{"float32"});
+  auto Y = graph.create<LayerNorm>(X, G, Bt, int64_t(-1));
+  auto Z = graph.create<ElementWise>(Y, "Gelu", MemorySpace::global);
+  auto W = graph.create<Binary>(Z, R, "Add");
+  auto module = generator.optimize(graph);
+  CHECK(module.calls.size() == 3);
+  auto hX = randn(rows * cols, 3), hG = randn(cols, 4, 0.1f, 1.f), hB = randn(cols, 5, 0.1f), hR = randn(rows * cols, 6);
+  Bindings bind;
+  void* dW = upload(nullptr, rows * cols * 4);
+  bind.set(X, upload(hX.data(), hX.size() * 4));
+  bind.set(G, upload(hG.data(), hG.size() * 4));
+  bind.set(Bt, upload(hB.data(), hB.size() * 4));
+  bind.set(R, upload(hR.data(), hR.size() * 4));
+  bind.set(Y, upload(nullptr, rows * cols * 4));
+  bind.set(Z, upload(nullptr, rows * cols * 4));
+  bind.set(W, dW);
+  CHECK(generator.run(module, bind) == KCG_OK);
+  cudaDeviceSynchronize();
+  std::vector<float> y(rows * cols), z(rows * cols), w(rows * cols);
+  oracle_layernorm_f32(hX.data(), hG.data(), hB.data(), y.data(), rows, cols, 1e-5f, 0);
+  oracle_unary_f32(5, y.data(), z.data(), z.size(), 0);
+  const int64_t sh[2] = {rows, cols};
+  oracle_binary_f32(0, 2, sh, 2, sh, z.data(), hR.data(), w.data());
+  CHECK(rel_fro(download(dW, w.size()), w) <= 1e-5);
+}
+
+static void gpu_fused_attention() {  // BatchedMatmul -> Softmax -> BatchedMatmul, bf16, fused
+  KernelCodeGenerator generator("CUDA");
+  auto graph = generator.createGraph("flash_attn_demo");
+  generator.opts.push_back(std::make_unique<FMHAOptimizer>());
+  const int64_t B = 2, H = 3, S = 256, D = 64;
+  auto Q = graph.create<PlaceHolder>(std::vector<int64_t>{B, H, S, D}, std::string{"bfloat16"});
+  auto K = graph.create<PlaceHolder>(std::vector<int64_t>{B, H, S, D}, std::string{"bfloat16"});
+  auto V = graph.create<PlaceHolder>(std::vector<int64_t>{B, H, S, D}, std::string{"bfloat16"});
+  auto Sc = graph.create<BatchedMatmul>(Q, Layout::rowMajor, K, Layout::colMajor);
+  auto P = graph.create<Softmax>(Sc, -1, MemorySpace::inplace, "", 0.125f, true);
+  auto O = graph.create<BatchedMatmul>(P, Layout::rowMajor, V, Layout::rowMajor);
+  auto module = generator.optimize(graph);
+  CHECK(module.calls.size() == 1 && module.calls[0].entry == "kcg_fmha_fwd");
+  const size_t n = size_t(B) * H * S * D;
+  auto fq = randn(n, 7), fk = randn(n, 8), fv = randn(n, 9);
+  std::vector<uint16_t> hq(n), hk(n), hv(n);
+  for (size_t i = 0; i < n; ++i) {
+    hq[i] = to_bf16(fq[i]); hk[i] = to_bf16(fk[i]); hv[i] = to_bf16(fv[i]);
+    fq[i] = from_bf16(hq[i]); fk[i] = from_bf16(hk[i]); fv[i] = from_bf16(hv[i]);
+  }
+  Bindings bind;
+  void* dO = upload(nullptr, n * 2);
+  bind.set(Q, upload(hq.data(), n * 2));
+  bind.set(K, upload(hk.data(), n * 2));
+  bind.set(V, upload(hv.data(), n * 2));
+  bind.set(O, dO);  // the scores and probabilities never exist in memory
+  CHECK(generator.run(module, bind) == KCG_OK);
+  cudaDeviceSynchronize();
+  CHECK(kcg_device_status() == KCG_OK);
+  std::vector<uint16_t> ho(n);
+  cudaMemcpy(ho.data(), dO, n * 2, 2);
+  std::vector<float> got(n), want(n);
+  for (size_t i = 0; i < n; ++i) got[i] = from_bf16(ho[i]);
+  const int64_t st[3] = {H * S * D, S * D, D};
+  oracle_attention_f32(fq.data(), fk.data(), fv.data(), want.data(), B, H, S, S, D, 0.125f, 1, st, st, st, st, 0, B * H, 0);
+  CHECK(rel_fro(got, want) <= 1e-2);
+}
+
+int main(int argc, char** argv) {
+  const std::string mode = argc > 1 ? argv[1] : "cpu";
+  if (mode == "cpu") {
+    test_operators_cast();
+    test_commented_sequences();
+    test_flash_attention_graph();
+    test_errors();
+  } else {
+    gpu_matmul_relu();
+    gpu_layernorm_gelu_add();
+    gpu_fused_attention();
+  }
+  if (failures) {
+    std::fprintf(stderr, "%d check(s) failed\n", failures);
+    return 1;
+  }
+  std::printf("frontend %s tests passed\n", mode.c_str());
+  return 0;
+}
