@@ -123,6 +123,40 @@ KCG_API int kcg_layernorm(int dtype, int64_t rows, int64_t cols, const void* x,
                           void* stream);
 
 /*
+ * LayerNorm through the split-row kernels, with no allocation of any kind.  This entry
+ * point has no counterpart in the reference (which never runs a kernel, let alone manages
+ * scratch memory).
+ *
+ * It is meant for callers that must not trigger a device allocation from inside a library
+ * call: a process that has handed all of HBM to its own memory pool (so a hidden
+ * cudaMalloc could fail), or a latency-critical loop in which cudaMalloc's implicit
+ * device-wide synchronisation, and the chance of an out-of-memory error in the middle of
+ * the loop, are not acceptable.  kcg_layernorm() may allocate (its split-row path grows a
+ * cached per-device buffer); this function never calls cudaMalloc, cudaFree or any
+ * allocating routine.
+ *
+ * Same arithmetic, arguments and result as kcg_layernorm(), always computed by the
+ * split-row kernels: each row is cut into chunks of 8192 elements, a first kernel writes
+ * the (mean, sum of squared deviations) of every chunk, a second merges them per row and
+ * normalises.  The per-chunk statistics live in a fixed array inside the library image
+ * (256 KiB of device memory on every GPU that loads the library, held until exit).
+ *
+ * Limit: rows * ceil(cols / 8192) <= 32768 and rows <= 65535; anything larger returns
+ * KCG_ERR_UNSUPPORTED with an explanatory kcg_last_error().
+ *
+ * The first call on each device looks up the device address of that array (one
+ * cudaGetSymbolAddress with that device current) and caches it; make that first call
+ * before starting any stream capture on the device.  All calls on a device share the one
+ * array and it keeps the previous call's contents; that is harmless because every entry
+ * read is first rewritten by the same call, so nothing needs clearing — but two calls that
+ * overlap on the GPU (different streams, or different host threads on one device) race on
+ * it: serialise them.
+ */
+KCG_API int kcg_layernorm_split_static(int dtype, int64_t rows, int64_t cols, const void* x,
+                                       const void* gamma, const void* beta, float eps, void* y,
+                                       void* stream);
+
+/*
  * Tuning switch with no counterpart in the reference: rows of up to 32 * vecs_per_lane
  * 16-byte vectors are normalised by one warp each (no block barrier); longer rows get one
  * thread block each.  Range 0..16, default 8.  Process-wide, not thread-safe.

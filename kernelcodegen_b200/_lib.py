@@ -32,6 +32,7 @@ SIGNATURES = {
     "kcg_device_status": ([], _ci),
     "kcg_dtype_size": ([_ci], ctypes.c_size_t),
     "kcg_layernorm": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _vp], _ci),
+    "kcg_layernorm_split_static": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _vp], _ci),
     "kcg_layernorm_set_warp_row_limit": ([_ci], None),
     "kcg_eltwise": ([_ci, _ci, _ci, _i64, _vp, _vp, _vp], _ci),
     "kcg_binary": ([_ci, _ci, _ci, _i64p, _ci, _i64p, _vp, _vp, _vp, _vp], _ci),

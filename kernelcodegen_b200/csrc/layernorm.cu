@@ -15,6 +15,8 @@
 //                  second kernel merges them (Chan's formula) and normalises.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace kcg {
 
 void* device_scratch(size_t bytes);  // runtime.cu
@@ -308,6 +310,88 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
 
 }  // namespace
 }  // namespace kcg
+
+// ---- split-row LayerNorm without any allocation -------------------------------------------
+// Scratch for kcg_layernorm_split_static(): per-(row, chunk) statistics live in this array,
+// which every GPU that loads the library holds until the process exits (256 KiB).
+namespace kcg {
+namespace {
+constexpr int64_t kStaticStatPairs = 32768;  // (row, chunk) pairs that fit
+static __device__ __align__(256) float g_ln_static_stats[kStaticStatPairs * 2];
+
+constexpr int kStaticMaxDevices = 64;
+float* g_ln_static_ptr[kStaticMaxDevices] = {nullptr};
+std::mutex g_ln_static_mutex;
+
+// Device address of g_ln_static_stats on the current device.  In host code the array's
+// name is only a handle, so the address is looked up once per device, with that device
+// current, and cached.
+int static_stats_ptr(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices)
+    return fail(KCG_ERR_CUDA, "layernorm_split_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(g_ln_static_mutex);
+  if (!g_ln_static_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_ln_static_stats);
+    if (e != cudaSuccess || !p)
+      return fail(KCG_ERR_CUDA, "layernorm_split_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_ln_static_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_ln_static_ptr[dev];
+  return KCG_OK;
+}
+
+template <typename T>
+int launch_ln_split_static(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* beta, float eps, T* y,
+                           cudaStream_t stream) {
+  const int64_t chunks64 = (cols + kChunk - 1) / kChunk;
+  if (rows > 65535 || rows * chunks64 > kStaticStatPairs)
+    return fail(KCG_ERR_UNSUPPORTED,
+                "layernorm_split_static: rows * ceil(cols / %d) = %lld exceeds the built-in scratch of %lld "
+                "(row, chunk) pairs (and rows must not exceed 65535); use kcg_layernorm",
+                kChunk, static_cast<long long>(rows * chunks64), static_cast<long long>(kStaticStatPairs));
+  float* stats = nullptr;
+  int rc = static_stats_ptr(&stats);
+  if (rc) return rc;
+  const int chunks = static_cast<int>(chunks64);
+  dim3 grid(chunks, static_cast<unsigned>(rows));
+  // Both kernels index stats[(row * chunks + c) * 2 + {0, 1}]; the first writes every entry
+  // the second reads, so nothing has to be cleared between calls.
+  ln_chunk_stats<T><<<grid, kChunkThreads, 0, stream>>>(x, stats, cols, chunks);
+  rc = check_launch("ln_chunk_stats");
+  if (rc) return rc;
+  ln_chunk_apply<T><<<grid, kChunkThreads, 0, stream>>>(x, gamma, beta, stats, y, cols, chunks, eps);
+  return check_launch("ln_chunk_apply");
+}
+}  // namespace
+}  // namespace kcg
+
+extern "C" int kcg_layernorm_split_static(int dtype, int64_t rows, int64_t cols, const void* x, const void* gamma,
+                                          const void* beta, float eps, void* y, void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (rows < 0 || cols < 0) return fail(KCG_ERR_INVALID_ARG, "layernorm_split_static: negative size");
+  if (rows == 0 || cols == 0) return KCG_OK;
+  if (!x || !gamma || !beta || !y) return fail(KCG_ERR_INVALID_ARG, "layernorm_split_static: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case KCG_F32:
+      return launch_ln_split_static<float>(rows, cols, static_cast<const float*>(x), static_cast<const float*>(gamma),
+                                           static_cast<const float*>(beta), eps, static_cast<float*>(y), s);
+    case KCG_BF16:
+      return launch_ln_split_static<__nv_bfloat16>(rows, cols, static_cast<const __nv_bfloat16*>(x),
+                                                   static_cast<const __nv_bfloat16*>(gamma),
+                                                   static_cast<const __nv_bfloat16*>(beta), eps,
+                                                   static_cast<__nv_bfloat16*>(y), s);
+    case KCG_F16:
+      return launch_ln_split_static<__half>(rows, cols, static_cast<const __half*>(x), static_cast<const __half*>(gamma),
+                                            static_cast<const __half*>(beta), eps, static_cast<__half*>(y), s);
+    default:
+      return fail(KCG_ERR_UNSUPPORTED, "layernorm_split_static: dtype %d has no kernel (float32, bfloat16, float16)", dtype);
+  }
+}
 
 extern "C" void kcg_layernorm_set_warp_row_limit(int vecs_per_lane) {
   kcg::g_warp_row_max_vecs = vecs_per_lane < 0 ? 0 : (vecs_per_lane > 16 ? 16 : vecs_per_lane);
