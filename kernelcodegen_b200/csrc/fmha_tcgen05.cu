@@ -381,6 +381,318 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Version 2: two 128-query tiles per CTA.
+//
+//   warps 0-3   softmax warpgroup of query tile 0 (one thread per row, TMEM lanes 0-127)
+//   warps 4-7   softmax warpgroup of query tile 1
+//   warp 8      TMA loader: both Q tiles once, then K_0, V_0, K_1, V_1, ... through one ring
+//   warp 9      MMA issuer
+// Tensor memory (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512).
+// P_i (16-bit, 64 columns) overwrites the first half of S_i once the owning thread has read
+// its score row.  The MMA thread issues, per key block j and tile i:  O_i += P_i(j) V_j  and
+// right behind it  S_i(j+1) = Q_i K_{j+1}^T.  MMAs of one thread execute in issue order, so
+// S_i(j+1) cannot overwrite P_i(j) before it has been read, and when the softmax threads see
+// S_i(j+1) complete, O_i is stable (PV_i(j) is behind them) and may be rescaled.  While tile
+// i is in its softmax, the tensor pipe works on tile 1-i, and every K / V tile is loaded once
+// for 256 query rows.
+constexpr int V2_THREADS = 320;
+
+template <typename T, int D, int NSLOT>
+__global__ void __launch_bounds__(V2_THREADS, 1)
+fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const FmhaParams p, const uint32_t idesc_qk,
+                 const uint32_t idesc_pv) {
+  constexpr int DB = D / 64;
+  constexpr int TILE = DB * TILE16K;   // bytes of one Q, K or V tile
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint8_t* q_smem = smem;                   // [2][TILE]
+  uint8_t* kv_smem = smem + 2 * TILE;       // [NSLOT][TILE]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_smem + NSLOT * TILE);
+  uint64_t* q_full = bars;                  // [1]
+  uint64_t* kv_full = bars + 1;             // [NSLOT]
+  uint64_t* kv_empty = kv_full + NSLOT;     // [NSLOT]
+  uint64_t* s_full = kv_empty + NSLOT;      // [2]
+  uint64_t* p_full = s_full + 2;            // [2]
+  uint64_t* drain_bar = p_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pairs = (p.q_tiles + 1) / 2;
+  const int pr = p.causal ? (pairs - 1 - static_cast<int>(blockIdx.x)) : static_cast<int>(blockIdx.x);
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int q0 = pr * 2 * BM;
+  const int off = p.Skv - p.Sq;
+  int n_blk[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    int kv_end = p.Skv;
+    if (p.causal) kv_end = min(p.Skv, q0 + (i + 1) * BM + off);
+    n_blk[i] = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
+  }
+  const int n_max = max(n_blk[0], n_blk[1]);  // == n_blk[1]: the later rows see at least as many keys
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    mbar_init(q_full, 1);
+    for (int s = 0; s < NSLOT; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA loader
+    if (lane == 0 && n_max > 0) {
+      bool ok = true;
+      mbar_expect_tx(q_full, 2 * TILE);
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int d = 0; d < DB; ++d)
+          tma_load_4d(q_smem + i * TILE + d * TILE16K, &tmQ, q_full, d * 64, q0 + i * BM, h, b);
+      int t = 0;  // ring item: 2j = K_j, 2j+1 = V_j
+      for (; t < 2 * n_max; ++t) {
+        const uint32_t s = t % NSLOT, ph = (t / NSLOT) & 1u;
+        if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(&kv_full[s], TILE);
+        const CUtensorMap* tm = (t & 1) ? &tmV : &tmK;
+#pragma unroll
+        for (int d = 0; d < DB; ++d)
+          tma_load_4d(kv_smem + s * TILE + d * TILE16K, tm, &kv_full[s], d * 64, (t >> 1) * BN, h, b);
+      }
+      if (!ok) {
+        if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
+        int zero = 0;
+        mbar_wait(q_full, 0, &zero, 2000000ull);
+        for (int u = t > NSLOT ? t - NSLOT : 0; u < t; ++u)
+          mbar_wait(&kv_full[u % NSLOT], (u / NSLOT) & 1u, &zero, 2000000ull);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    bool ok = n_max > 0;
+    const uint32_t q_addr = smem_u32(q_smem);
+    auto slot_addr = [&](int t) { return smem_u32(kv_smem + (t % NSLOT) * TILE); };
+    auto wait_item = [&](int t) { return mbar_wait(&kv_full[t % NSLOT], (t / NSLOT) & 1u, abort_flag); };
+    auto issue_s = [&](int i, int j) {  // S_i(j) = Q_i K_j^T   (lane 0 only)
+      const uint32_t k_addr = slot_addr(2 * j);
+#pragma unroll
+      for (int d = 0; d < DB; ++d)
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_ss<Kind::F16>(tmem_base + i * BN, make_smem_desc(q_addr + i * TILE + d * TILE16K + k * 32, 16, 1024),
+                            make_smem_desc(k_addr + d * TILE16K + k * 32, 16, 1024), idesc_qk, (d | k) != 0 ? 1u : 0u);
+    };
+    auto issue_pv = [&](int i, int j) {  // O_i += P_i(j) V_j
+      const uint32_t v_addr = slot_addr(2 * j + 1);
+#pragma unroll
+      for (int kk = 0; kk < BN / 16; ++kk)
+        mma_ts_f16(tmem_base + 256 + i * BN, tmem_base + i * BN + kk * 8, make_smem_desc(v_addr + kk * 2048, TILE16K, 1024),
+                   idesc_pv, (j | kk) != 0 ? 1u : 0u);
+    };
+    if (ok) ok = mbar_wait(q_full, 0, abort_flag);
+    if (ok) ok = wait_item(0);
+    if (ok) {
+      tc_fence_after();
+      if (lane == 0) {
+        for (int i = 0; i < 2; ++i)
+          if (n_blk[i] > 0) {
+            issue_s(i, 0);
+            mma_commit(&s_full[i]);
+          }
+        mma_commit(&kv_empty[0]);
+      }
+      __syncwarp();
+    }
+    for (int j = 0; j < n_max && ok; ++j) {
+      if (!wait_item(2 * j + 1)) { ok = false; break; }
+      const bool more = j + 1 < n_max;
+      if (more && !wait_item(2 * j + 2)) { ok = false; break; }
+      for (int i = 0; i < 2 && ok; ++i) {
+        if (j >= n_blk[i]) continue;
+        if (!mbar_wait(&p_full[i], j & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          issue_pv(i, j);
+          if (j + 1 < n_blk[i]) issue_s(i, j + 1);
+          // one commit covers both: the next score tile, or the finished output, is ready
+          mma_commit(&s_full[i]);
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) {
+        mma_commit(&kv_empty[(2 * j + 1) % NSLOT]);
+        if (more) mma_commit(&kv_empty[(2 * j + 2) % NSLOT]);
+      }
+      __syncwarp();
+    }
+    if (!ok && n_max > 0) {
+      if (lane == 0) {
+        if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
+        int zero = 0;
+        mma_commit(drain_bar);
+        mbar_wait(drain_bar, 0, &zero, 20000000ull);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / epilogue
+    const int i = warp >> 2;                      // query tile of this warpgroup
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const int qi = q0 + i * BM + r;
+    const float c = p.scale_log2;
+    const int n_mine = n_blk[i];
+    const uint32_t s_addr = tmem_base + lane_base + i * BN;
+    const uint32_t o_addr = tmem_base + lane_base + 256 + i * BN;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_mine; ++j) {
+      if (!mbar_wait(&s_full[i], j & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sreg[BN];
+      tmem_ld64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));
+      tmem_ld64(s_addr + 64, reinterpret_cast<uint32_t(&)[64]>(sreg[64]));
+      tmem_wait_ld();
+      const int kv0 = j * BN;
+      int limit = p.Skv - kv0;
+      if (p.causal) limit = min(limit, qi + off + 1 - kv0);
+      if (limit < BN) {
+#pragma unroll
+        for (int k = 0; k < BN; ++k)
+          if (k >= limit) sreg[k] = 0xff800000u;  // -inf
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < BN; k += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sreg[k]));
+        mx1 = fmaxf(mx1, __uint_as_float(sreg[k + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sreg[k + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sreg[k + 3]));
+      }
+      const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;
+      float alpha = 1.f;
+      bool rescale = false;
+      if ((mt > m + kRescaleThreshold || m == -INFINITY) && mt > m) {
+        alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - mt);
+        rescale = (j > 0);
+        m = mt;
+      }
+      const float neg_m = (m == -INFINITY) ? 0.f : -m;
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+      for (int k = 0; k < BN; k += 2) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sreg[k]), c, neg_m));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sreg[k + 1]), c, neg_m));
+        l0 += p0;
+        l1 += p1;
+        sreg[k >> 1] = pack2<T>(p0, p1);  // in place: word k/2 is never read again
+      }
+      l = l * alpha + (l0 + l1);
+      // S_i(j) being complete means PV_i(j-1) is complete: O_i may be rescaled now.
+      if (__any_sync(0xffffffffu, rescale)) {
+        const float a = rescale ? alpha : 1.f;
+#pragma unroll 1
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t oreg[32];
+          tmem_ld32(o_addr + cc * 32, oreg);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 32; ++k) oreg[k] = __float_as_uint(__uint_as_float(oreg[k]) * a);
+          tmem_st32(o_addr + cc * 32, oreg);
+        }
+      }
+      tmem_st64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[i]);
+    }
+    // epilogue: the commit after the last PV arrives on s_full once more
+    if (ok && n_mine > 0) ok = mbar_wait(&s_full[i], n_mine & 1u, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+      T* orow = static_cast<T*>(p.O) + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh +
+                static_cast<int64_t>(qi) * p.o_ss;
+#pragma unroll 1
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t oreg[32];
+        if (n_mine > 0) {
+          tmem_ld32(o_addr + cc * 32, oreg);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) oreg[k] = 0u;
+        }
+        if (qi < p.Sq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack2<T>(__uint_as_float(oreg[g * 8 + 0]) * inv_l, __uint_as_float(oreg[g * 8 + 1]) * inv_l);
+            o.y = pack2<T>(__uint_as_float(oreg[g * 8 + 2]) * inv_l, __uint_as_float(oreg[g * 8 + 3]) * inv_l);
+            o.z = pack2<T>(__uint_as_float(oreg[g * 8 + 4]) * inv_l, __uint_as_float(oreg[g * 8 + 5]) * inv_l);
+            o.w = pack2<T>(__uint_as_float(oreg[g * 8 + 6]) * inv_l, __uint_as_float(oreg[g * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) = o;
+          }
+        }
+      }
+    } else if (lane == 0 && !*abort_flag) {
+      *abort_flag = 1;
+      *p.status = KCG_ERR_TIMEOUT;
+      __threadfence_system();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <typename T, int D>
+int launch_fmha2(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FmhaParams& p,
+                 uint32_t fmt, cudaStream_t stream) {
+  constexpr int DB = D / 64;
+  constexpr int TILE = DB * TILE16K;
+  constexpr int NSLOT = D == 128 ? 5 : 8;
+  constexpr int SMEM = (2 + NSLOT) * TILE + 1024 + 256;
+  auto kern = fmha_fwd_kernel2<T, D, NSLOT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "fmha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  const uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, BM, BN);
+  const uint32_t idesc_pv = make_idesc(fmt, fmt, 0, 1, BM, D);
+  dim3 grid((p.q_tiles + 1) / 2, p.B * p.H);
+  kern<<<grid, V2_THREADS, SMEM, stream>>>(tmQ, tmK, tmV, p, idesc_qk, idesc_pv);
+  return check_launch("fmha_fwd_kernel2");
+}
+
 template <typename T, int D, bool kPTmem>
 int launch_fmha(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FmhaParams& p,
                 uint32_t fmt, cudaStream_t stream) {
@@ -396,7 +708,7 @@ int launch_fmha(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMa
   return check_launch("fmha_fwd_kernel");
 }
 
-int g_p_in_tmem = 1;
+int g_p_in_tmem = 2;
 
 }  // namespace
 
@@ -452,8 +764,9 @@ extern "C" int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const uint32_t fmt = dtype == KCG_BF16 ? 1u : 0u;
 #define KCG_FMHA(TT, DD)                                                                      \
-  (g_p_in_tmem ? launch_fmha<TT, DD, true>(tm[0], tm[1], tm[2], p, fmt, s)                    \
-               : launch_fmha<TT, DD, false>(tm[0], tm[1], tm[2], p, fmt, s))
+  (g_p_in_tmem == 2   ? launch_fmha2<TT, DD>(tm[0], tm[1], tm[2], p, fmt, s)                  \
+   : g_p_in_tmem == 1 ? launch_fmha<TT, DD, true>(tm[0], tm[1], tm[2], p, fmt, s)             \
+                      : launch_fmha<TT, DD, false>(tm[0], tm[1], tm[2], p, fmt, s))
   if (dtype == KCG_BF16) return D == 128 ? KCG_FMHA(__nv_bfloat16, 128) : KCG_FMHA(__nv_bfloat16, 64);
   return D == 128 ? KCG_FMHA(__half, 128) : KCG_FMHA(__half, 64);
 #undef KCG_FMHA
