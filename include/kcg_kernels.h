@@ -256,12 +256,15 @@ KCG_API int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Sk
                          const int64_t o_strides[3], void* stream);
 
 /*
- * Tuning switch with no counterpart in the reference: the probability tile P is handed
- * to the second MMA through tensor memory (1, the default) or through a swizzled
- * shared-memory tile (0).  Both give identical results; kept so the two data paths can
- * be compared on the same build.  Process-wide, not thread-safe.
+ * Tuning switch with no counterpart in the reference: which attention kernel runs.
+ *   -1 (default)  chosen by shape: two query tiles per CTA when Sq > 128, else one;
+ *    2            two 128-query tiles per CTA, P handed to the second MMA through tensor memory;
+ *    1            one query tile per CTA, P through tensor memory;
+ *    0            one query tile per CTA, P through a swizzled shared-memory tile.
+ * All variants give results within the same tolerance; kept so the data paths can be compared
+ * on one build.  Process-wide, not thread-safe.
  */
-KCG_API void kcg_fmha_set_p_in_tmem(int enabled);
+KCG_API void kcg_fmha_set_p_in_tmem(int variant);
 
 /*
  * Row-range owned by one rank when `total` independent units (GEMM rows of A/C,

@@ -56,6 +56,34 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return r;
 }
 
+
+// ---- packed fp32x2 arithmetic (two lanes of fp32 in one 64-bit register) --------------------
+// sm_100 executes fma / add on fp32 pairs in one instruction, which halves the FMA-pipe
+// instruction count of the softmax.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -416,8 +444,8 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* kv_full = bars + 1;             // [NSLOT]
   uint64_t* kv_empty = kv_full + NSLOT;     // [NSLOT]
   uint64_t* s_full = kv_empty + NSLOT;      // [2]
-  uint64_t* p_full = s_full + 2;            // [2]
-  uint64_t* drain_bar = p_full + 2;
+  uint64_t* p_full = s_full + 2;            // [2 tiles][2 column halves]
+  uint64_t* drain_bar = p_full + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -448,7 +476,8 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 4);
+      mbar_init(&p_full[2 * i], 4);
+      mbar_init(&p_full[2 * i + 1], 4);
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -506,18 +535,21 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           mma_ss<Kind::F16>(tmem_base + i * BN, make_smem_desc(q_addr + i * TILE + d * TILE16K + k * 32, 16, 1024),
                             make_smem_desc(k_addr + d * TILE16K + k * 32, 16, 1024), idesc_qk, (d | k) != 0 ? 1u : 0u);
     };
-    auto issue_pv = [&](int i, int j) {  // O_i += P_i(j) V_j
+    auto issue_pv = [&](int i, int j, int half) {  // O_i += P_i(j)[:, half] V_j[half, :]
       const uint32_t v_addr = slot_addr(2 * j + 1);
 #pragma unroll
-      for (int kk = 0; kk < BN / 16; ++kk)
+      for (int kk = half * 4; kk < half * 4 + 4; ++kk)
         mma_ts_f16(tmem_base + 256 + i * BN, tmem_base + i * BN + kk * 8, make_smem_desc(v_addr + kk * 2048, TILE16K, 1024),
                    idesc_pv, (j | kk) != 0 ? 1u : 0u);
     };
-    if (ok) ok = mbar_wait(q_full, 0, abort_flag);
-    if (ok) ok = wait_item(0);
-    if (ok) {
-      tc_fence_after();
-      if (lane == 0) {
+    // One thread runs the whole issue loop: nothing here needs the other lanes, and a single
+    // thread has no reconvergence points between a barrier wait and the MMAs that follow it.
+    // (An MMA is accepted only when the tensor pipe has room, so issuing blocks for about as
+    // long as the MMAs run: every instruction between two MMAs is tensor-pipe idle time.)
+    if (lane == 0 && ok) {
+      ok = mbar_wait(q_full, 0, abort_flag) && wait_item(0);
+      if (ok) {
+        tc_fence_after();
         for (int i = 0; i < 2; ++i)
           if (n_blk[i] > 0) {
             issue_s(i, 0);
@@ -525,39 +557,36 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         mma_commit(&kv_empty[0]);
       }
-      __syncwarp();
-    }
-    for (int j = 0; j < n_max && ok; ++j) {
-      if (!wait_item(2 * j + 1)) { ok = false; break; }
-      const bool more = j + 1 < n_max;
-      if (more && !wait_item(2 * j + 2)) { ok = false; break; }
-      for (int i = 0; i < 2 && ok; ++i) {
-        if (j >= n_blk[i]) continue;
-        if (!mbar_wait(&p_full[i], j & 1u, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        if (lane == 0) {
-          issue_pv(i, j);
+      for (int j = 0; j < n_max && ok; ++j) {
+        if (!wait_item(2 * j + 1)) { ok = false; break; }
+        const bool more = j + 1 < n_max;
+        if (more && !wait_item(2 * j + 2)) { ok = false; break; }
+        for (int i = 0; i < 2; ++i) {
+          if (j >= n_blk[i]) continue;
+          // P arrives in two column halves; the first four k-steps of PV start on the first
+          if (!mbar_wait(&p_full[2 * i], j & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(i, j, 0);
+          if (!mbar_wait(&p_full[2 * i + 1], j & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(i, j, 1);
           if (j + 1 < n_blk[i]) issue_s(i, j + 1);
           // one commit covers both: the next score tile, or the finished output, is ready
           mma_commit(&s_full[i]);
         }
-        __syncwarp();
+        if (ok) {
+          mma_commit(&kv_empty[(2 * j + 1) % NSLOT]);
+          if (more) mma_commit(&kv_empty[(2 * j + 2) % NSLOT]);
+        }
       }
-      if (ok && lane == 0) {
-        mma_commit(&kv_empty[(2 * j + 1) % NSLOT]);
-        if (more) mma_commit(&kv_empty[(2 * j + 2) % NSLOT]);
-      }
-      __syncwarp();
-    }
-    if (!ok && n_max > 0) {
-      if (lane == 0) {
+      if (!ok) {
         if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
         int zero = 0;
         mma_commit(drain_bar);
         mbar_wait(drain_bar, 0, &zero, 20000000ull);
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
     const int i = warp >> 2;                      // query tile of this warpgroup
@@ -588,11 +617,11 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int k = 0; k < BN; k += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(sreg[k]));
-        mx1 = fmaxf(mx1, __uint_as_float(sreg[k + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(sreg[k + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(sreg[k + 3]));
+      for (int k = 0; k < BN; k += 8) {
+        mx0 = max3(mx0, __uint_as_float(sreg[k]), __uint_as_float(sreg[k + 1]));
+        mx1 = max3(mx1, __uint_as_float(sreg[k + 2]), __uint_as_float(sreg[k + 3]));
+        mx2 = max3(mx2, __uint_as_float(sreg[k + 4]), __uint_as_float(sreg[k + 5]));
+        mx3 = max3(mx3, __uint_as_float(sreg[k + 6]), __uint_as_float(sreg[k + 7]));
       }
       const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;
       float alpha = 1.f;
@@ -603,16 +632,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m = mt;
       }
       const float neg_m = (m == -INFINITY) ? 0.f : -m;
-      float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-      for (int k = 0; k < BN; k += 2) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(sreg[k]), c, neg_m));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(sreg[k + 1]), c, neg_m));
-        l0 += p0;
-        l1 += p1;
-        sreg[k >> 1] = pack2<T>(p0, p1);  // in place: word k/2 is never read again
-      }
-      l = l * alpha + (l0 + l1);
+      const uint64_t c2 = f2_pack(c, c), nm2 = f2_pack(neg_m, neg_m);
       // S_i(j) being complete means PV_i(j-1) is complete: O_i may be rescaled now.
       if (__any_sync(0xffffffffu, rescale)) {
         const float a = rescale ? alpha : 1.f;
@@ -626,11 +646,29 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st32(o_addr + cc * 32, oreg);
         }
       }
-      tmem_st64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[i]);
+      uint64_t lsum_a = 0ull, lsum_b = 0ull;  // two (+0.f, +0.f) accumulators
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int k = half * 64; k < half * 64 + 64; k += 2) {
+          const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sreg[k]), __uint_as_float(sreg[k + 1])), c2, nm2);
+          float x0, x1;
+          f2_unpack(x2, x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          if ((k >> 1) & 1) lsum_b = f2_add(lsum_b, f2_pack(p0, p1));
+          else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
+          sreg[k >> 1] = pack2<T>(p0, p1);  // in place: word k/2 is never read again
+        }
+        // hand this half of P (32 packed columns) to the MMA thread
+        tmem_st32(s_addr + half * 32, reinterpret_cast<uint32_t(&)[32]>(sreg[half * 32]));
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[2 * i + half]);
+      }
+      float l0, l1;
+      f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
+      l = l * alpha + (l0 + l1);
     }
     // epilogue: the commit after the last PV arrives on s_full once more
     if (ok && n_mine > 0) ok = mbar_wait(&s_full[i], n_mine & 1u, abort_flag);
@@ -708,11 +746,12 @@ int launch_fmha(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMa
   return check_launch("fmha_fwd_kernel");
 }
 
-int g_p_in_tmem = 2;
+int g_p_in_tmem = -1;  // -1: choose by shape
 
 }  // namespace
 
-// Chooses whether P travels through tensor memory (1, default) or shared memory (0).
+// Kernel variant: -1 (default) picks by shape; 0 / 1 = one query tile per CTA with P through
+// shared / tensor memory; 2 = two query tiles per CTA.
 extern "C" __attribute__((visibility("default"))) void kcg_fmha_set_p_in_tmem(int v) { g_p_in_tmem = v; }
 
 }  // namespace kcg
@@ -763,10 +802,12 @@ extern "C" int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t
   if (!p.status) return fail(KCG_ERR_CUDA, "fmha: could not allocate the host-mapped status word");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const uint32_t fmt = dtype == KCG_BF16 ? 1u : 0u;
+  // Two query tiles per CTA pay off once there is more than one tile of queries.
+  const int variant = g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? 2 : 1);
 #define KCG_FMHA(TT, DD)                                                                      \
-  (g_p_in_tmem == 2   ? launch_fmha2<TT, DD>(tm[0], tm[1], tm[2], p, fmt, s)                  \
-   : g_p_in_tmem == 1 ? launch_fmha<TT, DD, true>(tm[0], tm[1], tm[2], p, fmt, s)             \
-                      : launch_fmha<TT, DD, false>(tm[0], tm[1], tm[2], p, fmt, s))
+  (variant == 2   ? launch_fmha2<TT, DD>(tm[0], tm[1], tm[2], p, fmt, s)                      \
+   : variant == 1 ? launch_fmha<TT, DD, true>(tm[0], tm[1], tm[2], p, fmt, s)                 \
+                  : launch_fmha<TT, DD, false>(tm[0], tm[1], tm[2], p, fmt, s))
   if (dtype == KCG_BF16) return D == 128 ? KCG_FMHA(__nv_bfloat16, 128) : KCG_FMHA(__nv_bfloat16, 64);
   return D == 128 ? KCG_FMHA(__half, 128) : KCG_FMHA(__half, 64);
 #undef KCG_FMHA
