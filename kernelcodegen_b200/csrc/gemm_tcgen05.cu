@@ -160,44 +160,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    uint32_t it = 0, tile_iter = 0;
-    bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tile_iter) {
-      const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
-      if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1u, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * BN;
-      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-        if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+    // A single thread runs the loop.  An MMA is accepted only when the tensor pipe has room,
+    // so every instruction between two MMAs competes with the pipe's run time: the descriptors
+    // of a stage are derived from one precomputed base by integer adds, and no other lane
+    // takes part (no reconvergence after the barrier waits).
+    if (lane == 0) {
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      const uint32_t smem_base = smem_u32(smem);
+      // Descriptors of k-step 0 in stage 0; later k-steps / stages differ only in the address
+      // field (bits [0,14), in 16-byte units), which cannot carry into the next field here.
+      const uint64_t adesc0 = kAMn ? make_smem_desc(smem_base, MN_BOX_BYTES, 1024) : make_smem_desc(smem_base, 16, 1024);
+      const uint64_t bdesc0 = kBMn ? make_smem_desc(smem_base + A_BYTES, MN_BOX_BYTES, 1024)
+                                   : make_smem_desc(smem_base + A_BYTES, 16, 1024);
+      constexpr uint32_t kStageStep = STAGE_BYTES >> 4;
+      constexpr uint32_t kAStep = (kAMn ? MN_KSTEP : 32) >> 4, kBStep = (kBMn ? MN_KSTEP : 32) >> 4;
+      for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_BYTES;
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = adesc0 + s * kStageStep, bdesc = bdesc0 + s * kStageStep;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adesc = kAMn ? make_smem_desc(a_addr + k * MN_KSTEP, MN_BOX_BYTES, 1024)
-                                        : make_smem_desc(a_addr + k * 32, 16, 1024);
-            const uint64_t bdesc = kBMn ? make_smem_desc(b_addr + k * MN_KSTEP, MN_BOX_BYTES, 1024)
-                                        : make_smem_desc(b_addr + k * 32, 16, 1024);
-            mma_ss<kKind>(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            mma_ss<kKind>(d_tmem, adesc + k * kAStep, bdesc + k * kBStep, idesc, (kb | k) != 0 ? 1u : 0u);
           mma_commit(&empty_bar[s]);
         }
-        __syncwarp();
+        if (ok) mma_commit(&tfull_bar[acc]);
       }
-      if (ok && lane == 0) mma_commit(&tfull_bar[acc]);
-      __syncwarp();
-    }
-    if (!ok) {
-      if (lane == 0) {
+      if (!ok) {
         if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
         int zero = 0;
         mma_commit(drain_bar);
         mbar_wait(drain_bar, 0, &zero, 20000000ull);
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;
