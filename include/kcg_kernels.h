@@ -236,6 +236,14 @@ KCG_API int kcg_gemm(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t 
                      const float* scale_b, void* stream);
 
 /*
+ * Tuning switch with no counterpart in the reference: -1 (default) runs the tensor-core GEMM on
+ * CTA pairs (tcgen05 cta_group::2, 256x256 tile per pair) when M >= 256 and on single CTAs
+ * (128x256 tile) otherwise; 0 forces single CTAs; 1 uses pairs whenever M > 128.  Results are
+ * identical.  Process-wide, not thread-safe.
+ */
+KCG_API void kcg_gemm_set_pair_mode(int mode);
+
+/*
  * Fused multi-head attention forward — replaces
  * `Fused_Multi_Head_Attention_{batch..}_SL{S}_HD{D}`, the kernel the reference
  * builds when it finds BatchMatmul(NT) -> Softmax -> BatchMatmul(NN)

@@ -39,6 +39,7 @@ SIGNATURES = {
     "kcg_softmax": ([_ci, _i64, _i64, _fp, _ci, _i64, _vp, _vp, _vp], _ci),
     "kcg_gemm": ([_ci, _ci, _i64, _i64, _i64, _i64, _ci, _ci, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64,
                   _vp, _vp, _vp], _ci),
+    "kcg_gemm_set_pair_mode": ([_ci], None),
     "kcg_fmha_fwd": ([_ci, _i64, _i64, _i64, _i64, _i64, _fp, _ci, _vp, _i64p, _vp, _i64p, _vp, _i64p, _vp, _i64p,
                       _vp], _ci),
     "kcg_fmha_set_p_in_tmem": ([_ci], None),

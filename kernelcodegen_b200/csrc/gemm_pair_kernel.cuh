@@ -1,0 +1,226 @@
+// CTA-pair variant of the tensor-core GEMM (included by gemm_tcgen05.cu inside its
+// anonymous namespace).
+//
+// Two CTAs of a cluster compute one 256x256 tile of C with tcgen05.mma.cta_group::2:
+// CTA r of the pair holds rows [128r, 128r+128) of the A tile and of the accumulator, and
+// columns [128r, 128r+128) of the B tile; the tensor cores of both SMs read both halves of B.
+// Per MMA each SM therefore reads 4 KB of A and 4 KB of B from its own shared memory for
+// 128 clocks of work (the single-CTA kernel reads 12 KB), and a stage is 32 KB instead of
+// 48 KB, so the ring is 6 deep.  Every load is an ordinary (non-multicast) TMA copy into the
+// issuing CTA's own shared memory; only barrier arrivals cross the pair:
+//   - TMA completion bytes of both CTAs are counted on the leader's (rank 0) full barrier;
+//   - one thread of the leader issues the MMAs and releases ring stages / publishes finished
+//     accumulators in both CTAs with a two-CTA tcgen05.commit;
+//   - the peer's epilogue warps hand accumulators back with a remote mbarrier arrive.
+#pragma once
+
+constexpr int PSTAGES = 6;
+constexpr int PA_BYTES = 128 * 128;           // 128 rows x 128 bytes of K
+constexpr int PB_BYTES = 128 * 128;           // this CTA's half of the B tile
+constexpr int PSTAGE_BYTES = PA_BYTES + PB_BYTES;
+constexpr int PBM = 256, PBN = 256;           // tile of the pair
+constexpr int PSMEM_BYTES = PSTAGES * PSTAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ void pair_tile_coords(int64_t tile, int m_pairs, int n_tiles, int& b, int& mp, int& nt) {
+  const int64_t per_batch = static_cast<int64_t>(m_pairs) * n_tiles;
+  b = static_cast<int>(tile / per_batch);
+  const int r = static_cast<int>(tile % per_batch);
+  constexpr int GROUP = GROUP_M / 2;  // in units of 256-row pairs
+  const int group_span = GROUP * n_tiles;
+  const int first = (r / group_span) * GROUP;
+  const int gsize = min(m_pairs - first, GROUP);
+  const int in_group = r % group_span;
+  mp = first + in_group % gsize;
+  nt = in_group / gsize;
+}
+
+template <Kind kKind, int kElemBytes, bool kAMn, bool kBMn, typename TOut>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const GemmParams p, const uint32_t idesc) {
+  constexpr int BK = 128 / kElemBytes;
+  constexpr int UMMA_K = 32 / kElemBytes;
+  constexpr int MN_BOX = 128 / kElemBytes;
+  constexpr int MN_BOX_BYTES = BK * 128;
+  constexpr int MN_KSTEP = UMMA_K * 128;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PSTAGES * PSTAGE_BYTES);
+  uint64_t* full_bar = bars;                    // [PSTAGES]  used in the leader
+  uint64_t* empty_bar = bars + PSTAGES;         // [PSTAGES]  one per CTA
+  uint64_t* tfull_bar = bars + 2 * PSTAGES;     // [2]        one per CTA
+  uint64_t* tempty_bar = bars + 2 * PSTAGES + 2;  // [2]      used in the leader, 8 arrivals
+  uint64_t* drain_bar = bars + 2 * PSTAGES + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PSTAGES + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int64_t cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const int m_pairs = (p.m_tiles + 1) / 2;
+  const int64_t total = static_cast<int64_t>(m_pairs) * p.n_tiles * (p.total_tiles / (static_cast<int64_t>(p.m_tiles) * p.n_tiles));
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    for (int s = 0; s < PSTAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 8);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t tile = cluster_id; tile < total && ok; tile += n_clusters) {
+        int b, mp, nt;
+        pair_tile_coords(tile, m_pairs, p.n_tiles, b, mp, nt);
+        const int m0 = mp * PBM + static_cast<int>(rank) * 128;
+        const int n0 = nt * PBN + static_cast<int>(rank) * 128;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % PSTAGES, ph = (it / PSTAGES) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* a_dst = smem + s * PSTAGE_BYTES;
+          uint8_t* b_dst = a_dst + PA_BYTES;
+          // completion bytes of both CTAs go to the leader's barrier
+          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * PSTAGE_BYTES);
+          const uint32_t bar = map_to_cta(&full_bar[s], 0);
+          const int k0 = kb * BK;
+          if constexpr (!kAMn) {
+            tma_load_3d_pair(a_dst, &tmA, bar, k0, m0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < PA_BYTES / MN_BOX_BYTES; ++j)
+              tma_load_3d_pair(a_dst + j * MN_BOX_BYTES, &tmA, bar, m0 + j * MN_BOX, k0, b);
+          }
+          if constexpr (!kBMn) {
+            tma_load_3d_pair(b_dst, &tmB, bar, k0, n0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < PB_BYTES / MN_BOX_BYTES; ++j)
+              tma_load_3d_pair(b_dst + j * MN_BOX_BYTES, &tmB, bar, n0 + j * MN_BOX, k0, b);
+          }
+        }
+      }
+      if (!ok && !*abort_flag) {
+        *abort_flag = 1;
+        *p.status = KCG_ERR_TIMEOUT;
+        __threadfence_system();
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      const uint32_t smem_base = smem_u32(smem);
+      const uint64_t adesc0 = kAMn ? make_smem_desc(smem_base, MN_BOX_BYTES, 1024) : make_smem_desc(smem_base, 16, 1024);
+      const uint64_t bdesc0 = kBMn ? make_smem_desc(smem_base + PA_BYTES, MN_BOX_BYTES, 1024)
+                                   : make_smem_desc(smem_base + PA_BYTES, 16, 1024);
+      constexpr uint32_t kStageStep = PSTAGE_BYTES >> 4;
+      constexpr uint32_t kAStep = (kAMn ? MN_KSTEP : 32) >> 4, kBStep = (kBMn ? MN_KSTEP : 32) >> 4;
+      for (int64_t tile = cluster_id; tile < total && ok; tile += n_clusters, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * PBN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % PSTAGES, ph = (it / PSTAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = adesc0 + s * kStageStep, bdesc = bdesc0 + s * kStageStep;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            mma_ss_pair<kKind>(d_tmem, adesc + k * kAStep, bdesc + k * kBStep, idesc, (kb | k) != 0 ? 1u : 0u);
+          mma_commit_pair(&empty_bar[s], 3);
+        }
+        if (ok) mma_commit_pair(&tfull_bar[acc], 3);
+      }
+      if (!ok) {
+        if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
+        int zero = 0;
+        mma_commit_pair(drain_bar, 1);
+        mbar_wait(drain_bar, 0, &zero, 20000000ull);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs)
+    const int quarter = warp & 3;
+    float alpha = 1.f;
+    if (p.scale_a) alpha *= *p.scale_a;
+    if (p.scale_b) alpha *= *p.scale_b;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (int64_t tile = cluster_id; tile < total && ok; tile += n_clusters, ++tile_iter) {
+      int b, mp, nt;
+      pair_tile_coords(tile, m_pairs, p.n_tiles, b, mp, nt);
+      const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
+      if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t row = static_cast<int64_t>(mp) * PBM + rank * 128 + quarter * 32 + lane;
+      const int64_t col0 = static_cast<int64_t>(nt) * PBN;
+      TOut* crow = static_cast<TOut*>(p.C) + b * p.stride_c + row * p.ldc;
+      const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * PBN;
+      constexpr int VW = Vec16<TOut>::N;
+#pragma unroll 1
+      for (int c = 0; c < PBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_base + c * 32, r);
+        tmem_wait_ld();
+        if (row < p.M) {
+          const int64_t cbase = col0 + c * 32;
+#pragma unroll
+          for (int g = 0; g < 32 / VW; ++g) {
+            const int64_t col = cbase + g * VW;
+            if (p.c_vec_ok && col + VW <= p.N) {
+              Vec16<TOut> o;
+#pragma unroll
+              for (int j = 0; j < VW; ++j) o.v[j] = Conv<TOut>::from_f(alpha * __uint_as_float(r[g * VW + j]));
+              st_vec(crow + col, o);
+            } else {
+#pragma unroll
+              for (int j = 0; j < VW; ++j)
+                if (col + j < p.N) crow[col + j] = Conv<TOut>::from_f(alpha * __uint_as_float(r[g * VW + j]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(&tempty_bar[acc], 0));
+    }
+    if (!ok && lane == 0 && !*abort_flag) {
+      *abort_flag = 1;
+      *p.status = KCG_ERR_TIMEOUT;
+      __threadfence_system();
+    }
+  }
+
+  // Neither CTA may leave (or free tensor memory) while the other can still signal it.
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}

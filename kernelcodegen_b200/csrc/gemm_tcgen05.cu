@@ -261,6 +261,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
+#include "gemm_pair_kernel.cuh"
+
 // ---- host side ----------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -313,29 +315,47 @@ int encode_tmap_sw128(CUtensorMap* out, int dtype, const void* base, int rank, c
 
 namespace {
 
+int g_pair_mode = -1;  // -1: CTA pairs when M >= 256; 0: never; 1: whenever the grid allows
+
 template <Kind kKind, int kElemBytes, bool kAMn, bool kBMn, typename TOut>
-int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, uint32_t idesc,
-                   cudaStream_t stream) {
+int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB_pair, const GemmParams& p,
+                   uint32_t idesc, uint32_t idesc_pair, bool pair, cudaStream_t stream) {
+  const int sms = sm_count();
+  if (pair) {
+    auto kern = gemm_tcgen05_pair_kernel<kKind, kElemBytes, kAMn, kBMn, TOut>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PSMEM_BYTES);
+    if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    const int64_t batch = p.total_tiles / (static_cast<int64_t>(p.m_tiles) * p.n_tiles);
+    const int64_t pair_tiles = static_cast<int64_t>((p.m_tiles + 1) / 2) * p.n_tiles * batch;
+    const int64_t clusters = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
+    kern<<<static_cast<int>(clusters * 2), NUM_THREADS, PSMEM_BYTES, stream>>>(tmA, tmB_pair, p, idesc_pair);
+    return check_launch("gemm_tcgen05_pair_kernel");
+  }
   auto kern = gemm_tcgen05_kernel<kKind, kElemBytes, kAMn, kBMn, TOut>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  const int sms = sm_count();
   const int grid = static_cast<int>(p.total_tiles < sms ? p.total_tiles : sms);
   kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p, idesc);
   return check_launch("gemm_tcgen05_kernel");
 }
 
 template <Kind kKind, int kElemBytes, typename TOut>
-int launch_layout(int trans_a, int trans_b, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                  uint32_t idesc, cudaStream_t s) {
+int launch_layout(int trans_a, int trans_b, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmBp,
+                  const GemmParams& p, uint32_t idesc, uint32_t idesc_pair, bool pair, cudaStream_t s) {
   // trans_a != 0: A is [K, M] row-major -> MN-major operand; trans_b == 0: B is [K, N] -> MN-major.
-  if (!trans_a && trans_b) return launch_variant<kKind, kElemBytes, false, false, TOut>(tmA, tmB, p, idesc, s);
-  if (!trans_a && !trans_b) return launch_variant<kKind, kElemBytes, false, true, TOut>(tmA, tmB, p, idesc, s);
-  if (trans_a && trans_b) return launch_variant<kKind, kElemBytes, true, false, TOut>(tmA, tmB, p, idesc, s);
-  return launch_variant<kKind, kElemBytes, true, true, TOut>(tmA, tmB, p, idesc, s);
+  if (!trans_a && trans_b)
+    return launch_variant<kKind, kElemBytes, false, false, TOut>(tmA, tmB, tmBp, p, idesc, idesc_pair, pair, s);
+  if (!trans_a && !trans_b)
+    return launch_variant<kKind, kElemBytes, false, true, TOut>(tmA, tmB, tmBp, p, idesc, idesc_pair, pair, s);
+  if (trans_a && trans_b)
+    return launch_variant<kKind, kElemBytes, true, false, TOut>(tmA, tmB, tmBp, p, idesc, idesc_pair, pair, s);
+  return launch_variant<kKind, kElemBytes, true, true, TOut>(tmA, tmB, tmBp, p, idesc, idesc_pair, pair, s);
 }
 
 }  // namespace
+
+// -1 (default): CTA pairs (cta_group::2) when M >= 256; 0: single-CTA kernel only; 1: pairs when M > 128.
+extern "C" __attribute__((visibility("default"))) void kcg_gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
 
 int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
                  int trans_b, const void* A, int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
@@ -353,7 +373,8 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
 
   const int BK = 128 / es;
   const uint32_t mn_box = 128 / es;
-  CUtensorMap tmA, tmB;
+  const bool pair = g_pair_mode == 0 ? false : (g_pair_mode == 1 ? M > BM : M >= 2 * BM);
+  CUtensorMap tmA, tmB, tmBp;
   {
     const uint64_t a_rows = trans_a ? K : M, a_cols = trans_a ? M : K;
     uint64_t dims[3] = {a_cols, a_rows, static_cast<uint64_t>(batch)};
@@ -375,6 +396,10 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
     box[2] = 1;
     int rc = encode_tmap_sw128(&tmB, dtype_in, B, 3, dims, strides, box);
     if (rc) return rc;
+    // the CTA-pair kernel loads half of the B tile (128 of its 256 columns) per CTA
+    if (trans_b) box[1] = BN / 2;
+    rc = encode_tmap_sw128(&tmBp, dtype_in, B, 3, dims, strides, box);
+    if (rc) return rc;
   }
 
   GemmParams p;
@@ -391,20 +416,20 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
 
   const uint32_t a_mn = trans_a ? 1u : 0u, b_mn = trans_b ? 0u : 1u;
   if (dtype_in == KCG_F8E4M3) {
-    const uint32_t idesc = make_idesc(0, 0, a_mn, b_mn, BM, BN);
+    const uint32_t idesc = make_idesc(0, 0, a_mn, b_mn, BM, BN), idesc_p = make_idesc(0, 0, a_mn, b_mn, 2 * BM, BN);
     if (dtype_out == KCG_BF16)
-      return launch_layout<Kind::F8F6F4, 1, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, p, idesc, stream);
+      return launch_layout<Kind::F8F6F4, 1, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, tmBp, p, idesc, idesc_p, pair, stream);
     if (dtype_out == KCG_F32)
-      return launch_layout<Kind::F8F6F4, 1, float>(trans_a, trans_b, tmA, tmB, p, idesc, stream);
+      return launch_layout<Kind::F8F6F4, 1, float>(trans_a, trans_b, tmA, tmB, tmBp, p, idesc, idesc_p, pair, stream);
     return fail(KCG_ERR_UNSUPPORTED, "gemm: float8_e4m3 inputs produce bfloat16 or float32 (got dtype %d)", dtype_out);
   }
   const uint32_t fmt = dtype_in == KCG_BF16 ? 1u : 0u;
-  const uint32_t idesc = make_idesc(fmt, fmt, a_mn, b_mn, BM, BN);
-  if (dtype_out == KCG_F32) return launch_layout<Kind::F16, 2, float>(trans_a, trans_b, tmA, tmB, p, idesc, stream);
+  const uint32_t idesc = make_idesc(fmt, fmt, a_mn, b_mn, BM, BN), idesc_p = make_idesc(fmt, fmt, a_mn, b_mn, 2 * BM, BN);
+  if (dtype_out == KCG_F32) return launch_layout<Kind::F16, 2, float>(trans_a, trans_b, tmA, tmB, tmBp, p, idesc, idesc_p, pair, stream);
   if (dtype_in == KCG_BF16 && dtype_out == KCG_BF16)
-    return launch_layout<Kind::F16, 2, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, p, idesc, stream);
+    return launch_layout<Kind::F16, 2, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, tmBp, p, idesc, idesc_p, pair, stream);
   if (dtype_in == KCG_F16 && dtype_out == KCG_F16)
-    return launch_layout<Kind::F16, 2, __half>(trans_a, trans_b, tmA, tmB, p, idesc, stream);
+    return launch_layout<Kind::F16, 2, __half>(trans_a, trans_b, tmA, tmB, tmBp, p, idesc, idesc_p, pair, stream);
   return fail(KCG_ERR_UNSUPPORTED, "gemm: dtype combination %d -> %d has no kernel", dtype_in, dtype_out);
 }
 
