@@ -40,7 +40,7 @@ constexpr int B_BYTES = BN * 128;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr int GROUP_M = 8;
+constexpr int GROUP_M = 16;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
 struct GemmParams {
