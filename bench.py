@@ -140,7 +140,11 @@ def run_reference(args) -> None:
     import numpy as np
     from oracle import oracle as O
 
-    threads = O.max_threads()
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core it may run on
+    try:
+        threads = len(os.sched_getaffinity(0))
+    except AttributeError:
+        threads = os.cpu_count() or 1
     rng = np.random.default_rng(0xC0DE)
     x = rng.standard_normal((ROWS, COLS), dtype=np.float32)
     g = (1.0 + 0.1 * rng.standard_normal(COLS)).astype(np.float32)
