@@ -414,7 +414,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 //
 //   warps 0-3   softmax warpgroup of query tile 0 (one thread per row, TMEM lanes 0-127)
 //   warps 4-7   softmax warpgroup of query tile 1
-//   warp 8      TMA loader: both Q tiles once, then K_0, V_0, K_1, V_1, ... through one ring
+//   warp 8      TMA loader: both Q tiles and K_0 once, then (V_j, K_{j+1}) per key block
 //   warp 9      MMA issuer
 // Tensor memory (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512).
 // P_i (16-bit, 64 columns) overwrites the first half of S_i once the owning thread has read
@@ -496,38 +496,45 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ------------------------------------------------------------------ TMA loader
     if (lane == 0 && n_max > 0) {
       bool ok = true;
-      mbar_expect_tx(q_full, 2 * TILE);
+      // Ring layout: K_0 travels with the Q tiles (slot 4, never reused); afterwards one ring
+      // entry per key block j holds V_j (slot 2r) and K_{j+1} (slot 2r+1), r = j & 1, under a
+      // single full / empty barrier pair, so the MMA thread pays one wait and one commit per block.
+      mbar_expect_tx(q_full, 3 * TILE);
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int d = 0; d < DB; ++d)
           tma_load_4d(q_smem + i * TILE + d * TILE16K, &tmQ, q_full, d * 64, q0 + i * BM, h, b);
-      int t = 0;  // ring item: 2j = K_j, 2j+1 = V_j
-      for (; t < 2 * n_max; ++t) {
-        const uint32_t s = t % NSLOT, ph = (t / NSLOT) & 1u;
-        if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-        mbar_expect_tx(&kv_full[s], TILE);
-        const CUtensorMap* tm = (t & 1) ? &tmV : &tmK;
+#pragma unroll
+      for (int d = 0; d < DB; ++d) tma_load_4d(kv_smem + 4 * TILE + d * TILE16K, &tmK, q_full, d * 64, 0, h, b);
+      int j = 0;
+      for (; j < n_max; ++j) {
+        const uint32_t r = j & 1u, ph = (j >> 1) & 1u;
+        if (!mbar_wait(&kv_empty[r], ph ^ 1u, abort_flag)) { ok = false; break; }
+        const bool more = j + 1 < n_max;
+        mbar_expect_tx(&kv_full[r], more ? 2 * TILE : TILE);
 #pragma unroll
         for (int d = 0; d < DB; ++d)
-          tma_load_4d(kv_smem + s * TILE + d * TILE16K, tm, &kv_full[s], d * 64, (t >> 1) * BN, h, b);
+          tma_load_4d(kv_smem + (2 * r) * TILE + d * TILE16K, &tmV, &kv_full[r], d * 64, j * BN, h, b);
+        if (more) {
+#pragma unroll
+          for (int d = 0; d < DB; ++d)
+            tma_load_4d(kv_smem + (2 * r + 1) * TILE + d * TILE16K, &tmK, &kv_full[r], d * 64, (j + 1) * BN, h, b);
+        }
       }
       if (!ok) {
         if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
         int zero = 0;
         mbar_wait(q_full, 0, &zero, 2000000ull);
-        for (int u = t > NSLOT ? t - NSLOT : 0; u < t; ++u)
-          mbar_wait(&kv_full[u % NSLOT], (u / NSLOT) & 1u, &zero, 2000000ull);
+        for (int u = j > 2 ? j - 2 : 0; u < j; ++u) mbar_wait(&kv_full[u & 1], (u >> 1) & 1u, &zero, 2000000ull);
       }
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     bool ok = n_max > 0;
     const uint32_t q_addr = smem_u32(q_smem);
-    auto slot_addr = [&](int t) { return smem_u32(kv_smem + (t % NSLOT) * TILE); };
-    auto wait_item = [&](int t) { return mbar_wait(&kv_full[t % NSLOT], (t / NSLOT) & 1u, abort_flag); };
     auto issue_s = [&](int i, int j) {  // S_i(j) = Q_i K_j^T   (lane 0 only)
-      const uint32_t k_addr = slot_addr(2 * j);
+      const uint32_t k_addr = smem_u32(kv_smem + (j == 0 ? 4 : 2 * ((j - 1) & 1) + 1) * TILE);
 #pragma unroll
       for (int d = 0; d < DB; ++d)
 #pragma unroll
@@ -536,7 +543,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                             make_smem_desc(k_addr + d * TILE16K + k * 32, 16, 1024), idesc_qk, (d | k) != 0 ? 1u : 0u);
     };
     auto issue_pv = [&](int i, int j, int half) {  // O_i += P_i(j)[:, half] V_j[half, :]
-      const uint32_t v_addr = slot_addr(2 * j + 1);
+      const uint32_t v_addr = smem_u32(kv_smem + 2 * (j & 1) * TILE);
 #pragma unroll
       for (int kk = half * 4; kk < half * 4 + 4; ++kk)
         mma_ts_f16(tmem_base + 256 + i * BN, tmem_base + i * BN + kk * 8, make_smem_desc(v_addr + kk * 2048, TILE16K, 1024),
@@ -547,7 +554,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // (An MMA is accepted only when the tensor pipe has room, so issuing blocks for about as
     // long as the MMAs run: every instruction between two MMAs is tensor-pipe idle time.)
     if (lane == 0 && ok) {
-      ok = mbar_wait(q_full, 0, abort_flag) && wait_item(0);
+      ok = mbar_wait(q_full, 0, abort_flag);
       if (ok) {
         tc_fence_after();
         for (int i = 0; i < 2; ++i)
@@ -555,12 +562,9 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             issue_s(i, 0);
             mma_commit(&s_full[i]);
           }
-        mma_commit(&kv_empty[0]);
       }
       for (int j = 0; j < n_max && ok; ++j) {
-        if (!wait_item(2 * j + 1)) { ok = false; break; }
-        const bool more = j + 1 < n_max;
-        if (more && !wait_item(2 * j + 2)) { ok = false; break; }
+        if (!mbar_wait(&kv_full[j & 1], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
         for (int i = 0; i < 2; ++i) {
           if (j >= n_blk[i]) continue;
           // P arrives in two column halves; the first four k-steps of PV start on the first
@@ -574,10 +578,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           // one commit covers both: the next score tile, or the finished output, is ready
           mma_commit(&s_full[i]);
         }
-        if (ok) {
-          mma_commit(&kv_empty[(2 * j + 1) % NSLOT]);
-          if (more) mma_commit(&kv_empty[(2 * j + 2) % NSLOT]);
-        }
+        if (ok) mma_commit(&kv_empty[j & 1]);
       }
       if (!ok) {
         if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
@@ -719,7 +720,7 @@ int launch_fmha2(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorM
                  uint32_t fmt, cudaStream_t stream) {
   constexpr int DB = D / 64;
   constexpr int TILE = DB * TILE16K;
-  constexpr int NSLOT = D == 128 ? 5 : 8;
+  constexpr int NSLOT = 5;  // two (V, K) ring entries plus the slot of K_0
   constexpr int SMEM = (2 + NSLOT) * TILE + 1024 + 256;
   auto kern = fmha_fwd_kernel2<T, D, NSLOT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
