@@ -123,6 +123,21 @@ KCG_API int kcg_layernorm(int dtype, int64_t rows, int64_t cols, const void* x,
                           void* stream);
 
 /*
+ * y = Gelu(LayerNorm(x)) + residual in one pass over memory — the fusion of the chain
+ * LayerNorm -> ElementWise "Gelu" -> Binary "Add" that the reference's roadmap calls the
+ * "KernelFusion Optimizer" (doc/Plan.md:68, :110; no implementation exists there).
+ * x, residual and y are [rows, cols]; gamma and beta hold `cols` elements.  The value is
+ * rounded to the storage dtype after each of the three steps, exactly where the separate
+ * kernels would store it, so the result is bit-identical to calling kcg_layernorm,
+ * kcg_eltwise(Gelu) and kcg_binary(Add) in turn, at 3 instead of 7 tensor passes.  y may
+ * alias x or residual.  Rows the one-pass kernels do not take (longer than 32768 bf16 /
+ * 16384 fp32 elements, or not 16-byte vectorisable) run as those three launches.
+ */
+KCG_API int kcg_layernorm_gelu_add(int dtype, int64_t rows, int64_t cols, const void* x,
+                                   const void* gamma, const void* beta, float eps,
+                                   const void* residual, void* y, void* stream);
+
+/*
  * LayerNorm through the split-row kernels, with no allocation of any kind.  This entry
  * point has no counterpart in the reference (which never runs a kernel, let alone manages
  * scratch memory).
@@ -234,6 +249,22 @@ KCG_API int kcg_gemm(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t 
                      int64_t stride_a, const void* B, int64_t ldb, int64_t stride_b, void* C,
                      int64_t ldc, int64_t stride_c, const float* scale_a,
                      const float* scale_b, void* stream);
+
+/*
+ * GEMM with a fused epilogue: C = act(alpha * op(A) op(B) + bias) — the fusion of
+ * Matmul -> Binary "Add" (bias of N elements broadcast over rows) -> ElementWise / Relu, e.g.
+ * the reference's own Matmul -> Relu(inplace) sequence (test/test.cc:62-63), which its
+ * roadmap assigns to a "KernelFusion Optimizer" (doc/Plan.md:68, :110).
+ *   bias: N values of dtype_out, or NULL.  activation: 0 none, 1 Relu, 2 Gelu.
+ * The value is rounded to dtype_out after each step, exactly where the separate kernels would
+ * store it, so the result is bit-identical to the unfused chain.  All other arguments as
+ * kcg_gemm(), which is this function with bias = NULL and activation = 0.
+ */
+KCG_API int kcg_gemm_fused(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K,
+                           int64_t batch, int trans_a, int trans_b, const void* A, int64_t lda,
+                           int64_t stride_a, const void* B, int64_t ldb, int64_t stride_b, void* C,
+                           int64_t ldc, int64_t stride_c, const float* scale_a,
+                           const float* scale_b, const void* bias, int activation, void* stream);
 
 /*
  * Tuning switch with no counterpart in the reference: -1 (default) runs the tensor-core GEMM on

@@ -32,6 +32,7 @@ SIGNATURES = {
     "kcg_device_status": ([], _ci),
     "kcg_dtype_size": ([_ci], ctypes.c_size_t),
     "kcg_layernorm": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _vp], _ci),
+    "kcg_layernorm_gelu_add": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _vp, _vp], _ci),
     "kcg_layernorm_split_static": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _vp], _ci),
     "kcg_layernorm_set_warp_row_limit": ([_ci], None),
     "kcg_eltwise": ([_ci, _ci, _ci, _i64, _vp, _vp, _vp], _ci),
@@ -39,6 +40,8 @@ SIGNATURES = {
     "kcg_softmax": ([_ci, _i64, _i64, _fp, _ci, _i64, _vp, _vp, _vp], _ci),
     "kcg_gemm": ([_ci, _ci, _i64, _i64, _i64, _i64, _ci, _ci, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64,
                   _vp, _vp, _vp], _ci),
+    "kcg_gemm_fused": ([_ci, _ci, _i64, _i64, _i64, _i64, _ci, _ci, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64,
+                        _vp, _vp, _vp, _ci, _vp], _ci),
     "kcg_gemm_set_pair_mode": ([_ci], None),
     "kcg_fmha_fwd": ([_ci, _i64, _i64, _i64, _i64, _i64, _fp, _ci, _vp, _i64p, _vp, _i64p, _vp, _i64p, _vp, _i64p,
                       _vp], _ci),

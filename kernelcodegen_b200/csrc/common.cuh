@@ -122,4 +122,42 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return warp_max(t);
 }
 
+
+// GELU in the reference's tanh form, with its literal constants and its operation order
+// (src/Frontend/Operators.cc:981-995): 0.5x * (tanh(0.797884 * (0.044715 * (x * (x*x)) + x)) + 1).
+// Every step is an explicitly rounded multiply or add, so no call site can be contracted into
+// FMAs differently from another: the stand-alone kernel and the fused kernels agree bit for bit.
+// kFast uses the hardware tanh approximation (error below the rounding of a 16-bit result).
+template <bool kFast>
+__device__ __forceinline__ float gelu_tanh(float v) {
+  const float t1 = __fmul_rn(v, 0.5f);
+  const float t3 = __fmul_rn(v, __fmul_rn(v, v));
+  const float t5 = __fadd_rn(__fmul_rn(0.044715f, t3), v);
+  const float t6 = __fmul_rn(0.797884f, t5);
+  float t7;
+  if constexpr (kFast) {
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t7) : "f"(t6));
+  } else {
+    t7 = tanhf(t6);
+  }
+  return __fmul_rn(t1, __fadd_rn(t7, 1.0f));
+}
+
+// Fused GEMM epilogue: out = act(alpha * acc + bias), rounded to TOut after each step where the
+// unfused chain (Matmul -> Binary Add -> ElementWise) would have stored the intermediate, so
+// the fused result is bit-identical to the chain.  act: 0 none, 1 Relu, 2 Gelu (tanh form with
+// the reference's constants, evaluated like the stand-alone elementwise kernel).
+template <typename TOut>
+__device__ __forceinline__ TOut gemm_epilogue_value(float acc, float alpha, const TOut* __restrict__ bias,
+                                                    int64_t col, int act) {
+  TOut v = Conv<TOut>::from_f(alpha * acc);
+  if (bias) v = Conv<TOut>::from_f(Conv<TOut>::to_f(v) + Conv<TOut>::to_f(bias[col]));
+  if (act == 1) {
+    v = Conv<TOut>::from_f(fmaxf(0.f, Conv<TOut>::to_f(v)));
+  } else if (act == 2) {
+    v = Conv<TOut>::from_f(gelu_tanh<(sizeof(TOut) < 4)>(Conv<TOut>::to_f(v)));
+  }
+  return v;
+}
+
 }  // namespace kcg

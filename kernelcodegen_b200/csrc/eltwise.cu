@@ -29,12 +29,7 @@ struct OpSqrt { template <bool F> static __device__ __forceinline__ float f(floa
 struct OpLog  { template <bool F> static __device__ __forceinline__ float f(float v) { return F ? __logf(v) : logf(v); } };
 struct OpRelu { template <bool F> static __device__ __forceinline__ float f(float v) { return fmaxf(0.f, v); } };
 struct OpCast { template <bool F> static __device__ __forceinline__ float f(float v) { return v; } };
-struct OpGelu {
-  template <bool F> static __device__ __forceinline__ float f(float v) {
-    const float inner = 0.797884f * (0.044715f * (v * (v * v)) + v);
-    return (v * 0.5f) * (tanh_f<F>(inner) + 1.0f);
-  }
-};
+struct OpGelu { template <bool F> static __device__ __forceinline__ float f(float v) { return gelu_tanh<F>(v); } };
 
 template <typename TI, typename TO, typename Op, int UNROLL>
 __global__ void __launch_bounds__(256)

@@ -5,19 +5,30 @@
 namespace kcg {
 int sgemm_f32(int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a, int trans_b, const float* A,
               int64_t lda, int64_t stride_a, const float* B, int64_t ldb, int64_t stride_b, float* C,
-              int64_t ldc, int64_t stride_c, const float* scale_a, const float* scale_b, cudaStream_t stream);
+              int64_t ldc, int64_t stride_c, const float* scale_a, const float* scale_b, const float* bias, int act,
+              cudaStream_t stream);
 int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
                  int trans_b, const void* A, int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
                  int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
-                 const float* scale_b, cudaStream_t stream);
+                 const float* scale_b, const void* bias, int act, cudaStream_t stream);
 }  // namespace kcg
 
 extern "C" int kcg_gemm(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch,
                         int trans_a, int trans_b, const void* A, int64_t lda, int64_t stride_a,
                         const void* B, int64_t ldb, int64_t stride_b, void* C, int64_t ldc,
                         int64_t stride_c, const float* scale_a, const float* scale_b, void* stream) {
+  return kcg_gemm_fused(dtype_in, dtype_out, M, N, K, batch, trans_a, trans_b, A, lda, stride_a, B, ldb, stride_b, C,
+                        ldc, stride_c, scale_a, scale_b, nullptr, 0, stream);
+}
+
+extern "C" int kcg_gemm_fused(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch,
+                              int trans_a, int trans_b, const void* A, int64_t lda, int64_t stride_a,
+                              const void* B, int64_t ldb, int64_t stride_b, void* C, int64_t ldc,
+                              int64_t stride_c, const float* scale_a, const float* scale_b,
+                              const void* bias, int activation, void* stream) {
   using namespace kcg;
   clear_error();
+  if (activation < 0 || activation > 2) return fail(KCG_ERR_INVALID_ARG, "gemm: activation %d (0 none, 1 Relu, 2 Gelu)", activation);
   if (M < 0 || N < 0 || K < 0 || batch < 0) return fail(KCG_ERR_INVALID_ARG, "gemm: negative extent");
   if (M == 0 || N == 0 || batch == 0) return KCG_OK;
   if (K == 0) return fail(KCG_ERR_INVALID_ARG, "gemm: K must be positive");
@@ -33,10 +44,10 @@ extern "C" int kcg_gemm(int dtype_in, int dtype_out, int64_t M, int64_t N, int64
     if (dtype_out != KCG_F32) return fail(KCG_ERR_UNSUPPORTED, "gemm: float32 inputs produce float32");
     return sgemm_f32(M, N, K, batch, trans_a, trans_b, static_cast<const float*>(A), lda, stride_a,
                      static_cast<const float*>(B), ldb, stride_b, static_cast<float*>(C), ldc, stride_c,
-                     scale_a, scale_b, s);
+                     scale_a, scale_b, static_cast<const float*>(bias), activation, s);
   }
   if (dtype_in == KCG_BF16 || dtype_in == KCG_F16 || dtype_in == KCG_F8E4M3)
     return gemm_tcgen05(dtype_in, dtype_out, M, N, K, batch, trans_a, trans_b, A, lda, stride_a, B, ldb,
-                        stride_b, C, ldc, stride_c, scale_a, scale_b, s);
+                        stride_b, C, ldc, stride_c, scale_a, scale_b, bias, activation, s);
   return fail(KCG_ERR_UNSUPPORTED, "gemm: input dtype %d has no kernel", dtype_in);
 }

@@ -169,6 +169,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     float alpha = 1.f;
     if (p.scale_a) alpha *= *p.scale_a;
     if (p.scale_b) alpha *= *p.scale_b;
+    const TOut* bias = static_cast<const TOut*>(p.bias);
     uint32_t tile_iter = 0;
     bool ok = true;
     for (int64_t tile = cluster_id; tile < total && ok; tile += n_clusters, ++tile_iter) {
@@ -195,12 +196,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             if (p.c_vec_ok && col + VW <= p.N) {
               Vec16<TOut> o;
 #pragma unroll
-              for (int j = 0; j < VW; ++j) o.v[j] = Conv<TOut>::from_f(alpha * __uint_as_float(r[g * VW + j]));
+              for (int j = 0; j < VW; ++j) o.v[j] = gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act);
               st_vec(crow + col, o);
             } else {
 #pragma unroll
               for (int j = 0; j < VW; ++j)
-                if (col + j < p.N) crow[col + j] = Conv<TOut>::from_f(alpha * __uint_as_float(r[g * VW + j]));
+                if (col + j < p.N) crow[col + j] = gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act);
             }
           }
         }

@@ -54,6 +54,8 @@ struct GemmParams {
   const float* scale_b;
   int* status;
   int c_vec_ok;
+  const void* bias;  // N values of the output dtype, or null
+  int act;           // 0 none, 1 Relu, 2 Gelu
 };
 
 __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, int& b, int& mt, int& nt) {
@@ -206,6 +208,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     float alpha = 1.f;
     if (p.scale_a) alpha *= *p.scale_a;
     if (p.scale_b) alpha *= *p.scale_b;
+    const TOut* bias = static_cast<const TOut*>(p.bias);
     uint32_t tile_iter = 0;
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tile_iter) {
@@ -232,12 +235,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (p.c_vec_ok && col + VW <= p.N) {
               Vec16<TOut> o;
 #pragma unroll
-              for (int j = 0; j < VW; ++j) o.v[j] = Conv<TOut>::from_f(alpha * __uint_as_float(r[g * VW + j]));
+              for (int j = 0; j < VW; ++j) o.v[j] = gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act);
               st_vec(crow + col, o);
             } else {
 #pragma unroll
               for (int j = 0; j < VW; ++j)
-                if (col + j < p.N) crow[col + j] = Conv<TOut>::from_f(alpha * __uint_as_float(r[g * VW + j]));
+                if (col + j < p.N) crow[col + j] = gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act);
             }
           }
         }
@@ -360,7 +363,7 @@ extern "C" __attribute__((visibility("default"))) void kcg_gemm_set_pair_mode(in
 int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
                  int trans_b, const void* A, int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
                  int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
-                 const float* scale_b, cudaStream_t stream) {
+                 const float* scale_b, const void* bias, int act, cudaStream_t stream) {
   const int es = dtype_in == KCG_F8E4M3 ? 1 : 2;
   if (!aligned16(A) || !aligned16(B))
     return fail(KCG_ERR_ALIGNMENT, "gemm: A and B must be 16-byte aligned for the tensor-core path");
@@ -409,6 +412,7 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
   p.total_tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles * batch;
   p.k_blocks = static_cast<int>((K + BK - 1) / BK);
   p.scale_a = scale_a; p.scale_b = scale_b;
+  p.bias = bias; p.act = act;
   p.status = device_status_word();
   if (!p.status) return fail(KCG_ERR_CUDA, "gemm: could not allocate the host-mapped status word");
   const size_t out_es = kcg_dtype_size(dtype_out);

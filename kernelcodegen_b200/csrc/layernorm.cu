@@ -68,10 +68,13 @@ __device__ __forceinline__ uint32_t opaque(uint32_t w) {
 // Loads, normalises and stores one row held by `nthr` cooperating threads (a warp or a
 // block); `reduce` sums a float over those threads.  kExact: the row is exactly
 // nthr * VPT vectors long, so no bounds checks are needed.
-template <typename T, int VPT, bool kExact, typename Reduce>
+// kFuse: the row is not stored after normalisation but run through GELU and added to the
+// matching row of `res` first, rounding to T after each step exactly where the three separate
+// kernels would have stored and re-loaded it, so the result is bit-identical to the chain.
+template <typename T, int VPT, bool kExact, bool kFuse, typename Reduce>
 __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __restrict__ gamma,
-                                       const T* __restrict__ beta, T* __restrict__ yr, int tid, int nthr,
-                                       int nvec, float inv_n, float eps, Reduce reduce) {
+                                       const T* __restrict__ beta, const T* __restrict__ res, T* __restrict__ yr,
+                                       int tid, int nthr, int nvec, float inv_n, float eps, Reduce reduce) {
   using W = Words<T>;
   constexpr int EPW = W::EPW;
   uint4 v[VPT];
@@ -130,6 +133,23 @@ __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __rest
         for (int e = 0; e < EPW; ++e) r[e] = fmaf(g[e], fmaf(f[e], rstd, shift), b[e]);
         o[k] = W::pack(r);
       }
+      if constexpr (kFuse) {
+        const uint4 r4 = __ldcs(reinterpret_cast<const uint4*>(res) + vi);
+        const uint32_t rw[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float y1[EPW], rs[EPW], t[EPW];
+          W::unpack(o[k], y1);            // LayerNorm result as stored (rounded to T)
+          W::unpack(rw[k], rs);
+#pragma unroll
+          for (int e = 0; e < EPW; ++e) t[e] = gelu_tanh<(sizeof(T) < 4)>(y1[e]);
+          uint32_t y2w = W::pack(t);      // GELU result as stored
+          W::unpack(y2w, t);
+#pragma unroll
+          for (int e = 0; e < EPW; ++e) t[e] = t[e] + rs[e];
+          o[k] = W::pack(t);
+        }
+      }
       __stcs(reinterpret_cast<uint4*>(yr) + vi, make_uint4(o[0], o[1], o[2], o[3]));
     }
   }
@@ -137,25 +157,27 @@ __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __rest
 
 // One warp per row, four rows per block, no shared memory and no block barrier; rows of
 // up to 32*VPT vectors.
-template <typename T, int VPT, bool kExact>
+template <typename T, int VPT, bool kExact, bool kFuse>
 __global__ void __launch_bounds__(128, 5)
 ln_warp_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
-             T* __restrict__ y, int64_t rows, int cols, float eps) {
+             const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps) {
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
-  ln_row<T, VPT, kExact>(x + row * cols, gamma, beta, y + row * cols, lane, 32, cols / Vec16<T>::N,
+  ln_row<T, VPT, kExact, kFuse>(x + row * cols, gamma, beta, kFuse ? res + row * cols : nullptr, y + row * cols, lane, 32,
+                                cols / Vec16<T>::N,
                          1.0f / static_cast<float>(cols), eps, [](float v) { return warp_sum(v); });
 }
 
 // One thread block per row for longer rows: blockDim.x threads hold up to VPT vectors each.
-template <typename T, int VPT, bool kExact>
+template <typename T, int VPT, bool kExact, bool kFuse>
 __global__ void __launch_bounds__(512)
 ln_block_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
-              T* __restrict__ y, int64_t rows, int cols, float eps) {
+              const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps) {
   __shared__ float red[33];
   const int64_t row = blockIdx.x;
-  ln_row<T, VPT, kExact>(x + row * cols, gamma, beta, y + row * cols, threadIdx.x, blockDim.x,
+  ln_row<T, VPT, kExact, kFuse>(x + row * cols, gamma, beta, kFuse ? res + row * cols : nullptr, y + row * cols,
+                                threadIdx.x, blockDim.x,
                          cols / Vec16<T>::N, 1.0f / static_cast<float>(cols), eps,
                          [&](float v) { return block_sum(v, red); });
 }
@@ -246,21 +268,24 @@ ln_chunk_apply(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
 
 template <typename T>
 int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* beta, float eps,
-              T* y, cudaStream_t stream) {
+              T* y, cudaStream_t stream, const T* res = nullptr) {
+  // res != nullptr: y = gelu(layernorm(x)) + res in one pass (row kernels only; the caller
+  // falls back to three launches when the row kernels do not apply).
   constexpr int VW = Vec16<T>::N;
   const bool vec_ok = (cols % VW == 0) && aligned16(x) && aligned16(y) && aligned16(gamma) &&
-                      aligned16(beta);
+                      aligned16(beta) && aligned16(res);
   const int64_t nvec = cols / VW;
+  const int icols = static_cast<int>(cols);
   if (rows > 0x7fffffffll * 4) return fail(KCG_ERR_UNSUPPORTED, "layernorm: more than 2^33 rows");
   if (vec_ok && nvec <= 32 * g_warp_row_max_vecs) {
     const unsigned grid = static_cast<unsigned>((rows + 3) / 4);
     const int vpt = static_cast<int>((nvec + 31) / 32);
-#define KCG_LN_WARP(V)                                                                             \
-  do {                                                                                             \
-    if (nvec == 32 * V)                                                                            \
-      ln_warp_rows<T, V, true><<<grid, 128, 0, stream>>>(x, gamma, beta, y, rows, static_cast<int>(cols), eps);  \
-    else                                                                                           \
-      ln_warp_rows<T, V, false><<<grid, 128, 0, stream>>>(x, gamma, beta, y, rows, static_cast<int>(cols), eps); \
+#define KCG_LN_LAUNCH(V, E, F) ln_warp_rows<T, V, E, F><<<grid, 128, 0, stream>>>(x, gamma, beta, res, y, rows, icols, eps)
+#define KCG_LN_WARP(V)                                                          \
+  do {                                                                          \
+    const bool exact = nvec == 32 * V;                                          \
+    if (res) { if (exact) KCG_LN_LAUNCH(V, true, true); else KCG_LN_LAUNCH(V, false, true); }   \
+    else     { if (exact) KCG_LN_LAUNCH(V, true, false); else KCG_LN_LAUNCH(V, false, false); } \
   } while (0)
     if (vpt <= 1) KCG_LN_WARP(1);
     else if (vpt <= 2) KCG_LN_WARP(2);
@@ -268,6 +293,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
     else if (vpt <= 8) KCG_LN_WARP(8);
     else KCG_LN_WARP(16);
 #undef KCG_LN_WARP
+#undef KCG_LN_LAUNCH
     return check_launch("ln_warp_rows");
   }
   // Block per row: at most 8 vectors per thread and at most 512 threads.
@@ -276,19 +302,21 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
     threads = (threads + 31) / 32 * 32;
     const int vpt = static_cast<int>((nvec + threads - 1) / threads);
     const unsigned grid = static_cast<unsigned>(rows);
-#define KCG_LN_BLOCK(V)                                                                            \
-  do {                                                                                             \
-    if (nvec == static_cast<int64_t>(threads) * V)                                                 \
-      ln_block_rows<T, V, true><<<grid, threads, 0, stream>>>(x, gamma, beta, y, rows, static_cast<int>(cols), eps);  \
-    else                                                                                           \
-      ln_block_rows<T, V, false><<<grid, threads, 0, stream>>>(x, gamma, beta, y, rows, static_cast<int>(cols), eps); \
+#define KCG_LN_LAUNCH(V, E, F) ln_block_rows<T, V, E, F><<<grid, threads, 0, stream>>>(x, gamma, beta, res, y, rows, icols, eps)
+#define KCG_LN_BLOCK(V)                                                         \
+  do {                                                                          \
+    const bool exact = nvec == static_cast<int64_t>(threads) * V;               \
+    if (res) { if (exact) KCG_LN_LAUNCH(V, true, true); else KCG_LN_LAUNCH(V, false, true); }   \
+    else     { if (exact) KCG_LN_LAUNCH(V, true, false); else KCG_LN_LAUNCH(V, false, false); } \
   } while (0)
     if (vpt <= 2) KCG_LN_BLOCK(2);
     else if (vpt <= 4) KCG_LN_BLOCK(4);
     else KCG_LN_BLOCK(8);
 #undef KCG_LN_BLOCK
+#undef KCG_LN_LAUNCH
     return check_launch("ln_block_rows");
   }
+  if (res) return KCG_ERR_UNSUPPORTED;  // no fused form beyond the row kernels
   // Split-row path.
   const int64_t chunks64 = (cols + kChunk - 1) / kChunk;
   if (chunks64 > 65535 * 32 || rows > 65535)
@@ -391,6 +419,46 @@ extern "C" int kcg_layernorm_split_static(int dtype, int64_t rows, int64_t cols,
     default:
       return fail(KCG_ERR_UNSUPPORTED, "layernorm_split_static: dtype %d has no kernel (float32, bfloat16, float16)", dtype);
   }
+}
+
+extern "C" int kcg_layernorm_gelu_add(int dtype, int64_t rows, int64_t cols, const void* x, const void* gamma,
+                                      const void* beta, float eps, const void* residual, void* y, void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (rows < 0 || cols < 0) return fail(KCG_ERR_INVALID_ARG, "layernorm_gelu_add: negative size");
+  if (rows == 0 || cols == 0) return KCG_OK;
+  if (!x || !gamma || !beta || !residual || !y) return fail(KCG_ERR_INVALID_ARG, "layernorm_gelu_add: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc;
+  switch (dtype) {
+    case KCG_F32:
+      rc = launch_ln<float>(rows, cols, static_cast<const float*>(x), static_cast<const float*>(gamma),
+                            static_cast<const float*>(beta), eps, static_cast<float*>(y), s,
+                            static_cast<const float*>(residual));
+      break;
+    case KCG_BF16:
+      rc = launch_ln<__nv_bfloat16>(rows, cols, static_cast<const __nv_bfloat16*>(x),
+                                    static_cast<const __nv_bfloat16*>(gamma), static_cast<const __nv_bfloat16*>(beta),
+                                    eps, static_cast<__nv_bfloat16*>(y), s, static_cast<const __nv_bfloat16*>(residual));
+      break;
+    case KCG_F16:
+      rc = launch_ln<__half>(rows, cols, static_cast<const __half*>(x), static_cast<const __half*>(gamma),
+                             static_cast<const __half*>(beta), eps, static_cast<__half*>(y), s,
+                             static_cast<const __half*>(residual));
+      break;
+    default:
+      return fail(KCG_ERR_UNSUPPORTED, "layernorm_gelu_add: dtype %d has no kernel (float32, bfloat16, float16)", dtype);
+  }
+  if (rc != KCG_ERR_UNSUPPORTED) return rc;
+  // Rows the one-pass kernels do not take (too long or not vectorisable): the same three
+  // operators back to back, in place in y.
+  clear_error();
+  rc = kcg_layernorm(dtype, rows, cols, x, gamma, beta, eps, y, stream);
+  if (rc) return rc;
+  rc = kcg_eltwise(KCG_UNARY_GELU, dtype, dtype, rows * cols, y, y, stream);
+  if (rc) return rc;
+  const int64_t shape[2] = {rows, cols};
+  return kcg_binary(KCG_BINARY_ADD, dtype, 2, shape, 2, shape, y, residual, y, stream);
 }
 
 extern "C" void kcg_layernorm_set_warp_row_limit(int vecs_per_lane) {

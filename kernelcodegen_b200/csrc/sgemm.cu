@@ -23,6 +23,7 @@ struct SgemmArgs {
   int64_t ldc;
   int64_t batch_a, batch_b, batch_c;
   const float* scale_a; const float* scale_b;
+  const float* bias; int act;
 };
 
 // kAK: A is contiguous along k (row-major [M,K]); otherwise contiguous along m.
@@ -113,13 +114,15 @@ __global__ void __launch_bounds__(256) sgemm_kernel(const SgemmArgs p) {
       const int64_t gn = n0 + jh * 64 + tx * 4;
       float* dst = C + gm * p.ldc + gn;
       if (vec && gn + 3 < p.N) {
-        float4 o = make_float4(alpha * acc[i][jh * 4 + 0], alpha * acc[i][jh * 4 + 1],
-                               alpha * acc[i][jh * 4 + 2], alpha * acc[i][jh * 4 + 3]);
+        float4 o = make_float4(gemm_epilogue_value<float>(acc[i][jh * 4 + 0], alpha, p.bias, gn + 0, p.act),
+                               gemm_epilogue_value<float>(acc[i][jh * 4 + 1], alpha, p.bias, gn + 1, p.act),
+                               gemm_epilogue_value<float>(acc[i][jh * 4 + 2], alpha, p.bias, gn + 2, p.act),
+                               gemm_epilogue_value<float>(acc[i][jh * 4 + 3], alpha, p.bias, gn + 3, p.act));
         *reinterpret_cast<float4*>(dst) = o;
       } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (gn + j < p.N) dst[j] = alpha * acc[i][jh * 4 + j];
+          if (gn + j < p.N) dst[j] = gemm_epilogue_value<float>(acc[i][jh * 4 + j], alpha, p.bias, gn + j, p.act);
       }
     }
   }
@@ -130,13 +133,13 @@ __global__ void __launch_bounds__(256) sgemm_kernel(const SgemmArgs p) {
 int sgemm_f32(int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a, int trans_b,
               const float* A, int64_t lda, int64_t stride_a, const float* B, int64_t ldb,
               int64_t stride_b, float* C, int64_t ldc, int64_t stride_c, const float* scale_a,
-              const float* scale_b, cudaStream_t stream) {
+              const float* scale_b, const float* bias, int act, cudaStream_t stream) {
   SgemmArgs p;
   p.A = A; p.B = B; p.C = C; p.M = M; p.N = N; p.K = K;
   if (!trans_a) { p.a_sm = lda; p.a_sk = 1; } else { p.a_sm = 1; p.a_sk = lda; }
   if (!trans_b) { p.b_sk = ldb; p.b_sn = 1; } else { p.b_sk = 1; p.b_sn = ldb; }
   p.ldc = ldc; p.batch_a = stride_a; p.batch_b = stride_b; p.batch_c = stride_c;
-  p.scale_a = scale_a; p.scale_b = scale_b;
+  p.scale_a = scale_a; p.scale_b = scale_b; p.bias = bias; p.act = act;
   const int64_t gx = (N + BN - 1) / BN, gy = (M + BM - 1) / BM;
   if (gy > 65535 || batch > 65535)
     return fail(KCG_ERR_UNSUPPORTED, "fp32 gemm: M/128 and batch must not exceed 65535");

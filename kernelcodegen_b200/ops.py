@@ -90,6 +90,23 @@ def layernorm(x, scale, bias, axis: int, eps: float = 1e-5, inplace: bool = Fals
     return y
 
 
+def layernorm_gelu_add(x, scale, bias, residual, eps: float = 1e-5, out=None):
+    """Gelu(LayerNorm(x over the last dim)) + residual in one kernel; bit-identical to the chain
+    layernorm -> elementwise("Gelu") -> binary("Add")."""
+    _need_cuda(x, scale, bias, residual)
+    if tuple(residual.shape) != tuple(x.shape) or residual.dtype != x.dtype:
+        raise ValueError("residual must match x in shape and dtype")
+    cols = x.shape[-1]
+    if tuple(scale.shape) != (cols,) or tuple(bias.shape) != (cols,):
+        raise ValueError("scale and bias must have the length of the last dim")
+    rows = x.numel() // cols if cols else 0
+    y = out if out is not None else torch.empty_like(x)
+    check(_lib.load().kcg_layernorm_gelu_add(_dt(x), rows, cols, x.data_ptr(), scale.data_ptr(), bias.data_ptr(),
+                                             float(eps), residual.data_ptr(), y.data_ptr(), _stream()),
+          "kcg_layernorm_gelu_add")
+    return y
+
+
 def elementwise(x, operation: str, dtype=None, inplace: bool = False, out=None):
     """Unary map (reference: ElementWise::build, Operators.h:114-123)."""
     _need_cuda(x)
@@ -152,8 +169,11 @@ def _scale_ptr(s):
     return s.data_ptr()
 
 
+_ACT = {None: 0, "": 0, "Relu": 1, "Gelu": 2}
+
+
 def batched_matmul(A, B, trans_a: bool = False, trans_b: bool = False, out_dtype=None, scale_a=None,
-                   scale_b=None, out=None):
+                   scale_b=None, out=None, bias=None, activation=None):
     """C = op(A) op(B) over leading batch dims (reference: BatchedMatmul::build with
     Layout::rowMajor / Layout::colMajor, Operators.h:87-89; trans_x=True is colMajor)."""
     _need_cuda(A, B)
@@ -169,21 +189,24 @@ def batched_matmul(A, B, trans_a: bool = False, trans_b: bool = False, out_dtype
     if out_dtype is None:
         out_dtype = torch.bfloat16 if A.dtype == getattr(torch, "float8_e4m3fn", None) else A.dtype
     C = out if out is not None else torch.empty(tuple(A.shape[:-2]) + (m, n), dtype=out_dtype, device=A.device)
-    check(_lib.load().kcg_gemm(_dt(A), _DT[C.dtype], m, n, k1, batch, int(trans_a), int(trans_b),
-                               A.data_ptr(), A.shape[-1], A.shape[-1] * A.shape[-2],
-                               B.data_ptr(), B.shape[-1], B.shape[-1] * B.shape[-2],
-                               C.data_ptr(), n, m * n, _scale_ptr(scale_a), _scale_ptr(scale_b), _stream()),
+    if bias is not None and (not bias.is_cuda or bias.dtype != C.dtype or bias.numel() != n):
+        raise ValueError("bias holds N values of the output dtype on the device")
+    check(_lib.load().kcg_gemm_fused(_dt(A), _DT[C.dtype], m, n, k1, batch, int(trans_a), int(trans_b),
+                                     A.data_ptr(), A.shape[-1], A.shape[-1] * A.shape[-2],
+                                     B.data_ptr(), B.shape[-1], B.shape[-1] * B.shape[-2],
+                                     C.data_ptr(), n, m * n, _scale_ptr(scale_a), _scale_ptr(scale_b),
+                                     None if bias is None else bias.data_ptr(), _ACT[activation], _stream()),
           "kcg_gemm")
     return C
 
 
-def matmul(A, B, out_dtype=None, scale_a=None, scale_b=None, out=None):
+def matmul(A, B, out_dtype=None, scale_a=None, scale_b=None, out=None, bias=None, activation=None):
     """C[M,N] = A[M,K] B[K,N], both row-major (reference: Matmul::build, Operators.h:79-81)."""
     if A.dim() != 2 or B.dim() != 2:
         raise ValueError("Matmul takes rank-2 operands")
     if A.shape[1] != B.shape[0]:
         raise ValueError("Can't apply Matmul Operation due to imcompatible K-dim.")
-    return batched_matmul(A, B, False, False, out_dtype, scale_a, scale_b, out)
+    return batched_matmul(A, B, False, False, out_dtype, scale_a, scale_b, out, bias, activation)
 
 
 def fmha(Q, K, V, softmax_scale: float = 1.0, causal: bool = False, out_layout: str = "bhsd", out=None):
