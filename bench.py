@@ -366,6 +366,19 @@ def main() -> None:
         gbs = world * bytes_step[op_name] / (ms * 1e-3) / 1e9
         workloads[f"{op_name}_bf16_{ROWS}x{COLS}"] = {"ms": ms, "value": gbs, "unit": "GB/s",
                                                      "frac_of_hbm_peak": gbs / world / peaks["hbm_gbs"]}
+    if not args.no_extras:
+        # the same three operators as one fused pass (x and the residual in, y out: 3 tensor passes, not 7)
+        def fused(i=[0]):
+            s = sets[i[0] % BUFFER_SETS]; i[0] += 1
+            ops.layernorm_gelu_add(s["x"], gamma, beta, s["a"], 1e-5, out=s["y"])
+        ms = time_op(fused, 40)
+        fb = 3 * ROWS * COLS * 2 + 2 * COLS * 2
+        workloads[f"layernorm_gelu_add_fused_bf16_{ROWS}x{COLS}"] = {
+            "ms": ms, "value": world * fb / (ms * 1e-3) / 1e9, "unit": "GB/s",
+            "frac_of_hbm_peak": fb / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "speedup_vs_three_kernels": (workloads[f"layernorm_bf16_{ROWS}x{COLS}"]["ms"] +
+                                         workloads[f"gelu_bf16_{ROWS}x{COLS}"]["ms"] +
+                                         workloads[f"add_bf16_{ROWS}x{COLS}"]["ms"]) / ms}
     del sets
     torch.cuda.empty_cache()
 

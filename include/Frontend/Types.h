@@ -65,7 +65,7 @@ struct TensorInfo {
   int alias_of = -1;       // tensor whose storage this one shares (inplace results)
 };
 
-enum class OpKind { Matmul, BatchedMatmul, Softmax, LayerNorm, ElementWise, Binary, FusedAttention };
+enum class OpKind { Matmul, BatchedMatmul, Softmax, LayerNorm, ElementWise, Binary, FusedAttention, FusedLayerNormGeluAdd };
 
 // One recorded operator call (the reference's func.call); `func` names the per-(op, shape)
 // function it calls (the reference's func.func symbol).
@@ -82,6 +82,8 @@ struct OpNode {
   float scale = 1.0f;                  // Softmax / attention extension
   bool causal = false;                 // Softmax / attention extension
   int scale_a = -1, scale_b = -1;      // tensors holding per-tensor fp32 scales (FP8 Matmul)
+  int bias = -1;                       // fused GEMM epilogue: tensor of N values added to every row
+  std::string activation;              // fused GEMM epilogue: "", "Relu" or "Gelu"
   bool erased = false;                 // consumed by a fusion
 };
 

@@ -97,7 +97,7 @@ class KernelCodeGenerator {
   std::string platform;
   float minLatency = FLT_MAX;
   std::vector<std::map<std::string, int>> matmulConfigs, fmhaConfigs, binaryConfigs, elementWiseConfigs,
-      gatherConfigs, layerNormConfigs, batchMatmulConfigs, softmaxConfigs;
+      gatherConfigs, layerNormConfigs, batchMatmulConfigs, softmaxConfigs, fusionConfigs;
 };
 
 }  // namespace KernelCodeGen

@@ -62,6 +62,26 @@ struct FMHAOptimizer : Optimizer {
   std::vector<Chain> chains;
 };
 
+// The "KernelFusion Optimizer" of the reference's roadmap (doc/Plan.md:68, :110; not implemented
+// there).  Two patterns, both requiring every intermediate to have a single user:
+//   Matmul / BatchedMatmul [-> Binary "Add" with an [N] bias] [-> Relu | ElementWise "Relu"/"Gelu"]
+//       becomes one GEMM launch with a fused epilogue (test/test.cc:62-63 is Matmul -> Relu);
+//   LayerNorm (last dim) -> ElementWise "Gelu" -> Binary "Add" with a same-shape tensor
+//       becomes one pass over memory.
+// Push it before the family optimizers so that it sees the chains still unselected.
+struct KernelFusionOptimizer : Optimizer {
+  KernelFusionOptimizer() { this->name = "KernelFusion"; }
+  bool applicable(Module& module) override;
+  void applyOptimzer(Module& module, OpBuilder& builder) override;
+  static std::map<std::string, int> fusionConfig;
+
+ private:
+  struct GemmChain { int gemm, add, act; };     // op indices, -1 where absent
+  struct LnChain { int ln, gelu, add; };
+  std::vector<GemmChain> gemm_chains;
+  std::vector<LnChain> ln_chains;
+};
+
 #undef KCG_DECLARE_OPTIMIZER
 
 }  // namespace KernelCodeGen

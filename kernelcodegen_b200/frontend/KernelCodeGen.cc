@@ -23,6 +23,7 @@ const char* entry_for(OpKind k) {
     case OpKind::ElementWise: return "kcg_eltwise";
     case OpKind::Binary: return "kcg_binary";
     case OpKind::FusedAttention: return "kcg_fmha_fwd";
+    case OpKind::FusedLayerNormGeluAdd: return "kcg_layernorm_gelu_add";
   }
   return "?";
 }
@@ -42,6 +43,8 @@ std::string shape_str(const std::vector<int64_t>& s) {
   for (size_t i = 0; i < s.size(); ++i) r += (i ? "," : "") + std::to_string(s[i]);
   return r + "]";
 }
+
+int act_code(const std::string& a) { return a == "Relu" ? 1 : (a == "Gelu" ? 2 : 0); }
 
 int index_of(const std::vector<std::string>& v, const std::string& s) {
   for (size_t i = 0; i < v.size(); ++i)
@@ -75,6 +78,7 @@ KernelCodeGenerator::KernelCodeGenerator(const std::string& platform_) : platfor
   layerNormConfigs = {{{"WARP_ROW_VECS", 8}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}}};
   gatherConfigs = {};
   softmaxConfigs = {{{"BLOCK_SIZE", 256}}};
+  fusionConfigs = {{{"EPILOGUE", 1}}};
   fmhaConfigs = {{{"BLOCK_SIZE", 192}, {"Br", 128}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}}};
 }
 
@@ -131,6 +135,7 @@ Module& KernelCodeGenerator::optimize(ComputeDAG& graph_) {
     else if (*opt == GatherOptimizer()) { table = &gatherConfigs; slot = &GatherOptimizer::gatherConfig; }
     else if (*opt == BatchMatmulOptimizer()) { table = &batchMatmulConfigs; slot = &BatchMatmulOptimizer::batchMatmulConfig; }
     else if (*opt == SoftmaxOptimizer()) { table = &softmaxConfigs; slot = &SoftmaxOptimizer::softmaxConfig; }
+    else if (*opt == KernelFusionOptimizer()) { table = &fusionConfigs; slot = &KernelFusionOptimizer::fusionConfig; }
     bool applied = false;
     if (table) {
       for (auto& cfg : *table) {
@@ -244,8 +249,8 @@ int KernelCodeGenerator::run(Module& module, const Bindings& bindings, void* str
         const int64_t m = t0.shape[0], k = t0.shape[1], n = g.tensors[op.inputs[1]].shape[1];
         const float* sa = op.scale_a >= 0 ? static_cast<const float*>(ptr(op.scale_a)) : nullptr;
         const float* sb = op.scale_b >= 0 ? static_cast<const float*>(ptr(op.scale_b)) : nullptr;
-        rc = kcg_gemm(static_cast<int>(t0.dtype), static_cast<int>(to.dtype), m, n, k, 1, 0, 0, in[0], k, 0, in[1], n, 0,
-                      out, n, 0, sa, sb, stream);
+        rc = kcg_gemm_fused(static_cast<int>(t0.dtype), static_cast<int>(to.dtype), m, n, k, 1, 0, 0, in[0], k, 0, in[1], n,
+                            0, out, n, 0, sa, sb, op.bias >= 0 ? ptr(op.bias) : nullptr, act_code(op.activation), stream);
         break;
       }
       case OpKind::BatchedMatmul: {
@@ -257,9 +262,9 @@ int KernelCodeGenerator::run(Module& module, const Bindings& bindings, void* str
         const int64_t n = tb ? sb[r - 2] : sb[r - 1];
         int64_t batch = 1;
         for (size_t d = 0; d + 2 < r; ++d) batch *= sa[d];
-        rc = kcg_gemm(static_cast<int>(t0.dtype), static_cast<int>(to.dtype), m, n, k, batch, ta, tb, in[0], sa[r - 1],
-                      sa[r - 1] * sa[r - 2], in[1], sb[r - 1], sb[r - 1] * sb[r - 2], out, n, m * n, nullptr, nullptr,
-                      stream);
+        rc = kcg_gemm_fused(static_cast<int>(t0.dtype), static_cast<int>(to.dtype), m, n, k, batch, ta, tb, in[0],
+                            sa[r - 1], sa[r - 1] * sa[r - 2], in[1], sb[r - 1], sb[r - 1] * sb[r - 2], out, n, m * n,
+                            nullptr, nullptr, op.bias >= 0 ? ptr(op.bias) : nullptr, act_code(op.activation), stream);
         break;
       }
       case OpKind::Softmax: {
@@ -293,6 +298,13 @@ int KernelCodeGenerator::run(Module& module, const Bindings& bindings, void* str
         rc = kcg_binary(index_of(Binary::operations(), op.operation), static_cast<int>(t0.dtype),
                         static_cast<int>(sa.size()), sa.data(), static_cast<int>(sb.size()), sb.data(), in[0], in[1], out,
                         stream);
+        break;
+      }
+      case OpKind::FusedLayerNormGeluAdd: {
+        const int64_t cols = t0.shape.back();
+        const int64_t rows = cols ? numel(op.inputs[0]) / cols : 0;
+        rc = kcg_layernorm_gelu_add(static_cast<int>(t0.dtype), rows, cols, in[0], in[1], in[2], op.eps, in[3], out,
+                                    stream);
         break;
       }
       case OpKind::FusedAttention: {

@@ -143,3 +143,135 @@ void FMHAOptimizer::applyOptimzer(Module& module, OpBuilder&) {
 }
 
 }  // namespace KernelCodeGen
+
+// ---------------------------------------------------------------------------- KernelFusion
+namespace KernelCodeGen {
+
+std::map<std::string, int> KernelFusionOptimizer::fusionConfig;
+
+namespace {
+// The single live op that reads `tensor` as its first input, or -1 (also -1 when the tensor has
+// more than one reader: a second reader needs the intermediate in memory).
+int sole_consumer(const GraphData& g, int tensor) {
+  if (g.users(tensor) != 1) return -1;
+  for (int j = 0; j < static_cast<int>(g.ops.size()); ++j) {
+    const OpNode& op = g.ops[j];
+    if (op.erased) continue;
+    for (int in : op.inputs)
+      if (in == tensor) return j;
+  }
+  return -1;
+}
+}  // namespace
+
+bool KernelFusionOptimizer::applicable(Module& module) {
+  gemm_chains.clear();
+  ln_chains.clear();
+  auto& g = *module.graph;
+  auto cpu = [&](int op) { return op >= 0 && g.funcs[g.ops[op].func].state == "cpu"; };
+  for (int i = 0; i < static_cast<int>(g.ops.size()); ++i) {
+    const OpNode& op = g.ops[i];
+    if (op.erased || !cpu(i)) continue;
+    if (op.kind == OpKind::Matmul || op.kind == OpKind::BatchedMatmul) {
+      if (op.bias >= 0 || !op.activation.empty()) continue;  // already fused
+      GemmChain c{i, -1, -1};
+      int tail = op.output;
+      const int64_t n = g.tensors[op.output].shape.back();
+      int next = sole_consumer(g, tail);
+      if (cpu(next) && g.ops[next].kind == OpKind::Binary && g.ops[next].operation == "Add" &&
+          g.ops[next].inputs[0] == tail) {
+        const auto& bias = g.tensors[g.ops[next].inputs[1]];
+        if (bias.shape.size() == 1 && bias.shape[0] == n && bias.dtype == g.tensors[tail].dtype &&
+            g.tensors[g.ops[next].output].shape == g.tensors[tail].shape) {
+          c.add = next;
+          tail = g.ops[next].output;
+          next = sole_consumer(g, tail);
+        }
+      }
+      if (cpu(next) && g.ops[next].kind == OpKind::ElementWise && g.ops[next].inputs[0] == tail &&
+          (g.ops[next].operation == "Relu" || g.ops[next].operation == "Gelu") &&
+          g.tensors[g.ops[next].output].dtype == g.tensors[tail].dtype)
+        c.act = next;
+      if (c.add >= 0 || c.act >= 0) gemm_chains.push_back(c);
+    } else if (op.kind == OpKind::LayerNorm) {
+      const auto& x = g.tensors[op.inputs[0]];
+      if (op.axis != static_cast<int64_t>(x.shape.size()) - 1) continue;
+      const int64_t cols = x.shape.back();
+      const auto& sc = g.tensors[op.inputs[1]];
+      const auto& bi = g.tensors[op.inputs[2]];
+      if (sc.shape != std::vector<int64_t>{cols} || bi.shape != std::vector<int64_t>{cols}) continue;
+      const int ge = sole_consumer(g, op.output);
+      if (!cpu(ge) || g.ops[ge].kind != OpKind::ElementWise || g.ops[ge].operation != "Gelu") continue;
+      const int ad = sole_consumer(g, g.ops[ge].output);
+      if (!cpu(ad) || g.ops[ad].kind != OpKind::Binary || g.ops[ad].operation != "Add") continue;
+      const OpNode& add = g.ops[ad];
+      const int other = add.inputs[0] == g.ops[ge].output ? add.inputs[1] : add.inputs[0];
+      if (other == g.ops[ge].output) continue;  // y + y
+      if (g.tensors[other].shape != x.shape || g.tensors[other].dtype != x.dtype) continue;
+      ln_chains.push_back({i, ge, ad});
+    }
+  }
+  return !gemm_chains.empty() || !ln_chains.empty();
+}
+
+void KernelFusionOptimizer::applyOptimzer(Module& module, OpBuilder&) {
+  auto& g = *module.graph;
+  auto add_func = [&](const std::string& name) {
+    if (!g.funcs.count(name)) g.func_order.insert(g.func_order.begin(), name);
+    auto& info = g.funcs[name];
+    info.state = "gpu";
+    info.optimizer = this->name;
+    info.config = fusionConfig;
+  };
+  for (const auto& c : gemm_chains) {
+    OpNode fused = g.ops[c.gemm];
+    const int last = c.act >= 0 ? c.act : c.add;
+    fused.func = "Fused_" + g.ops[c.gemm].func;
+    if (c.add >= 0) {
+      fused.bias = g.ops[c.add].inputs[1];
+      fused.inputs.push_back(fused.bias);
+      fused.func += "_Bias";
+    }
+    if (c.act >= 0) {
+      fused.activation = g.ops[c.act].operation;
+      fused.func += "_" + fused.activation;
+    }
+    // the fused launch writes the last tensor of the chain; an in-place result keeps naming the
+    // storage of the tensor it was a view of, so a pointer bound to either handle is found
+    fused.output = g.ops[last].output;
+    g.tensors[fused.output].producer = last;
+    g.ops[c.gemm].erased = true;
+    if (c.add >= 0) g.ops[c.add].erased = true;
+    if (c.act >= 0) g.ops[c.act].erased = true;
+    g.ops[last] = fused;
+    add_func(fused.func);
+  }
+  for (const auto& c : ln_chains) {
+    const OpNode& ln = g.ops[c.ln];
+    const OpNode& add = g.ops[c.add];
+    OpNode fused = ln;
+    fused.kind = OpKind::FusedLayerNormGeluAdd;
+    fused.func = "Fused_" + ln.func + "_Gelu_Add";
+    const int other = add.inputs[0] == g.ops[c.gelu].output ? add.inputs[1] : add.inputs[0];
+    fused.inputs = {ln.inputs[0], ln.inputs[1], ln.inputs[2], other};
+    fused.output = add.output;
+    g.tensors[fused.output].producer = c.add;
+    g.ops[c.ln].erased = true;
+    g.ops[c.gelu].erased = true;
+    g.ops[c.add] = fused;
+    add_func(fused.func);
+  }
+  // functions that lost their last caller disappear
+  for (auto it = g.func_order.begin(); it != g.func_order.end();) {
+    bool used = false;
+    for (const auto& op : g.ops) used = used || (!op.erased && op.func == *it);
+    if (!used) {
+      g.funcs.erase(*it);
+      it = g.func_order.erase(it);
+    } else {
+      ++it;
+    }
+  }
+}
+
+}  // namespace KernelCodeGen

@@ -151,6 +151,45 @@ static void test_flash_attention_graph() {  // test/test.cc:107-147
   CHECK(module.calls.size() == 4);
 }
 
+static void test_kernel_fusion() {
+  KernelCodeGenerator generator("CUDA");
+  generator.opts.push_back(std::make_unique<KernelFusionOptimizer>());
+  generator.opts.push_back(std::make_unique<MatmulOptimizer>());
+  generator.opts.push_back(std::make_unique<LayerNormOptimizer>());
+  generator.opts.push_back(std::make_unique<ElementWiseOptimizer>());
+  generator.opts.push_back(std::make_unique<BinaryOptimizer>());
+  auto graph = generator.createGraph("fusion");
+  auto A = graph.create<PlaceHolder>(std::vector<int64_t>{512, 128}, std::string{"bfloat16"});
+  auto B = graph.create<PlaceHolder>(std::vector<int64_t>{128, 256}, std::string{"bfloat16"});
+  auto bias = graph.create<PlaceHolder>(std::vector<int64_t>{256}, std::string{"bfloat16"});
+  auto C = graph.create<Matmul>(A, B);
+  auto Cb = graph.create<Binary>(C, bias, "Add");
+  auto D = graph.create<ElementWise>(Cb, "Gelu", MemorySpace::global);
+  // Matmul -> Relu(inplace), the reference's own sequence (test/test.cc:62-63)
+  auto E = graph.create<Matmul>(A, B);
+  auto F = graph.create<Relu>(E, MemorySpace::inplace);
+  // LayerNorm -> Gelu -> Add
+  auto X = graph.create<PlaceHolder>(std::vector<int64_t>{64, 256}, std::string{"bfloat16"});
+  auto G = graph.create<PlaceHolder>(std::vector<int64_t>{256}, std::string{"bfloat16"});
+  auto R = graph.create<PlaceHolder>(std::vector<int64_t>{64, 256}, std::string{"bfloat16"});
+  auto Y = graph.create<LayerNorm>(X, G, G, int64_t(-1));
+  auto Z = graph.create<ElementWise>(Y, "Gelu", MemorySpace::global);
+  auto W = graph.create<Binary>(Z, R, "Add");
+  // a Gelu whose input has a second reader must stay unfused
+  auto H = graph.create<Matmul>(A, B);
+  auto I = graph.create<ElementWise>(H, "Gelu", MemorySpace::global);
+  auto J = graph.create<ElementWise>(H, "Tanh", MemorySpace::global);
+  (void)D; (void)F; (void)W; (void)I; (void)J;
+  auto module = generator.optimize(graph);
+  auto plan = generator.codegen(module);
+  CHECK(module.calls.size() == 6);  // fused gemm+bias+gelu, fused gemm+relu, fused LN chain, gemm, gelu, tanh
+  CHECK(has(plan, "@Fused_Matmul_m512n256k128_Bias_Gelu"));
+  CHECK(has(plan, "@Fused_Matmul_m512n256k128_Relu"));
+  CHECK(has(plan, "launch kcg_layernorm_gelu_add") && has(plan, "@Fused_LayerNorm_64_256_axis_1_Gelu_Add"));
+  CHECK(has(plan, "@Gelu_Elementwise_512_256") && has(plan, "@Tanh_Elementwise_512_256"));
+  for (const auto& kv : module.graph->funcs) CHECK(kv.second.state == "gpu");
+}
+
 static void test_errors() {
   KernelCodeGenerator generator("CUDA");
   auto graph = generator.createGraph("errors");
@@ -298,6 +337,60 @@ static void gpu_layernorm_gelu_add() {  // the headline chain through the graph 
   CHECK(rel_fro(download(dW, w.size()), w) <= 1e-5);
 }
 
+static void gpu_kernel_fusion() {  // LayerNorm -> Gelu -> Add fused by KernelFusionOptimizer, fp32
+  KernelCodeGenerator generator("CUDA");
+  auto graph = generator.createGraph("ln_gelu_add_fused");
+  generator.opts.push_back(std::make_unique<KernelFusionOptimizer>());
+  const int64_t rows = 96, cols = 4096;
+  auto X = graph.create<PlaceHolder>(std::vector<int64_t>{rows, cols}, std::string{"float32"});
+  auto G = graph.create<PlaceHolder>(std::vector<int64_t>{cols}, std::string{"float32"});
+  auto Bt = graph.create<PlaceHolder>(std::vector<int64_t>{cols}, std::string{"float32"});
+  auto R = graph.create<PlaceHolder>(std::vector<int64_t>{rows, cols}, std::string{"float32"});
+  auto Y = graph.create<LayerNorm>(X, G, Bt, int64_t(-1));
+  auto Z = graph.create<ElementWise>(Y, "Gelu", MemorySpace::global);
+  auto W = graph.create<Binary>(Z, R, "Add");
+  auto module = generator.optimize(graph);
+  CHECK(module.calls.size() == 1 && module.calls[0].entry == "kcg_layernorm_gelu_add");
+  auto hX = randn(rows * cols, 13), hG = randn(cols, 14, 0.1f, 1.f), hB = randn(cols, 15, 0.1f), hR = randn(rows * cols, 16);
+  Bindings bind;
+  void* dW = upload(nullptr, rows * cols * 4);
+  bind.set(X, upload(hX.data(), hX.size() * 4));
+  bind.set(G, upload(hG.data(), hG.size() * 4));
+  bind.set(Bt, upload(hB.data(), hB.size() * 4));
+  bind.set(R, upload(hR.data(), hR.size() * 4));
+  bind.set(W, dW);  // Y and Z never exist in memory
+  CHECK(generator.run(module, bind) == KCG_OK);
+  cudaDeviceSynchronize();
+  std::vector<float> y(rows * cols), z(rows * cols), w(rows * cols);
+  oracle_layernorm_f32(hX.data(), hG.data(), hB.data(), y.data(), rows, cols, 1e-5f, 0);
+  oracle_unary_f32(5, y.data(), z.data(), z.size(), 0);
+  const int64_t sh[2] = {rows, cols};
+  oracle_binary_f32(0, 2, sh, 2, sh, z.data(), hR.data(), w.data());
+  CHECK(rel_fro(download(dW, w.size()), w) <= 1e-5);
+  // Matmul -> Relu(inplace) fused into the GEMM epilogue; the pointer is bound to C only
+  auto g2 = generator.createGraph("matmul_relu_fused");
+  const int m = 256, n = 128, k = 64;
+  auto A = g2.create<PlaceHolder>(std::vector<int64_t>{m, k}, std::string{"float32"});
+  auto B = g2.create<PlaceHolder>(std::vector<int64_t>{k, n}, std::string{"float32"});
+  auto C = g2.create<Matmul>(A, B);
+  auto D = g2.create<Relu>(C, MemorySpace::inplace);
+  (void)D;
+  auto m2 = generator.optimize(g2);
+  CHECK(m2.calls.size() == 1 && m2.calls[0].entry == "kcg_gemm");
+  auto hA = randn(size_t(m) * k, 17), hBm = randn(size_t(k) * n, 18);
+  Bindings b2;
+  void* dC = upload(nullptr, size_t(m) * n * 4);
+  b2.set(A, upload(hA.data(), hA.size() * 4));
+  b2.set(B, upload(hBm.data(), hBm.size() * 4));
+  b2.set(C, dC);
+  CHECK(generator.run(m2, b2) == KCG_OK);
+  cudaDeviceSynchronize();
+  std::vector<float> want(size_t(m) * n), relu(size_t(m) * n);
+  oracle_matmul_f32(hA.data(), hBm.data(), want.data(), m, n, k, 0, m, 0);
+  oracle_unary_f32(3, want.data(), relu.data(), relu.size(), 0);
+  CHECK(rel_fro(download(dC, relu.size()), relu) <= 1e-5);
+}
+
 static void gpu_fused_attention() {  // BatchedMatmul -> Softmax -> BatchedMatmul, bf16, fused
   KernelCodeGenerator generator("CUDA");
   auto graph = generator.createGraph("flash_attn_demo");
@@ -342,10 +435,12 @@ int main(int argc, char** argv) {
     test_operators_cast();
     test_commented_sequences();
     test_flash_attention_graph();
+    test_kernel_fusion();
     test_errors();
   } else {
     gpu_matmul_relu();
     gpu_layernorm_gelu_add();
+    gpu_kernel_fusion();
     gpu_fused_attention();
   }
   if (failures) {
