@@ -81,6 +81,14 @@ __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __rest
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
     if (kExact || i * nthr + tid < nvec) v[i] = __ldcs(reinterpret_cast<const uint4*>(xr) + i * nthr + tid);
+  // fused form: the residual row is requested together with x, so that its latency is spent
+  // under the two reductions instead of after them
+  uint4 rv[kFuse ? VPT : 1];
+  if constexpr (kFuse) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+      if (kExact || i * nthr + tid < nvec) rv[i] = __ldcs(reinterpret_cast<const uint4*>(res) + i * nthr + tid);
+  }
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
@@ -134,7 +142,7 @@ __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __rest
         o[k] = W::pack(r);
       }
       if constexpr (kFuse) {
-        const uint4 r4 = __ldcs(reinterpret_cast<const uint4*>(res) + vi);
+        const uint4 r4 = rv[i];
         const uint32_t rw[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
