@@ -179,6 +179,51 @@ def run_reference(args) -> None:
     }))
 
 
+def cpu_side_by_side(workloads: dict) -> None:
+    """Put the CPU loop nests' throughput beside each GEMM / FMHA workload: a bounded sample of
+    the same shape, in fp32, on every host core this process may run on."""
+    import numpy as np
+    from oracle import oracle as O
+    try:
+        threads = len(os.sched_getaffinity(0))
+    except AttributeError:
+        threads = os.cpu_count() or 1
+    rng = np.random.default_rng(0xC0DE)
+
+    def note(key, flops, dtc, sample):
+        if key in workloads:
+            workloads[key]["cpu"] = {"value": flops / dtc / 1e12, "unit": "TFLOP/s", "cores": threads,
+                                     "kind": "port", "sample": sample}
+
+    if "gemm_f32_1024" in workloads:
+        n = 1024
+        A = rng.uniform(-1, 1, (n, n)).astype(np.float32); B = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+        t0 = time.perf_counter()
+        O.ref32.matmul(A, B, threads=threads)
+        note("gemm_f32_1024", 2 * n ** 3, time.perf_counter() - t0, "the full 1024^3 product, fp32 loop nest")
+    if "gemm_bf16_8192" in workloads:
+        n, rows = 8192, 32
+        A = rng.standard_normal((n, n), dtype=np.float32); B = rng.standard_normal((n, n), dtype=np.float32)
+        t0 = time.perf_counter()
+        O.ref32.matmul(A, B, rows=(0, rows), threads=threads)
+        dtc = time.perf_counter() - t0
+        for key in ("gemm_bf16_8192", "gemm_fp8_8192"):
+            note(key, 2 * rows * n * n, dtc, f"{rows} of the 8192 rows of C at N = K = 8192, fp32 loop nest")
+        del A, B
+    for causal in (False, True):
+        key = f"fmha_bf16_s4096_{'causal' if causal else 'full'}"
+        if key not in workloads:
+            continue
+        S, D = 4096, 128
+        Q, K, V = (rng.standard_normal((1, 1, S, D), dtype=np.float32) for _ in range(3))
+        t0 = time.perf_counter()
+        O.ref32.attention(Q, K, V, D ** -0.5, causal, threads=threads)
+        fl = 4 * S * S * D if not causal else 2 * S * (S + 1) * D
+        note(key, fl, time.perf_counter() - t0,
+             "one of the 256 (batch, head) slices at S = 4096, D = 128: the unfused fp32 chain "
+             "BatchedMatmul -> Softmax -> BatchedMatmul")
+
+
 # ------------------------------------------------------------------------------ our arm
 def main() -> None:
     ap = argparse.ArgumentParser()
@@ -187,7 +232,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM/FMHA/fp32 side measurements")
-    ap.add_argument("--only", default="", help="comma list of extras to run (gemm,fmha,fp32,sgemm)")
+    ap.add_argument("--only", default="", help="comma list of extras to run (bw,fp32,gemm,sgemm,fmha,sweep)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -446,6 +491,40 @@ def main() -> None:
                 "frac_of_nominal_2250": tf / world / 2250.0}
         del Q, K, V, Oo
         torch.cuda.empty_cache()
+    if want("sweep"):
+        # the other sizes of the GEMM and FMHA configurations (per GPU; N ranks run N copies)
+        for n in (1024, 2048, 4096, 16384):
+            for tdt, tag in ((torch.bfloat16, "bf16"), (torch.float16, "f16")):
+                A = rnd((n, n), tdt, std=n ** -0.5); B = rnd((n, n), tdt)
+                C = torch.empty((n, n), dtype=tdt, device="cuda")
+                ms = time_op(lambda: ops.matmul(A, B, out=C), 20 if n <= 4096 else 8)
+                tf = world * 2 * n ** 3 / (ms * 1e-3) / 1e12
+                workloads[f"gemm_{tag}_{n}"] = {"ms": ms, "value": tf, "unit": "TFLOP/s",
+                                                "frac_of_nominal_2250": tf / world / 2250.0}
+                if n <= 4096:
+                    workloads[f"gemm_{tag}_{n}"]["note"] = "operands fit the 126 MB L2 (compute-bound shape)"
+                del A, B, C
+            A8 = rnd((n, n), torch.float32, std=n ** -0.5).to(torch.float8_e4m3fn)
+            B8 = rnd((n, n), torch.float32).to(torch.float8_e4m3fn)
+            C = torch.empty((n, n), dtype=dt, device="cuda")
+            one = torch.ones(1, device="cuda")
+            ms = time_op(lambda: ops.matmul(A8, B8, out_dtype=dt, scale_a=one, scale_b=one, out=C), 20 if n <= 4096 else 8)
+            tf = world * 2 * n ** 3 / (ms * 1e-3) / 1e12
+            workloads[f"gemm_fp8_{n}"] = {"ms": ms, "value": tf, "unit": "TFLOP/s", "frac_of_nominal_4500": tf / world / 4500.0}
+            del A8, B8, C
+            torch.cuda.empty_cache()
+        Bq, H, D = 8, 32, 128
+        for S in (1024, 2048):
+            Q, K, V = rnd((Bq, H, S, D)), rnd((Bq, H, S, D)), rnd((Bq, H, S, D))
+            Oo = torch.empty_like(Q)
+            for causal in (False, True):
+                ms = time_op(lambda: ops.fmha(Q, K, V, D ** -0.5, causal, out=Oo), 20)
+                fl = 4 * Bq * H * S * S * D if not causal else 2 * Bq * H * S * (S + 1) * D
+                tf = world * fl / (ms * 1e-3) / 1e12
+                workloads[f"fmha_bf16_s{S}_{'causal' if causal else 'full'}"] = {
+                    "ms": ms, "value": tf, "unit": "TFLOP/s", "frac_of_nominal_2250": tf / world / 2250.0}
+            del Q, K, V, Oo
+        torch.cuda.empty_cache()
     if world > 1 and not args.no_extras:
         # the optional exchange: NCCL all-gather of a sharded output (here the 128 MiB bf16 C
         # block of the GEMM shard and the 64 MiB LayerNorm block), timed on the device
@@ -465,6 +544,8 @@ def main() -> None:
             workloads[name] = {"ms": ms, "value": recv / (ms * 1e-3) / 1e9, "unit": "GB/s received per GPU"}
             del loc, out
         torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and not args.no_extras:
+        cpu_side_by_side(workloads)
     if _lib.device_status() != 0:
         raise SystemExit("a kernel reported a timed-out device-side wait")
 

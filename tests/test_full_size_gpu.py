@@ -1,0 +1,206 @@
+"""Parity at the benchmark's full sizes, where the float64 oracle cannot cover every element
+in seconds: the oracle checks a sample (rows/columns that touch every tile, whole heads),
+and size-independent properties cover the rest — bit-equality between the single-CTA and the
+CTA-pair GEMM kernels, exact scaling by a power of two, a float64 column checksum,
+replicated heads that must come out bit-identical, softmax rows that sum to one."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests.helpers import TOL, f64, rel_fro, sync_ok
+
+pytestmark = pytest.mark.gpu
+
+
+def ops():
+    from kernelcodegen_b200 import ops as _ops
+    return _ops
+
+
+def dev_randn(shape, dtype, seed, std=1.0, mean=0.0):
+    g = torch.Generator(device="cuda").manual_seed(0xC0DE + seed)
+    t = torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * std + mean
+    return t.to(dtype)
+
+
+def sample_index(n, tile):
+    """First, last and one interior index of a few tiles, plus the ends of the range."""
+    idx = {0, 1, tile - 1, tile, n // 2 - 1, n // 2, n - tile, n - 1}
+    for t in range(3, n // tile, max(1, n // tile // 5)):
+        idx.add(t * tile + (7 * t) % tile)
+    return torch.tensor(sorted(i for i in idx if 0 <= i < n), device="cuda")
+
+
+# ---------------------------------------------------------------- GEMM
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("n", [8192, 16384])
+def test_gemm_full_size(n, dtype):
+    from kernelcodegen_b200 import _lib
+    A = dev_randn((n, n), dtype, 900, std=1.0 / np.sqrt(n))
+    B = dev_randn((n, n), dtype, 901)
+    C = ops().matmul(A, B)
+    sync_ok()
+    # (1) oracle on rows from many M tiles x a column stride that visits every N tile
+    rows = sample_index(n, 128)
+    cols = torch.arange(0, n, 37, device="cuda")
+    want = f64(A[rows]) @ f64(B[:, cols])
+    assert rel_fro(C[rows][:, cols], want) <= TOL[dtype]
+    # (2) float64 column checksum over all of C: 1^T C = (1^T A) B
+    colsum = (A.double().sum(0, keepdim=True) @ B.double()).squeeze(0)
+    got = C.double().sum(0)
+    # rounding of n outputs to 8 (bf16) / 11 (fp16) bits averages out in the sum
+    assert float((got - colsum).norm() / colsum.norm()) <= TOL[dtype]
+    # (3) the single-CTA kernel and the CTA-pair kernel accumulate in the same order
+    try:
+        _lib.load().kcg_gemm_set_pair_mode(0)
+        C1 = ops().matmul(A, B)
+        sync_ok()
+    finally:
+        _lib.load().kcg_gemm_set_pair_mode(-1)
+    assert torch.equal(C, C1)
+    # (4) scaling an operand by a power of two scales the result exactly
+    C2 = ops().matmul(A * 2, B)
+    sync_ok()
+    # (fp16 results below the smallest normal, 2^-14, sit on the fixed subnormal grid and are exempt)
+    assert bool(((C2 == C * 2) | (C.abs() < 2.0 ** -13)).all())
+
+
+@pytest.mark.parametrize("n", [8192, 16384])
+def test_gemm_fp8_full_size(n):
+    a32 = dev_randn((n, n), torch.float32, 910, std=1.0 / np.sqrt(n))
+    b32 = dev_randn((n, n), torch.float32, 911)
+    sa = float(a32.abs().max()) / 448.0
+    sb = float(b32.abs().max()) / 448.0
+    A8 = (a32 / sa).to(torch.float8_e4m3fn)
+    B8 = (b32 / sb).to(torch.float8_e4m3fn)
+    del a32, b32
+    sa_t = torch.tensor([sa], device="cuda"); sb_t = torch.tensor([sb], device="cuda")
+    C = ops().matmul(A8, B8, out_dtype=torch.bfloat16, scale_a=sa_t, scale_b=sb_t)
+    sync_ok()
+    rows = sample_index(n, 128)
+    cols = torch.arange(0, n, 37, device="cuda")
+    # decode the very bytes the kernel read with the oracle's own e4m3 decoder
+    av = O.decode_e4m3(A8[rows].view(torch.uint8).cpu().numpy()).astype(np.float64)
+    bv = O.decode_e4m3(B8.view(torch.uint8)[:, cols].cpu().numpy()).astype(np.float64)
+    want = (av @ bv) * (np.float64(np.float32(sa)) * np.float64(np.float32(sb)))
+    assert rel_fro(C[rows][:, cols], want) <= TOL["fp8"]
+    # transposed-B layout on the same data must agree bit for bit (same products, same order)
+    Ct = ops().batched_matmul(A8, B8.t().contiguous(), False, True, out_dtype=torch.bfloat16,
+                              scale_a=sa_t, scale_b=sb_t)
+    sync_ok()
+    assert torch.equal(C, Ct)
+
+
+def test_gemm_sharded_config_slice():
+    # the 8-GPU config's per-GPU share: M = 65536 / 8, N = K = 8192, checked on this rank's rows
+    from kernelcodegen_b200 import shard
+    M, N, K = 65536, 8192, 8192
+    lo, cnt = shard.shard_range(M, 128, world=8, rank=3)
+    hi = lo + cnt
+    assert (lo, hi) == (3 * 8192, 4 * 8192)
+    A = dev_randn((hi - lo, K), torch.bfloat16, 920, std=1.0 / np.sqrt(K))
+    B = dev_randn((K, N), torch.bfloat16, 921)
+    C = ops().matmul(A, B)
+    sync_ok()
+    rows = sample_index(hi - lo, 128)
+    cols = torch.arange(5, N, 41, device="cuda")
+    assert rel_fro(C[rows][:, cols], f64(A[rows]) @ f64(B[:, cols])) <= 1e-2
+
+
+# ---------------------------------------------------------------- FMHA
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("S", [2048, 4096])
+def test_fmha_full_size(S, causal):
+    B, H, D = 8, 32, 128
+    scale = 1.0 / np.sqrt(D)
+    Q, K, V = (dev_randn((B, H, S, D), torch.bfloat16, 930 + i) for i in range(3))
+    out = ops().fmha(Q, K, V, scale, causal)
+    sync_ok()
+    assert out.shape == (B, H, S, D)
+    # (1) whole heads against the float64 oracle
+    for (b, h) in [(0, 0), (5, 13), (7, 31)]:
+        want = O.attention_f64(f64(Q[b:b + 1, h:h + 1]), f64(K[b:b + 1, h:h + 1]), f64(V[b:b + 1, h:h + 1]),
+                               scale, causal)
+        assert rel_fro(out[b:b + 1, h:h + 1], want) <= 1e-2
+    # (2) a head's result does not depend on where it sits in the batch: every (b, h) recomputed
+    #     alone must reproduce the batched bits (same tiles, same order of key blocks)
+    for (b, h) in [(1, 2), (6, 30)]:
+        alone = ops().fmha(Q[b:b + 1, h:h + 1].contiguous(), K[b:b + 1, h:h + 1].contiguous(),
+                           V[b:b + 1, h:h + 1].contiguous(), scale, causal)
+        sync_ok()
+        assert torch.equal(alone[0, 0], out[b, h])
+    # (3) output stored as [B,S,H,D] holds the same bits
+    o2 = ops().fmha(Q, K, V, scale, causal, out_layout="bshd")
+    sync_ok()
+    # (a [B,H,S,D] view over [B,S,H,D] storage)
+    assert o2.shape == (B, H, S, D) and o2.stride() == (S * H * D, D, H * D, 1)
+    assert torch.equal(o2, out)
+
+
+def test_fmha_full_size_replicated_heads_and_unit_rows():
+    # 4 distinct heads tiled over B*H = 256: every copy must give the bits of its original,
+    # which the oracle checks; with V = 1 every softmax row sums to one.
+    B, H, S, D = 8, 32, 4096, 128
+    scale = 1.0 / np.sqrt(D)
+    base = [dev_randn((4, S, D), torch.bfloat16, 940 + i) for i in range(3)]
+    Q, K, V = (t.repeat(B * H // 4, 1, 1).view(B, H, S, D) for t in base)
+    for causal in (False, True):
+        out = ops().fmha(Q, K, V, scale, causal).view(B * H // 4, 4, S, D)
+        sync_ok()
+        assert bool((out == out[0:1]).all())
+        for j in range(4):
+            want = O.attention_f64(f64(base[0][j])[None, None], f64(base[1][j])[None, None],
+                                   f64(base[2][j])[None, None], scale, causal)
+            assert rel_fro(out[0, j][None, None], want) <= 1e-2
+        ones = ops().fmha(Q, K, torch.ones_like(V), scale, causal)
+        sync_ok()
+        # the row sum is accumulated in fp32 from bf16-rounded probabilities
+        assert float((ones.float() - 1.0).abs().max()) <= 2.0 ** -7
+
+
+# ---------------------------------------------------------------- LayerNorm / elementwise
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_bandwidth_config_full(dtype):
+    # x~N(0,1), gamma~N(1,0.1), beta~N(0,0.1), eps 1e-5 on [8192, 4096]; then GELU(tanh) and an add
+    R, Cn = 8192, 4096
+    x = dev_randn((R, Cn), dtype, 950)
+    g = dev_randn((Cn,), dtype, 951, std=0.1, mean=1.0)
+    b = dev_randn((Cn,), dtype, 952, std=0.1)
+    y = ops().layernorm(x, g, b, 1, 1e-5)
+    sync_ok()
+    want = O.layernorm_f64(f64(x), f64(g), f64(b), 1, 1e-5)
+    assert rel_fro(y, want) <= TOL[dtype]
+    z = ops().elementwise(y, "Gelu")
+    sync_ok()
+    assert rel_fro(z, O.unary_f64("Gelu", f64(y))) <= TOL[dtype]
+    w = ops().binary(z, x, "Add")
+    sync_ok()
+    assert rel_fro(w, f64(z) + f64(x)) <= TOL[dtype]
+    if dtype == torch.float32:
+        # bit-exact against the reference-order fp32 loop nests for add
+        assert np.array_equal(w.cpu().numpy(), O.ref32.binary_same("Add", z.cpu().numpy(), x.cpu().numpy(), threads=0))
+    # the fused kernel reproduces the three-kernel chain bit for bit
+    f = ops().layernorm_gelu_add(x, g, b, x, 1e-5)
+    sync_ok()
+    assert torch.equal(f, w)
+
+
+def test_layernorm_sharded_config_slice():
+    # the 8-GPU config's per-GPU share of [262144, 8192]: 32768 rows of 8192
+    R, Cn = 32768, 8192
+    x = dev_randn((R, Cn), torch.bfloat16, 960)
+    g = dev_randn((Cn,), torch.bfloat16, 961, std=0.1, mean=1.0)
+    b = dev_randn((Cn,), torch.bfloat16, 962, std=0.1)
+    y = ops().layernorm(x, g, b, 1, 1e-5)
+    sync_ok()
+    rows = torch.arange(0, R, 257, device="cuda")
+    assert rel_fro(y[rows], O.layernorm_f64(f64(x[rows]), f64(g), f64(b), 1, 1e-5)) <= 1e-2
+    # rows are independent: a permutation of the rows permutes the result
+    perm = torch.randperm(R, device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
+    y2 = ops().layernorm(x[perm].contiguous(), g, b, 1, 1e-5)
+    sync_ok()
+    assert torch.equal(y2, y[perm])
