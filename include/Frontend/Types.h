@@ -65,7 +65,8 @@ struct TensorInfo {
   int alias_of = -1;       // tensor whose storage this one shares (inplace results)
 };
 
-enum class OpKind { Matmul, BatchedMatmul, Softmax, LayerNorm, ElementWise, Binary, FusedAttention, FusedLayerNormGeluAdd };
+enum class OpKind { Matmul, BatchedMatmul, Softmax, LayerNorm, ElementWise, Binary, Gather, Transpose, FusedAttention,
+                    FusedLayerNormGeluAdd };
 
 // One recorded operator call (the reference's func.call); `func` names the per-(op, shape)
 // function it calls (the reference's func.func symbol).

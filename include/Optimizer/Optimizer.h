@@ -47,6 +47,8 @@ KCG_DECLARE_OPTIMIZER(GatherOptimizer, "Gather", gatherConfig);
 KCG_DECLARE_OPTIMIZER(BatchMatmulOptimizer, "BatchMatmul", batchMatmulConfig);
 // Extension: the reference has no stand-alone softmax schedule (softmax only exists fused).
 KCG_DECLARE_OPTIMIZER(SoftmaxOptimizer, "Softmax", softmaxConfig);
+// Extension: Transpose is declared by the reference without a body or a schedule.
+KCG_DECLARE_OPTIMIZER(TransposeOptimizer, "Transpose", transposeConfig);
 
 // Finds BatchMatmul(NT) -> Softmax -> BatchMatmul(NN) chains whose intermediate results have
 // a single user (reference: src/Optimizer/Optimizer.cc:2113-2199) and replaces each by one

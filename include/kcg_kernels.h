@@ -172,6 +172,21 @@ KCG_API int kcg_layernorm_split_static(int dtype, int64_t rows, int64_t cols, co
                                        void* stream);
 
 /*
+ * LayerNorm that also returns the per-row statistics, with optional scale and bias — the
+ * argument list the reference's authors planned for the emitted kernel,
+ * `(X, scale, bias, Y, mean, invStdDev)` (doc/pass.md:789-791, :806-822; the shipped builder
+ * returns Y only, src/Frontend/Operators.cc:1076-1251).  y is computed exactly as by
+ * kcg_layernorm (bit-identical for the same gamma/beta); mean[r] and inv_std[r] are the fp32
+ * row mean and 1/sqrt(var + eps) it used, `rows` values each.  gamma == NULL means a scale of
+ * one, beta == NULL a bias of zero; the library then reads a constant vector that it keeps
+ * per device (allocated and filled, with one stream synchronisation, the first time a call
+ * needs `cols` elements of it).
+ */
+KCG_API int kcg_layernorm_stats(int dtype, int64_t rows, int64_t cols, const void* x,
+                                const void* gamma, const void* beta, float eps, void* y,
+                                float* mean, float* inv_std, void* stream);
+
+/*
  * Tuning switch with no counterpart in the reference: rows of up to 32 * vecs_per_lane
  * 16-byte vectors are normalised by one warp each (no block barrier); longer rows get one
  * thread block each.  Range 0..16, default 8.  Process-wide, not thread-safe.
@@ -304,6 +319,34 @@ KCG_API int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Sk
  * on one build.  Process-wide, not thread-safe.
  */
 KCG_API void kcg_fmha_set_p_in_tmem(int variant);
+
+/*
+ * Gather along one axis — replaces the kernel emitted for
+ * `Gather_{dims}_indices_{dims}_axis_{a}` (builder: src/Frontend/Operators.cc:1253-1352;
+ * schedule: src/Optimizer/Optimizer.cc:1934-2074).
+ *
+ *   The input is viewed as [outer, axis_len, inner] (dims before, at and after `axis`), the
+ *   indices as n_idx values in row-major order: out[o, i, r] = in[o, indices[i], r], an
+ *   [outer, n_idx, inner] tensor (the reference's output shape is the input's with the axis
+ *   replaced by the shape of `indices`, or dropped when `indices` has shape [1]).
+ *   dtype: any kcg_dtype (elements are moved, not interpreted).  index_dtype: KCG_I32 or
+ *   KCG_I64.  A negative index counts from the end of the axis.  An index still out of range
+ *   is not dereferenced: the output slice is zero-filled and kcg_device_status() reports
+ *   KCG_ERR_INVALID_ARG after the stream has been synchronised.
+ */
+KCG_API int kcg_gather(int dtype, int index_dtype, int64_t outer, int64_t axis_len, int64_t inner,
+                       int64_t n_idx, const void* input, const void* indices, void* output,
+                       void* stream);
+
+/*
+ * Transpose of the two innermost dims, out[b, j, i] = in[b, i, j] for a [batch, rows, cols]
+ * input — `Transpose::build(graph, input)` is declared by the reference but its body is empty
+ * (include/Frontend/Operators.h:97-99, src/Frontend/Operators.cc:459-460); this is the meaning
+ * its signature (one operand, no permutation) admits.  dtype: any kcg_dtype.  Input and output
+ * must not alias.
+ */
+KCG_API int kcg_transpose(int dtype, int64_t batch, int64_t rows, int64_t cols, const void* input,
+                          void* output, void* stream);
 
 /*
  * Row-range owned by one rank when `total` independent units (GEMM rows of A/C,

@@ -34,6 +34,7 @@ SIGNATURES = {
     "kcg_layernorm": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _vp], _ci),
     "kcg_layernorm_gelu_add": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _vp, _vp], _ci),
     "kcg_layernorm_split_static": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _vp], _ci),
+    "kcg_layernorm_stats": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _vp], _ci),
     "kcg_layernorm_set_warp_row_limit": ([_ci], None),
     "kcg_eltwise": ([_ci, _ci, _ci, _i64, _vp, _vp, _vp], _ci),
     "kcg_binary": ([_ci, _ci, _ci, _i64p, _ci, _i64p, _vp, _vp, _vp, _vp], _ci),
@@ -46,6 +47,8 @@ SIGNATURES = {
     "kcg_fmha_fwd": ([_ci, _i64, _i64, _i64, _i64, _i64, _fp, _ci, _vp, _i64p, _vp, _i64p, _vp, _i64p, _vp, _i64p,
                       _vp], _ci),
     "kcg_fmha_set_p_in_tmem": ([_ci], None),
+    "kcg_gather": ([_ci, _ci, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp], _ci),
+    "kcg_transpose": ([_ci, _i64, _i64, _i64, _vp, _vp, _vp], _ci),
     "kcg_shard_range": ([_i64, _ci, _ci, _i64, _i64p, _i64p], _ci),
 }
 

@@ -74,7 +74,8 @@ __device__ __forceinline__ uint32_t opaque(uint32_t w) {
 template <typename T, int VPT, bool kExact, bool kFuse, typename Reduce>
 __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __restrict__ gamma,
                                        const T* __restrict__ beta, const T* __restrict__ res, T* __restrict__ yr,
-                                       int tid, int nthr, int nvec, float inv_n, float eps, Reduce reduce) {
+                                       int tid, int nthr, int nvec, float inv_n, float eps, Reduce reduce,
+                                       float* mean_out = nullptr, float* rstd_out = nullptr) {
   using W = Words<T>;
   constexpr int EPW = W::EPW;
   uint4 v[VPT];
@@ -121,6 +122,10 @@ __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __rest
     }
   const float rstd = 1.0f / sqrtf(reduce(q) * inv_n + eps);
   const float shift = -mean * rstd;
+  if (mean_out != nullptr && tid == 0) {  // the row's statistics, when the caller asked for them
+    *mean_out = mean;
+    *rstd_out = rstd;
+  }
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int vi = i * nthr + tid;
@@ -168,26 +173,30 @@ __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __rest
 template <typename T, int VPT, bool kExact, bool kFuse>
 __global__ void __launch_bounds__(128, 5)
 ln_warp_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
-             const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps) {
+             const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps,
+             float* __restrict__ mean_out, float* __restrict__ rstd_out) {
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
   ln_row<T, VPT, kExact, kFuse>(x + row * cols, gamma, beta, kFuse ? res + row * cols : nullptr, y + row * cols, lane, 32,
                                 cols / Vec16<T>::N,
-                         1.0f / static_cast<float>(cols), eps, [](float v) { return warp_sum(v); });
+                         1.0f / static_cast<float>(cols), eps, [](float v) { return warp_sum(v); },
+                         mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr);
 }
 
 // One thread block per row for longer rows: blockDim.x threads hold up to VPT vectors each.
 template <typename T, int VPT, bool kExact, bool kFuse>
 __global__ void __launch_bounds__(512)
 ln_block_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
-              const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps) {
+              const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps,
+              float* __restrict__ mean_out, float* __restrict__ rstd_out) {
   __shared__ float red[33];
   const int64_t row = blockIdx.x;
   ln_row<T, VPT, kExact, kFuse>(x + row * cols, gamma, beta, kFuse ? res + row * cols : nullptr, y + row * cols,
                                 threadIdx.x, blockDim.x,
                          cols / Vec16<T>::N, 1.0f / static_cast<float>(cols), eps,
-                         [&](float v) { return block_sum(v, red); });
+                         [&](float v) { return block_sum(v, red); },
+                         mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr);
 }
 
 // ---- split-row path ----------------------------------------------------------------
@@ -236,7 +245,7 @@ template <typename T>
 __global__ void __launch_bounds__(kChunkThreads)
 ln_chunk_apply(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                const float* __restrict__ stats, T* __restrict__ y, int64_t cols, int chunks,
-               float eps) {
+               float eps, float* __restrict__ mean_out = nullptr, float* __restrict__ rstd_out = nullptr) {
   __shared__ float red[33];
   const int c = blockIdx.x;
   const int64_t row = blockIdx.y;
@@ -257,6 +266,10 @@ ln_chunk_apply(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
     m2 += st[2 * k + 1] + n_c * d * d;
   }
   const float rstd = 1.0f / sqrtf(block_sum(m2, red) / n_all + eps);
+  if (mean_out != nullptr && c == 0 && threadIdx.x == 0) {
+    mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
 
   const int64_t base = static_cast<int64_t>(c) * kChunk;
   const int len = static_cast<int>(min(static_cast<int64_t>(kChunk), cols - base));
@@ -276,7 +289,8 @@ ln_chunk_apply(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
 
 template <typename T>
 int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* beta, float eps,
-              T* y, cudaStream_t stream, const T* res = nullptr) {
+              T* y, cudaStream_t stream, const T* res = nullptr, float* mean_out = nullptr,
+              float* rstd_out = nullptr) {
   // res != nullptr: y = gelu(layernorm(x)) + res in one pass (row kernels only; the caller
   // falls back to three launches when the row kernels do not apply).
   constexpr int VW = Vec16<T>::N;
@@ -288,7 +302,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
   if (vec_ok && nvec <= 32 * g_warp_row_max_vecs) {
     const unsigned grid = static_cast<unsigned>((rows + 3) / 4);
     const int vpt = static_cast<int>((nvec + 31) / 32);
-#define KCG_LN_LAUNCH(V, E, F) ln_warp_rows<T, V, E, F><<<grid, 128, 0, stream>>>(x, gamma, beta, res, y, rows, icols, eps)
+#define KCG_LN_LAUNCH(V, E, F) ln_warp_rows<T, V, E, F><<<grid, 128, 0, stream>>>(x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
 #define KCG_LN_WARP(V)                                                          \
   do {                                                                          \
     const bool exact = nvec == 32 * V;                                          \
@@ -310,7 +324,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
     threads = (threads + 31) / 32 * 32;
     const int vpt = static_cast<int>((nvec + threads - 1) / threads);
     const unsigned grid = static_cast<unsigned>(rows);
-#define KCG_LN_LAUNCH(V, E, F) ln_block_rows<T, V, E, F><<<grid, threads, 0, stream>>>(x, gamma, beta, res, y, rows, icols, eps)
+#define KCG_LN_LAUNCH(V, E, F) ln_block_rows<T, V, E, F><<<grid, threads, 0, stream>>>(x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
 #define KCG_LN_BLOCK(V)                                                         \
   do {                                                                          \
     const bool exact = nvec == static_cast<int64_t>(threads) * V;               \
@@ -340,7 +354,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
   ln_chunk_stats<T><<<grid, kChunkThreads, 0, stream>>>(x, stats, cols, chunks);
   int rc = check_launch("ln_chunk_stats");
   if (rc) return rc;
-  ln_chunk_apply<T><<<grid, kChunkThreads, 0, stream>>>(x, gamma, beta, stats, y, cols, chunks, eps);
+  ln_chunk_apply<T><<<grid, kChunkThreads, 0, stream>>>(x, gamma, beta, stats, y, cols, chunks, eps, mean_out, rstd_out);
   return check_launch("ln_chunk_apply");
 }
 
@@ -498,5 +512,73 @@ extern "C" int kcg_layernorm(int dtype, int64_t rows, int64_t cols, const void* 
                                eps, static_cast<__half*>(y), s);
     default:
       return fail(KCG_ERR_UNSUPPORTED, "layernorm: dtype %d has no kernel (float32, bfloat16, float16)", dtype);
+  }
+}
+
+// ---- LayerNorm that also returns the row statistics, with optional scale / bias -----------
+namespace kcg {
+namespace {
+
+template <typename T>
+__global__ void fill_const(T* p, int64_t n, float value) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = Conv<T>::from_f(value);
+}
+
+// A vector of `n` ones (slot 0) or zeros (slot 1) of element size sizeof(T), kept per device
+// and grown on demand; stands in for an absent scale / bias operand so that the row kernels
+// keep a single code path.  Its contents never change once written.
+struct ConstVec { void* ptr = nullptr; int64_t n = 0; };
+ConstVec g_const_vec[kStaticMaxDevices][3][2];
+std::mutex g_const_mutex;
+
+template <typename T>
+const T* const_vector(int dtype_slot, int which, int64_t n, cudaStream_t stream) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_const_mutex);
+  ConstVec& cv = g_const_vec[dev][dtype_slot][which];
+  if (cv.n < n) {
+    if (cv.ptr) cudaFree(cv.ptr);  // waits for kernels that still read the old vector
+    cv.ptr = nullptr; cv.n = 0;
+    const int64_t cap = (n + 4095) / 4096 * 4096;
+    if (cudaMalloc(&cv.ptr, static_cast<size_t>(cap) * sizeof(T)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    fill_const<T><<<static_cast<unsigned>((cap + 255) / 256), 256, 0, stream>>>(static_cast<T*>(cv.ptr), cap, which == 0 ? 1.f : 0.f);
+    // later calls may use other streams: make the fill visible to all of them now
+    if (cudaStreamSynchronize(stream) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    cv.n = cap;
+  }
+  return static_cast<const T*>(cv.ptr);
+}
+
+template <typename T>
+int layernorm_stats_t(int slot, int64_t rows, int64_t cols, const void* x, const void* gamma, const void* beta,
+                      float eps, void* y, float* mean, float* inv_std, cudaStream_t s) {
+  const T* g = static_cast<const T*>(gamma);
+  const T* b = static_cast<const T*>(beta);
+  if (!g) g = const_vector<T>(slot, 0, cols, s);
+  if (!b) b = const_vector<T>(slot, 1, cols, s);
+  if (!g || !b) return fail(KCG_ERR_CUDA, "layernorm_stats: could not allocate the default scale / bias vector");
+  return launch_ln<T>(rows, cols, static_cast<const T*>(x), g, b, eps, static_cast<T*>(y), s, nullptr, mean, inv_std);
+}
+
+}  // namespace
+}  // namespace kcg
+
+extern "C" int kcg_layernorm_stats(int dtype, int64_t rows, int64_t cols, const void* x, const void* gamma,
+                                   const void* beta, float eps, void* y, float* mean, float* inv_std,
+                                   void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (rows < 0 || cols < 0) return fail(KCG_ERR_INVALID_ARG, "layernorm_stats: negative size");
+  if (rows == 0 || cols == 0) return KCG_OK;
+  if (!x || !y || !mean || !inv_std) return fail(KCG_ERR_INVALID_ARG, "layernorm_stats: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case KCG_F32: return layernorm_stats_t<float>(0, rows, cols, x, gamma, beta, eps, y, mean, inv_std, s);
+    case KCG_BF16: return layernorm_stats_t<__nv_bfloat16>(1, rows, cols, x, gamma, beta, eps, y, mean, inv_std, s);
+    case KCG_F16: return layernorm_stats_t<__half>(2, rows, cols, x, gamma, beta, eps, y, mean, inv_std, s);
+    default:
+      return fail(KCG_ERR_UNSUPPORTED, "layernorm_stats: dtype %d has no kernel (float32, bfloat16, float16)", dtype);
   }
 }

@@ -22,6 +22,8 @@ const char* entry_for(OpKind k) {
     case OpKind::LayerNorm: return "kcg_layernorm";
     case OpKind::ElementWise: return "kcg_eltwise";
     case OpKind::Binary: return "kcg_binary";
+    case OpKind::Gather: return "kcg_gather";
+    case OpKind::Transpose: return "kcg_transpose";
     case OpKind::FusedAttention: return "kcg_fmha_fwd";
     case OpKind::FusedLayerNormGeluAdd: return "kcg_layernorm_gelu_add";
   }
@@ -76,7 +78,7 @@ KernelCodeGenerator::KernelCodeGenerator(const std::string& platform_) : platfor
   binaryConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
   elementWiseConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
   layerNormConfigs = {{{"WARP_ROW_VECS", 8}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}}};
-  gatherConfigs = {};
+  gatherConfigs = {{{"BLOCK_SIZE", 256}, {"VECTORIZE_WIDTH", 16}}};
   softmaxConfigs = {{{"BLOCK_SIZE", 256}}};
   fusionConfigs = {{{"EPILOGUE", 1}}};
   fmhaConfigs = {{{"BLOCK_SIZE", 192}, {"Br", 128}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}}};
@@ -298,6 +300,22 @@ int KernelCodeGenerator::run(Module& module, const Bindings& bindings, void* str
         rc = kcg_binary(index_of(Binary::operations(), op.operation), static_cast<int>(t0.dtype),
                         static_cast<int>(sa.size()), sa.data(), static_cast<int>(sb.size()), sb.data(), in[0], in[1], out,
                         stream);
+        break;
+      }
+      case OpKind::Gather: {
+        const auto& ti = g.tensors[op.inputs[1]];
+        int64_t outer = 1, inner = 1;
+        for (int64_t d = 0; d < op.axis; ++d) outer *= t0.shape[d];
+        for (size_t d = op.axis + 1; d < t0.shape.size(); ++d) inner *= t0.shape[d];
+        rc = kcg_gather(static_cast<int>(t0.dtype), static_cast<int>(ti.dtype), outer, t0.shape[op.axis], inner,
+                        numel(op.inputs[1]), in[0], in[1], out, stream);
+        break;
+      }
+      case OpKind::Transpose: {
+        const size_t r = t0.shape.size();
+        const int64_t rows = t0.shape[r - 2], cols = t0.shape[r - 1];
+        const int64_t batch = (rows != 0 && cols != 0) ? numel(op.inputs[0]) / (rows * cols) : 0;
+        rc = kcg_transpose(static_cast<int>(t0.dtype), batch, rows, cols, in[0], out, stream);
         break;
       }
       case OpKind::FusedLayerNormGeluAdd: {

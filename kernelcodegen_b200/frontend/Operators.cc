@@ -317,11 +317,22 @@ Value Softmax::build(ComputeDAG* graph, Value input, int axis, MemorySpace, cons
   return add_op(graph, node, input.shape(), input.dtype(), MemorySpace::inplace, input.id);
 }
 
+// The reference declares Transpose with one operand and leaves the body empty
+// (Operators.h:97-99, Operators.cc:459-460); here it swaps the two innermost dims.
 Value Transpose::build(ComputeDAG* graph, Value input) {
-  (void)graph;
-  (void)input;
-  std::cerr << "Transpose has no definition in the reference (empty body); nothing is built.\n";
-  return {};
+  if (!valid(graph, input, "Type of operand of Transpose is not Memref.\n")) return {};
+  const auto& in = input.shape();
+  if (in.size() < 2) {
+    std::cerr << "Transpose takes an operand of rank 2 or more.\n";
+    return {};
+  }
+  std::vector<int64_t> out = in;
+  std::swap(out[out.size() - 1], out[out.size() - 2]);
+  OpNode node;
+  node.kind = OpKind::Transpose;
+  node.func = "Transpose" + dims(in);
+  node.inputs = {input.id};
+  return add_op(graph, node, out, input.dtype(), MemorySpace::global, -1);
 }
 
 // ---- Binary (reference: Operators.cc:772-889) ---------------------------------------------------
@@ -448,10 +459,41 @@ Value LayerNorm::build(ComputeDAG* graph, Value input, Value scale, Value bias, 
   return add_op(graph, node, in, input.dtype(), ms, ms == MemorySpace::inplace ? input.id : -1);
 }
 
+// ---- Gather (reference: Operators.cc:1253-1352) ------------------------------------------------------
 Value Gather::build(ComputeDAG* graph, Value input, Value indices, const std::int64_t& axis, const std::string& dtype_) {
-  (void)graph; (void)input; (void)indices; (void)axis; (void)dtype_;
-  std::cerr << "Gather is not part of the accelerated operator set; nothing is built.\n";
-  return {};
+  if (!valid(graph, input, "Type of operand of Gather is not Memref.\n")) return {};
+  if (!valid(graph, indices, "Type of operand of Gather is not Memref.\n")) return {};
+  const auto& in = input.shape();
+  const auto& idx = indices.shape();
+  if (axis < 0 || axis >= static_cast<int64_t>(in.size())) {
+    std::cerr << "Can't apply Gather Operation due to axis is greater than shape of input.\n";
+    return {};
+  }
+  if (indices.dtype() != DType::i32 && indices.dtype() != DType::i64) {
+    std::cerr << "Gather: indices must be int32 or int64 (index).\n";
+    return {};
+  }
+  DType dt;
+  if (!resolve_dtype(dtype_, input.dtype(), dt, "Gather")) return {};
+  if (dt != input.dtype()) {
+    std::cerr << "Gather moves elements; it cannot change the element type.\n";
+    return {};
+  }
+  // the axis is erased and, unless the indices are a single [1] vector, their dims take its place
+  std::vector<int64_t> out = in;
+  out.erase(out.begin() + axis);
+  if (!(idx.size() == 1 && idx[0] == 1)) out.insert(out.begin() + axis, idx.begin(), idx.end());
+  OpNode node;
+  node.kind = OpKind::Gather;
+  std::string name = "Gather";
+  for (auto d : in) name += "_" + std::to_string(d);
+  name += "_indices";
+  for (auto d : idx) name += "_" + std::to_string(d);
+  name += "_axis_" + std::to_string(axis);
+  node.func = name;
+  node.inputs = {input.id, indices.id};
+  node.axis = axis;
+  return add_op(graph, node, out, input.dtype(), MemorySpace::global, -1);
 }
 
 }  // namespace KernelCodeGen

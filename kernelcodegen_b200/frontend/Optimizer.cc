@@ -14,6 +14,7 @@ std::map<std::string, int> BinaryOptimizer::binaryConfig;
 std::map<std::string, int> ElementWiseOptimizer::elementWiseConfig;
 std::map<std::string, int> LayerNormOptimizer::layerNormConfig;
 std::map<std::string, int> GatherOptimizer::gatherConfig;
+std::map<std::string, int> TransposeOptimizer::transposeConfig;
 std::map<std::string, int> BatchMatmulOptimizer::batchMatmulConfig;
 std::map<std::string, int> SoftmaxOptimizer::softmaxConfig;
 
@@ -50,11 +51,9 @@ KCG_SIMPLE_OPTIMIZER(ElementWiseOptimizer, "Elementwise", "", elementWiseConfig)
 KCG_SIMPLE_OPTIMIZER(LayerNormOptimizer, "LayerNorm", "", layerNormConfig)
 KCG_SIMPLE_OPTIMIZER(BatchMatmulOptimizer, "BatchMatmul", "", batchMatmulConfig)
 KCG_SIMPLE_OPTIMIZER(SoftmaxOptimizer, "Softmax", "", softmaxConfig)
+KCG_SIMPLE_OPTIMIZER(GatherOptimizer, "Gather", "", gatherConfig)
+KCG_SIMPLE_OPTIMIZER(TransposeOptimizer, "Transpose", "", transposeConfig)
 #undef KCG_SIMPLE_OPTIMIZER
-
-// No Gather kernel exists in this library, so there is never anything to select.
-bool GatherOptimizer::applicable(Module&) { return false; }
-void GatherOptimizer::applyOptimzer(Module&, OpBuilder&) {}
 
 bool FMHAOptimizer::applicable(Module& module) {
   chains.clear();

@@ -4,8 +4,8 @@ Names and argument meaning follow the reference's operator builders
 (include/Frontend/Operators.h:75-133): ``matmul`` (Matmul), ``batched_matmul``
 (BatchedMatmul with Layout flags), ``softmax``, ``layernorm`` (axis, eps), ``elementwise``
 ("Tanh" | "Sqrt" | "Log" | "Relu" | "Cast" | "Gelu"), ``relu``, ``binary`` ("Add" | "Mul" |
-"Div" | "Sub" | "Pow" | "Equal" | "Greater") and ``fmha`` for the fused
-BatchedMatmul -> Softmax -> BatchedMatmul chain.  torch only supplies device memory and
+"Div" | "Sub" | "Pow" | "Equal" | "Greater"), ``gather``, ``transpose`` and ``fmha`` for the
+fused BatchedMatmul -> Softmax -> BatchedMatmul chain.  torch only supplies device memory and
 the current stream; every computation is a call through the C ABI into the sm_100a
 kernels, and there is no fallback path.
 """
@@ -88,6 +88,34 @@ def layernorm(x, scale, bias, axis: int, eps: float = 1e-5, inplace: bool = Fals
     check(_lib.load().kcg_layernorm(_dt(x), rows, cols, x.data_ptr(), scale.data_ptr(), bias.data_ptr(),
                                     float(eps), y.data_ptr(), _stream()), "kcg_layernorm")
     return y
+
+
+def layernorm_with_stats(x, scale, bias, axis: int, eps: float = 1e-5, out=None):
+    """(Y, mean, invStdDev): LayerNorm over dims [axis..] that also returns the fp32 row mean and
+    1/sqrt(var + eps), shaped like x with the normalised dims removed — the result tuple the
+    reference's design notes plan (doc/pass.md:789-791).  ``scale`` / ``bias`` may be None."""
+    _need_cuda(x, *[t for t in (scale, bias) if t is not None])
+    nd = x.dim()
+    if axis >= nd or axis <= -nd:
+        raise ValueError("axis is out of bounds for array of dimension.")
+    if axis < 0:
+        axis += nd
+    norm_shape = tuple(x.shape[axis:])
+    cols = math.prod(norm_shape)
+    rows = x.numel() // cols if cols else 0
+    if scale is not None and tuple(scale.shape) != norm_shape:
+        scale = scale.expand(norm_shape).contiguous()
+    if bias is not None and tuple(bias.shape) != norm_shape:
+        bias = bias.expand(norm_shape).contiguous()
+    y = out if out is not None else torch.empty_like(x)
+    mean = torch.empty(tuple(x.shape[:axis]), dtype=torch.float32, device=x.device)
+    inv_std = torch.empty_like(mean)
+    check(_lib.load().kcg_layernorm_stats(_dt(x), rows, cols, x.data_ptr(),
+                                          scale.data_ptr() if scale is not None else None,
+                                          bias.data_ptr() if bias is not None else None,
+                                          float(eps), y.data_ptr(), mean.data_ptr(), inv_std.data_ptr(), _stream()),
+          "kcg_layernorm_stats")
+    return y, mean, inv_std
 
 
 def layernorm_gelu_add(x, scale, bias, residual, eps: float = 1e-5, out=None):
@@ -207,6 +235,50 @@ def matmul(A, B, out_dtype=None, scale_a=None, scale_b=None, out=None, bias=None
     if A.shape[1] != B.shape[0]:
         raise ValueError("Can't apply Matmul Operation due to imcompatible K-dim.")
     return batched_matmul(A, B, False, False, out_dtype, scale_a, scale_b, out, bias, activation)
+
+
+_ESIZE_DT = {1: _lib.BOOL, 2: _lib.I16, 4: _lib.I32, 8: _lib.I64}
+
+
+def _move_dt(t: torch.Tensor) -> int:
+    """dtype code for kernels that move elements without interpreting them."""
+    return _DT.get(t.dtype, _ESIZE_DT[t.element_size()])
+
+
+def gather(x, indices, axis: int = 0, out=None):
+    """out = take(x, indices, axis) (reference: Gather::build, Operators.cc:1253-1352): the dim
+    ``axis`` of x is replaced by the shape of ``indices`` — or dropped when ``indices`` has
+    shape [1], as the reference does."""
+    _need_cuda(x, indices)
+    if indices.dtype not in (torch.int32, torch.int64):
+        raise TypeError("gather: indices must be int32 or int64")
+    if axis >= x.dim() or axis < 0:
+        raise ValueError("Can't apply Gather Operation due to axis is greater than shape of input.")
+    outer = math.prod(x.shape[:axis])
+    inner = math.prod(x.shape[axis + 1:])
+    idx_shape = () if tuple(indices.shape) == (1,) else tuple(indices.shape)
+    shape = tuple(x.shape[:axis]) + idx_shape + tuple(x.shape[axis + 1:])
+    if out is None:
+        out = torch.empty(shape, dtype=x.dtype, device=x.device)
+    check(_lib.load().kcg_gather(_move_dt(x), _lib.I32 if indices.dtype == torch.int32 else _lib.I64, outer,
+                                 x.shape[axis], inner, indices.numel(), x.data_ptr(), indices.data_ptr(),
+                                 out.data_ptr(), _stream()), "kcg_gather")
+    return out
+
+
+def transpose(x, out=None):
+    """Swap the two innermost dims (reference: Transpose::build is declared with a single operand
+    and an empty body, Operators.h:97-99)."""
+    _need_cuda(x)
+    if x.dim() < 2:
+        raise ValueError("Transpose takes an operand of rank 2 or more")
+    r, c = x.shape[-2], x.shape[-1]
+    batch = math.prod(x.shape[:-2])
+    if out is None:
+        out = torch.empty(tuple(x.shape[:-2]) + (c, r), dtype=x.dtype, device=x.device)
+    check(_lib.load().kcg_transpose(_move_dt(x), batch, r, c, x.data_ptr(), out.data_ptr(), _stream()),
+          "kcg_transpose")
+    return out
 
 
 def fmha(Q, K, V, softmax_scale: float = 1.0, causal: bool = False, out_layout: str = "bhsd", out=None):

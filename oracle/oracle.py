@@ -209,6 +209,59 @@ def layernorm_f64(x, gamma, beta, axis, eps=1e-5):
     return np.asarray(gamma, np.float64) * (d / np.sqrt(var + np.float64(np.float32(eps)))) + np.asarray(beta, np.float64)
 
 
+def layernorm_stats_f64(x, axis, eps=1e-5):
+    """(mean, invStdDev) of the same statistics layernorm_f64 uses, with the normalised dims
+    removed (the extra results the reference's notes plan, doc/pass.md:789-791)."""
+    x = np.asarray(x, np.float64)
+    axis = axis + x.ndim if axis < 0 else axis
+    ax = tuple(range(axis, x.ndim))
+    mean = x.mean(axis=ax)
+    d = x - x.mean(axis=ax, keepdims=True)
+    var = (d * d).mean(axis=ax)
+    return mean, 1.0 / np.sqrt(var + np.float64(np.float32(eps)))
+
+
+def gather_shape(in_shape, idx_shape, axis):
+    """Operators.cc:1286-1293: the axis is erased, then the index dims are inserted there unless
+    the indices are a single [1] vector."""
+    shape = list(in_shape)
+    del shape[axis]
+    if tuple(idx_shape) != (1,):
+        shape[axis:axis] = list(idx_shape)
+    return tuple(shape)
+
+
+def gather_nest(x, indices, axis):
+    """The reference's loop nest, literally (Operators.cc:1320-1340): one iteration per output
+    element; the output's index dims select indices[...], which replaces them in the input index.
+    Pure-Python loops: small cases only."""
+    x = np.asarray(x); indices = np.asarray(indices)
+    single = tuple(indices.shape) == (1,)
+    out = np.empty(gather_shape(x.shape, indices.shape, axis), x.dtype)
+    for ivs in np.ndindex(*out.shape):
+        if single:
+            k = int(indices[0])
+            src = list(ivs)
+        else:
+            k = int(indices[tuple(ivs[axis:axis + indices.ndim])])
+            src = list(ivs[:axis]) + list(ivs[axis + indices.ndim:])
+        src.insert(axis, k)
+        out[ivs] = x[tuple(src)]
+    return out
+
+
+def gather_take(x, indices, axis):
+    """numpy formulation of the same operator, for sizes the loop nest cannot do in seconds."""
+    x = np.asarray(x); indices = np.asarray(indices)
+    out = np.take(x, indices, axis=axis)
+    return out.reshape(gather_shape(x.shape, indices.shape, axis))
+
+
+def transpose_last2(x):
+    """out[..., j, i] = in[..., i, j] (Transpose has a declaration only, Operators.h:97-99)."""
+    return np.ascontiguousarray(np.swapaxes(np.asarray(x), -1, -2))
+
+
 def unary_f64(op, x):
     """Operators.cc:960-995; Gelu uses the reference's literal fp32 constants."""
     x = np.asarray(x, np.float64)

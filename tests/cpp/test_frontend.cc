@@ -190,6 +190,33 @@ static void test_kernel_fusion() {
   for (const auto& kv : module.graph->funcs) CHECK(kv.second.state == "gpu");
 }
 
+static void test_gather_transpose_graph() {  // test/test.cc:17-23 (the commented Gather sequence)
+  KernelCodeGenerator generator("CUDA");
+  generator.opts.push_back(std::make_unique<GatherOptimizer>());
+  generator.opts.push_back(std::make_unique<TransposeOptimizer>());
+  auto graph = generator.createGraph("gather_demo");
+  auto A = graph.create<PlaceHolder>(std::vector<int64_t>{4, 9, 6}, std::string{"float32"});
+  auto idx = graph.create<PlaceHolder>(std::vector<int64_t>{3, 2}, std::string{"int64"});
+  auto one = graph.create<PlaceHolder>(std::vector<int64_t>{1}, std::string{"int32"});
+  int64_t axis = 1;
+  auto G = graph.create<Gather>(A, idx, axis);
+  auto G1 = graph.create<Gather>(A, one, axis);
+  auto G0 = graph.create<Gather>(A, idx);                   // axis defaults to 0
+  auto T = graph.create<Transpose>(G);
+  CHECK(bool(G) && G.shape() == (std::vector<int64_t>{4, 3, 2, 6}));
+  CHECK(bool(G1) && G1.shape() == (std::vector<int64_t>{4, 6}));   // a [1] index drops the axis
+  CHECK(bool(G0) && G0.shape() == (std::vector<int64_t>{3, 2, 9, 6}));
+  CHECK(bool(T) && T.shape() == (std::vector<int64_t>{4, 3, 6, 2}));
+  const auto& f = graph.data->funcs;
+  CHECK(f.count("Gather_4_9_6_indices_3_2_axis_1") && f.count("Gather_4_9_6_indices_1_axis_1"));
+  CHECK(f.count("Transpose_4_3_2_6"));
+  auto module = generator.optimize(graph);
+  for (const auto& kv : module.graph->funcs) CHECK(kv.second.state == "gpu");
+  CHECK(module.graph->funcs.at("Gather_4_9_6_indices_3_2_axis_1").optimizer == "Gather");
+  auto plan = generator.codegen(module);
+  CHECK(has(plan, "launch kcg_gather") && has(plan, "launch kcg_transpose"));
+}
+
 static void test_errors() {
   KernelCodeGenerator generator("CUDA");
   auto graph = generator.createGraph("errors");
@@ -203,8 +230,11 @@ static void test_errors() {
   CHECK(!graph.create<Softmax>(A, 0));                      // only the last dim
   CHECK(!graph.create<PlaceHolder>(std::vector<int64_t>{4}, std::string{"complex64"}));
   CHECK(!graph.create<Matmul>(Value{}, B));                 // null operand
-  CHECK(!graph.create<Transpose>(A));
-  CHECK(!graph.create<Gather>(A, A));
+  auto V1 = graph.create<PlaceHolder>(std::vector<int64_t>{7}, std::string{"float32"});
+  CHECK(!graph.create<Transpose>(V1));                      // rank below 2
+  CHECK(!graph.create<Gather>(A, A));                       // indices must be integers
+  auto I1 = graph.create<PlaceHolder>(std::vector<int64_t>{3}, std::string{"int64"});
+  CHECK(!graph.create<Gather>(A, I1, int64_t(2)));          // axis past the input's rank
   CHECK(getDType("bfloat16") == DType::bf16 && getDType("float8_e4m3") == DType::f8e4m3 && toStr(DType::f16) == "float16");
   // run() refuses functions no optimizer selected, and unbound tensors
   auto C = graph.create<ElementWise>(A, "Gelu", MemorySpace::global);
@@ -429,6 +459,40 @@ static void gpu_fused_attention() {  // BatchedMatmul -> Softmax -> BatchedMatmu
   CHECK(rel_fro(got, want) <= 1e-2);
 }
 
+static void gpu_gather_transpose() {  // embedding-style row gather, then a transpose, fp32
+  KernelCodeGenerator generator("CUDA");
+  generator.opts.push_back(std::make_unique<GatherOptimizer>());
+  generator.opts.push_back(std::make_unique<TransposeOptimizer>());
+  auto graph = generator.createGraph("gather_run");
+  const int rows = 300, cols = 72, n = 129;
+  auto A = graph.create<PlaceHolder>(std::vector<int64_t>{rows, cols}, std::string{"float32"});
+  auto I = graph.create<PlaceHolder>(std::vector<int64_t>{n}, std::string{"int32"});
+  auto G = graph.create<Gather>(A, I);
+  auto T = graph.create<Transpose>(G);
+  auto module = generator.optimize(graph);
+  auto hA = randn(size_t(rows) * cols, 31);
+  std::vector<int32_t> hI(n);
+  for (int i = 0; i < n; ++i) hI[i] = (i * 37 + 11) % rows;
+  void* dG = upload(nullptr, size_t(n) * cols * 4);
+  void* dT = upload(nullptr, size_t(n) * cols * 4);
+  Bindings bind;
+  bind.set(A, upload(hA.data(), hA.size() * 4));
+  bind.set(I, upload(hI.data(), hI.size() * 4));
+  bind.set(G, dG);
+  bind.set(T, dT);
+  CHECK(generator.run(module, bind) == KCG_OK);
+  cudaDeviceSynchronize();
+  CHECK(kcg_device_status() == KCG_OK);
+  auto g = download(dG, size_t(n) * cols), t = download(dT, size_t(n) * cols);
+  bool ok = true;
+  for (int i = 0; i < n && ok; ++i)
+    for (int c = 0; c < cols; ++c) {
+      const float want = hA[size_t(hI[i]) * cols + c];   // the reference's loop nest, Operators.cc:1320-1340
+      if (g[size_t(i) * cols + c] != want || t[size_t(c) * n + i] != want) { ok = false; break; }
+    }
+  CHECK(ok);
+}
+
 int main(int argc, char** argv) {
   const std::string mode = argc > 1 ? argv[1] : "cpu";
   if (mode == "cpu") {
@@ -436,12 +500,14 @@ int main(int argc, char** argv) {
     test_commented_sequences();
     test_flash_attention_graph();
     test_kernel_fusion();
+    test_gather_transpose_graph();
     test_errors();
   } else {
     gpu_matmul_relu();
     gpu_layernorm_gelu_add();
     gpu_kernel_fusion();
     gpu_fused_attention();
+    gpu_gather_transpose();
   }
   if (failures) {
     std::fprintf(stderr, "%d check(s) failed\n", failures);

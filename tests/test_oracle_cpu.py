@@ -127,3 +127,29 @@ def test_threads_do_not_change_results():
     x = randn((32, 100), torch.float32, 22).numpy()
     g = np.ones(100, np.float32); b = np.zeros(100, np.float32)
     assert np.array_equal(O.ref32.layernorm(x, g, b, 1, threads=1), O.ref32.layernorm(x, g, b, 1, threads=4))
+
+
+def test_gather_loop_nest_against_numpy_take():
+    rng = np.random.default_rng(77)
+    for shape, idx_shape, axis in [((5, 4), (3,), 0), ((5, 4), (3,), 1), ((3, 6, 2), (2, 2), 1), ((3, 6, 2), (1,), 1),
+                                   ((2, 3, 4), (5,), 2)]:
+        x = rng.standard_normal(shape).astype(np.float32)
+        idx = rng.integers(0, shape[axis], idx_shape)
+        a, b = O.gather_nest(x, idx, axis), O.gather_take(x, idx, axis)
+        assert a.shape == b.shape == O.gather_shape(shape, idx_shape, axis)
+        assert np.array_equal(a, b)
+    # the reference's shape rule: a [1] index vector drops the axis, any other shape replaces it
+    assert O.gather_shape((4, 9, 6), (1,), 1) == (4, 6)
+    assert O.gather_shape((4, 9, 6), (3, 2), 1) == (4, 3, 2, 6)
+    assert O.gather_shape((4, 9, 6), (1, 1), 1) == (4, 1, 1, 6)
+
+
+def test_layernorm_stats_consistent_with_layernorm():
+    rng = np.random.default_rng(78)
+    x = rng.standard_normal((6, 5, 40)) * 3 + 1
+    g = rng.standard_normal((5, 40)); b = rng.standard_normal((5, 40))
+    mean, rstd = O.layernorm_stats_f64(x, 1, 1e-5)
+    assert mean.shape == rstd.shape == (6,)
+    y = g * ((x - mean[:, None, None]) * rstd[:, None, None]) + b
+    assert O.rel_fro(y, O.layernorm_f64(x, g, b, 1, 1e-5)) < 1e-14
+    assert np.array_equal(O.transpose_last2(np.arange(6).reshape(1, 2, 3)), np.array([[[0, 3], [1, 4], [2, 5]]]))
