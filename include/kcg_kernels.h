@@ -349,6 +349,40 @@ KCG_API int kcg_transpose(int dtype, int64_t batch, int64_t rows, int64_t cols, 
                           void* output, void* stream);
 
 /*
+ * GEMM with the all-gather of C done by its epilogue (no counterpart in the reference, which
+ * has no multi-GPU code; the sharding is the one kcg_shard_range describes).  Rank `rank` of
+ * `world` (<= 8) computes its M x N block C = op(A) op(B) exactly as kcg_gemm_fused would
+ * (same kernel, same bits) and stores every tile into rows [row_offset, row_offset + M) of
+ * each of the `world` gathered matrices gathered[r] (leading dimension ldc, `N` columns used):
+ * gathered[rank] is this GPU's own buffer, the others are the peers' buffers mapped into this
+ * process (kcg_peer_open).  Stores to peers are whole 128-byte row segments written straight
+ * from the epilogue, so the transfer overlaps the tensor-core work of the following tiles.
+ * The call only launches; the rows written by the other ranks are complete once every rank's
+ * launch has finished (synchronise the ranks, e.g. with a barrier on the stream, before reading
+ * and before the next call overwrites the buffers).  Tensor-core input dtypes only, M > 128,
+ * 16-byte aligned pointers / ldc / N.
+ */
+KCG_API int kcg_gemm_allgather(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K,
+                               int trans_a, int trans_b, const void* A, int64_t lda,
+                               const void* B, int64_t ldb, void* const* gathered, int world,
+                               int rank, int64_t row_offset, int64_t ldc, const float* scale_a,
+                               const float* scale_b, const void* bias, int activation,
+                               void* stream);
+
+/*
+ * Device memory that other processes on the node can map (CUDA IPC).  kcg_peer_alloc returns a
+ * plain device allocation; kcg_peer_export fills a 64-byte handle that another process passes
+ * to kcg_peer_open to obtain a pointer valid on its own GPU (peer access is enabled on first
+ * use; loads and stores through it cross NVLink).  Close every opened pointer before the owner
+ * frees the allocation.
+ */
+KCG_API int kcg_peer_alloc(size_t bytes, void** ptr);
+KCG_API int kcg_peer_free(void* ptr);
+KCG_API int kcg_peer_export(void* ptr, unsigned char handle[64]);
+KCG_API int kcg_peer_open(const unsigned char handle[64], void** ptr);
+KCG_API int kcg_peer_close(void* ptr);
+
+/*
  * Row-range owned by one rank when `total` independent units (GEMM rows of A/C,
  * attention batch*head slices, LayerNorm / elementwise rows) are split over
  * `world` GPUs in contiguous blocks rounded to `granule` units.  The reference

@@ -10,7 +10,8 @@ int sgemm_f32(int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a, int t
 int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
                  int trans_b, const void* A, int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
                  int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
-                 const float* scale_b, const void* bias, int act, cudaStream_t stream);
+                 const float* scale_b, const void* bias, int act, cudaStream_t stream, void* const* extra_c = nullptr,
+                 int n_extra = 0);
 }  // namespace kcg
 
 extern "C" int kcg_gemm(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch,
@@ -50,4 +51,41 @@ extern "C" int kcg_gemm_fused(int dtype_in, int dtype_out, int64_t M, int64_t N,
     return gemm_tcgen05(dtype_in, dtype_out, M, N, K, batch, trans_a, trans_b, A, lda, stride_a, B, ldb,
                         stride_b, C, ldc, stride_c, scale_a, scale_b, bias, activation, s);
   return fail(KCG_ERR_UNSUPPORTED, "gemm: input dtype %d has no kernel", dtype_in);
+}
+
+// GEMM whose epilogue also performs the all-gather of C: every output tile is stored into
+// this rank's row block of each rank's gathered matrix (gathered[r], r < world), the local one
+// included, with plain stores — to peer GPUs through their mapped memory.
+extern "C" int kcg_gemm_allgather(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int trans_a,
+                                  int trans_b, const void* A, int64_t lda, const void* B, int64_t ldb,
+                                  void* const* gathered, int world, int rank, int64_t row_offset, int64_t ldc,
+                                  const float* scale_a, const float* scale_b, const void* bias, int activation,
+                                  void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (world < 1 || world > 8 || rank < 0 || rank >= world)
+    return fail(KCG_ERR_INVALID_ARG, "gemm_allgather: world %d (1..8), rank %d", world, rank);
+  if (!gathered) return fail(KCG_ERR_INVALID_ARG, "gemm_allgather: null pointer");
+  if (row_offset < 0 || ldc < N) return fail(KCG_ERR_INVALID_ARG, "gemm_allgather: bad row offset or ldc");
+  if (activation < 0 || activation > 2) return fail(KCG_ERR_INVALID_ARG, "gemm: activation %d (0 none, 1 Relu, 2 Gelu)", activation);
+  if (M < 0 || N < 0 || K < 0) return fail(KCG_ERR_INVALID_ARG, "gemm: negative extent");
+  if (M == 0 || N == 0) return KCG_OK;
+  if (K == 0) return fail(KCG_ERR_INVALID_ARG, "gemm: K must be positive");
+  if (!A || !B) return fail(KCG_ERR_INVALID_ARG, "gemm: null pointer");
+  if (dtype_in != KCG_BF16 && dtype_in != KCG_F16 && dtype_in != KCG_F8E4M3)
+    return fail(KCG_ERR_UNSUPPORTED, "gemm_allgather: tensor-core input dtypes only (bfloat16, float16, float8_e4m3)");
+  const int64_t a_cols = trans_a ? M : K, b_cols = trans_b ? K : N;
+  if (lda < a_cols || ldb < b_cols) return fail(KCG_ERR_INVALID_ARG, "gemm: leading dimension shorter than a row");
+  const size_t out_es = kcg_dtype_size(dtype_out);
+  void* mine = nullptr;
+  void* others[8];
+  int n_others = 0;
+  for (int r = 0; r < world; ++r) {
+    if (!gathered[r]) return fail(KCG_ERR_INVALID_ARG, "gemm_allgather: gathered[%d] is null", r);
+    void* blk = static_cast<char*>(gathered[r]) + static_cast<size_t>(row_offset) * ldc * out_es;
+    if (r == rank) mine = blk; else others[n_others++] = blk;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return gemm_tcgen05(dtype_in, dtype_out, M, N, K, 1, trans_a, trans_b, A, lda, 0, B, ldb, 0, mine, ldc, 0, scale_a,
+                      scale_b, bias, activation, s, others, n_others);
 }

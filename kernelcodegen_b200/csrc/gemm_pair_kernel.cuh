@@ -19,7 +19,8 @@ constexpr int PA_BYTES = 128 * 128;           // 128 rows x 128 bytes of K
 constexpr int PB_BYTES = 128 * 128;           // this CTA's half of the B tile
 constexpr int PSTAGE_BYTES = PA_BYTES + PB_BYTES;
 constexpr int PBM = 256, PBN = 256;           // tile of the pair
-constexpr int PSMEM_BYTES = PSTAGES * PSTAGE_BYTES + 1024 + 256;
+constexpr int PEPI_STAGE_BYTES = 32 * 128;   // per epilogue warp: 32 rows x 128 bytes of output
+constexpr int PSMEM_BYTES = PSTAGES * PSTAGE_BYTES + 1024 + 256 + 4 * PEPI_STAGE_BYTES;
 
 __device__ __forceinline__ void pair_tile_coords(int64_t tile, int m_pairs, int n_tiles, int& b, int& mp, int& nt) {
   const int64_t per_batch = static_cast<int64_t>(m_pairs) * n_tiles;
@@ -183,6 +184,45 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       TOut* crow = static_cast<TOut*>(p.C) + b * p.stride_c + row * p.ldc;
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * PBN;
       constexpr int VW = Vec16<TOut>::N;
+      if (p.n_extra > 0) {
+        // Staged stores: the warp's 32 rows x 128 bytes go through a swizzled shared-memory
+        // tile so that eight lanes write one whole 128-byte row segment per instruction —
+        // the granularity a store to another GPU's memory should have — and every
+        // destination receives the same registers.
+        constexpr int RC = 128 / static_cast<int>(sizeof(TOut));   // columns per round
+        uint8_t* stg = smem + PSTAGES * PSTAGE_BYTES + 256 + quarter * PEPI_STAGE_BYTES;
+        const int64_t tile_row0 = static_cast<int64_t>(mp) * PBM + rank * 128 + quarter * 32;
+#pragma unroll 1
+        for (int c = 0; c < PBN / RC; ++c) {
+          uint32_t r[RC];
+          if constexpr (RC == 64) tmem_ld64(t_base + c * RC, r); else tmem_ld32(t_base + c * RC, r);
+          tmem_wait_ld();
+          const int64_t cbase = col0 + c * RC;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            Vec16<TOut> o;
+            const int64_t col = cbase + g * VW;
+#pragma unroll
+            for (int j = 0; j < VW; ++j)
+              o.v[j] = col + VW <= p.N ? gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act)
+                                       : TOut(0.f);
+            *reinterpret_cast<uint4*>(stg + lane * 128 + ((g ^ (lane & 7)) << 4)) = *reinterpret_cast<const uint4*>(&o);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + (lane >> 3), ch = lane & 7;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((ch ^ (rr & 7)) << 4));
+            const int64_t grow = tile_row0 + rr, col = cbase + ch * VW;
+            if (grow < p.M && col + VW <= p.N) {
+              const int64_t off = b * p.stride_c + grow * p.ldc + col;
+              *reinterpret_cast<uint4*>(static_cast<TOut*>(p.C) + off) = v;
+              for (int e = 0; e < p.n_extra; ++e) *reinterpret_cast<uint4*>(static_cast<TOut*>(p.extra_c[e]) + off) = v;
+            }
+          }
+          __syncwarp();
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < PBN / 32; ++c) {
         uint32_t r[32];
@@ -205,6 +245,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             }
           }
         }
+      }
       }
       tc_fence_before();
       __syncwarp();

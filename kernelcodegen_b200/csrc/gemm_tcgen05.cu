@@ -41,6 +41,7 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int GROUP_M = 16;
+#define KCG_MAX_EXTRA_C 7
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
 struct GemmParams {
@@ -56,6 +57,10 @@ struct GemmParams {
   int c_vec_ok;
   const void* bias;  // N values of the output dtype, or null
   int act;           // 0 none, 1 Relu, 2 Gelu
+  // Further copies of C (same ldc / stride_c), typically this rank's block inside the gather
+  // buffers of peer GPUs: the CTA-pair kernel's epilogue stores every tile to each of them.
+  void* extra_c[KCG_MAX_EXTRA_C];
+  int n_extra;
 };
 
 __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, int& b, int& mt, int& nt) {
@@ -363,7 +368,8 @@ extern "C" __attribute__((visibility("default"))) void kcg_gemm_set_pair_mode(in
 int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
                  int trans_b, const void* A, int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
                  int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
-                 const float* scale_b, const void* bias, int act, cudaStream_t stream) {
+                 const float* scale_b, const void* bias, int act, cudaStream_t stream, void* const* extra_c,
+                 int n_extra) {
   const int es = dtype_in == KCG_F8E4M3 ? 1 : 2;
   if (!aligned16(A) || !aligned16(B))
     return fail(KCG_ERR_ALIGNMENT, "gemm: A and B must be 16-byte aligned for the tensor-core path");
@@ -376,7 +382,13 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
 
   const int BK = 128 / es;
   const uint32_t mn_box = 128 / es;
-  const bool pair = g_pair_mode == 0 ? false : (g_pair_mode == 1 ? M > BM : M >= 2 * BM);
+  bool pair = g_pair_mode == 0 ? false : (g_pair_mode == 1 ? M > BM : M >= 2 * BM);
+  if (n_extra > 0) {
+    // only the CTA-pair kernel has the staged epilogue that writes whole 128-byte row segments
+    if (n_extra > KCG_MAX_EXTRA_C) return fail(KCG_ERR_UNSUPPORTED, "gemm: at most %d extra outputs", KCG_MAX_EXTRA_C);
+    if (M <= BM) return fail(KCG_ERR_UNSUPPORTED, "gemm: extra outputs need M > 128 (got %lld)", static_cast<long long>(M));
+    pair = true;
+  }
   CUtensorMap tmA, tmB, tmBp;
   {
     const uint64_t a_rows = trans_a ? K : M, a_cols = trans_a ? M : K;
@@ -417,6 +429,14 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
   if (!p.status) return fail(KCG_ERR_CUDA, "gemm: could not allocate the host-mapped status word");
   const size_t out_es = kcg_dtype_size(dtype_out);
   p.c_vec_ok = aligned16(C) && (ldc * out_es) % 16 == 0 && (stride_c * out_es) % 16 == 0;
+  p.n_extra = n_extra;
+  for (int i = 0; i < KCG_MAX_EXTRA_C; ++i) p.extra_c[i] = i < n_extra ? extra_c[i] : nullptr;
+  if (n_extra > 0) {
+    bool ok = p.c_vec_ok && (N * out_es) % 16 == 0;
+    for (int i = 0; i < n_extra; ++i) ok = ok && extra_c[i] != nullptr && aligned16(extra_c[i]);
+    if (!ok)
+      return fail(KCG_ERR_ALIGNMENT, "gemm: extra outputs need 16-byte aligned pointers, ldc and N (in bytes)");
+  }
 
   const uint32_t a_mn = trans_a ? 1u : 0u, b_mn = trans_b ? 0u : 1u;
   if (dtype_in == KCG_F8E4M3) {

@@ -146,3 +146,51 @@ extern "C" int kcg_shard_range(int64_t total, int world, int rank, int64_t granu
   *count = e - b;
   return KCG_OK;
 }
+
+// ---- device memory that other processes on the node can map ---------------------------------
+// Plain cudaMalloc allocations shared through CUDA IPC handles: the owner exports a 64-byte
+// handle, each peer process opens it and gets a pointer it can hand to kernels on its own GPU
+// (loads and stores then travel over NVLink).
+static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the C ABI passes IPC handles as 64 bytes");
+
+extern "C" int kcg_peer_alloc(size_t bytes, void** ptr) {
+  using namespace kcg;
+  clear_error();
+  if (!ptr || bytes == 0) return fail(KCG_ERR_INVALID_ARG, "peer_alloc: null pointer or zero size");
+  KCG_CUDA_OK(cudaMalloc(ptr, bytes));
+  return KCG_OK;
+}
+
+extern "C" int kcg_peer_free(void* ptr) {
+  using namespace kcg;
+  clear_error();
+  if (ptr) KCG_CUDA_OK(cudaFree(ptr));
+  return KCG_OK;
+}
+
+extern "C" int kcg_peer_export(void* ptr, unsigned char handle[64]) {
+  using namespace kcg;
+  clear_error();
+  if (!ptr || !handle) return fail(KCG_ERR_INVALID_ARG, "peer_export: null pointer");
+  cudaIpcMemHandle_t h;
+  KCG_CUDA_OK(cudaIpcGetMemHandle(&h, ptr));
+  std::memcpy(handle, &h, 64);
+  return KCG_OK;
+}
+
+extern "C" int kcg_peer_open(const unsigned char handle[64], void** ptr) {
+  using namespace kcg;
+  clear_error();
+  if (!ptr || !handle) return fail(KCG_ERR_INVALID_ARG, "peer_open: null pointer");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  KCG_CUDA_OK(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return KCG_OK;
+}
+
+extern "C" int kcg_peer_close(void* ptr) {
+  using namespace kcg;
+  clear_error();
+  if (ptr) KCG_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+  return KCG_OK;
+}

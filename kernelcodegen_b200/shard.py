@@ -124,3 +124,120 @@ def fmha(Q_local, K_local, V_local, softmax_scale: float = 1.0, causal: bool = F
     if total_slices is None:
         raise ValueError("gather=True needs total_slices")
     return all_gather_rows(O_local, total_slices, 1, group)
+
+
+# ---- gather fused into the GEMM epilogue: tiles stored straight into every rank's buffer -----
+
+class _CudaArray:
+    """Minimal __cuda_array_interface__ carrier so torch can view memory this library allocated."""
+
+    def __init__(self, ptr: int, shape, typestr: str, owner):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
+        self._owner = owner
+
+
+_TYPESTR = {torch.bfloat16: None, torch.float16: "<f2", torch.float32: "<f4"}
+
+
+class GatherBuffers:
+    """One [total_rows, cols] matrix per rank, each mapped into every process of the group.
+
+    ``local`` is this rank's matrix as a torch tensor; ``ptrs[r]`` is the address of rank r's
+    matrix as seen from this process (rank's own allocation, or a CUDA-IPC mapping of a peer's).
+    Collective: every rank of the group must construct it (handles are exchanged with
+    all_gather_object) and ``close()`` it.
+    """
+
+    def __init__(self, total_rows: int, cols: int, dtype: torch.dtype, group=None):
+        import ctypes
+        self.world, self.rank = world_and_rank(group)
+        self.group = group
+        self.total_rows, self.cols, self.dtype = int(total_rows), int(cols), dtype
+        esize = torch.empty((), dtype=dtype).element_size()
+        self.nbytes = self.total_rows * self.cols * esize
+        lib = _lib.load()
+        p = ctypes.c_void_p()
+        _lib.check(lib.kcg_peer_alloc(self.nbytes, ctypes.byref(p)), "kcg_peer_alloc")
+        self._own = p.value
+        self.ptrs = [None] * self.world
+        self.ptrs[self.rank] = self._own
+        self._opened = []
+        if self.world > 1:
+            h = ctypes.create_string_buffer(64)
+            _lib.check(lib.kcg_peer_export(self._own, h), "kcg_peer_export")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(h.raw), group=group)
+            for r, hb in enumerate(handles):
+                if r == self.rank:
+                    continue
+                q = ctypes.c_void_p()
+                _lib.check(lib.kcg_peer_open(ctypes.create_string_buffer(hb, 64), ctypes.byref(q)), "kcg_peer_open")
+                self.ptrs[r] = q.value
+                self._opened.append(q.value)
+        # torch view of the local matrix (bf16 has no array-interface code: view 16-bit words)
+        ts = _TYPESTR[dtype] or "<i2"
+        t = torch.as_tensor(_CudaArray(self._own, (self.total_rows, self.cols), ts, self), device="cuda")
+        self.local = t.view(dtype) if t.dtype != dtype else t
+
+    def close(self) -> None:
+        """Unmap the peers' matrices, then (after every rank has done so) free the local one."""
+        lib = _lib.load()
+        for q in self._opened:
+            lib.kcg_peer_close(q)
+        self._opened = []
+        if self.world > 1 and dist.is_initialized():
+            dist.barrier(group=self.group)
+        if self._own:
+            self.local = None
+            lib.kcg_peer_free(self._own)
+            self._own = None
+
+
+_barrier_word = {}
+
+
+def stream_barrier(group=None) -> None:
+    """All ranks meet on the current CUDA stream (a one-element all-reduce): work queued after it
+    starts only when every rank's earlier work on its stream has finished.  The host does not wait."""
+    dev = torch.cuda.current_device()
+    w = _barrier_word.get(dev)
+    if w is None:
+        w = _barrier_word[dev] = torch.zeros(1, device="cuda")
+    dist.all_reduce(w, group=group)
+
+
+def matmul_allgather(A_local: torch.Tensor, B: torch.Tensor, bufs: GatherBuffers, trans_b: bool = False,
+                     scale_a=None, scale_b=None, bias=None, activation=None, sync: bool = True) -> torch.Tensor:
+    """Replicated C = A B with A split along M: each rank's GEMM epilogue writes its row block
+    into every rank's buffer (peer stores over NVLink), so no separate all-gather runs.
+
+    With ``sync`` the ranks meet on the stream before the launch (nobody still reads the buffers)
+    and after it (every block has landed); pass False to place those barriers yourself.
+    Returns ``bufs.local``.
+    """
+    import ctypes
+    from . import ops
+    if not (A_local.is_cuda and B.is_cuda and A_local.is_contiguous() and B.is_contiguous()):
+        raise ValueError("operands must be contiguous CUDA tensors")
+    M, K = A_local.shape
+    N = B.shape[0] if trans_b else B.shape[1]
+    if (B.shape[1] if trans_b else B.shape[0]) != K:
+        raise ValueError("Can't apply Matmul Operation due to imcompatible K-dim.")
+    if N != bufs.cols:
+        raise ValueError("buffer width does not match N")
+    begin, count = _lib.shard_range(bufs.total_rows, bufs.world, bufs.rank, GEMM_ROW_GRANULE)
+    if count != M:
+        raise ValueError(f"this rank owns {count} rows of the gathered matrix, A_local has {M}")
+    act = {None: 0, "": 0, "Relu": 1, "Gelu": 2}[activation]
+    stream = torch.cuda.current_stream().cuda_stream
+    if sync and bufs.world > 1:
+        stream_barrier(bufs.group)
+    arr = (ctypes.c_void_p * bufs.world)(*bufs.ptrs)
+    _lib.check(_lib.load().kcg_gemm_allgather(
+        ops._dt(A_local), ops._DT[bufs.dtype], M, N, K, 0, int(trans_b), A_local.data_ptr(), A_local.stride(0),
+        B.data_ptr(), B.stride(0), arr, bufs.world, bufs.rank, begin, bufs.cols,
+        scale_a.data_ptr() if scale_a is not None else None, scale_b.data_ptr() if scale_b is not None else None,
+        bias.data_ptr() if bias is not None else None, act, stream), "kcg_gemm_allgather")
+    if sync and bufs.world > 1:
+        stream_barrier(bufs.group)
+    return bufs.local

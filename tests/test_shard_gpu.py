@@ -39,6 +39,16 @@ def _worker(rank, world, port, results):
         Oo = shard.fmha(shard.shard_rows(Q).contiguous(), shard.shard_rows(K).contiguous(),
                         shard.shard_rows(V).contiguous(), 128 ** -0.5, True, total_slices=6, gather=True)
         ok = ok and torch.equal(Oo, ops.fmha(Q, K, V, 128 ** -0.5, True))
+        # the gather done by the GEMM epilogue itself: peer stores into every rank's buffer
+        bufs = shard.GatherBuffers(A.shape[0], B.shape[1], torch.bfloat16)
+        try:
+            for _ in range(3):    # repeated use of the same buffers, barriers placed by the call
+                bufs.local.zero_()
+                out = shard.matmul_allgather(A[b0:b0 + c0].contiguous(), B, bufs)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(out, full)
+        finally:
+            bufs.close()
         torch.cuda.synchronize()
         ok = ok and _lib.device_status() == 0
         results[rank] = bool(ok)
