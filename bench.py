@@ -232,7 +232,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM/FMHA/fp32 side measurements")
-    ap.add_argument("--only", default="", help="comma list of extras to run (bw,fp32,gemm,sgemm,fmha,sweep)")
+    ap.add_argument("--only", default="", help="comma list of extras to run (bw,fp32,gemm,sgemm,fmha,sweep,gather)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -543,6 +543,42 @@ def main() -> None:
             recv = (world - 1) * loc.numel() * 2
             workloads[name] = {"ms": ms, "value": recv / (ms * 1e-3) / 1e9, "unit": "GB/s received per GPU"}
             del loc, out
+        torch.cuda.empty_cache()
+    if world > 1 and want("gather"):
+        # replicated C from a row-sharded GEMM, two ways: the epilogue that stores every tile into
+        # all ranks' buffers (peer stores over NVLink) against the plain kernel followed by an
+        # NCCL all-gather.  Per rank M = N = K = 8192; ranks meet on the stream once per iteration.
+        from kernelcodegen_b200 import shard
+        n = 8192
+        A = rnd((n, n), std=n ** -0.5); B = rnd((n, n))
+        bufs = shard.GatherBuffers(world * n, n, dt)
+        Cl = torch.empty((n, n), dtype=dt, device="cuda")
+        Cg = torch.empty((world * n, n), dtype=dt, device="cuda")
+
+        def fused_iter():
+            shard.matmul_allgather(A, B, bufs, sync=False)
+            shard.stream_barrier()
+
+        def nccl_iter():
+            ops.matmul(A, B, out=Cl)
+            dist.all_gather_into_tensor(Cg, Cl)
+
+        for name, fn in (("gemm_allgather_fused_epilogue", fused_iter), ("gemm_then_nccl_allgather", nccl_iter)):
+            for _ in range(3):
+                fn()
+            barrier()
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record()
+            barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1)) / 10
+            workloads[name] = {"ms": ms, "value": world * 2 * n ** 3 / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                               "bytes_sent_per_gpu": (world - 1) * n * n * 2,
+                               "link_gbs_per_gpu": (world - 1) * n * n * 2 / (ms * 1e-3) / 1e9}
+        workloads["gemm_allgather_fused_epilogue"]["bit_identical_to_nccl_path"] = bool(torch.equal(bufs.local, Cg))
+        del A, B, Cl, Cg
+        bufs.close()
         torch.cuda.empty_cache()
     if rank == 0 and world == 1 and not args.no_extras:
         cpu_side_by_side(workloads)
