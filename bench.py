@@ -80,8 +80,9 @@ def ncu_traffic(kernel: str):
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML while a timed region runs."""
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, interval: float = 0.004):
         self.index = index
+        self.interval = interval
         self.samples = []
         self.reasons = set()
         self.max_mhz = None
@@ -120,7 +121,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.004)
+            time.sleep(self.interval)
 
     def stop(self) -> dict:
         self._stop.set()
@@ -373,14 +374,29 @@ def main() -> None:
     del hx, hu, ha, hb, oy, ov, oc
 
     # ---- the other operators of the library, each timed on its BASELINE configuration
-    workloads = {}
+    pending_clock = []
+
+    class Workloads(dict):
+        """Each entry gets the SM clock sampled while its timed region ran (see time_op)."""
+
+        def __setitem__(self, key, entry):
+            if pending_clock and isinstance(entry, dict):
+                c = pending_clock.pop()
+                entry = dict(entry, sm_mhz=c["sm_mhz"], throttle_reasons=c["reasons"])
+            super().__setitem__(key, entry)
+
+    workloads = Workloads()
     only = set(filter(None, args.only.split(",")))
 
     def want(name):
         return not args.no_extras and (not only or name in only)
 
     def time_op(fn, iters, warm=3):
-        """Average device time of `fn`: `iters` calls captured in a CUDA graph, replayed once timed."""
+        """Average device time of `fn`: `iters` calls captured in a CUDA graph, replayed once timed.
+        A short idle gap first lets the power-capped SM clock recover from the previous workload,
+        so every entry is a burst figure from the same starting state."""
+        torch.cuda.synchronize()
+        time.sleep(0.25)
         with torch.cuda.stream(cap_stream):
             for _ in range(warm):
                 fn()
@@ -391,10 +407,13 @@ def main() -> None:
                 fn()
         g.replay()
         barrier()
+        smp = ClockSampler(local_rank, interval=0.001).start()
         e0.record()
         g.replay()
         e1.record()
         barrier()
+        del pending_clock[:]
+        pending_clock.append(smp.stop())
         return max_over_ranks(e0.elapsed_time(e1)) / iters
 
     for op_name in ("layernorm", "gelu", "add"):
@@ -493,6 +512,18 @@ def main() -> None:
         torch.cuda.empty_cache()
     if want("sweep"):
         # the other sizes of the GEMM and FMHA configurations (per GPU; N ranks run N copies)
+        Bq, H, D = 8, 32, 128
+        for S in (1024, 2048):
+            Q, K, V = rnd((Bq, H, S, D)), rnd((Bq, H, S, D)), rnd((Bq, H, S, D))
+            Oo = torch.empty_like(Q)
+            for causal in (False, True):
+                ms = time_op(lambda: ops.fmha(Q, K, V, D ** -0.5, causal, out=Oo), 20)
+                fl = 4 * Bq * H * S * S * D if not causal else 2 * Bq * H * S * (S + 1) * D
+                tf = world * fl / (ms * 1e-3) / 1e12
+                workloads[f"fmha_bf16_s{S}_{'causal' if causal else 'full'}"] = {
+                    "ms": ms, "value": tf, "unit": "TFLOP/s", "frac_of_nominal_2250": tf / world / 2250.0}
+            del Q, K, V, Oo
+        torch.cuda.empty_cache()
         for n in (1024, 2048, 4096, 16384):
             for tdt, tag in ((torch.bfloat16, "bf16"), (torch.float16, "f16")):
                 A = rnd((n, n), tdt, std=n ** -0.5); B = rnd((n, n), tdt)
@@ -513,18 +544,6 @@ def main() -> None:
             workloads[f"gemm_fp8_{n}"] = {"ms": ms, "value": tf, "unit": "TFLOP/s", "frac_of_nominal_4500": tf / world / 4500.0}
             del A8, B8, C
             torch.cuda.empty_cache()
-        Bq, H, D = 8, 32, 128
-        for S in (1024, 2048):
-            Q, K, V = rnd((Bq, H, S, D)), rnd((Bq, H, S, D)), rnd((Bq, H, S, D))
-            Oo = torch.empty_like(Q)
-            for causal in (False, True):
-                ms = time_op(lambda: ops.fmha(Q, K, V, D ** -0.5, causal, out=Oo), 20)
-                fl = 4 * Bq * H * S * S * D if not causal else 2 * Bq * H * S * (S + 1) * D
-                tf = world * fl / (ms * 1e-3) / 1e12
-                workloads[f"fmha_bf16_s{S}_{'causal' if causal else 'full'}"] = {
-                    "ms": ms, "value": tf, "unit": "TFLOP/s", "frac_of_nominal_2250": tf / world / 2250.0}
-            del Q, K, V, Oo
-        torch.cuda.empty_cache()
     if world > 1 and not args.no_extras:
         # the optional exchange: NCCL all-gather of a sharded output (here the 128 MiB bf16 C
         # block of the GEMM shard and the 64 MiB LayerNorm block), timed on the device

@@ -74,9 +74,15 @@ class KernelCodeGenerator {
   // returns the best module (reference: src/KernelCodeGen.cc:8-120).
   Module& optimize(ComputeDAG& graph_);
 
-  // Latency estimate of a candidate; 0 like the reference until autotuning lands, so the
-  // first config of each table wins.
-  float evaluate(Module& module) { (void)module; return 0.0f; }
+  // Latency of a candidate module.  With `autotune` off (the default) it returns 0 like the
+  // reference (include/KernelCodeGen.h:134-136), so the first config of each table wins.  With
+  // `autotune` on and a GPU present it runs the module's selected kernels on scratch buffers
+  // (zero-filled, allocated and freed here) and returns the mean device time in milliseconds.
+  float evaluate(Module& module);
+
+  // Candidate tile/variant configurations of one optimizer family ("Matmul", "BatchMatmul",
+  // "LayerNorm", "FMHA", ...); optimize() tries each entry in turn.  Empty name -> nullptr.
+  std::vector<std::map<std::string, int>>* configs(const std::string& family);
 
   std::string codegen(Module module);
 
@@ -84,6 +90,11 @@ class KernelCodeGenerator {
   // launch touches must be bound.  Returns a kcg_status; functions no optimizer selected
   // are an error (there is no CPU execution path).
   int run(Module& module, const Bindings& bindings, void* stream = nullptr);
+
+  // Time every candidate config on the device inside optimize() (see evaluate()).
+  bool autotune = false;
+  // Latency evaluate() returned for the candidate the last optimizer kept (0 without autotuning).
+  float bestLatency() const { return minLatency; }
 
   void setLogMode(Log level) { KCGLog::level = level; }
 
@@ -96,6 +107,7 @@ class KernelCodeGenerator {
   ComputeDAG graph;
   std::string platform;
   float minLatency = FLT_MAX;
+  int runSelected(Module& module, const Bindings& bindings, void* stream, bool skipUnselected);
   std::vector<std::map<std::string, int>> matmulConfigs, fmhaConfigs, binaryConfigs, elementWiseConfigs,
       gatherConfigs, layerNormConfigs, batchMatmulConfigs, softmaxConfigs, fusionConfigs;
 };

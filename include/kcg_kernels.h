@@ -383,6 +383,18 @@ KCG_API int kcg_peer_open(const unsigned char handle[64], void** ptr);
 KCG_API int kcg_peer_close(void* ptr);
 
 /*
+ * Device utilities for host code that does not link the CUDA runtime itself (the C++ front
+ * end's autotuner): number of visible devices (0 without a driver, never an error), an
+ * asynchronous byte fill, and a stream timer — kcg_timer_begin records an event on `stream`,
+ * kcg_timer_end records a second one, waits for it and returns the elapsed device time,
+ * releasing the timer.  Buffers come from kcg_peer_alloc / kcg_peer_free.
+ */
+KCG_API int kcg_device_count(int* count);
+KCG_API int kcg_device_memset(void* ptr, int byte_value, size_t bytes, void* stream);
+KCG_API int kcg_timer_begin(void* stream, void** timer);
+KCG_API int kcg_timer_end(void* stream, void* timer, float* milliseconds);
+
+/*
  * Row-range owned by one rank when `total` independent units (GEMM rows of A/C,
  * attention batch*head slices, LayerNorm / elementwise rows) are split over
  * `world` GPUs in contiguous blocks rounded to `granule` units.  The reference

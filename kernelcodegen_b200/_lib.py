@@ -56,6 +56,10 @@ SIGNATURES = {
     "kcg_fmha_set_p_in_tmem": ([_ci], None),
     "kcg_gather": ([_ci, _ci, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp], _ci),
     "kcg_transpose": ([_ci, _i64, _i64, _i64, _vp, _vp, _vp], _ci),
+    "kcg_device_count": ([ctypes.POINTER(_ci)], _ci),
+    "kcg_device_memset": ([_vp, _ci, ctypes.c_size_t, _vp], _ci),
+    "kcg_timer_begin": ([_vp, ctypes.POINTER(_vp)], _ci),
+    "kcg_timer_end": ([_vp, _vp, ctypes.POINTER(_fp)], _ci),
     "kcg_shard_range": ([_i64, _ci, _ci, _i64, _i64p, _i64p], _ci),
 }
 

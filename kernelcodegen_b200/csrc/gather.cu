@@ -142,10 +142,84 @@ transpose_tiles(const E* __restrict__ in, E* __restrict__ out, int64_t R, int64_
   }
 }
 
+// Wide-tile variant for 2- and 4-byte elements whose extents are tile multiples: a block moves
+// 64 rows x 64 32-bit words (16 KB) with 16-byte global accesses, so that eight resident blocks
+// keep well over 100 KB per SM in flight.  Shared memory holds words with an odd pitch; for
+// 2-byte elements a word carries two horizontally adjacent elements and the store phase
+// re-pairs the halves of two rows (a 2x2 transpose in registers).
+template <int ES>
+__global__ void __launch_bounds__(256)
+transpose_wide(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, int64_t R, int64_t C, int tiles_c,
+               int tiles_r) {
+  constexpr int EPW = 4 / ES;          // elements per word: 1 or 2
+  constexpr int TR = 64, TW = 64;      // tile: 64 rows x 64 words (= 64 * EPW columns)
+  constexpr int PITCH = TW + 1;
+  __shared__ uint32_t tile[TR * PITCH];
+  const int64_t per_batch = static_cast<int64_t>(tiles_c) * tiles_r;
+  const int64_t b = blockIdx.x / per_batch;
+  const int rem = static_cast<int>(blockIdx.x % per_batch);
+  const int tr = rem / tiles_c, tc = rem % tiles_c;
+  const int64_t in_pitch = C / EPW, out_pitch = R / EPW;   // row pitches in words
+  const uint32_t* src = in + b * R * in_pitch + static_cast<int64_t>(tr) * TR * in_pitch + static_cast<int64_t>(tc) * TW;
+  const int t = threadIdx.x;
+  const int j = t & 15, rsub = t >> 4;   // 16 threads x 16 bytes span one 256-byte tile row
+  uint4 v[4];
+#pragma unroll
+  for (int p = 0; p < 4; ++p) v[p] = __ldcs(reinterpret_cast<const uint4*>(src + (p * 16 + rsub) * in_pitch) + j);
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    uint32_t* row = tile + (p * 16 + rsub) * PITCH + 4 * j;
+    row[0] = v[p].x; row[1] = v[p].y; row[2] = v[p].z; row[3] = v[p].w;
+  }
+  __syncthreads();
+  if constexpr (EPW == 1) {
+    // output row c (input column c) takes 64 words from input rows 0..63: 16 threads x 16 bytes
+    uint32_t* dst = out + b * R * in_pitch + (static_cast<int64_t>(tc) * TW) * out_pitch + static_cast<int64_t>(tr) * TR;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int c = p * 16 + rsub;
+      uint4 o;
+      o.x = tile[(4 * j + 0) * PITCH + c]; o.y = tile[(4 * j + 1) * PITCH + c];
+      o.z = tile[(4 * j + 2) * PITCH + c]; o.w = tile[(4 * j + 3) * PITCH + c];
+      __stcs(reinterpret_cast<uint4*>(dst + c * out_pitch) + j, o);
+    }
+  } else {
+    // 128 output rows (input columns) of 64 elements = 32 words each: 8 threads x 16 bytes per
+    // row, 32 rows per pass.  Output word m of row c pairs in[2m][c] with in[2m+1][c].
+    uint32_t* dst = out + b * R * in_pitch + (static_cast<int64_t>(tc) * TW * EPW) * out_pitch + static_cast<int64_t>(tr) * (TR / EPW);
+    const int q = t & 7, csub = t >> 3;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int c = p * 32 + csub;           // element column inside the tile
+      const int cw = c >> 1;
+      const uint32_t sel = (c & 1) ? 0x7632u : 0x5410u;   // high halves or low halves of two words
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[i] = tile[(8 * q + i) * PITCH + cw];
+      uint4 o;
+      o.x = __byte_perm(w[0], w[1], sel); o.y = __byte_perm(w[2], w[3], sel);
+      o.z = __byte_perm(w[4], w[5], sel); o.w = __byte_perm(w[6], w[7], sel);
+      __stcs(reinterpret_cast<uint4*>(dst + c * out_pitch) + q, o);
+    }
+  }
+}
+
 template <typename E>
 int launch_transpose(int64_t batch, int64_t R, int64_t C, const void* in, void* out, cudaStream_t stream) {
   constexpr int EPW = sizeof(E) >= 4 ? 1 : 4 / sizeof(E);
   constexpr int TD = 32 * EPW;
+  if constexpr (sizeof(E) == 2 || sizeof(E) == 4) {
+    constexpr int ES = static_cast<int>(sizeof(E));
+    constexpr int WCOLS = 64 * (4 / ES);   // tile width in elements
+    if (R % 64 == 0 && C % WCOLS == 0 && aligned16(in) && aligned16(out)) {
+      const int64_t wt_r = R / 64, wt_c = C / WCOLS, nblk = batch * wt_r * wt_c;
+      if (nblk <= 0x7fffffffll) {
+        transpose_wide<ES><<<static_cast<unsigned>(nblk), 256, 0, stream>>>(
+            static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out), R, C, static_cast<int>(wt_c), static_cast<int>(wt_r));
+        return check_launch("transpose_wide");
+      }
+    }
+  }
   const int64_t tiles_r = (R + TD - 1) / TD, tiles_c = (C + TD - 1) / TD;
   const int64_t blocks = batch * tiles_r * tiles_c;
   if (blocks > 0x7fffffffll || tiles_r > 0x7fffffffll || tiles_c > 0x7fffffffll)

@@ -194,3 +194,55 @@ extern "C" int kcg_peer_close(void* ptr) {
   if (ptr) KCG_CUDA_OK(cudaIpcCloseMemHandle(ptr));
   return KCG_OK;
 }
+
+// ---- small device utilities for host code that does not link the CUDA runtime itself ---------
+extern "C" int kcg_device_count(int* count) {
+  using namespace kcg;
+  clear_error();
+  if (!count) return fail(KCG_ERR_INVALID_ARG, "device_count: null pointer");
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  *count = n;
+  return KCG_OK;
+}
+
+extern "C" int kcg_device_memset(void* ptr, int byte_value, size_t bytes, void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (!ptr && bytes) return fail(KCG_ERR_INVALID_ARG, "device_memset: null pointer");
+  if (bytes) KCG_CUDA_OK(cudaMemsetAsync(ptr, byte_value, bytes, static_cast<cudaStream_t>(stream)));
+  return KCG_OK;
+}
+
+namespace {
+struct KcgTimer { cudaEvent_t begin, end; };
+}
+
+extern "C" int kcg_timer_begin(void* stream, void** timer) {
+  using namespace kcg;
+  clear_error();
+  if (!timer) return fail(KCG_ERR_INVALID_ARG, "timer_begin: null pointer");
+  KcgTimer* t = new KcgTimer;
+  if (cudaEventCreate(&t->begin) != cudaSuccess || cudaEventCreate(&t->end) != cudaSuccess) {
+    delete t;
+    return fail(KCG_ERR_CUDA, "timer_begin: cudaEventCreate failed: %s", cudaGetErrorString(cudaGetLastError()));
+  }
+  cudaEventRecord(t->begin, static_cast<cudaStream_t>(stream));
+  *timer = t;
+  return KCG_OK;
+}
+
+extern "C" int kcg_timer_end(void* stream, void* timer, float* milliseconds) {
+  using namespace kcg;
+  clear_error();
+  if (!timer || !milliseconds) return fail(KCG_ERR_INVALID_ARG, "timer_end: null pointer");
+  KcgTimer* t = static_cast<KcgTimer*>(timer);
+  cudaEventRecord(t->end, static_cast<cudaStream_t>(stream));
+  cudaError_t e = cudaEventSynchronize(t->end);
+  if (e == cudaSuccess) e = cudaEventElapsedTime(milliseconds, t->begin, t->end);
+  cudaEventDestroy(t->begin);
+  cudaEventDestroy(t->end);
+  delete t;
+  if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "timer_end: %s", cudaGetErrorString(e));
+  return KCG_OK;
+}

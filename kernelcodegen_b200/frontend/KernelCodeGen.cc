@@ -72,16 +72,25 @@ void Module::dump() const {
 KernelCodeGenerator::KernelCodeGenerator(const std::string& platform_) : platform(platform_) {
   // Default tile-config tables with the reference's keys (include/KernelCodeGen.h:35-58).  The
   // matmul / fmha entries describe the sm_100a kernels: CTA tile, k-block, ring depth.
-  matmulConfigs = {{{"BLOCK_SIZE_M", 128}, {"BLOCK_SIZE_N", 256}, {"BLOCK_SIZE_K", 64}, {"GROUP_SIZE_M", 8},
-                    {"STAGES", 4}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}}};
+  // Candidates differ in the keys the kernels really switch on: CTA_PAIR (256x256 tiles on two
+  // SMs with cta_group::2, or 128x256 on one), WARP_ROW_VECS (LayerNorm rows of up to 32*v
+  // 16-byte vectors are handled by one warp), VARIANT (attention data path).
+  matmulConfigs = {{{"BLOCK_SIZE_M", 256}, {"BLOCK_SIZE_N", 256}, {"BLOCK_SIZE_K", 64}, {"GROUP_SIZE_M", 8},
+                    {"STAGES", 6}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}, {"CTA_PAIR", 1}},
+                   {{"BLOCK_SIZE_M", 128}, {"BLOCK_SIZE_N", 256}, {"BLOCK_SIZE_K", 64}, {"GROUP_SIZE_M", 16},
+                    {"STAGES", 4}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}, {"CTA_PAIR", 0}}};
   batchMatmulConfigs = matmulConfigs;
   binaryConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
   elementWiseConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
-  layerNormConfigs = {{{"WARP_ROW_VECS", 8}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}}};
+  layerNormConfigs = {{{"WARP_ROW_VECS", 8}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}},
+                      {{"WARP_ROW_VECS", 16}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}},
+                      {{"WARP_ROW_VECS", 4}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}},
+                      {{"WARP_ROW_VECS", 0}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}}};
   gatherConfigs = {{{"BLOCK_SIZE", 256}, {"VECTORIZE_WIDTH", 16}}};
   softmaxConfigs = {{{"BLOCK_SIZE", 256}}};
   fusionConfigs = {{{"EPILOGUE", 1}}};
-  fmhaConfigs = {{{"BLOCK_SIZE", 192}, {"Br", 128}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}}};
+  fmhaConfigs = {{{"BLOCK_SIZE", 320}, {"Br", 256}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}, {"VARIANT", 2}},
+                 {{"BLOCK_SIZE", 192}, {"Br", 128}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}, {"VARIANT", 1}}};
 }
 
 ComputeDAG& KernelCodeGenerator::createGraph(const std::string& graphName) {
@@ -140,31 +149,40 @@ Module& KernelCodeGenerator::optimize(ComputeDAG& graph_) {
     else if (*opt == KernelFusionOptimizer()) { table = &fusionConfigs; slot = &KernelFusionOptimizer::fusionConfig; }
     bool applied = false;
     if (table) {
+      // Each candidate is applied to a fresh copy of the module and timed; the fastest one is
+      // kept.  With evaluate() == 0 (no autotuning) the comparison is strict, so the first entry
+      // of the table wins, as in the reference (src/KernelCodeGen.cc:15-118).
+      float best = FLT_MAX;
+      std::map<std::string, int> bestCfg;
       for (auto& cfg : *table) {
         *slot = cfg;
         resetModule(module);
         if (opt->applicable(module)) {
           opt->applyOptimzer(module, builder);
           const float latency = evaluate(module);
-          // The reference compares with `<` against a minimum that evaluate()==0 reaches at
-          // once, so later optimizers would never update the best module; every selection is
-          // kept here (`<=`), which is what its one-optimizer-per-run tests observe anyway.
-          if (latency <= minLatency) {
-            minLatency = latency;
+          if (KCGLog::level == Log::Debug && autotune) {
+            std::cerr << "autotune " << opt->name << ":";
+            for (const auto& kv : cfg) std::cerr << " " << kv.first << "=" << kv.second;
+            std::cerr << " -> " << latency << " ms\n";
+          }
+          if (latency < best) {
+            best = latency;
+            bestCfg = cfg;
             saveBestModule(module);
             applied = true;
           }
         }
       }
       if (!applied) resetModule(module);
-      else module.graph = clone(bestModule.graph);
+      else {
+        module.graph = clone(bestModule.graph);
+        *slot = bestCfg;
+        minLatency = best;
+      }
     } else if (opt->applicable(module)) {
       opt->applyOptimzer(module, builder);
-      const float latency = evaluate(module);
-      if (latency <= minLatency) {
-        minLatency = latency;
-        saveBestModule(module);
-      }
+      minLatency = evaluate(module);
+      saveBestModule(module);
     }
   }
   return bestModule;
@@ -208,7 +226,87 @@ std::string KernelCodeGenerator::codegen(Module module) {
   return "";
 }
 
+std::vector<std::map<std::string, int>>* KernelCodeGenerator::configs(const std::string& family) {
+  if (family == "Matmul") return &matmulConfigs;
+  if (family == "BatchMatmul") return &batchMatmulConfigs;
+  if (family == "FMHA") return &fmhaConfigs;
+  if (family == "Binary") return &binaryConfigs;
+  if (family == "ElementWise") return &elementWiseConfigs;
+  if (family == "Gather") return &gatherConfigs;
+  if (family == "LayerNorm") return &layerNormConfigs;
+  if (family == "Softmax") return &softmaxConfigs;
+  if (family == "KernelFusion") return &fusionConfigs;
+  return nullptr;
+}
+
+float KernelCodeGenerator::evaluate(Module& module) {
+  if (!autotune || !module.graph) return 0.0f;
+  int devices = 0;
+  kcg_device_count(&devices);
+  if (devices <= 0) return 0.0f;
+  rebuild_calls(module);
+  const auto& g = *module.graph;
+  // one zero-filled scratch buffer per tensor that owns storage (zeros are valid indices for
+  // Gather and harmless operands for everything else; timing does not depend on the values)
+  Bindings bind;
+  std::vector<void*> owned;
+  bool ok = true;
+  for (size_t t = 0; t < g.tensors.size() && ok; ++t) {
+    if (g.tensors[t].alias_of >= 0) continue;
+    size_t bytes = dtypeSize(g.tensors[t].dtype);
+    for (auto d : g.tensors[t].shape) bytes *= static_cast<size_t>(d);
+    bytes = (bytes + 255) / 256 * 256 + 256;
+    void* p = nullptr;
+    if (kcg_peer_alloc(bytes, &p) != KCG_OK || kcg_device_memset(p, 0, bytes, nullptr) != KCG_OK) { ok = false; break; }
+    owned.push_back(p);
+    bind.ptrs[static_cast<int>(t)] = p;
+  }
+  float ms = FLT_MAX;
+  if (ok && runSelected(module, bind, nullptr, true) == KCG_OK) {  // warm-up (first-use set-up, caches)
+    constexpr int kRuns = 5;
+    void* timer = nullptr;
+    if (kcg_timer_begin(nullptr, &timer) == KCG_OK) {
+      int rc = KCG_OK;
+      for (int i = 0; i < kRuns && rc == KCG_OK; ++i) rc = runSelected(module, bind, nullptr, true);
+      float total = 0.f;
+      if (kcg_timer_end(nullptr, timer, &total) == KCG_OK && rc == KCG_OK && kcg_device_status() == KCG_OK)
+        ms = total / kRuns;
+    }
+  }
+  for (void* p : owned) kcg_peer_free(p);
+  return ms;
+}
+
+namespace {
+// The kernels' process-wide switches that a function's chosen config maps to.
+void apply_knobs(OpKind kind, const std::map<std::string, int>& cfg, bool restore) {
+  auto find = [&](const char* key, int& v) {
+    auto it = cfg.find(key);
+    if (it == cfg.end()) return false;
+    v = it->second;
+    return true;
+  };
+  int v = 0;
+  switch (kind) {
+    case OpKind::Matmul: case OpKind::BatchedMatmul:
+      if (find("CTA_PAIR", v)) kcg_gemm_set_pair_mode(restore ? -1 : (v ? -1 : 0));
+      break;
+    case OpKind::LayerNorm: case OpKind::FusedLayerNormGeluAdd:
+      if (find("WARP_ROW_VECS", v)) kcg_layernorm_set_warp_row_limit(restore ? 8 : v);
+      break;
+    case OpKind::FusedAttention:
+      if (find("VARIANT", v)) kcg_fmha_set_p_in_tmem(restore ? -1 : v);
+      break;
+    default: break;
+  }
+}
+}  // namespace
+
 int KernelCodeGenerator::run(Module& module, const Bindings& bindings, void* stream) {
+  return runSelected(module, bindings, stream, false);
+}
+
+int KernelCodeGenerator::runSelected(Module& module, const Bindings& bindings, void* stream, bool skipUnselected) {
   if (!module.graph) return KCG_ERR_INVALID_ARG;
   const auto& g = *module.graph;
   auto ptr = [&](int id) -> void* {
@@ -224,6 +322,7 @@ int KernelCodeGenerator::run(Module& module, const Bindings& bindings, void* str
   for (const auto& c : module.calls) {
     const auto& op = g.ops[c.op];
     const auto& info = g.funcs.at(op.func);
+    if (info.state != "gpu" && skipUnselected) continue;
     if (info.state != "gpu") {
       std::cerr << "run: no optimizer selected a kernel for @" << op.func
                 << " (push the matching Optimizer into opts); there is no CPU execution path.\n";
@@ -246,6 +345,7 @@ int KernelCodeGenerator::run(Module& module, const Bindings& bindings, void* str
     const auto& t0 = g.tensors[op.inputs[0]];
     const auto& to = g.tensors[op.output];
     int rc = KCG_OK;
+    apply_knobs(op.kind, info.config, false);
     switch (op.kind) {
       case OpKind::Matmul: {
         const int64_t m = t0.shape[0], k = t0.shape[1], n = g.tensors[op.inputs[1]].shape[1];
@@ -337,6 +437,7 @@ int KernelCodeGenerator::run(Module& module, const Bindings& bindings, void* str
         break;
       }
     }
+    apply_knobs(op.kind, info.config, true);
     if (rc != KCG_OK) {
       std::cerr << "run: " << c.entry << " for @" << op.func << " failed: " << kcg_last_error() << "\n";
       return rc;

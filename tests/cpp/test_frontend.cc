@@ -217,6 +217,28 @@ static void test_gather_transpose_graph() {  // test/test.cc:17-23 (the commente
   CHECK(has(plan, "launch kcg_gather") && has(plan, "launch kcg_transpose"));
 }
 
+static void test_config_candidates_without_autotune() {
+  // evaluate() is 0 without autotuning, so the first entry of each table is the one recorded
+  KernelCodeGenerator generator("CUDA");
+  generator.opts.push_back(std::make_unique<MatmulOptimizer>());
+  generator.opts.push_back(std::make_unique<LayerNormOptimizer>());
+  CHECK(generator.configs("Matmul") && generator.configs("Matmul")->size() >= 2);
+  CHECK(generator.configs("nope") == nullptr);
+  auto graph = generator.createGraph("cands");
+  auto A = graph.create<PlaceHolder>(std::vector<int64_t>{512, 256}, std::string{"bfloat16"});
+  auto B = graph.create<PlaceHolder>(std::vector<int64_t>{256, 512}, std::string{"bfloat16"});
+  auto C = graph.create<Matmul>(A, B);
+  auto gm = graph.create<PlaceHolder>(std::vector<int64_t>{512}, std::string{"bfloat16"});
+  auto Y = graph.create<LayerNorm>(C, gm, gm, int64_t(1), 1e-5f);
+  auto module = generator.optimize(graph);
+  CHECK(generator.evaluate(module) == 0.0f && generator.bestLatency() == 0.0f);
+  CHECK(module.graph->funcs.at("Matmul_m512n512k256").config.at("CTA_PAIR") == generator.configs("Matmul")->front().at("CTA_PAIR"));
+  CHECK(module.graph->funcs.at("LayerNorm_512_512_axis_1").config.at("WARP_ROW_VECS") == 8);
+  auto plan = generator.codegen(module);
+  CHECK(has(plan, "CTA_PAIR=1") && has(plan, "WARP_ROW_VECS=8"));   // the choice is part of the saved plan
+  (void)Y;
+}
+
 static void test_errors() {
   KernelCodeGenerator generator("CUDA");
   auto graph = generator.createGraph("errors");
@@ -493,6 +515,57 @@ static void gpu_gather_transpose() {  // embedding-style row gather, then a tran
   CHECK(ok);
 }
 
+static void gpu_autotune() {  // every candidate timed on the device; any choice gives the same bits
+  auto build = [](KernelCodeGenerator& generator, Value& A, Value& B, Value& gm, Value& C, Value& Y) {
+    generator.opts.push_back(std::make_unique<MatmulOptimizer>());
+    generator.opts.push_back(std::make_unique<LayerNormOptimizer>());
+    auto graph = generator.createGraph("tuned");
+    A = graph.create<PlaceHolder>(std::vector<int64_t>{1024, 512}, std::string{"bfloat16"});
+    B = graph.create<PlaceHolder>(std::vector<int64_t>{512, 2048}, std::string{"bfloat16"});
+    C = graph.create<Matmul>(A, B);
+    gm = graph.create<PlaceHolder>(std::vector<int64_t>{2048}, std::string{"bfloat16"});
+    Y = graph.create<LayerNorm>(C, gm, gm, int64_t(1), 1e-5f);
+    return graph;
+  };
+  auto hA32 = randn(size_t(1024) * 512, 51), hB32 = randn(size_t(512) * 2048, 52), hg32 = randn(2048, 53);
+  std::vector<uint16_t> hA(hA32.size()), hB(hB32.size()), hg(hg32.size());
+  for (size_t i = 0; i < hA.size(); ++i) hA[i] = to_bf16(hA32[i] * 0.05f);
+  for (size_t i = 0; i < hB.size(); ++i) hB[i] = to_bf16(hB32[i]);
+  for (size_t i = 0; i < hg.size(); ++i) hg[i] = to_bf16(1.0f + 0.1f * hg32[i]);
+  std::vector<std::vector<uint16_t>> results;
+  for (int tuned = 0; tuned < 2; ++tuned) {
+    KernelCodeGenerator generator("CUDA");
+    generator.autotune = tuned == 1;
+    Value A, B, gm, C, Y;
+    auto graph = build(generator, A, B, gm, C, Y);
+    auto module = generator.optimize(graph);
+    if (tuned) {
+      CHECK(generator.bestLatency() > 0.0f && generator.bestLatency() < 1e3f);   // a measured time, in ms
+      const auto& cfg = module.graph->funcs.at("LayerNorm_1024_2048_axis_1").config;
+      bool known = false;
+      for (const auto& cand : *generator.configs("LayerNorm")) known = known || cand == cfg;
+      CHECK(known);
+      std::printf("autotune kept CTA_PAIR=%d WARP_ROW_VECS=%d, %.4f ms\n",
+                  module.graph->funcs.at("Matmul_m1024n2048k512").config.at("CTA_PAIR"), cfg.at("WARP_ROW_VECS"),
+                  generator.bestLatency());
+    }
+    Bindings bind;
+    void* dY = upload(nullptr, size_t(1024) * 2048 * 2);
+    bind.set(A, upload(hA.data(), hA.size() * 2));
+    bind.set(B, upload(hB.data(), hB.size() * 2));
+    bind.set(gm, upload(hg.data(), hg.size() * 2));
+    bind.set(C, upload(nullptr, size_t(1024) * 2048 * 2));
+    bind.set(Y, dY);
+    CHECK(generator.run(module, bind) == KCG_OK);
+    cudaDeviceSynchronize();
+    CHECK(kcg_device_status() == KCG_OK);
+    std::vector<uint16_t> out(size_t(1024) * 2048);
+    cudaMemcpy(out.data(), dY, out.size() * 2, 2);
+    results.push_back(out);
+  }
+  CHECK(results[0] == results[1]);
+}
+
 int main(int argc, char** argv) {
   const std::string mode = argc > 1 ? argv[1] : "cpu";
   if (mode == "cpu") {
@@ -501,6 +574,7 @@ int main(int argc, char** argv) {
     test_flash_attention_graph();
     test_kernel_fusion();
     test_gather_transpose_graph();
+    test_config_candidates_without_autotune();
     test_errors();
   } else {
     gpu_matmul_relu();
@@ -508,6 +582,7 @@ int main(int argc, char** argv) {
     gpu_kernel_fusion();
     gpu_fused_attention();
     gpu_gather_transpose();
+    gpu_autotune();
   }
   if (failures) {
     std::fprintf(stderr, "%d check(s) failed\n", failures);

@@ -75,7 +75,8 @@ def test_gather_negative_and_out_of_range_indices():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.int32, torch.int64, torch.uint8])
-@pytest.mark.parametrize("shape", [(1, 1), (32, 32), (64, 64), (33, 65), (3, 100, 7), (2, 2, 129, 255), (1024, 4096)])
+@pytest.mark.parametrize("shape", [(1, 1), (32, 32), (64, 64), (33, 65), (3, 100, 7), (2, 2, 129, 255), (1024, 4096),
+                                   (3, 128, 256), (192, 128), (2, 64, 384)])
 def test_transpose_bit_exact(shape, dtype):
     g = torch.Generator(device="cpu").manual_seed(730)
     if dtype.is_floating_point:
