@@ -233,7 +233,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM/FMHA/fp32 side measurements")
-    ap.add_argument("--only", default="", help="comma list of extras to run (bw,fp32,gemm,sgemm,fmha,sweep,gather)")
+    ap.add_argument("--only", default="", help="comma list of extras to run (bw,fp32,gemm,sgemm,fmha,move,sweep,gather)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -509,6 +509,24 @@ def main() -> None:
                 "frac_of_measured_bf16_peak": tf / world / peaks["bf16_tflops"],
                 "frac_of_nominal_2250": tf / world / 2250.0}
         del Q, K, V, Oo
+        torch.cuda.empty_cache()
+    if want("move"):
+        # data-movement operators: embedding-style row gather and a batched transpose
+        rows_t, width, n_idx = 200000, 4096, 131072
+        table = rnd((rows_t, width))
+        idx = torch.randint(0, rows_t, (n_idx,), generator=gen, device="cuda")
+        out = torch.empty((n_idx, width), dtype=dt, device="cuda")
+        ms = time_op(lambda: ops.gather(table, idx, 0, out=out), 20)
+        gbs = world * 2 * out.numel() * 2 / (ms * 1e-3) / 1e9
+        workloads["gather_rows_bf16_131072x4096"] = {"ms": ms, "value": gbs, "unit": "GB/s",
+                                                     "frac_of_hbm_peak": gbs / world / peaks["hbm_gbs"]}
+        del table, idx, out
+        x = rnd((4, 8192, 8192)); y = torch.empty((4, 8192, 8192), dtype=dt, device="cuda")
+        ms = time_op(lambda: ops.transpose(x, out=y), 20)
+        gbs = world * 2 * x.numel() * 2 / (ms * 1e-3) / 1e9
+        workloads["transpose_bf16_4x8192x8192"] = {"ms": ms, "value": gbs, "unit": "GB/s",
+                                                   "frac_of_hbm_peak": gbs / world / peaks["hbm_gbs"]}
+        del x, y
         torch.cuda.empty_cache()
     if want("sweep"):
         # the other sizes of the GEMM and FMHA configurations (per GPU; N ranks run N copies)
