@@ -223,29 +223,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           __syncwarp();
         }
       } else {
-#pragma unroll 1
-      for (int c = 0; c < PBN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_base + c * 32, r);
-        tmem_wait_ld();
-        if (row < p.M) {
-          const int64_t cbase = col0 + c * 32;
-#pragma unroll
-          for (int g = 0; g < 32 / VW; ++g) {
-            const int64_t col = cbase + g * VW;
-            if (p.c_vec_ok && col + VW <= p.N) {
-              Vec16<TOut> o;
-#pragma unroll
-              for (int j = 0; j < VW; ++j) o.v[j] = gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act);
-              st_vec(crow + col, o);
-            } else {
-#pragma unroll
-              for (int j = 0; j < VW; ++j)
-                if (col + j < p.N) crow[col + j] = gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act);
-            }
-          }
-        }
-      }
+        epilogue_row<TOut, PBN>(t_base, crow, row < p.M, col0, p, alpha, bias);
       }
       tc_fence_before();
       __syncwarp();

@@ -76,6 +76,70 @@ __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, i
   nt = in_group / gsize;
 }
 
+// 16 bytes of output from VW consecutive accumulators scaled by alpha (no bias, no activation):
+// the same fmul + round-to-nearest as gemm_epilogue_value, with two results per conversion.
+template <typename TOut> __device__ __forceinline__ uint4 scale_pack16(const uint32_t* r, float alpha);
+template <> __device__ __forceinline__ uint4 scale_pack16<float>(const uint32_t* r, float alpha) {
+  return make_uint4(__float_as_uint(alpha * __uint_as_float(r[0])), __float_as_uint(alpha * __uint_as_float(r[1])),
+                    __float_as_uint(alpha * __uint_as_float(r[2])), __float_as_uint(alpha * __uint_as_float(r[3])));
+}
+template <> __device__ __forceinline__ uint4 scale_pack16<__nv_bfloat16>(const uint32_t* r, float alpha) {
+  uint4 o;
+  __nv_bfloat162 v;
+  v = __floats2bfloat162_rn(alpha * __uint_as_float(r[0]), alpha * __uint_as_float(r[1])); o.x = *reinterpret_cast<uint32_t*>(&v);
+  v = __floats2bfloat162_rn(alpha * __uint_as_float(r[2]), alpha * __uint_as_float(r[3])); o.y = *reinterpret_cast<uint32_t*>(&v);
+  v = __floats2bfloat162_rn(alpha * __uint_as_float(r[4]), alpha * __uint_as_float(r[5])); o.z = *reinterpret_cast<uint32_t*>(&v);
+  v = __floats2bfloat162_rn(alpha * __uint_as_float(r[6]), alpha * __uint_as_float(r[7])); o.w = *reinterpret_cast<uint32_t*>(&v);
+  return o;
+}
+template <> __device__ __forceinline__ uint4 scale_pack16<__half>(const uint32_t* r, float alpha) {
+  uint4 o;
+  __half2 v;
+  v = __floats2half2_rn(alpha * __uint_as_float(r[0]), alpha * __uint_as_float(r[1])); o.x = *reinterpret_cast<uint32_t*>(&v);
+  v = __floats2half2_rn(alpha * __uint_as_float(r[2]), alpha * __uint_as_float(r[3])); o.y = *reinterpret_cast<uint32_t*>(&v);
+  v = __floats2half2_rn(alpha * __uint_as_float(r[4]), alpha * __uint_as_float(r[5])); o.z = *reinterpret_cast<uint32_t*>(&v);
+  v = __floats2half2_rn(alpha * __uint_as_float(r[6]), alpha * __uint_as_float(r[7])); o.w = *reinterpret_cast<uint32_t*>(&v);
+  return o;
+}
+
+// Epilogue of one thread for its row of a finished accumulator (kTileN columns starting at
+// col0): tensor memory is read 64 columns per round trip; full, aligned blocks without bias or
+// activation take the packed path above, everything else goes element by element.
+template <typename TOut, int kTileN>
+__device__ __forceinline__ void epilogue_row(uint32_t t_base, TOut* crow, bool row_ok, int64_t col0,
+                                             const GemmParams& p, float alpha, const TOut* bias) {
+  constexpr int VW = Vec16<TOut>::N;
+  const bool plain = bias == nullptr && p.act == 0 && p.c_vec_ok != 0;
+#pragma unroll 1
+  for (int c = 0; c < kTileN / 64; ++c) {
+    uint32_t r[64];
+    tmem_ld64(t_base + c * 64, r);
+    tmem_wait_ld();
+    if (!row_ok) continue;
+    const int64_t cbase = col0 + c * 64;
+    if (plain && cbase + 64 <= p.N) {
+#pragma unroll
+      for (int g = 0; g < 64 / VW; ++g)
+        *reinterpret_cast<uint4*>(crow + cbase + g * VW) = scale_pack16<TOut>(&r[g * VW], alpha);
+    } else {
+#pragma unroll
+      for (int g = 0; g < 64 / VW; ++g) {
+        const int64_t col = cbase + g * VW;
+        if (p.c_vec_ok && col + VW <= p.N) {
+          Vec16<TOut> o;
+#pragma unroll
+          for (int j = 0; j < VW; ++j) o.v[j] = gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act);
+          st_vec(crow + col, o);
+        } else {
+#pragma unroll
+          for (int j = 0; j < VW; ++j)
+            if (col + j < p.N) crow[col + j] = gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act);
+        }
+      }
+    }
+  }
+}
+
 template <Kind kKind, int kElemBytes, bool kAMn, bool kBMn, typename TOut>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -226,30 +290,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int64_t col0 = static_cast<int64_t>(nt) * BN;
       TOut* crow = static_cast<TOut*>(p.C) + b * p.stride_c + row * p.ldc;
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-      constexpr int VW = Vec16<TOut>::N;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_base + c * 32, r);
-        tmem_wait_ld();
-        if (row < p.M) {
-          const int64_t cbase = col0 + c * 32;
-#pragma unroll
-          for (int g = 0; g < 32 / VW; ++g) {
-            const int64_t col = cbase + g * VW;
-            if (p.c_vec_ok && col + VW <= p.N) {
-              Vec16<TOut> o;
-#pragma unroll
-              for (int j = 0; j < VW; ++j) o.v[j] = gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act);
-              st_vec(crow + col, o);
-            } else {
-#pragma unroll
-              for (int j = 0; j < VW; ++j)
-                if (col + j < p.N) crow[col + j] = gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act);
-            }
-          }
-        }
-      }
+      epilogue_row<TOut, BN>(t_base, crow, row < p.M, col0, p, alpha, bias);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
