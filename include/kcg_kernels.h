@@ -282,10 +282,11 @@ KCG_API int kcg_gemm_fused(int dtype_in, int dtype_out, int64_t M, int64_t N, in
                            const float* scale_b, const void* bias, int activation, void* stream);
 
 /*
- * Tuning switch with no counterpart in the reference: -1 (default) runs the tensor-core GEMM on
- * CTA pairs (tcgen05 cta_group::2, 256x256 tile per pair) when M >= 256 and on single CTAs
- * (128x256 tile) otherwise; 0 forces single CTAs; 1 uses pairs whenever M > 128.  Results are
- * identical.  Process-wide, not thread-safe.
+ * Tuning switch with no counterpart in the reference, choosing the tile of the tensor-core
+ * GEMM: -1 (default) picks, per problem, whichever of the three shapes below fills the SMs most
+ * evenly (large problems get CTA pairs); 0 forces 128x256 tiles on single CTAs; 1 forces CTA
+ * pairs (tcgen05 cta_group::2, one 256x256 tile per two SMs) whenever M > 128; 2 forces 128x128
+ * tiles on single CTAs.  Results are identical.  Process-wide, not thread-safe.
  */
 KCG_API void kcg_gemm_set_pair_mode(int mode);
 

@@ -34,15 +34,13 @@ int* device_status_word();  // runtime.cu: host-mapped word the kernels report f
 namespace {
 using namespace sm100;
 
-constexpr int BM = 128, BN = 256, STAGES = 4;
+constexpr int BM = 128, BN = 256;
 constexpr int A_BYTES = BM * 128;
-constexpr int B_BYTES = BN * 128;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int GROUP_M = 16;
 #define KCG_MAX_EXTRA_C 7
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = 4 * (A_BYTES + BN * 128) + 1024 + 256;   // = 6 * (A_BYTES + 128 * 128) + ... for the narrow tile
 
 struct GemmParams {
   void* C;
@@ -140,10 +138,17 @@ __device__ __forceinline__ void epilogue_row(uint32_t t_base, TOut* crow, bool r
   }
 }
 
-template <Kind kKind, int kElemBytes, bool kAMn, bool kBMn, typename TOut>
+// kBN: width of the CTA tile, 256 (4-stage ring of 48 KB) or 128 (6 stages of 32 KB).  The narrow
+// tile costs more shared-memory and L2 traffic per flop but quantises better: it is chosen when
+// the problem has too few 128x256 tiles to fill the SMs evenly (see pick_tiling()).
+template <Kind kKind, int kElemBytes, bool kAMn, bool kBMn, typename TOut, int kBN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmParams p, const uint32_t idesc) {
+  constexpr int BN = kBN;
+  constexpr int B_BYTES = BN * 128;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int STAGES = kBN == 256 ? 4 : 6;
   constexpr int BK = 128 / kElemBytes;             // elements per k-block (128 bytes of K)
   constexpr int UMMA_K = 32 / kElemBytes;          // elements per MMA (32 bytes of K)
   constexpr int MN_BOX = 128 / kElemBytes;         // inner extent of an MN-major TMA box
@@ -364,46 +369,82 @@ int encode_tmap_sw128(CUtensorMap* out, int dtype, const void* base, int rank, c
 
 namespace {
 
-int g_pair_mode = -1;  // -1: CTA pairs when M >= 256; 0: never; 1: whenever the grid allows
+int g_pair_mode = -1;  // -1: pick_tiling(); 0: 128x256 single CTA; 1: CTA pairs when M > 128; 2: 128x128 single CTA
+
+enum Tiling { kWide = 0, kPair = 1, kNarrow = 2 };
+struct Idescs { uint32_t wide, pair, narrow; };
+
+// Chooses the CTA tile from a small cost model fitted to measurements on a B200 (microseconds):
+// waves of tiles x time of one tile's main loop + a fixed cost per launch.  A 128x128 block of
+// output costs an SM about 2.1 ns per unit of K (64 clocks per 16 of K at ~1.9 GHz); the 256x256
+// pair tile and the 128x256 tile are two such blocks per SM, the latter ~4 % slower per flop;
+// the 128x128 tile is one block but runs at the shared-memory bandwidth limit (A and B tiles are
+// equally large), ~40 % slower per flop, and only pays when the wider shapes leave most SMs idle.
+// Fixed costs (launch, pipeline fill, the last tile's epilogue): 5.7 / 6.9 / 5.0 us measured for
+// wide / pair / narrow.
+Tiling pick_tiling(int64_t M, int64_t N, int64_t K, int64_t batch, int elem_bytes, int sms) {
+  auto cdiv = [](int64_t a, int64_t b) { return (a + b - 1) / b; };
+  const double unit = 2.1e-3 * static_cast<double>(K) * (elem_bytes == 1 ? 0.5 : 1.0);  // 8-bit inputs run at twice the rate
+  const int64_t wide = cdiv(M, 128) * cdiv(N, 256) * batch, narrow = cdiv(M, 128) * cdiv(N, 128) * batch;
+  const int64_t pairs = cdiv(M, 256) * cdiv(N, 256) * batch;
+  const double c_wide = static_cast<double>(cdiv(wide, sms)) * 2 * 1.04 * unit + 5.7;
+  const double c_narrow = static_cast<double>(cdiv(narrow, sms)) * 1.40 * unit + 5.0;
+  const double c_pair = M >= 2 * BM ? static_cast<double>(cdiv(pairs, sms / 2)) * 2 * unit + 6.9 : 1e30;
+  if (c_pair <= c_wide && c_pair <= c_narrow) return kPair;
+  return c_narrow < c_wide ? kNarrow : kWide;
+}
 
 template <Kind kKind, int kElemBytes, bool kAMn, bool kBMn, typename TOut>
 int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB_pair, const GemmParams& p,
-                   uint32_t idesc, uint32_t idesc_pair, bool pair, cudaStream_t stream) {
+                   const Idescs& idescs, Tiling tiling, cudaStream_t stream) {
   const int sms = sm_count();
-  if (pair) {
+  if (tiling == kPair) {
     auto kern = gemm_tcgen05_pair_kernel<kKind, kElemBytes, kAMn, kBMn, TOut>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PSMEM_BYTES);
     if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     const int64_t batch = p.total_tiles / (static_cast<int64_t>(p.m_tiles) * p.n_tiles);
     const int64_t pair_tiles = static_cast<int64_t>((p.m_tiles + 1) / 2) * p.n_tiles * batch;
     const int64_t clusters = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
-    kern<<<static_cast<int>(clusters * 2), NUM_THREADS, PSMEM_BYTES, stream>>>(tmA, tmB_pair, p, idesc_pair);
+    kern<<<static_cast<int>(clusters * 2), NUM_THREADS, PSMEM_BYTES, stream>>>(tmA, tmB_pair, p, idescs.pair);
     return check_launch("gemm_tcgen05_pair_kernel");
   }
-  auto kern = gemm_tcgen05_kernel<kKind, kElemBytes, kAMn, kBMn, TOut>;
+  if (tiling == kNarrow) {
+    // 128x128 tiles: the half-width B box is the one the pair kernel's map already describes
+    GemmParams q = p;
+    q.n_tiles = static_cast<int>((p.N + 127) / 128);
+    q.total_tiles = static_cast<int64_t>(q.m_tiles) * q.n_tiles * (p.total_tiles / (static_cast<int64_t>(p.m_tiles) * p.n_tiles));
+    auto kern = gemm_tcgen05_kernel<kKind, kElemBytes, kAMn, kBMn, TOut, 128>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    const int grid = static_cast<int>(q.total_tiles < sms ? q.total_tiles : sms);
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB_pair, q, idescs.narrow);
+    return check_launch("gemm_tcgen05_kernel (128x128)");
+  }
+  auto kern = gemm_tcgen05_kernel<kKind, kElemBytes, kAMn, kBMn, TOut, 256>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   const int grid = static_cast<int>(p.total_tiles < sms ? p.total_tiles : sms);
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p, idesc);
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p, idescs.wide);
   return check_launch("gemm_tcgen05_kernel");
 }
 
 template <Kind kKind, int kElemBytes, typename TOut>
 int launch_layout(int trans_a, int trans_b, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmBp,
-                  const GemmParams& p, uint32_t idesc, uint32_t idesc_pair, bool pair, cudaStream_t s) {
+                  const GemmParams& p, const Idescs& idescs, Tiling tiling, cudaStream_t s) {
   // trans_a != 0: A is [K, M] row-major -> MN-major operand; trans_b == 0: B is [K, N] -> MN-major.
   if (!trans_a && trans_b)
-    return launch_variant<kKind, kElemBytes, false, false, TOut>(tmA, tmB, tmBp, p, idesc, idesc_pair, pair, s);
+    return launch_variant<kKind, kElemBytes, false, false, TOut>(tmA, tmB, tmBp, p, idescs, tiling, s);
   if (!trans_a && !trans_b)
-    return launch_variant<kKind, kElemBytes, false, true, TOut>(tmA, tmB, tmBp, p, idesc, idesc_pair, pair, s);
+    return launch_variant<kKind, kElemBytes, false, true, TOut>(tmA, tmB, tmBp, p, idescs, tiling, s);
   if (trans_a && trans_b)
-    return launch_variant<kKind, kElemBytes, true, false, TOut>(tmA, tmB, tmBp, p, idesc, idesc_pair, pair, s);
-  return launch_variant<kKind, kElemBytes, true, true, TOut>(tmA, tmB, tmBp, p, idesc, idesc_pair, pair, s);
+    return launch_variant<kKind, kElemBytes, true, false, TOut>(tmA, tmB, tmBp, p, idescs, tiling, s);
+  return launch_variant<kKind, kElemBytes, true, true, TOut>(tmA, tmB, tmBp, p, idescs, tiling, s);
 }
 
 }  // namespace
 
-// -1 (default): CTA pairs (cta_group::2) when M >= 256; 0: single-CTA kernel only; 1: pairs when M > 128.
+// -1 (default): tile shape chosen by pick_tiling(); 0: 128x256 single-CTA tiles; 1: CTA pairs
+// (cta_group::2, 256x256) whenever M > 128; 2: 128x128 single-CTA tiles.
 extern "C" __attribute__((visibility("default"))) void kcg_gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
 
 int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
@@ -423,12 +464,15 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
 
   const int BK = 128 / es;
   const uint32_t mn_box = 128 / es;
-  bool pair = g_pair_mode == 0 ? false : (g_pair_mode == 1 ? M > BM : M >= 2 * BM);
+  Tiling tiling = g_pair_mode == 0 ? kWide
+                  : g_pair_mode == 2 ? kNarrow
+                  : g_pair_mode == 1 ? (M > BM ? kPair : kWide)
+                                     : pick_tiling(M, N, K, batch, es, sm_count());
   if (n_extra > 0) {
     // only the CTA-pair kernel has the staged epilogue that writes whole 128-byte row segments
     if (n_extra > KCG_MAX_EXTRA_C) return fail(KCG_ERR_UNSUPPORTED, "gemm: at most %d extra outputs", KCG_MAX_EXTRA_C);
     if (M <= BM) return fail(KCG_ERR_UNSUPPORTED, "gemm: extra outputs need M > 128 (got %lld)", static_cast<long long>(M));
-    pair = true;
+    tiling = kPair;
   }
   CUtensorMap tmA, tmB, tmBp;
   {
@@ -481,20 +525,22 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
 
   const uint32_t a_mn = trans_a ? 1u : 0u, b_mn = trans_b ? 0u : 1u;
   if (dtype_in == KCG_F8E4M3) {
-    const uint32_t idesc = make_idesc(0, 0, a_mn, b_mn, BM, BN), idesc_p = make_idesc(0, 0, a_mn, b_mn, 2 * BM, BN);
+    const Idescs ids = {make_idesc(0, 0, a_mn, b_mn, BM, BN), make_idesc(0, 0, a_mn, b_mn, 2 * BM, BN),
+                        make_idesc(0, 0, a_mn, b_mn, BM, 128)};
     if (dtype_out == KCG_BF16)
-      return launch_layout<Kind::F8F6F4, 1, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, tmBp, p, idesc, idesc_p, pair, stream);
+      return launch_layout<Kind::F8F6F4, 1, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, tmBp, p, ids, tiling, stream);
     if (dtype_out == KCG_F32)
-      return launch_layout<Kind::F8F6F4, 1, float>(trans_a, trans_b, tmA, tmB, tmBp, p, idesc, idesc_p, pair, stream);
+      return launch_layout<Kind::F8F6F4, 1, float>(trans_a, trans_b, tmA, tmB, tmBp, p, ids, tiling, stream);
     return fail(KCG_ERR_UNSUPPORTED, "gemm: float8_e4m3 inputs produce bfloat16 or float32 (got dtype %d)", dtype_out);
   }
   const uint32_t fmt = dtype_in == KCG_BF16 ? 1u : 0u;
-  const uint32_t idesc = make_idesc(fmt, fmt, a_mn, b_mn, BM, BN), idesc_p = make_idesc(fmt, fmt, a_mn, b_mn, 2 * BM, BN);
-  if (dtype_out == KCG_F32) return launch_layout<Kind::F16, 2, float>(trans_a, trans_b, tmA, tmB, tmBp, p, idesc, idesc_p, pair, stream);
+  const Idescs ids = {make_idesc(fmt, fmt, a_mn, b_mn, BM, BN), make_idesc(fmt, fmt, a_mn, b_mn, 2 * BM, BN),
+                      make_idesc(fmt, fmt, a_mn, b_mn, BM, 128)};
+  if (dtype_out == KCG_F32) return launch_layout<Kind::F16, 2, float>(trans_a, trans_b, tmA, tmB, tmBp, p, ids, tiling, stream);
   if (dtype_in == KCG_BF16 && dtype_out == KCG_BF16)
-    return launch_layout<Kind::F16, 2, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, tmBp, p, idesc, idesc_p, pair, stream);
+    return launch_layout<Kind::F16, 2, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, tmBp, p, ids, tiling, stream);
   if (dtype_in == KCG_F16 && dtype_out == KCG_F16)
-    return launch_layout<Kind::F16, 2, __half>(trans_a, trans_b, tmA, tmB, tmBp, p, idesc, idesc_p, pair, stream);
+    return launch_layout<Kind::F16, 2, __half>(trans_a, trans_b, tmA, tmB, tmBp, p, ids, tiling, stream);
   return fail(KCG_ERR_UNSUPPORTED, "gemm: dtype combination %d -> %d has no kernel", dtype_in, dtype_out);
 }
 

@@ -78,7 +78,9 @@ KernelCodeGenerator::KernelCodeGenerator(const std::string& platform_) : platfor
   matmulConfigs = {{{"BLOCK_SIZE_M", 256}, {"BLOCK_SIZE_N", 256}, {"BLOCK_SIZE_K", 64}, {"GROUP_SIZE_M", 8},
                     {"STAGES", 6}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}, {"CTA_PAIR", 1}},
                    {{"BLOCK_SIZE_M", 128}, {"BLOCK_SIZE_N", 256}, {"BLOCK_SIZE_K", 64}, {"GROUP_SIZE_M", 16},
-                    {"STAGES", 4}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}, {"CTA_PAIR", 0}}};
+                    {"STAGES", 4}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}, {"CTA_PAIR", 0}},
+                   {{"BLOCK_SIZE_M", 128}, {"BLOCK_SIZE_N", 128}, {"BLOCK_SIZE_K", 64}, {"GROUP_SIZE_M", 16},
+                    {"STAGES", 6}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}, {"CTA_PAIR", 0}}};
   batchMatmulConfigs = matmulConfigs;
   binaryConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
   elementWiseConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
@@ -289,7 +291,12 @@ void apply_knobs(OpKind kind, const std::map<std::string, int>& cfg, bool restor
   int v = 0;
   switch (kind) {
     case OpKind::Matmul: case OpKind::BatchedMatmul:
-      if (find("CTA_PAIR", v)) kcg_gemm_set_pair_mode(restore ? -1 : (v ? -1 : 0));
+      if (find("CTA_PAIR", v)) {
+        int bn = 256;
+        find("BLOCK_SIZE_N", bn);
+        // CTA_PAIR=1: the library's own choice; 0: single-CTA tiles of the stated width
+        kcg_gemm_set_pair_mode(restore ? -1 : (v ? -1 : (bn == 128 ? 2 : 0)));
+      }
       break;
     case OpKind::LayerNorm: case OpKind::FusedLayerNormGeluAdd:
       if (find("WARP_ROW_VECS", v)) kcg_layernorm_set_warp_row_limit(restore ? 8 : v);
