@@ -617,6 +617,40 @@ def main() -> None:
         del A, B, Cl, Cg
         bufs.close()
         torch.cuda.empty_cache()
+        # the same comparison for attention: 8 batches x 32 heads per rank, S = 4096, D = 128, causal
+        Bq, H, S, D = 8, 32, 4096, 128
+        Q, K, V = rnd((Bq, H, S, D)), rnd((Bq, H, S, D)), rnd((Bq, H, S, D))
+        fb = shard.GatherBuffers(world * Bq * H * S, D, dt)
+        Ol = torch.empty_like(Q)
+        Og = torch.empty((world * Bq, H, S, D), dtype=dt, device="cuda")
+
+        def fused_attn():
+            shard.fmha_allgather(Q, K, V, fb, world * Bq, D ** -0.5, True, sync=False)
+            shard.stream_barrier()
+
+        def nccl_attn():
+            ops.fmha(Q, K, V, D ** -0.5, True, out=Ol)
+            dist.all_gather_into_tensor(Og, Ol)
+
+        fl = 2 * Bq * H * S * (S + 1) * D
+        for name, fn in (("fmha_allgather_fused_epilogue", fused_attn), ("fmha_then_nccl_allgather", nccl_attn)):
+            for _ in range(3):
+                fn()
+            barrier()
+            e0.record()
+            for _ in range(5):
+                fn()
+            e1.record()
+            barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1)) / 5
+            workloads[name] = {"ms": ms, "value": world * fl / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                               "bytes_sent_per_gpu": (world - 1) * Q.numel() * 2,
+                               "link_gbs_per_gpu": (world - 1) * Q.numel() * 2 / (ms * 1e-3) / 1e9}
+        workloads["fmha_allgather_fused_epilogue"]["bit_identical_to_nccl_path"] = bool(
+            torch.equal(fb.local.view(world * Bq, H, S, D), Og))
+        del Q, K, V, Ol, Og
+        fb.close()
+        torch.cuda.empty_cache()
     if rank == 0 and world == 1 and not args.no_extras:
         cpu_side_by_side(workloads)
     if _lib.device_status() != 0:

@@ -371,6 +371,23 @@ KCG_API int kcg_gemm_allgather(int dtype_in, int dtype_out, int64_t M, int64_t N
                                void* stream);
 
 /*
+ * Attention forward with the all-gather of O done by its epilogue (no counterpart in the
+ * reference).  Rank `rank` of `world` (<= 8) computes its B batches exactly as kcg_fmha_fwd would
+ * (two-tile kernel, same bits) and stores every output row into batches [batch_offset,
+ * batch_offset + B) of each rank's gathered tensor gathered[r] (element strides o_strides, as
+ * for kcg_fmha_fwd); gathered[rank] is local, the others are peers' buffers mapped with
+ * kcg_peer_open.  Rows leave as whole D-element lines (256 bytes at D = 128).  Synchronise the
+ * ranks as for kcg_gemm_allgather.
+ */
+KCG_API int kcg_fmha_fwd_allgather(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv,
+                                   int64_t D, float softmax_scale, int causal, const void* Q,
+                                   const int64_t q_strides[3], const void* K,
+                                   const int64_t k_strides[3], const void* V,
+                                   const int64_t v_strides[3], void* const* gathered, int world,
+                                   int rank, int64_t batch_offset, const int64_t o_strides[3],
+                                   void* stream);
+
+/*
  * Device memory that other processes on the node can map (CUDA IPC).  kcg_peer_alloc returns a
  * plain device allocation; kcg_peer_export fills a 64-byte handle that another process passes
  * to kcg_peer_open to obtain a pointer valid on its own GPU (peer access is enabled on first

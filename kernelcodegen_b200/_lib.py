@@ -53,6 +53,8 @@ SIGNATURES = {
     "kcg_peer_close": ([_vp], _ci),
     "kcg_fmha_fwd": ([_ci, _i64, _i64, _i64, _i64, _i64, _fp, _ci, _vp, _i64p, _vp, _i64p, _vp, _i64p, _vp, _i64p,
                       _vp], _ci),
+    "kcg_fmha_fwd_allgather": ([_ci, _i64, _i64, _i64, _i64, _i64, _fp, _ci, _vp, _i64p, _vp, _i64p, _vp, _i64p,
+                                ctypes.POINTER(_vp), _ci, _ci, _i64, _i64p, _vp], _ci),
     "kcg_fmha_set_p_in_tmem": ([_ci], None),
     "kcg_gather": ([_ci, _ci, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp], _ci),
     "kcg_transpose": ([_ci, _i64, _i64, _i64, _vp, _vp, _vp], _ci),

@@ -48,6 +48,10 @@ struct FmhaParams {
   int causal;
   int q_tiles;
   int* status;
+  // further copies of O (same strides), typically this rank's slices inside the gather buffers
+  // of peer GPUs; written by the two-tile kernel's epilogue
+  void* extra_o[7];
+  int n_extra;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -678,6 +682,50 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const float inv_l = l > 0.f ? 1.0f / l : 0.f;
       T* orow = static_cast<T*>(p.O) + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh +
                 static_cast<int64_t>(qi) * p.o_ss;
+      if (p.n_extra > 0) {
+        // Staged stores for remote destinations: this warp's 32 output rows pass through the
+        // (now idle) shared memory of its Q tile, swizzled, and leave as whole rows of D
+        // elements (256 bytes at D = 128), so that a store to another GPU's memory carries full
+        // lines; every destination receives the same registers.
+        constexpr int ROWB = D * 2;          // bytes per output row
+        constexpr int CH = ROWB / 16;        // 16-byte chunks per row
+        constexpr int RPI = 32 / CH;         // rows per store instruction
+        uint8_t* stg = q_smem + i * TILE + quarter * (32 * ROWB);
+#pragma unroll 1
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t oreg[32];
+          if (n_mine > 0) {
+            tmem_ld32(o_addr + cc * 32, oreg);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) oreg[k] = 0u;
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack2<T>(__uint_as_float(oreg[g * 8 + 0]) * inv_l, __uint_as_float(oreg[g * 8 + 1]) * inv_l);
+            o.y = pack2<T>(__uint_as_float(oreg[g * 8 + 2]) * inv_l, __uint_as_float(oreg[g * 8 + 3]) * inv_l);
+            o.z = pack2<T>(__uint_as_float(oreg[g * 8 + 4]) * inv_l, __uint_as_float(oreg[g * 8 + 5]) * inv_l);
+            o.w = pack2<T>(__uint_as_float(oreg[g * 8 + 6]) * inv_l, __uint_as_float(oreg[g * 8 + 7]) * inv_l);
+            const int gc = cc * 4 + g;
+            *reinterpret_cast<uint4*>(stg + lane * ROWB + ((gc ^ (lane & (CH - 1))) << 4)) = o;
+          }
+        }
+        __syncwarp();
+        const int64_t slice = static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh;
+        const int row0 = q0 + i * BM + quarter * 32;
+#pragma unroll
+        for (int it = 0; it < 32 / RPI; ++it) {
+          const int rr = it * RPI + lane / CH, ch = lane % CH;
+          const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * ROWB + ((ch ^ (rr & (CH - 1))) << 4));
+          if (row0 + rr < p.Sq) {
+            const int64_t off = slice + static_cast<int64_t>(row0 + rr) * p.o_ss + ch * 8;
+            *reinterpret_cast<uint4*>(static_cast<T*>(p.O) + off) = v;
+            for (int e = 0; e < p.n_extra; ++e) *reinterpret_cast<uint4*>(static_cast<T*>(p.extra_o[e]) + off) = v;
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int cc = 0; cc < D / 32; ++cc) {
         uint32_t oreg[32];
@@ -699,6 +747,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) = o;
           }
         }
+      }
       }
     } else if (lane == 0 && !*abort_flag) {
       *abort_flag = 1;
@@ -757,12 +806,54 @@ extern "C" __attribute__((visibility("default"))) void kcg_fmha_set_p_in_tmem(in
 
 }  // namespace kcg
 
+namespace kcg {
+namespace {
+int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int64_t D, float softmax_scale, int causal,
+                  const void* Q, const int64_t q_strides[3], const void* K, const int64_t k_strides[3], const void* V,
+                  const int64_t v_strides[3], void* O, const int64_t o_strides[3], void* stream, void* const* extra_o,
+                  int n_extra);
+}
+}  // namespace kcg
+
 extern "C" int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int64_t D,
                             float softmax_scale, int causal, const void* Q, const int64_t q_strides[3],
                             const void* K, const int64_t k_strides[3], const void* V,
                             const int64_t v_strides[3], void* O, const int64_t o_strides[3], void* stream) {
+  kcg::clear_error();
+  return kcg::fmha_fwd_impl(dtype, B, H, Sq, Skv, D, softmax_scale, causal, Q, q_strides, K, k_strides, V, v_strides, O,
+                            o_strides, stream, nullptr, 0);
+}
+
+// Attention forward whose epilogue also performs the all-gather of O: the slices this rank
+// computes are stored into every rank's gathered tensor, peers included, as whole output rows.
+extern "C" int kcg_fmha_fwd_allgather(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int64_t D,
+                                      float softmax_scale, int causal, const void* Q, const int64_t q_strides[3],
+                                      const void* K, const int64_t k_strides[3], const void* V,
+                                      const int64_t v_strides[3], void* const* gathered, int world, int rank,
+                                      int64_t batch_offset, const int64_t o_strides[3], void* stream) {
   using namespace kcg;
   clear_error();
+  if (world < 1 || world > 8 || rank < 0 || rank >= world)
+    return fail(KCG_ERR_INVALID_ARG, "fmha_allgather: world %d (1..8), rank %d", world, rank);
+  if (!gathered || !o_strides || batch_offset < 0) return fail(KCG_ERR_INVALID_ARG, "fmha_allgather: bad argument");
+  void* mine = nullptr;
+  void* others[8];
+  int n_others = 0;
+  for (int r = 0; r < world; ++r) {
+    if (!gathered[r]) return fail(KCG_ERR_INVALID_ARG, "fmha_allgather: gathered[%d] is null", r);
+    void* blk = static_cast<char*>(gathered[r]) + static_cast<size_t>(batch_offset) * o_strides[0] * 2;
+    if (r == rank) mine = blk; else others[n_others++] = blk;
+  }
+  return fmha_fwd_impl(dtype, B, H, Sq, Skv, D, softmax_scale, causal, Q, q_strides, K, k_strides, V, v_strides, mine,
+                       o_strides, stream, others, n_others);
+}
+
+namespace kcg {
+namespace {
+int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int64_t D, float softmax_scale, int causal,
+                  const void* Q, const int64_t q_strides[3], const void* K, const int64_t k_strides[3], const void* V,
+                  const int64_t v_strides[3], void* O, const int64_t o_strides[3], void* stream, void* const* extra_o,
+                  int n_extra) {
   if (B < 0 || H < 0 || Sq < 0 || Skv < 0) return fail(KCG_ERR_INVALID_ARG, "fmha: negative extent");
   if (dtype != KCG_BF16 && dtype != KCG_F16)
     return fail(KCG_ERR_UNSUPPORTED, "fmha: dtype %d has no kernel (bfloat16, float16)", dtype);
@@ -801,10 +892,15 @@ extern "C" int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t
   p.q_tiles = static_cast<int>((Sq + BM - 1) / BM);
   p.status = device_status_word();
   if (!p.status) return fail(KCG_ERR_CUDA, "fmha: could not allocate the host-mapped status word");
+  p.n_extra = n_extra;
+  for (int i = 0; i < 7; ++i) p.extra_o[i] = i < n_extra ? extra_o[i] : nullptr;
+  for (int i = 0; i < n_extra; ++i)
+    if (!extra_o[i] || !aligned16(extra_o[i])) return fail(KCG_ERR_ALIGNMENT, "fmha: extra output %d is null or not 16-byte aligned", i);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const uint32_t fmt = dtype == KCG_BF16 ? 1u : 0u;
-  // Two query tiles per CTA pay off once there is more than one tile of queries.
-  const int variant = g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? 2 : 1);
+  // Two query tiles per CTA pay off once there is more than one tile of queries; only that
+  // kernel writes extra outputs.
+  const int variant = n_extra > 0 ? 2 : (g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? 2 : 1));
 #define KCG_FMHA(TT, DD)                                                                      \
   (variant == 2   ? launch_fmha2<TT, DD>(tm[0], tm[1], tm[2], p, fmt, s)                      \
    : variant == 1 ? launch_fmha<TT, DD, true>(tm[0], tm[1], tm[2], p, fmt, s)                 \
@@ -813,3 +909,5 @@ extern "C" int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t
   return D == 128 ? KCG_FMHA(__half, 128) : KCG_FMHA(__half, 64);
 #undef KCG_FMHA
 }
+}  // namespace
+}  // namespace kcg

@@ -241,3 +241,34 @@ def matmul_allgather(A_local: torch.Tensor, B: torch.Tensor, bufs: GatherBuffers
     if sync and bufs.world > 1:
         stream_barrier(bufs.group)
     return bufs.local
+
+
+def fmha_allgather(Q_local: torch.Tensor, K_local: torch.Tensor, V_local: torch.Tensor, bufs: GatherBuffers,
+                   total_batches: int, softmax_scale: float = 1.0, causal: bool = False, sync: bool = True) -> torch.Tensor:
+    """Replicated attention output with whole batches split over ranks: each rank's epilogue writes
+    its [B_local, H, S, D] block into every rank's buffer.  ``bufs`` must hold total_batches*H*S
+    rows of D columns; returns the local buffer viewed as [total_batches, H, S, D]."""
+    import ctypes
+    from . import ops
+    Bl, H, Sq, D = Q_local.shape
+    Skv = K_local.shape[2]
+    if bufs.cols != D or bufs.total_rows != total_batches * H * Sq:
+        raise ValueError("buffer shape does not match [total_batches*H*S, D]")
+    begin, count = _lib.shard_range(total_batches, bufs.world, bufs.rank, 1)
+    if count != Bl:
+        raise ValueError(f"this rank owns {count} batches, the operands hold {Bl}")
+    for t in (Q_local, K_local, V_local):
+        if not t.is_cuda or t.dim() != 4 or t.stride(-1) != 1:
+            raise ValueError("fmha takes [B,H,S,D] CUDA tensors with a contiguous head dimension")
+    st = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    ost = (ctypes.c_int64 * 3)(H * Sq * D, Sq * D, D)
+    if sync and bufs.world > 1:
+        stream_barrier(bufs.group)
+    arr = (ctypes.c_void_p * bufs.world)(*bufs.ptrs)
+    _lib.check(_lib.load().kcg_fmha_fwd_allgather(
+        ops._dt(Q_local), Bl, H, Sq, Skv, D, float(softmax_scale), int(causal), Q_local.data_ptr(), st(Q_local),
+        K_local.data_ptr(), st(K_local), V_local.data_ptr(), st(V_local), arr, bufs.world, bufs.rank, begin, ost,
+        torch.cuda.current_stream().cuda_stream), "kcg_fmha_fwd_allgather")
+    if sync and bufs.world > 1:
+        stream_barrier(bufs.group)
+    return bufs.local.view(total_batches, H, Sq, D)

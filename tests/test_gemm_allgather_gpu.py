@@ -100,3 +100,26 @@ def test_gather_buffers_single_process():
         assert torch.equal(out, ops.matmul(A, B))
     finally:
         bufs.close()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("Bl,H,S,D,world", [(1, 2, 256, 128, 2), (2, 3, 200, 128, 3), (1, 2, 384, 64, 4), (1, 1, 1024, 128, 8)])
+def test_fmha_every_destination_gets_the_slices(Bl, H, S, D, world, causal):
+    # attention whose epilogue writes its batches into several gathered tensors (here all local)
+    from kernelcodegen_b200 import _lib, ops
+    Q, K, V = (randn((Bl, H, S, D), torch.bfloat16, 850 + i).cuda() for i in range(3))
+    want = ops.fmha(Q, K, V, D ** -0.5, causal)
+    sync_ok()
+    i64 = ctypes.c_int64
+    st = (i64 * 3)(H * S * D, S * D, D)
+    for rank in (0, world - 1):
+        bufs = [torch.full((world * Bl, H, S, D), 3.0, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+        arr = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+        rc = _lib.load().kcg_fmha_fwd_allgather(2, Bl, H, S, S, D, D ** -0.5, int(causal), Q.data_ptr(), st, K.data_ptr(), st,
+                                                V.data_ptr(), st, arr, world, rank, rank * Bl, st,
+                                                torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        sync_ok()
+        for b in bufs:
+            assert torch.equal(b[rank * Bl:(rank + 1) * Bl], want)     # same kernel, same bits
+            assert bool((b[:rank * Bl] == 3.0).all()) and bool((b[(rank + 1) * Bl:] == 3.0).all())

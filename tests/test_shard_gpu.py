@@ -49,6 +49,15 @@ def _worker(rank, world, port, results):
             ok = ok and torch.equal(out, full)
         finally:
             bufs.close()
+        # attention with the gather in its epilogue: 6 batches over the ranks
+        fb = shard.GatherBuffers(6 * 2 * 256, 128, torch.bfloat16)
+        try:
+            out = shard.fmha_allgather(shard.shard_rows(Q).contiguous(), shard.shard_rows(K).contiguous(),
+                                       shard.shard_rows(V).contiguous(), fb, 6, 128 ** -0.5, True)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(out, ops.fmha(Q, K, V, 128 ** -0.5, True))
+        finally:
+            fb.close()
         torch.cuda.synchronize()
         ok = ok and _lib.device_status() == 0
         results[rank] = bool(ok)
