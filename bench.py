@@ -233,7 +233,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM/FMHA/fp32 side measurements")
-    ap.add_argument("--only", default="", help="comma list of extras to run (bw,fp32,gemm,sgemm,fmha,move,sweep,gather)")
+    ap.add_argument("--only", default="", help="comma list of extras to run (bw,fp32,bw2,gemm,sgemm,fmha,move,sweep,gather)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -509,6 +509,36 @@ def main() -> None:
                 "frac_of_measured_bf16_peak": tf / world / peaks["bf16_tflops"],
                 "frac_of_nominal_2250": tf / world / 2250.0}
         del Q, K, V, Oo
+        torch.cuda.empty_cache()
+    if want("bw2"):
+        # the remaining bandwidth operators on the headline shape: softmax over the last dim (in
+        # place, as the reference does it), a bias-style broadcast add, and a widening Cast
+        xs2 = [rnd((ROWS, COLS)) for _ in range(4)]
+        bias_v = rnd((COLS,))
+        outs2 = [torch.empty((ROWS, COLS), dtype=dt, device="cuda") for _ in range(4)]
+        wide = [torch.empty((ROWS, COLS), dtype=torch.float32, device="cuda") for _ in range(2)]
+        esz = 2
+
+        def sm(i=[0]):
+            i[0] += 1
+            ops.softmax(xs2[i[0] % 4])
+
+        def badd(i=[0]):
+            i[0] += 1
+            ops.binary(xs2[i[0] % 4], bias_v, "Add", out=outs2[i[0] % 4])
+
+        def cast(i=[0]):
+            i[0] += 1
+            ops.elementwise(xs2[i[0] % 4], "Cast", dtype=torch.float32, out=wide[i[0] % 2])
+
+        for name, fn, nbytes in (("softmax_inplace", sm, 2 * ROWS * COLS * esz),
+                                 ("broadcast_add_row", badd, 2 * ROWS * COLS * esz + COLS * esz),
+                                 ("cast_bf16_to_f32", cast, ROWS * COLS * (esz + 4))):
+            ms = time_op(fn, 40)
+            gbs = world * nbytes / (ms * 1e-3) / 1e9
+            workloads[f"{name}_bf16_{ROWS}x{COLS}"] = {"ms": ms, "value": gbs, "unit": "GB/s",
+                                                       "frac_of_hbm_peak": gbs / world / peaks["hbm_gbs"]}
+        del xs2, outs2, wide
         torch.cuda.empty_cache()
     if want("move"):
         # data-movement operators: embedding-style row gather and a batched transpose

@@ -311,9 +311,118 @@ softmax_rows(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int64_t c
   }
 }
 
+// Rows that fit in the registers of one thread block (up to 512 threads x 8 16-byte vectors):
+// the row is read once, kept packed, and passes through max, exp / sum and the normalised store
+// without touching memory again.  exp(v - m) is evaluated as 2^((v - m) * log2 e) on the
+// special-function unit; masked (causal) positions produce exact zeros.
+template <typename T, int VPT, bool kExact, bool kMasked>
+__global__ void __launch_bounds__(512)
+softmax_block_rows(const T* __restrict__ x, T* __restrict__ y, int cols, float scale, int causal, int64_t q_len) {
+  using W = Words<T>;
+  constexpr int EPW = W::EPW;
+  constexpr int EPV = 4 * EPW;   // elements per 16-byte vector
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int nvec = cols / EPV;
+  int valid = cols;
+  if (kMasked && causal) {
+    const int64_t v = (row % q_len) + (cols - q_len) + 1;
+    valid = v > cols ? cols : (v < 0 ? 0 : static_cast<int>(v));
+  }
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
+  uint4 v[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+    if (kExact || i * nthr + tid < nvec) v[i] = __ldcs(xr + i * nthr + tid);
+  const float c = scale * 1.4426950408889634f;   // scores are compared and exponentiated in log2 units
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+    if (kExact || i * nthr + tid < nvec) {
+      const int e0 = (i * nthr + tid) * EPV;
+      const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float f[EPW];
+        W::unpack(w[k], f);
+#pragma unroll
+        for (int e = 0; e < EPW; ++e)
+          if (!kMasked || e0 + k * EPW + e < valid) m = fmaxf(m, f[e] * c);
+      }
+    }
+  m = block_max(m, red);
+  const float neg_m = m == -INFINITY ? 0.f : -m;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+    if (kExact || i * nthr + tid < nvec) {
+      const int e0 = (i * nthr + tid) * EPV;
+      const uint32_t w[4] = {opaque(v[i].x), opaque(v[i].y), opaque(v[i].z), opaque(v[i].w)};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float f[EPW];
+        W::unpack(w[k], f);
+#pragma unroll
+        for (int e = 0; e < EPW; ++e)
+          if (!kMasked || e0 + k * EPW + e < valid) s += exp2f_approx(fmaf(f[e], c, neg_m));
+      }
+    }
+  s = block_sum(s, red);
+  // the division by the row sum rides in the exponent: p / s = 2^(v - m - log2 s)
+  const float shift = s > 0.f ? neg_m - log2f(s) : -INFINITY;
+  uint4* yr = reinterpret_cast<uint4*>(y + row * cols);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = i * nthr + tid;
+    if (kExact || vi < nvec) {
+      const int e0 = vi * EPV;
+      const uint32_t w[4] = {opaque(v[i].x), opaque(v[i].y), opaque(v[i].z), opaque(v[i].w)};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float f[EPW], r[EPW];
+        W::unpack(w[k], f);
+#pragma unroll
+        for (int e = 0; e < EPW; ++e)
+          r[e] = (!kMasked || e0 + k * EPW + e < valid) ? exp2f_approx(fmaf(f[e], c, shift)) : 0.f;
+        o[k] = W::pack(r);
+      }
+      __stcs(yr + vi, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+  }
+}
+
 template <typename T>
 int launch_softmax(int64_t rows, int64_t cols, float scale, int causal, int64_t q_len,
                    const void* x, void* y, cudaStream_t stream) {
+  constexpr int VW = Vec16<T>::N;
+  const int64_t nvec = cols / VW;
+  if (cols % VW == 0 && nvec <= 512 * 8 && aligned16(x) && aligned16(y) && rows <= 0x7fffffffll) {
+    int threads = static_cast<int>((nvec + 7) / 8);
+    threads = (threads + 31) / 32 * 32;
+    const int vpt = static_cast<int>((nvec + threads - 1) / threads);
+    const unsigned grid = static_cast<unsigned>(rows);
+    const T* xp = static_cast<const T*>(x);
+    T* yp = static_cast<T*>(y);
+    const int icols = static_cast<int>(cols);
+    const bool exact = nvec == static_cast<int64_t>(threads) * (vpt <= 2 ? 2 : (vpt <= 4 ? 4 : 8));
+#define KCG_SM_LAUNCH(V)                                                                                    \
+  do {                                                                                                      \
+    if (causal) {                                                                                           \
+      if (exact) softmax_block_rows<T, V, true, true><<<grid, threads, 0, stream>>>(xp, yp, icols, scale, causal, q_len);   \
+      else softmax_block_rows<T, V, false, true><<<grid, threads, 0, stream>>>(xp, yp, icols, scale, causal, q_len);        \
+    } else {                                                                                                \
+      if (exact) softmax_block_rows<T, V, true, false><<<grid, threads, 0, stream>>>(xp, yp, icols, scale, causal, q_len);  \
+      else softmax_block_rows<T, V, false, false><<<grid, threads, 0, stream>>>(xp, yp, icols, scale, causal, q_len);       \
+    }                                                                                                       \
+  } while (0)
+    if (vpt <= 2) KCG_SM_LAUNCH(2);
+    else if (vpt <= 4) KCG_SM_LAUNCH(4);
+    else KCG_SM_LAUNCH(8);
+#undef KCG_SM_LAUNCH
+    return check_launch("softmax_block_rows");
+  }
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   softmax_rows<T><<<static_cast<int>(rows < cap ? rows : cap), 256, 0, stream>>>(
       static_cast<const T*>(x), static_cast<T*>(y), rows, cols, scale, causal, q_len);

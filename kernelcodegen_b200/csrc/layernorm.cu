@@ -26,45 +26,6 @@ namespace {
 // Longest row (in 16-byte vectors per lane) that is given to the warp-per-row kernel.
 int g_warp_row_max_vecs = 8;
 
-// A row sits in registers as raw 32-bit words (two 16-bit elements or one fp32 per word)
-// and is unpacked three times: for the sum, for the centred sum of squares and for the
-// output.  Keeping the packed form (a bf16 row of 4096 is 64 registers per lane at one warp
-// per row) is what lets enough warps be resident to cover HBM latency; `opaque` stops the
-// compiler from keeping an unpacked fp32 copy alive across the three passes instead.
-template <typename T> struct Words;
-template <> struct Words<float> {
-  static constexpr int EPW = 1;
-  static __device__ __forceinline__ void unpack(uint32_t w, float (&f)[1]) { f[0] = __uint_as_float(w); }
-  static __device__ __forceinline__ uint32_t pack(const float (&f)[1]) { return __float_as_uint(f[0]); }
-};
-template <> struct Words<__nv_bfloat16> {
-  static constexpr int EPW = 2;
-  static __device__ __forceinline__ void unpack(uint32_t w, float (&f)[2]) {
-    f[0] = __uint_as_float(w << 16);
-    f[1] = __uint_as_float(w & 0xffff0000u);
-  }
-  static __device__ __forceinline__ uint32_t pack(const float (&f)[2]) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(f[0], f[1]);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-};
-template <> struct Words<__half> {
-  static constexpr int EPW = 2;
-  static __device__ __forceinline__ void unpack(uint32_t w, float (&f)[2]) {
-    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w));
-    f[0] = v.x;
-    f[1] = v.y;
-  }
-  static __device__ __forceinline__ uint32_t pack(const float (&f)[2]) {
-    __half2 v = __floats2half2_rn(f[0], f[1]);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-};
-__device__ __forceinline__ uint32_t opaque(uint32_t w) {
-  asm volatile("" : "+r"(w));
-  return w;
-}
-
 // Loads, normalises and stores one row held by `nthr` cooperating threads (a warp or a
 // block); `reduce` sums a float over those threads.  kExact: the row is exactly
 // nthr * VPT vectors long, so no bounds checks are needed.

@@ -205,7 +205,8 @@ def test_binary_rejects_mismatch_and_inplace():
 
 # --------------------------------------------------------------------------- softmax
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", [(2, 3, 64, 64), (5, 1000), (1, 2, 17, 333)])
+@pytest.mark.parametrize("shape", [(2, 3, 64, 64), (5, 1000), (1, 2, 17, 333), (16, 4096), (2, 2, 128, 512), (3, 16384),
+                                   (2, 3, 40, 2056), (2, 40000)])
 @pytest.mark.parametrize("causal", [False, True])
 def test_softmax(shape, dtype, causal):
     if causal and len(shape) < 3:
@@ -216,3 +217,11 @@ def test_softmax(shape, dtype, causal):
     sync_ok()
     assert y.data_ptr() == xd.data_ptr()  # in place, like the reference op
     assert rel_fro(y, O.softmax_f64(f64(x), 0.5, causal)) <= TOL[dtype]
+
+
+def test_softmax_negative_scale_and_out_of_place():
+    x = randn((33, 2048), torch.float32, 410)
+    y = ops().softmax(x.cuda(), -1, scale=-1.5, inplace=False)
+    sync_ok()
+    assert rel_fro(y, O.softmax_f64(f64(x), -1.5, False)) <= 1e-5
+    assert float((y.sum(-1) - 1).abs().max()) <= 1e-5
