@@ -86,6 +86,19 @@ __device__ __forceinline__ void st_vec_stream(T* p, const Vec16<T>& r) {
   __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&r));
 }
 
+// 32-byte (256-bit) streaming accesses: one instruction per thread where an operand is twice as
+// wide as the other (Cast between 16- and 32-bit types).  The address must be 32-byte aligned.
+__device__ __forceinline__ void ld_256(const void* p, uint4& lo, uint4& hi) {
+  asm volatile("ld.global.cs.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+               : "l"(p));
+}
+__device__ __forceinline__ void st_256(void* p, const uint4& lo, const uint4& hi) {
+  asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+               "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+               : "memory");
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -6,6 +6,8 @@
 // softmax :462-578.  The reference schedules (src/Optimizer/Optimizer.cc:928-1175)
 // tile a near-square 2-D view 64x64 with 4x4 elements per thread; here every map is a
 // flat stream of 128-bit accesses, because the ops are HBM-bound and have no reuse.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace kcg {
@@ -33,7 +35,7 @@ struct OpGelu { template <bool F> static __device__ __forceinline__ float f(floa
 
 template <typename TI, typename TO, typename Op, int UNROLL>
 __global__ void __launch_bounds__(256)
-unary_vec(const TI* __restrict__ x, TO* __restrict__ y, int64_t ngroups) {
+unary_vec(const TI* __restrict__ x, TO* __restrict__ y, int64_t ngroups, bool wide32) {
   // One group = EPT elements = whole 16-byte vectors on both sides.
   constexpr int EPT = 16 / (sizeof(TI) < sizeof(TO) ? sizeof(TI) : sizeof(TO));
   constexpr int NI = EPT * sizeof(TI) / 16, NO = EPT * sizeof(TO) / 16;
@@ -46,6 +48,12 @@ unary_vec(const TI* __restrict__ x, TO* __restrict__ y, int64_t ngroups) {
     for (int u = 0; u < UNROLL; ++u) {
       const int64_t g = g0 + static_cast<int64_t>(u) * blockDim.x;
       if (g < ngroups) {
+        if constexpr (NI == 2) {
+          if (wide32) {
+            ld_256(x + g * EPT, *reinterpret_cast<uint4*>(&in[u][0]), *reinterpret_cast<uint4*>(&in[u][1]));
+            continue;
+          }
+        }
 #pragma unroll
         for (int k = 0; k < NI; ++k) in[u][k] = ld_vec_stream(x + g * EPT + k * Vec16<TI>::N);
       }
@@ -59,6 +67,12 @@ unary_vec(const TI* __restrict__ x, TO* __restrict__ y, int64_t ngroups) {
         for (int e = 0; e < EPT; ++e) {
           const float v = Conv<TI>::to_f(in[u][e / Vec16<TI>::N].v[e % Vec16<TI>::N]);
           out[e / Vec16<TO>::N].v[e % Vec16<TO>::N] = Conv<TO>::from_f(Op::template f<kFast>(v));
+        }
+        if constexpr (NO == 2) {
+          if (wide32) {
+            st_256(y + g * EPT, *reinterpret_cast<const uint4*>(&out[0]), *reinterpret_cast<const uint4*>(&out[1]));
+            continue;
+          }
         }
 #pragma unroll
         for (int k = 0; k < NO; ++k) st_vec_stream(y + g * EPT + k * Vec16<TO>::N, out[k]);
@@ -88,7 +102,8 @@ int launch_unary(int64_t n, const void* xv, void* yv, cudaStream_t stream) {
     const int64_t ngroups = n / EPT;
     const int64_t want = (ngroups + 256 * UNROLL - 1) / (256 * UNROLL);
     const int64_t cap = static_cast<int64_t>(sms) * 8;
-    unary_vec<TI, TO, Op, UNROLL><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(x, y, ngroups);
+    unary_vec<TI, TO, Op, UNROLL><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
+        x, y, ngroups, (reinterpret_cast<uintptr_t>(x) & 31u) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0);
     int rc = check_launch("unary_vec");
     if (rc) return rc;
     done = ngroups * EPT;
@@ -230,6 +245,41 @@ binary_bcast(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ c
   }
 }
 
+// The bias-shaped broadcast: one operand has the full [rows, inner] shape, the other is an
+// `inner`-long vector repeated over the rows (any number of leading broadcast dims collapse to
+// this).  A thread keeps its 16-byte piece of the vector in registers and walks down the rows, so
+// the full operand streams with no index arithmetic; kSwap: the vector is the left operand.
+template <typename T, typename Op, bool kSwap, int UNROLL>
+__global__ void __launch_bounds__(256)
+binary_row_vector(const T* __restrict__ full, const T* __restrict__ vec, T* __restrict__ c, int64_t rows,
+                  int64_t inner_vecs) {
+  constexpr int VW = Vec16<T>::N;
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (j >= inner_vecs) return;
+  const Vec16<T> vv = ld_vec(vec + j * VW);
+  float fv[VW];
+#pragma unroll
+  for (int e = 0; e < VW; ++e) fv[e] = Conv<T>::to_f(vv.v[e]);
+  const int64_t pitch = inner_vecs * VW;
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.y) * UNROLL; r0 < rows; r0 += static_cast<int64_t>(gridDim.y) * UNROLL) {
+    Vec16<T> in[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      if (r0 + u < rows) in[u] = ld_vec_stream(full + (r0 + u) * pitch + j * VW);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      if (r0 + u < rows) {
+        Vec16<T> o;
+#pragma unroll
+        for (int e = 0; e < VW; ++e) {
+          const float x = Conv<T>::to_f(in[u].v[e]);
+          o.v[e] = Conv<T>::from_f(kSwap ? Op::f(fv[e], x) : Op::f(x, fv[e]));
+        }
+        st_vec_stream(c + (r0 + u) * pitch + j * VW, o);
+      }
+  }
+}
+
 template <typename T, typename Op>
 int launch_binary(const BcastDims& d, bool same_shape, int64_t total, const void* av,
                   const void* bv, void* cv, cudaStream_t stream) {
@@ -252,6 +302,23 @@ int launch_binary(const BcastDims& d, bool same_shape, int64_t total, const void
   bool vec_ok = al && d.extent[0] % VW == 0;
   for (int k = 1; k < d.rank && vec_ok; ++k)
     vec_ok = (d.stride_a[k] % VW == 0) && (d.stride_b[k] % VW == 0);
+  // [rows, inner] (op) [inner] in either order
+  if (vec_ok && d.rank == 2 && d.stride_a[0] == 1 && d.stride_b[0] == 1 &&
+      ((d.stride_a[1] == d.extent[0] && d.stride_b[1] == 0) || (d.stride_b[1] == d.extent[0] && d.stride_a[1] == 0))) {
+    constexpr int UNROLL = 4;
+    const bool swap = d.stride_a[1] == 0;   // the vector is the left operand
+    const int64_t inner_vecs = d.extent[0] / VW, rows = d.extent[1];
+    const int64_t gx = (inner_vecs + 255) / 256;
+    int64_t gy = (rows + UNROLL - 1) / UNROLL;
+    const int64_t gy_cap = std::max<int64_t>(1, cap * 2 / gx);
+    if (gy > gy_cap) gy = gy_cap;
+    if (gx <= 0x7fffffffll && gy <= 65535) {
+      dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+      if (swap) binary_row_vector<T, Op, true, UNROLL><<<grid, 256, 0, stream>>>(b, a, c, rows, inner_vecs);
+      else binary_row_vector<T, Op, false, UNROLL><<<grid, 256, 0, stream>>>(a, b, c, rows, inner_vecs);
+      return check_launch("binary_row_vector");
+    }
+  }
   if (vec_ok) {
     const int64_t ngroups = total / VW;
     const int64_t want = (ngroups + 255) / 256;
