@@ -494,7 +494,15 @@ def main() -> None:
         A = (torch.rand((n, n), generator=gen, device="cuda") * 2 - 1); B = (torch.rand((n, n), generator=gen, device="cuda") * 2 - 1)
         C = torch.empty((n, n), device="cuda")
         ms = time_op(lambda: ops.matmul(A, B, out=C), 20)
-        workloads["gemm_f32_1024"] = {"ms": ms, "value": world * 2 * n ** 3 / (ms * 1e-3) / 1e12, "unit": "TFLOP/s"}
+        workloads["gemm_f32_1024"] = {"ms": ms, "value": world * 2 * n ** 3 / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                      "path": "tensor cores: three tf32 products of hi/lo-split operands, K in chunks of 256"}
+        _lib.load().kcg_gemm_set_fp32_mode(0)
+        try:
+            ms = time_op(lambda: ops.matmul(A, B, out=C), 20)
+        finally:
+            _lib.load().kcg_gemm_set_fp32_mode(-1)
+        workloads["gemm_f32_1024_cuda_cores"] = {"ms": ms, "value": world * 2 * n ** 3 / (ms * 1e-3) / 1e12,
+                                                 "unit": "TFLOP/s", "path": "FFMA kernel, reference accumulation order"}
 
     if want("fmha"):
         Bq, H, S, D = 8, 32, 4096, 128

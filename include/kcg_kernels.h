@@ -350,6 +350,17 @@ KCG_API int kcg_transpose(int dtype, int64_t batch, int64_t rows, int64_t cols, 
                           void* output, void* stream);
 
 /*
+ * How float32 GEMMs are computed (no counterpart in the reference, whose SGEMM is CUDA-core
+ * code): 0 = the CUDA-core FFMA kernel, one fp32 accumulator per output summed in increasing k
+ * like the reference's loop nest; 1 = the tensor cores, as three tf32 products of operands
+ * split into hi + lo parts (a b = a_hi b_hi + a_lo b_hi + a_hi b_lo, fp32 accumulation; results
+ * within ~1e-6 relative of a float64 product, several times faster; uses a cached per-device
+ * scratch buffer of 12 (M + N) K bytes per batch entry); -1 (default) = 1 when M N K >= 256^3,
+ * else 0.  Process-wide, not thread-safe.
+ */
+KCG_API void kcg_gemm_set_fp32_mode(int mode);
+
+/*
  * GEMM with the all-gather of C done by its epilogue (no counterpart in the reference, which
  * has no multi-GPU code; the sharding is the one kcg_shard_range describes).  Rank `rank` of
  * `world` (<= 8) computes its M x N block C = op(A) op(B) exactly as kcg_gemm_fused would

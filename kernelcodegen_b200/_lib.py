@@ -44,6 +44,7 @@ SIGNATURES = {
     "kcg_gemm_fused": ([_ci, _ci, _i64, _i64, _i64, _i64, _ci, _ci, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64,
                         _vp, _vp, _vp, _ci, _vp], _ci),
     "kcg_gemm_set_pair_mode": ([_ci], None),
+    "kcg_gemm_set_fp32_mode": ([_ci], None),
     "kcg_gemm_allgather": ([_ci, _ci, _i64, _i64, _i64, _ci, _ci, _vp, _i64, _vp, _i64, ctypes.POINTER(_vp), _ci, _ci,
                             _i64, _i64, _vp, _vp, _vp, _ci, _vp], _ci),
     "kcg_peer_alloc": ([ctypes.c_size_t, ctypes.POINTER(_vp)], _ci),

@@ -12,7 +12,16 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
                  int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
                  const float* scale_b, const void* bias, int act, cudaStream_t stream, void* const* extra_c = nullptr,
                  int n_extra = 0);
+int gemm_f32_tensor(int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a, int trans_b, const float* A,
+                    int64_t lda, int64_t stride_a, const float* B, int64_t ldb, int64_t stride_b, float* C,
+                    int64_t ldc, int64_t stride_c, const float* scale_a, const float* scale_b, const float* bias,
+                    int act, cudaStream_t stream);
+namespace {
+int g_fp32_mode = -1;  // -1: by size; 0: CUDA-core kernel; 1: tensor cores (three tf32 products)
+}
 }  // namespace kcg
+
+extern "C" void kcg_gemm_set_fp32_mode(int mode) { kcg::g_fp32_mode = mode; }
 
 extern "C" int kcg_gemm(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch,
                         int trans_a, int trans_b, const void* A, int64_t lda, int64_t stride_a,
@@ -43,6 +52,16 @@ extern "C" int kcg_gemm_fused(int dtype_in, int dtype_out, int64_t M, int64_t N,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype_in == KCG_F32) {
     if (dtype_out != KCG_F32) return fail(KCG_ERR_UNSUPPORTED, "gemm: float32 inputs produce float32");
+    // Large enough products go to the tensor cores as three tf32 products of split operands
+    // (results within ~1e-6 of fp64); small ones, where the two split passes would dominate,
+    // and anything the split path declines stay on the CUDA-core kernel.
+    const bool big = static_cast<double>(M) * static_cast<double>(N) * static_cast<double>(K) >= 256.0 * 256.0 * 256.0;
+    if (g_fp32_mode == 1 || (g_fp32_mode == -1 && big)) {
+      const int rc = gemm_f32_tensor(M, N, K, batch, trans_a, trans_b, static_cast<const float*>(A), lda, stride_a,
+                                     static_cast<const float*>(B), ldb, stride_b, static_cast<float*>(C), ldc, stride_c,
+                                     scale_a, scale_b, static_cast<const float*>(bias), activation, s);
+      if (rc != KCG_ERR_UNSUPPORTED || kcg_last_error()[0] != 0) return rc;
+    }
     return sgemm_f32(M, N, K, batch, trans_a, trans_b, static_cast<const float*>(A), lda, stride_a,
                      static_cast<const float*>(B), ldb, stride_b, static_cast<float*>(C), ldc, stride_c,
                      scale_a, scale_b, static_cast<const float*>(bias), activation, s);

@@ -384,7 +384,8 @@ struct Idescs { uint32_t wide, pair, narrow; };
 // wide / pair / narrow.
 Tiling pick_tiling(int64_t M, int64_t N, int64_t K, int64_t batch, int elem_bytes, int sms) {
   auto cdiv = [](int64_t a, int64_t b) { return (a + b - 1) / b; };
-  const double unit = 2.1e-3 * static_cast<double>(K) * (elem_bytes == 1 ? 0.5 : 1.0);  // 8-bit inputs run at twice the rate
+  // 8-bit inputs run at twice, tf32 at half the 16-bit rate
+  const double unit = 2.1e-3 * static_cast<double>(K) * (elem_bytes == 1 ? 0.5 : (elem_bytes == 4 ? 2.0 : 1.0));
   const int64_t wide = cdiv(M, 128) * cdiv(N, 256) * batch, narrow = cdiv(M, 128) * cdiv(N, 128) * batch;
   const int64_t pairs = cdiv(M, 256) * cdiv(N, 256) * batch;
   const double c_wide = static_cast<double>(cdiv(wide, sms)) * 2 * 1.04 * unit + 5.7;
@@ -452,7 +453,7 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
                  int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
                  const float* scale_b, const void* bias, int act, cudaStream_t stream, void* const* extra_c,
                  int n_extra) {
-  const int es = dtype_in == KCG_F8E4M3 ? 1 : 2;
+  const int es = dtype_in == KCG_F8E4M3 ? 1 : (dtype_in == KCG_F32 ? 4 : 2);   // fp32 words are read as tf32
   if (!aligned16(A) || !aligned16(B))
     return fail(KCG_ERR_ALIGNMENT, "gemm: A and B must be 16-byte aligned for the tensor-core path");
   if ((lda * es) % 16 || (ldb * es) % 16 || (batch > 1 && ((stride_a * es) % 16 || (stride_b * es) % 16)))
@@ -532,6 +533,13 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
     if (dtype_out == KCG_F32)
       return launch_layout<Kind::F8F6F4, 1, float>(trans_a, trans_b, tmA, tmB, tmBp, p, ids, tiling, stream);
     return fail(KCG_ERR_UNSUPPORTED, "gemm: float8_e4m3 inputs produce bfloat16 or float32 (got dtype %d)", dtype_out);
+  }
+  if (dtype_in == KCG_F32) {
+    // tf32 operands (both K-major: the caller has laid them out that way), fp32 result
+    if (trans_a || !trans_b || dtype_out != KCG_F32)
+      return fail(KCG_ERR_UNSUPPORTED, "gemm: the tf32 path takes K-major operands and produces float32");
+    const Idescs ids = {make_idesc(2, 2, 0, 0, BM, BN), make_idesc(2, 2, 0, 0, 2 * BM, BN), make_idesc(2, 2, 0, 0, BM, 128)};
+    return launch_variant<Kind::TF32, 4, false, false, float>(tmA, tmB, tmBp, p, ids, tiling, stream);
   }
   const uint32_t fmt = dtype_in == KCG_BF16 ? 1u : 0u;
   const Idescs ids = {make_idesc(fmt, fmt, a_mn, b_mn, BM, BN), make_idesc(fmt, fmt, a_mn, b_mn, 2 * BM, BN),

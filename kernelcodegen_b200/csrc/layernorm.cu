@@ -19,7 +19,7 @@
 
 namespace kcg {
 
-void* device_scratch(size_t bytes);  // runtime.cu
+void* device_scratch(size_t bytes, int slot);  // runtime.cu
 
 namespace {
 
@@ -308,7 +308,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
                 "%lld columns (got %lld)",
                 static_cast<long long>(rows), 65535LL * 32 * kChunk, static_cast<long long>(cols));
   const int chunks = static_cast<int>(chunks64);
-  float* stats = static_cast<float*>(device_scratch(static_cast<size_t>(rows) * chunks * 2 * sizeof(float)));
+  float* stats = static_cast<float*>(device_scratch(static_cast<size_t>(rows) * chunks * 2 * sizeof(float), 0));
   if (!stats) return fail(KCG_ERR_CUDA, "layernorm: could not allocate %zu bytes of scratch",
                           static_cast<size_t>(rows) * chunks * 2 * sizeof(float));
   dim3 grid(chunks, static_cast<unsigned>(rows));

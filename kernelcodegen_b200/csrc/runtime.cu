@@ -10,10 +10,11 @@ namespace kcg {
 namespace {
 thread_local char g_error[512] = {0};
 
+constexpr int kScratchSlots = 2;   // 0: LayerNorm split-row statistics, 1: fp32 GEMM operand splits
 struct DeviceState {
   int sms = 0;
-  void* scratch = nullptr;
-  size_t scratch_bytes = 0;
+  void* scratch[kScratchSlots] = {nullptr, nullptr};
+  size_t scratch_bytes[kScratchSlots] = {0, 0};
 };
 constexpr int kMaxDevices = 64;
 DeviceState g_dev[kMaxDevices];
@@ -48,18 +49,18 @@ int sm_count() {
   return g_dev[d].sms;
 }
 
-// Returns a device buffer of at least `bytes` bytes that stays valid until a larger
-// request replaces it (cudaFree of the old buffer waits for work in flight).
-void* device_scratch(size_t bytes) {
+// Returns a device buffer of at least `bytes` bytes that stays valid until a larger request
+// for the same slot replaces it (cudaFree of the old buffer waits for work in flight).
+void* device_scratch(size_t bytes, int slot) {
   const int d = current_device();
-  if (d < 0) return nullptr;
+  if (d < 0 || slot < 0 || slot >= kScratchSlots) return nullptr;
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState& st = g_dev[d];
-  if (st.scratch_bytes >= bytes && st.scratch) return st.scratch;
-  if (st.scratch) {
-    cudaFree(st.scratch);
-    st.scratch = nullptr;
-    st.scratch_bytes = 0;
+  if (st.scratch_bytes[slot] >= bytes && st.scratch[slot]) return st.scratch[slot];
+  if (st.scratch[slot]) {
+    cudaFree(st.scratch[slot]);
+    st.scratch[slot] = nullptr;
+    st.scratch_bytes[slot] = 0;
   }
   size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
   void* p = nullptr;
@@ -67,8 +68,8 @@ void* device_scratch(size_t bytes) {
     cudaGetLastError();
     return nullptr;
   }
-  st.scratch = p;
-  st.scratch_bytes = want;
+  st.scratch[slot] = p;
+  st.scratch_bytes[slot] = want;
   return p;
 }
 

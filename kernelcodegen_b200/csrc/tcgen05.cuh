@@ -198,7 +198,7 @@ __device__ __forceinline__ void tmem_st64(uint32_t taddr, const uint32_t (&r)[64
 }
 
 // ---- MMA ---------------------------------------------------------------------------
-enum class Kind { F16, F8F6F4 };
+enum class Kind { F16, F8F6F4, TF32 };
 
 // D(tmem) (+)= A(smem) * B(smem); issued by ONE thread.  `accumulate` == 0 overwrites D.
 template <Kind kKind>
@@ -209,6 +209,13 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
         "{\n\t.reg .pred P;\n\t"
         "setp.ne.b32 P, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, P;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else if constexpr (kKind == Kind::TF32) {
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "setp.ne.b32 P, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, P;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
   } else {
@@ -283,6 +290,13 @@ __device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, ui
         "{\n\t.reg .pred P;\n\t"
         "setp.ne.b32 P, %4, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, P;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else if constexpr (kKind == Kind::TF32) {
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "setp.ne.b32 P, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, P;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
   } else {

@@ -204,3 +204,23 @@ def test_layernorm_sharded_config_slice():
     y2 = ops().layernorm(x[perm].contiguous(), g, b, 1, 1e-5)
     sync_ok()
     assert torch.equal(y2, y[perm])
+
+
+def test_fp32_gemm_tensor_path_large():
+    # float32 GEMM through the split-operand tensor-core path, large enough that the partial
+    # products are produced in two column panels (16 chunks of K, 8192 x 4096 output)
+    M, N, K = 8192, 4096, 4096
+    A = dev_randn((M, K), torch.float32, 970, std=1.0 / np.sqrt(K))
+    B = dev_randn((K, N), torch.float32, 971)
+    bias = dev_randn((N,), torch.float32, 972)
+    C = ops().matmul(A, B, bias=bias, activation="Relu")
+    sync_ok()
+    rows = sample_index(M, 128)
+    cols = torch.arange(0, N, 29, device="cuda")
+    want = np.maximum(f64(A[rows]) @ f64(B[:, cols]) + f64(bias[cols]), 0.0)
+    assert rel_fro(C[rows][:, cols], want) <= 1e-5
+    # column checksum over the whole output without the epilogue
+    C2 = ops().matmul(A, B)
+    sync_ok()
+    colsum = (A.double().sum(0, keepdim=True) @ B.double()).squeeze(0)
+    assert float((C2.double().sum(0) - colsum).norm() / colsum.norm()) <= 1e-5

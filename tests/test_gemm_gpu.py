@@ -140,3 +140,44 @@ def test_tile_shapes_give_identical_bits(m, n, k):
     assert rel_fro(outs[0], O.matmul_f64(f64(A), f64(B))) <= 1e-2
     for o in outs[1:]:
         assert torch.equal(o, outs[0])
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (130, 70, 33), (257, 129, 100), (1000, 520, 1001)])
+def test_fp32_on_tensor_cores_split_operands(m, n, k, ta, tb):
+    # three tf32 products of hi/lo-split operands: fp32-grade accuracy from the tensor cores
+    from kernelcodegen_b200 import _lib
+    A = randn((2,) + ((k, m) if ta else (m, k)), torch.float32, 590)
+    B = randn((2,) + ((n, k) if tb else (k, n)), torch.float32, 591)
+    try:
+        _lib.load().kcg_gemm_set_fp32_mode(1)
+        C = ops().batched_matmul(A.cuda(), B.cuda(), ta, tb)
+        sync_ok()
+        _lib.load().kcg_gemm_set_fp32_mode(0)
+        C0 = ops().batched_matmul(A.cuda(), B.cuda(), ta, tb)
+        sync_ok()
+    finally:
+        _lib.load().kcg_gemm_set_fp32_mode(-1)
+    want = O.matmul_f64(f64(A), f64(B), ta, tb)
+    assert rel_fro(C, want) <= 1e-5
+    assert rel_fro(C0, want) <= 1e-5
+    assert rel_fro(C, want) <= 4e-6      # in practice an order of magnitude inside the tolerance
+
+
+def test_fp32_tensor_path_special_values_and_epilogue():
+    from kernelcodegen_b200 import _lib
+    A = randn((256, 256), torch.float32, 592)
+    B = randn((256, 256), torch.float32, 593)
+    A[3, 5] = float("inf"); A[7, :] = 0.0; B[:, 9] = 1e-30
+    bias = randn((256,), torch.float32, 594).cuda()
+    try:
+        _lib.load().kcg_gemm_set_fp32_mode(1)
+        C = ops().matmul(A.cuda(), B.cuda(), bias=bias, activation="Relu")
+        sync_ok()
+    finally:
+        _lib.load().kcg_gemm_set_fp32_mode(-1)
+    ref = torch.relu(A.double() @ B.double() + bias.cpu().double())
+    row_ok = torch.ones(256, dtype=torch.bool); row_ok[3] = False
+    assert rel_fro(C[row_ok], ref[row_ok].numpy()) <= 1e-5
+    assert bool(torch.isinf(C[3]).logical_or(torch.isnan(C[3])).logical_or(C[3] == 0).all())   # the infinite row stays non-finite or is clamped by Relu
+    assert bool((C[7].cpu() == torch.relu(bias.cpu())).all())
