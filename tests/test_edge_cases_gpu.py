@@ -1,0 +1,89 @@
+"""Empty inputs are accepted (nothing is launched) and malformed calls return a status with a
+message instead of faulting: every entry point of the C ABI, called directly."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def lib():
+    from kernelcodegen_b200 import _lib
+    return _lib
+
+
+def test_empty_inputs_return_ok():
+    L = lib()
+    l = L.load()
+    ops = __import__("kernelcodegen_b200.ops", fromlist=["ops"])
+    e = torch.empty((0, 64), dtype=torch.bfloat16, device="cuda")
+    g = torch.ones(64, dtype=torch.bfloat16, device="cuda")
+    assert ops.layernorm(e, g, g, 1).shape == (0, 64)
+    assert ops.elementwise(e, "Gelu").shape == (0, 64)
+    assert ops.binary(e, e, "Add").shape == (0, 64)
+    assert ops.binary(e, g, "Mul").shape == (0, 64)
+    assert ops.softmax(e).shape == (0, 64)
+    assert ops.transpose(e).shape == (64, 0)
+    idx = torch.empty((0,), dtype=torch.int64, device="cuda")
+    assert ops.gather(torch.ones((5, 8), device="cuda"), idx, 0).shape == (0, 8)
+    A0 = torch.empty((0, 64), dtype=torch.bfloat16, device="cuda")
+    B = torch.ones((64, 128), dtype=torch.bfloat16, device="cuda")
+    assert ops.matmul(A0, B).shape == (0, 128)
+    assert ops.matmul(torch.ones((128, 64), dtype=torch.bfloat16, device="cuda"),
+                      torch.empty((64, 0), dtype=torch.bfloat16, device="cuda")).shape == (128, 0)
+    q0 = torch.empty((0, 2, 128, 128), dtype=torch.bfloat16, device="cuda")
+    assert ops.fmha(q0, q0, q0).shape == (0, 2, 128, 128)
+    torch.cuda.synchronize()
+    assert L.device_status() == 0
+
+
+def test_malformed_calls_report_a_status():
+    L = lib()
+    l = L.load()
+    x = torch.ones((4, 64), dtype=torch.bfloat16, device="cuda")
+    p = x.data_ptr()
+    st = (ctypes.c_int64 * 3)(64, 64, 64)
+    sh = (ctypes.c_int64 * 2)(4, 64)
+    cases = [
+        (l.kcg_layernorm(L.BF16, 4, 64, None, p, p, 1e-5, p, None), L.ERR_INVALID_ARG),
+        (l.kcg_layernorm(L.BF16, -1, 64, p, p, p, 1e-5, p, None), L.ERR_INVALID_ARG),
+        (l.kcg_layernorm(L.I32, 4, 64, p, p, p, 1e-5, p, None), L.ERR_UNSUPPORTED),
+        (l.kcg_layernorm_stats(L.BF16, 4, 64, p, None, None, 1e-5, p, None, None, None), L.ERR_INVALID_ARG),
+        (l.kcg_eltwise(99, L.BF16, L.BF16, 8, p, p, None), L.ERR_INVALID_ARG),
+        (l.kcg_eltwise(L.UNARY_OPS["Gelu"], L.BF16, L.F32, 8, p, p, None), L.ERR_INVALID_ARG),
+        (l.kcg_binary(L.BINARY_OPS["Add"], L.BF16, 2, sh, 2, (ctypes.c_int64 * 2)(3, 64), p, p, p, None), L.ERR_INVALID_ARG),
+        (l.kcg_softmax(L.BF16, 4, 64, 1.0, 0, 4, None, p, None), L.ERR_INVALID_ARG),
+        (l.kcg_gemm(L.BF16, L.BF16, 4, 64, 0, 1, 0, 0, p, 64, 0, p, 64, 0, p, 64, 0, None, None, None), L.ERR_INVALID_ARG),
+        (l.kcg_gemm(L.BF16, L.BF16, 4, 64, 64, 1, 0, 0, p, 8, 0, p, 64, 0, p, 64, 0, None, None, None), L.ERR_INVALID_ARG),
+        (l.kcg_gemm(L.BF16, L.BF16, 4, 64, 64, 1, 0, 0, p + 2, 64, 0, p, 64, 0, p, 64, 0, None, None, None), L.ERR_ALIGNMENT),
+        (l.kcg_gemm(L.I32, L.I32, 4, 64, 64, 1, 0, 0, p, 64, 0, p, 64, 0, p, 64, 0, None, None, None), L.ERR_UNSUPPORTED),
+        (l.kcg_fmha_fwd(L.BF16, 1, 1, 4, 4, 96, 1.0, 0, p, st, p, st, p, st, p, st, None), L.ERR_UNSUPPORTED),
+        (l.kcg_fmha_fwd(L.F32, 1, 1, 4, 4, 64, 1.0, 0, p, st, p, st, p, st, p, st, None), L.ERR_UNSUPPORTED),
+        (l.kcg_gather(L.BF16, L.F32, 1, 4, 64, 2, p, p, p, None), L.ERR_UNSUPPORTED),
+        (l.kcg_transpose(L.BF16, 1, 4, 64, p, p, None), L.ERR_INVALID_ARG),
+        (l.kcg_peer_alloc(0, None), L.ERR_INVALID_ARG),
+    ]
+    for i, (got, want) in enumerate(cases):
+        assert got == want, f"case {i}: status {got}, expected {want}: {l.kcg_last_error().decode()}"
+        assert l.kcg_last_error()      # a message was recorded
+    assert l.kcg_status_string(L.ERR_TIMEOUT) == b"device-side wait timed out"
+    torch.cuda.synchronize()
+    assert L.device_status() == 0
+
+
+def test_device_utilities():
+    L = lib()
+    l = L.load()
+    n = ctypes.c_int(-1)
+    assert l.kcg_device_count(ctypes.byref(n)) == 0 and n.value >= 1
+    p = ctypes.c_void_p()
+    assert l.kcg_peer_alloc(1 << 20, ctypes.byref(p)) == 0 and p.value
+    t = ctypes.c_void_p()
+    assert l.kcg_timer_begin(None, ctypes.byref(t)) == 0
+    assert l.kcg_device_memset(p, 0x5a, 1 << 20, None) == 0
+    ms = ctypes.c_float(-1.0)
+    assert l.kcg_timer_end(None, t, ctypes.byref(ms)) == 0 and ms.value >= 0.0
+    h = ctypes.create_string_buffer(64)
+    assert l.kcg_peer_export(p, h) == 0 and any(h.raw)
+    assert l.kcg_peer_free(p) == 0
