@@ -428,7 +428,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // S_i(j+1) complete, O_i is stable (PV_i(j) is behind them) and may be rescaled.  While tile
 // i is in its softmax, the tensor pipe works on tile 1-i, and every K / V tile is loaded once
 // for 256 query rows.
-constexpr int V2_THREADS = 320;
+// 12 warps: two softmax warpgroups, then a warpgroup holding the loader (warp 8) and the MMA
+// issuer (warp 9); warps 10-11 only take part in the register hand-over.  The third warpgroup
+// gives most of its registers to the softmax warpgroups (setmaxnreg), whose 128-element score
+// rows otherwise spill at the 168 registers a 384-thread CTA gets per thread.
+constexpr int V2_THREADS = 384;
+constexpr int V2_REGS_SOFTMAX = 216, V2_REGS_SERVICE = 72;   // 2*128*216 + 128*72 = 64512 <= 65536
 
 template <typename T, int D, int NSLOT>
 __global__ void __launch_bounds__(V2_THREADS, 1)
@@ -498,6 +503,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA loader
+    reg_dealloc<V2_REGS_SERVICE>();
     if (lane == 0 && n_max > 0) {
       bool ok = true;
       // Ring layout: K_0 travels with the Q tiles (slot 4, never reused); afterwards one ring
@@ -535,6 +541,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
+    reg_dealloc<V2_REGS_SERVICE>();
     bool ok = n_max > 0;
     const uint32_t q_addr = smem_u32(q_smem);
     auto issue_s = [&](int i, int j) {  // S_i(j) = Q_i K_j^T   (lane 0 only)
@@ -592,8 +599,9 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp < 8) {
     // ------------------------------------------------------------------ softmax / epilogue
+    reg_alloc<V2_REGS_SOFTMAX>();
     const int i = warp >> 2;                      // query tile of this warpgroup
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
@@ -754,6 +762,8 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       *p.status = KCG_ERR_TIMEOUT;
       __threadfence_system();
     }
+  } else {
+    reg_dealloc<V2_REGS_SERVICE>();   // warps 10-11: only the hand-over
   }
 
   tc_fence_before();

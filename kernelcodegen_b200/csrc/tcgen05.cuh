@@ -198,6 +198,15 @@ __device__ __forceinline__ void tmem_st64(uint32_t taddr, const uint32_t (&r)[64
 }
 
 // ---- MMA ---------------------------------------------------------------------------
+// Register hand-over between warpgroups (all four warps of a warpgroup must execute it): a
+// warpgroup that needs few registers releases the rest, one that needs many claims them.
+template <uint32_t kRegs> __device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(kRegs));
+}
+template <uint32_t kRegs> __device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kRegs));
+}
+
 enum class Kind { F16, F8F6F4, TF32 };
 
 // D(tmem) (+)= A(smem) * B(smem); issued by ONE thread.  `accumulate` == 0 overwrites D.
