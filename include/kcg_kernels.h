@@ -355,8 +355,10 @@ KCG_API int kcg_transpose(int dtype, int64_t batch, int64_t rows, int64_t cols, 
  * like the reference's loop nest; 1 = the tensor cores, as three tf32 products of operands
  * split into hi + lo parts (a b = a_hi b_hi + a_lo b_hi + a_hi b_lo, fp32 accumulation; results
  * within ~1e-6 relative of a float64 product, several times faster; uses a cached per-device
- * scratch buffer of 12 (M + N) K bytes per batch entry); -1 (default) = 1 when M N K >= 256^3,
- * else 0.  Process-wide, not thread-safe.
+ * scratch buffer of 12 (M + N) K bytes per batch entry plus up to 1 GiB of partial products,
+ * shared by all float32 GEMMs of a device: serialise float32 GEMMs that could overlap on one
+ * device from different streams); -1 (default) = 1 when M N K >= 256^3, else 0.  Process-wide,
+ * not thread-safe.
  */
 KCG_API void kcg_gemm_set_fp32_mode(int mode);
 
