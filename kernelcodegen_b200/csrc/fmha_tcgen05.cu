@@ -39,7 +39,7 @@ constexpr int TILE16K = 16384;   // one 128-row x 128-byte swizzled block
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 #ifndef KCG_FMHA_PACKED_EXP
-#define KCG_FMHA_PACKED_EXP 1
+#define KCG_FMHA_PACKED_EXP 0
 #endif
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units: rescale O only when the max grew by > 2^8
 
