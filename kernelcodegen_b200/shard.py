@@ -156,24 +156,48 @@ class GatherBuffers:
         esize = torch.empty((), dtype=dtype).element_size()
         self.nbytes = self.total_rows * self.cols * esize
         lib = _lib.load()
-        p = ctypes.c_void_p()
-        _lib.check(lib.kcg_peer_alloc(self.nbytes, ctypes.byref(p)), "kcg_peer_alloc")
-        self._own = p.value
-        self.ptrs = [None] * self.world
-        self.ptrs[self.rank] = self._own
+        self._own = None
         self._opened = []
+        self.ptrs = [None] * self.world
+        # Every step that can fail on one rank is followed by an exchange of its outcome, so that
+        # all ranks raise together instead of leaving the others inside a collective.
+        err = None
+        handle = None
+        p = ctypes.c_void_p()
+        try:
+            _lib.check(lib.kcg_peer_alloc(self.nbytes, ctypes.byref(p)), "kcg_peer_alloc")
+            self._own = p.value
+            self.ptrs[self.rank] = self._own
+            if self.world > 1:
+                h = ctypes.create_string_buffer(64)
+                _lib.check(lib.kcg_peer_export(self._own, h), "kcg_peer_export")
+                handle = bytes(h.raw)
+        except Exception as e:   # noqa: BLE001 - reported to every rank below
+            err = f"rank {self.rank}: {e}"
         if self.world > 1:
-            h = ctypes.create_string_buffer(64)
-            _lib.check(lib.kcg_peer_export(self._own, h), "kcg_peer_export")
-            handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(h.raw), group=group)
-            for r, hb in enumerate(handles):
-                if r == self.rank:
-                    continue
-                q = ctypes.c_void_p()
-                _lib.check(lib.kcg_peer_open(ctypes.create_string_buffer(hb, 64), ctypes.byref(q)), "kcg_peer_open")
-                self.ptrs[r] = q.value
-                self._opened.append(q.value)
+            got = [None] * self.world
+            dist.all_gather_object(got, (handle, err), group=group)
+            errs = [e for _, e in got if e]
+            if not errs:
+                for r, (hb, _) in enumerate(got):
+                    if r == self.rank:
+                        continue
+                    q = ctypes.c_void_p()
+                    rc = lib.kcg_peer_open(ctypes.create_string_buffer(hb, 64), ctypes.byref(q))
+                    if rc != 0:
+                        err = f"rank {self.rank}: kcg_peer_open of rank {r}'s buffer: status {rc} ({lib.kcg_last_error().decode()})"
+                        break
+                    self.ptrs[r] = q.value
+                    self._opened.append(q.value)
+                got2 = [None] * self.world
+                dist.all_gather_object(got2, err, group=group)
+                errs = [e for e in got2 if e]
+            if errs:
+                self.local = None
+                self.close()
+                raise RuntimeError("GatherBuffers: " + "; ".join(errs))
+        elif err:
+            raise RuntimeError("GatherBuffers: " + err)
         # torch view of the local matrix (bf16 has no array-interface code: view 16-bit words)
         ts = _TYPESTR[dtype] or "<i2"
         t = torch.as_tensor(_CudaArray(self._own, (self.total_rows, self.cols), ts, self), device="cuda")
