@@ -38,9 +38,6 @@ constexpr int KV_STAGES = 2;
 constexpr int TILE16K = 16384;   // one 128-row x 128-byte swizzled block
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
-#ifndef KCG_FMHA_PACKED_EXP
-#define KCG_FMHA_PACKED_EXP 0
-#endif
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units: rescale O only when the max grew by > 2^8
 
 struct FmhaParams {
@@ -99,29 +96,6 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
 template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   __half2 v = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// 2^x for a pair of scores straight into the 16-bit P word: the arguments are rounded to the
-// storage type first and one special-function instruction produces both results, already packed
-// — half the special-function work of two fp32 ex2, and the precision of P is that of its 16-bit
-// storage either way.  lo / hi return the results as fp32 for the row sum.
-template <typename T> __device__ __forceinline__ uint32_t exp2_pair_packed(float x0, float x1, float& lo, float& hi);
-template <> __device__ __forceinline__ uint32_t exp2_pair_packed<__nv_bfloat16>(float x0, float x1, float& lo, float& hi) {
-  const uint32_t w = pack2<__nv_bfloat16>(x0, x1);
-  uint32_t r;
-  asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(r) : "r"(w));
-  lo = __uint_as_float(r << 16);
-  hi = __uint_as_float(r & 0xffff0000u);
-  return r;
-}
-template <> __device__ __forceinline__ uint32_t exp2_pair_packed<__half>(float x0, float x1, float& lo, float& hi) {
-  const uint32_t w = pack2<__half>(x0, x1);
-  uint32_t r;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(r) : "r"(w));
-  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&r));
-  lo = f.x;
-  hi = f.y;
-  return r;
 }
 
 // kPTmem: P is written to tensor memory and the PV MMA reads its A operand from there;
@@ -691,17 +665,12 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int k = half * 64; k < half * 64 + 64; k += 2) {
           const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sreg[k]), __uint_as_float(sreg[k + 1])), c2, nm2);
-          float x0, x1, p0, p1;
+          float x0, x1;
           f2_unpack(x2, x0, x1);
-#if KCG_FMHA_PACKED_EXP
-          const uint32_t pw = exp2_pair_packed<T>(x0, x1, p0, p1);
-#else
-          p0 = fast_exp2(x0); p1 = fast_exp2(x1);
-          const uint32_t pw = pack2<T>(p0, p1);
-#endif
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
           if ((k >> 1) & 1) lsum_b = f2_add(lsum_b, f2_pack(p0, p1));
           else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
-          sreg[k >> 1] = pw;  // in place: word k/2 is never read again
+          sreg[k >> 1] = pack2<T>(p0, p1);  // in place: word k/2 is never read again
         }
         // hand this half of P (32 packed columns) to the MMA thread
         tmem_st32(s_addr + half * 32, reinterpret_cast<uint32_t(&)[32]>(sreg[half * 32]));
