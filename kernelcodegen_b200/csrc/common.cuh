@@ -156,6 +156,40 @@ __device__ __forceinline__ float gelu_tanh(float v) {
   return __fmul_rn(t1, __fadd_rn(t7, 1.0f));
 }
 
+// The same function for two values at once with packed fp32x2 instructions (each lane of
+// mul / add .rn.f32x2 rounds exactly like the scalar instruction, and the operation sequence is
+// the scalar one, so the results are the bits gelu_tanh() gives); 8 packed instructions and two
+// tanh instead of 16 + 2.
+template <bool kFast>
+__device__ __forceinline__ void gelu_tanh_pair(float& a, float& b) {
+  if constexpr (!kFast) {
+    a = gelu_tanh<false>(a);
+    b = gelu_tanh<false>(b);
+  } else {
+    uint64_t v, half2v, c1, c0, one, t1, vv, t3, m, t5, t6;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(a), "f"(b));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(half2v) : "f"(0.5f));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(c1) : "f"(0.044715f));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(c0) : "f"(0.797884f));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(one) : "f"(1.0f));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(t1) : "l"(v), "l"(half2v));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(vv) : "l"(v), "l"(v));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(t3) : "l"(v), "l"(vv));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(m) : "l"(c1), "l"(t3));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(t5) : "l"(m), "l"(v));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(t6) : "l"(c0), "l"(t5));
+    float x0, x1, y0, y1;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(t6));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y0) : "f"(x0));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y1) : "f"(x1));
+    uint64_t t7, s, r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(t7) : "f"(y0), "f"(y1));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(s) : "l"(t7), "l"(one));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(t1), "l"(s));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
+  }
+}
+
 // 2^x on the special-function unit (relative error about 2^-22, denormal results flushed).
 __device__ __forceinline__ float exp2f_approx(float x) {
   float r;
