@@ -197,6 +197,27 @@ __device__ __forceinline__ float exp2f_approx(float x) {
   return r;
 }
 
+// Two fp32 values in one 64-bit register for the packed .f32x2 instructions of sm_100 (each lane
+// rounds like the scalar instruction).
+__device__ __forceinline__ uint64_t pk_make(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void pk_split(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t pk_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t pk_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
 // Row kernels (LayerNorm, softmax) keep a row in registers as raw 32-bit words (two 16-bit
 // elements or one fp32 per word) and unpack it once per pass over the row.  Keeping the packed
 // form (a bf16 row of 4096 is 64 registers per lane at one warp per row) is what lets enough

@@ -51,7 +51,10 @@ __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __rest
     for (int i = 0; i < VPT; ++i)
       if (kExact || i * nthr + tid < nvec) rv[i] = __ldcs(reinterpret_cast<const uint4*>(res) + i * nthr + tid);
   }
+  // 16-bit types: the two elements of a word go through the packed fp32x2 pipe together (the
+  // even and the odd elements of the thread form two partial sums that are added at the end).
   float s = 0.f;
+  uint64_t s2 = 0ull;
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
     if (kExact || i * nthr + tid < nvec) {
@@ -60,12 +63,19 @@ __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __rest
       for (int k = 0; k < 4; ++k) {
         float f[EPW];
         W::unpack(w[k], f);
-#pragma unroll
-        for (int e = 0; e < EPW; ++e) s += f[e];
+        if constexpr (EPW == 2) s2 = pk_add(s2, pk_make(f[0], f[1]));
+        else s += f[0];
       }
     }
+  if constexpr (EPW == 2) {
+    float a, b;
+    pk_split(s2, a, b);
+    s = a + b;
+  }
   const float mean = reduce(s) * inv_n;
   float q = 0.f;
+  uint64_t q2 = 0ull;
+  const uint64_t nmean2 = pk_make(-mean, -mean);
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
     if (kExact || i * nthr + tid < nvec) {
@@ -74,15 +84,23 @@ __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __rest
       for (int k = 0; k < 4; ++k) {
         float f[EPW];
         W::unpack(w[k], f);
-#pragma unroll
-        for (int e = 0; e < EPW; ++e) {
-          const float d = f[e] - mean;
+        if constexpr (EPW == 2) {
+          const uint64_t d2 = pk_add(pk_make(f[0], f[1]), nmean2);
+          q2 = pk_fma(d2, d2, q2);
+        } else {
+          const float d = f[0] - mean;
           q = fmaf(d, d, q);
         }
       }
     }
+  if constexpr (EPW == 2) {
+    float a, b;
+    pk_split(q2, a, b);
+    q = a + b;
+  }
   const float rstd = 1.0f / sqrtf(reduce(q) * inv_n + eps);
   const float shift = -mean * rstd;
+  const uint64_t rstd2 = pk_make(rstd, rstd), shift2 = pk_make(shift, shift);
   if (mean_out != nullptr && tid == 0) {  // the row's statistics, when the caller asked for them
     *mean_out = mean;
     *rstd_out = rstd;
@@ -103,8 +121,12 @@ __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __rest
         W::unpack(w[k], f);
         W::unpack(gw[k], g);
         W::unpack(bw[k], b);
-#pragma unroll
-        for (int e = 0; e < EPW; ++e) r[e] = fmaf(g[e], fmaf(f[e], rstd, shift), b[e]);
+        if constexpr (EPW == 2) {
+          const uint64_t t2 = pk_fma(pk_make(f[0], f[1]), rstd2, shift2);
+          pk_split(pk_fma(pk_make(g[0], g[1]), t2, pk_make(b[0], b[1])), r[0], r[1]);
+        } else {
+          r[0] = fmaf(g[0], fmaf(f[0], rstd, shift), b[0]);
+        }
         o[k] = W::pack(r);
       }
       if constexpr (kFuse) {
