@@ -38,18 +38,7 @@ constexpr int KV_STAGES = 2;
 constexpr int TILE16K = 16384;   // one 128-row x 128-byte swizzled block
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
-#ifndef KCG_FMHA_EMU_PERIOD
-#define KCG_FMHA_EMU_PERIOD 0
-#endif
-constexpr int kEmuPeriod = KCG_FMHA_EMU_PERIOD;   // every kEmuPeriod-th pair of exponentials on the FMA pipe (0: none)
-constexpr float kRescaleThreshold = 8.0f;
-#ifdef KCG_FMHA_TRACE
-// Development aid (never built into the library): per-event clock stamps of one CTA.
-__device__ long long g_fmha_trace[4096];
-#define KCG_TR(slot) do { if (blockIdx.x == 3 && blockIdx.y == 7) g_fmha_trace[(slot)] = clock64(); } while (0)
-#else
-#define KCG_TR(slot) do { } while (0)
-#endif  // in log2 units: rescale O only when the max grew by > 2^8
+constexpr float kRescaleThreshold = 8.0f;  // in log2 units: rescale O only when the max grew by > 2^8
 
 struct FmhaParams {
   void* O;
@@ -97,31 +86,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
-}
-
-// 2^x for a pair of fp32 values on the FMA and integer pipes instead of the special-function
-// unit: x is split into its nearest integer n (by adding 1.5 * 2^23, which leaves n in the low
-// mantissa bits) and a remainder f in [-0.5, 0.5]; 2^f comes from a cubic (relative error
-// 8e-5, well under the rounding of P to 16 bits) and n is added into the exponent field.
-// Inputs below -126 are clamped (the result is then ~1e-38 instead of 0); -inf must not be
-// passed where an exact zero is required.
-__device__ __forceinline__ void exp2_pair_fma(uint64_t x2, float& p0, float& p1) {
-  float x0, x1;
-  f2_unpack(x2, x0, x1);
-  x0 = fmaxf(x0, -126.f);
-  x1 = fmaxf(x1, -126.f);
-  const uint64_t xc = f2_pack(x0, x1);
-  const uint64_t t2 = f2_add(xc, f2_pack(12582912.f, 12582912.f));
-  const uint64_t n2 = f2_add(t2, f2_pack(-12582912.f, -12582912.f));
-  const uint64_t f2 = f2_fma(n2, f2_pack(-1.f, -1.f), xc);
-  uint64_t r2 = f2_fma(f2_pack(0.05508868f, 0.05508868f), f2, f2_pack(0.24260405f, 0.24260405f));
-  r2 = f2_fma(r2, f2, f2_pack(0.69327623f, 0.69327623f));
-  r2 = f2_fma(r2, f2, f2_pack(0.99992895f, 0.99992895f));
-  float r0, r1, t0, t1;
-  f2_unpack(r2, r0, r1);
-  f2_unpack(t2, t0, t1);
-  p0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(t0) << 23));
-  p1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
 }
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -622,19 +586,13 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < 2; ++i) {
           if (j >= n_blk[i]) continue;
           // P arrives in two column halves; the first four k-steps of PV start on the first
-          KCG_TR(2048 + (j * 2 + i) * 8 + 0);
           if (!mbar_wait(&p_full[2 * i], j & 1u, abort_flag)) { ok = false; break; }
-          KCG_TR(2048 + (j * 2 + i) * 8 + 1);
           tc_fence_after();
           issue_pv(i, j, 0);
-          KCG_TR(2048 + (j * 2 + i) * 8 + 2);
           if (!mbar_wait(&p_full[2 * i + 1], j & 1u, abort_flag)) { ok = false; break; }
-          KCG_TR(2048 + (j * 2 + i) * 8 + 3);
           tc_fence_after();
           issue_pv(i, j, 1);
-          KCG_TR(2048 + (j * 2 + i) * 8 + 4);
           if (j + 1 < n_blk[i]) issue_s(i, j + 1);
-          KCG_TR(2048 + (j * 2 + i) * 8 + 5);
           // one commit covers both: the next score tile, or the finished output, is ready
           mma_commit(&s_full[i]);
         }
@@ -663,16 +621,12 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_mine; ++j) {
-#define KCG_TRS(e) do { if (quarter == 0 && lane == 0) KCG_TR((j * 2 + i) * 8 + (e)); } while (0)
-      KCG_TRS(0);
       if (!mbar_wait(&s_full[i], j & 1u, abort_flag)) { ok = false; break; }
-      KCG_TRS(1);
       tc_fence_after();
       uint32_t sreg[BN];
       tmem_ld64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));
       tmem_ld64(s_addr + 64, reinterpret_cast<uint32_t(&)[64]>(sreg[64]));
       tmem_wait_ld();
-      KCG_TRS(2);
       const int kv0 = j * BN;
       int limit = p.Skv - kv0;
       if (p.causal) limit = min(limit, qi + off + 1 - kv0);
@@ -700,7 +654,6 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       const float neg_m = (m == -INFINITY) ? 0.f : -m;
       const uint64_t c2 = f2_pack(c, c), nm2 = f2_pack(neg_m, neg_m);
-      KCG_TRS(3);
       // S_i(j) being complete means PV_i(j-1) is complete: O_i may be rescaled now.
       if (__any_sync(0xffffffffu, rescale)) {
         const float a = rescale ? alpha : 1.f;
@@ -715,32 +668,24 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       uint64_t lsum_a = 0ull, lsum_b = 0ull;  // two (+0.f, +0.f) accumulators
-      const bool unmasked = limit >= BN;   // masked blocks keep ex2 everywhere: its 2^-inf is an exact zero
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
 #pragma unroll
         for (int k = half * 64; k < half * 64 + 64; k += 2) {
           const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sreg[k]), __uint_as_float(sreg[k + 1])), c2, nm2);
-          float p0, p1;
-          if (kEmuPeriod > 0 && unmasked && ((k >> 1) % (kEmuPeriod > 0 ? kEmuPeriod : 1)) == kEmuPeriod - 1) {
-            exp2_pair_fma(x2, p0, p1);
-          } else {
-            float x0, x1;
-            f2_unpack(x2, x0, x1);
-            p0 = fast_exp2(x0); p1 = fast_exp2(x1);
-          }
+          float x0, x1;
+          f2_unpack(x2, x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
           if ((k >> 1) & 1) lsum_b = f2_add(lsum_b, f2_pack(p0, p1));
           else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
           sreg[k >> 1] = pack2<T>(p0, p1);  // in place: word k/2 is never read again
         }
         // hand this half of P (32 packed columns) to the MMA thread
-        KCG_TRS(4 + half * 2);
         tmem_st32(s_addr + half * 32, reinterpret_cast<uint32_t(&)[32]>(sreg[half * 32]));
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[2 * i + half]);
-        KCG_TRS(5 + half * 2);
       }
       float l0, l1;
       f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
@@ -984,9 +929,3 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
 }
 }  // namespace
 }  // namespace kcg
-
-#ifdef KCG_FMHA_TRACE
-extern "C" __attribute__((visibility("default"))) int kcg_fmha_trace_read(long long* host, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, kcg::g_fmha_trace, sizeof(long long) * n));
-}
-#endif
