@@ -426,6 +426,16 @@ KCG_API int kcg_timer_begin(void* stream, void** timer);
 KCG_API int kcg_timer_end(void* stream, void* timer, float* milliseconds);
 
 /*
+ * Diagnostic: launches one thread block that waits, with the same bounded wait all tensor-core
+ * kernels use, on a barrier that nothing signals, for at most budget_ns (<= 100 ms) nanoseconds.
+ * The kernel then gives up exactly as a real kernel would: it writes KCG_ERR_TIMEOUT to the word
+ * kcg_device_status() reports, stores the time it waited to *waited_ns_device (device memory)
+ * and exits normally, leaving the context usable.  No counterpart in the reference.
+ */
+KCG_API int kcg_selftest_bounded_wait(uint64_t budget_ns, unsigned long long* waited_ns_device,
+                                      void* stream);
+
+/*
  * Row-range owned by one rank when `total` independent units (GEMM rows of A/C,
  * attention batch*head slices, LayerNorm / elementwise rows) are split over
  * `world` GPUs in contiguous blocks rounded to `granule` units.  The reference

@@ -63,6 +63,7 @@ SIGNATURES = {
     "kcg_device_memset": ([_vp, _ci, ctypes.c_size_t, _vp], _ci),
     "kcg_timer_begin": ([_vp, ctypes.POINTER(_vp)], _ci),
     "kcg_timer_end": ([_vp, _vp, ctypes.POINTER(_fp)], _ci),
+    "kcg_selftest_bounded_wait": ([ctypes.c_uint64, _vp, _vp], _ci),
     "kcg_shard_range": ([_i64, _ci, _ci, _i64, _i64p, _i64p], _ci),
 }
 

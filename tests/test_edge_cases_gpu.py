@@ -87,3 +87,20 @@ def test_device_utilities():
     h = ctypes.create_string_buffer(64)
     assert l.kcg_peer_export(p, h) == 0 and any(h.raw)
     assert l.kcg_peer_free(p) == 0
+
+
+def test_bounded_wait_gives_up_and_context_survives():
+    # a barrier nobody signals: the wait must run out of its budget, report a status and return
+    L = lib()
+    l = L.load()
+    waited = torch.zeros(1, dtype=torch.int64, device="cuda")
+    assert l.kcg_selftest_bounded_wait(2_000_000, waited.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert L.device_status() == L.ERR_TIMEOUT
+    assert L.device_status() == 0                      # reading clears it
+    assert 2_000_000 <= int(waited.item()) < 50_000_000   # gave up after the budget, well before 50 ms
+    # the context is intact: an ordinary kernel runs and is correct afterwards
+    from kernelcodegen_b200 import ops
+    x = torch.randn(64, 256, device="cuda").bfloat16()
+    assert torch.equal(ops.elementwise(x, "Relu"), torch.relu(x))
+    assert l.kcg_selftest_bounded_wait(0, waited.data_ptr(), None) == L.ERR_INVALID_ARG
