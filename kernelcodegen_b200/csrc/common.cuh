@@ -34,6 +34,35 @@ inline int check_launch(const char* what) {
   return KCG_OK;
 }
 
+// ---- overlapped launches ------------------------------------------------------------
+// A kernel launched with launch_overlapped() may become resident while the previous kernel in
+// the stream is still draining (programmatic dependent launch): its CTAs take the SM slots that
+// free up and block in grid_dependency_wait() until the previous grid has completed and its
+// writes are visible.  The launch latency and the ramp-up of one kernel then hide under the tail
+// of the one before, which is worth 1-2 us between two 25 us bandwidth kernels.
+// Rule: every kernel launched this way calls grid_dependency_wait() in all threads before its
+// first global access and calls grid_launch_dependents() once.  (A kernel that skipped the wait
+// could finish before its predecessor and release its own successor too early.)
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+bool overlap_launch_enabled();
+template <typename... KArgs, typename... Args>
+inline void launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_launch_enabled() ? 1 : 0;
+  // an error is left for check_launch() (cudaGetLastError) to report
+  (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Number of SMs of the current device (cached per device).

@@ -41,6 +41,8 @@ unary_vec(const TI* __restrict__ x, TO* __restrict__ y, int64_t ngroups, bool wi
   constexpr int EPT = 16 / (sizeof(TI) < sizeof(TO) ? sizeof(TI) : sizeof(TO));
   constexpr int NI = EPT * sizeof(TI) / 16, NO = EPT * sizeof(TO) / 16;
   constexpr bool kFast = sizeof(TO) < 4;
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   int64_t g0 = static_cast<int64_t>(blockIdx.x) * blockDim.x * UNROLL + threadIdx.x;
   for (; g0 < ngroups; g0 += stride * UNROLL) {
@@ -115,8 +117,8 @@ int launch_unary(int64_t n, const void* xv, void* yv, cudaStream_t stream) {
     const int64_t ngroups = n / EPT;
     const int64_t want = (ngroups + 256 * UNROLL - 1) / (256 * UNROLL);
     const int64_t cap = static_cast<int64_t>(sms) * 8;
-    unary_vec<TI, TO, Op, UNROLL><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
-        x, y, ngroups, (reinterpret_cast<uintptr_t>(x) & 31u) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0);
+    launch_overlapped(unary_vec<TI, TO, Op, UNROLL>, dim3(static_cast<unsigned>(want < cap ? want : cap)), dim3(256), 0, stream,
+                      x, y, ngroups, (reinterpret_cast<uintptr_t>(x) & 31u) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0);
     int rc = check_launch("unary_vec");
     if (rc) return rc;
     done = ngroups * EPT;
@@ -169,6 +171,8 @@ template <typename T, typename Op, int UNROLL>
 __global__ void __launch_bounds__(256)
 binary_same_vec(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ c, int64_t nvec) {
   constexpr int VW = Vec16<T>::N;
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   int64_t g0 = static_cast<int64_t>(blockIdx.x) * blockDim.x * UNROLL + threadIdx.x;
   for (; g0 < nvec; g0 += stride * UNROLL) {
@@ -267,6 +271,8 @@ __global__ void __launch_bounds__(256)
 binary_row_vector(const T* __restrict__ full, const T* __restrict__ vec, T* __restrict__ c, int64_t rows,
                   int64_t inner_vecs) {
   constexpr int VW = Vec16<T>::N;
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (j >= inner_vecs) return;
   const Vec16<T> vv = ld_vec(vec + j * VW);
@@ -307,7 +313,8 @@ int launch_binary(const BcastDims& d, bool same_shape, int64_t total, const void
     constexpr int UNROLL = 4;
     const int64_t nvec = total / VW;
     const int64_t want = (nvec + 256 * UNROLL - 1) / (256 * UNROLL);
-    binary_same_vec<T, Op, UNROLL><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(a, b, c, nvec);
+    launch_overlapped(binary_same_vec<T, Op, UNROLL>, dim3(static_cast<unsigned>(want < cap ? want : cap)), dim3(256), 0, stream,
+                      a, b, c, nvec);
     return check_launch("binary_same_vec");
   }
   // Vector accesses along the innermost dimension need every outer stride to keep
@@ -327,8 +334,8 @@ int launch_binary(const BcastDims& d, bool same_shape, int64_t total, const void
     if (gy > gy_cap) gy = gy_cap;
     if (gx <= 0x7fffffffll && gy <= 65535) {
       dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
-      if (swap) binary_row_vector<T, Op, true, UNROLL><<<grid, 256, 0, stream>>>(b, a, c, rows, inner_vecs);
-      else binary_row_vector<T, Op, false, UNROLL><<<grid, 256, 0, stream>>>(a, b, c, rows, inner_vecs);
+      if (swap) launch_overlapped(binary_row_vector<T, Op, true, UNROLL>, grid, dim3(256), 0, stream, b, a, c, rows, inner_vecs);
+      else launch_overlapped(binary_row_vector<T, Op, false, UNROLL>, grid, dim3(256), 0, stream, a, b, c, rows, inner_vecs);
       return check_launch("binary_row_vector");
     }
   }
@@ -402,6 +409,8 @@ softmax_block_rows(const T* __restrict__ x, T* __restrict__ y, int cols, float s
   constexpr int EPW = W::EPW;
   constexpr int EPV = 4 * EPW;   // elements per 16-byte vector
   __shared__ float red[33];
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t row = blockIdx.x;
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int nvec = cols / EPV;
@@ -490,11 +499,11 @@ int launch_softmax(int64_t rows, int64_t cols, float scale, int causal, int64_t 
 #define KCG_SM_LAUNCH(V)                                                                                    \
   do {                                                                                                      \
     if (causal) {                                                                                           \
-      if (exact) softmax_block_rows<T, V, true, true><<<grid, threads, 0, stream>>>(xp, yp, icols, scale, causal, q_len);   \
-      else softmax_block_rows<T, V, false, true><<<grid, threads, 0, stream>>>(xp, yp, icols, scale, causal, q_len);        \
+      if (exact) launch_overlapped(softmax_block_rows<T, V, true, true>, dim3(grid), dim3(threads), 0, stream, xp, yp, icols, scale, causal, q_len);   \
+      else launch_overlapped(softmax_block_rows<T, V, false, true>, dim3(grid), dim3(threads), 0, stream, xp, yp, icols, scale, causal, q_len);        \
     } else {                                                                                                \
-      if (exact) softmax_block_rows<T, V, true, false><<<grid, threads, 0, stream>>>(xp, yp, icols, scale, causal, q_len);  \
-      else softmax_block_rows<T, V, false, false><<<grid, threads, 0, stream>>>(xp, yp, icols, scale, causal, q_len);       \
+      if (exact) launch_overlapped(softmax_block_rows<T, V, true, false>, dim3(grid), dim3(threads), 0, stream, xp, yp, icols, scale, causal, q_len);  \
+      else launch_overlapped(softmax_block_rows<T, V, false, false>, dim3(grid), dim3(threads), 0, stream, xp, yp, icols, scale, causal, q_len);       \
     }                                                                                                       \
   } while (0)
     if (vpt <= 2) KCG_SM_LAUNCH(2);

@@ -433,7 +433,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // gives most of its registers to the softmax warpgroups (setmaxnreg), whose 128-element score
 // rows otherwise spill at the 168 registers a 384-thread CTA gets per thread.
 constexpr int V2_THREADS = 384;
-constexpr int V2_REGS_SOFTMAX = 216, V2_REGS_SERVICE = 72;   // 2*128*216 + 128*72 = 64512 <= 65536
+constexpr int V2_REGS_SOFTMAX = 208, V2_REGS_SERVICE = 88;   // 2*128*208 + 128*88 = 64512 <= 65536
 
 template <typename T, int D, int NSLOT>
 __global__ void __launch_bounds__(V2_THREADS, 1)
@@ -465,14 +465,12 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int b = bh / p.H, h = bh % p.H;
   const int q0 = pr * 2 * BM;
   const int off = p.Skv - p.Sq;
-  int n_blk[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    int kv_end = p.Skv;
-    if (p.causal) kv_end = min(p.Skv, q0 + (i + 1) * BM + off);
-    n_blk[i] = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
-  }
-  const int n_max = max(n_blk[0], n_blk[1]);  // == n_blk[1]: the later rows see at least as many keys
+  // key blocks of the two tiles, as scalars: an array indexed by the tile would live in local memory
+  const int kv_end0 = p.causal ? min(p.Skv, q0 + BM + off) : p.Skv;
+  const int kv_end1 = p.causal ? min(p.Skv, q0 + 2 * BM + off) : p.Skv;
+  const int n_blk0 = kv_end0 > 0 ? (kv_end0 + BN - 1) / BN : 0;
+  const int n_blk1 = kv_end1 > 0 ? (kv_end1 + BN - 1) / BN : 0;
+  const int n_max = max(n_blk0, n_blk1);  // == n_blk1: the later rows see at least as many keys
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmQ);
@@ -575,16 +573,19 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = mbar_wait(q_full, 0, abort_flag);
       if (ok) {
         tc_fence_after();
+#pragma unroll
         for (int i = 0; i < 2; ++i)
-          if (n_blk[i] > 0) {
+          if ((i == 0 ? n_blk0 : n_blk1) > 0) {
             issue_s(i, 0);
             mma_commit(&s_full[i]);
           }
       }
       for (int j = 0; j < n_max && ok; ++j) {
         if (!mbar_wait(&kv_full[j & 1], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+#pragma unroll
         for (int i = 0; i < 2; ++i) {
-          if (j >= n_blk[i]) continue;
+          const int n_i = i == 0 ? n_blk0 : n_blk1;
+          if (j >= n_i) continue;
           // P arrives in two column halves; the first four k-steps of PV start on the first
           if (!mbar_wait(&p_full[2 * i], j & 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
@@ -592,7 +593,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (!mbar_wait(&p_full[2 * i + 1], j & 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
           issue_pv(i, j, 1);
-          if (j + 1 < n_blk[i]) issue_s(i, j + 1);
+          if (j + 1 < n_i) issue_s(i, j + 1);
           // one commit covers both: the next score tile, or the finished output, is ready
           mma_commit(&s_full[i]);
         }
@@ -615,7 +616,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const int qi = q0 + i * BM + r;
     const float c = p.scale_log2;
-    const int n_mine = n_blk[i];
+    const int n_mine = i == 0 ? n_blk0 : n_blk1;
     const uint32_t s_addr = tmem_base + lane_base + i * BN;
     const uint32_t o_addr = tmem_base + lane_base + 256 + i * BN;
     float m = -INFINITY, l = 0.f;

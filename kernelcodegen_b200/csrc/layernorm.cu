@@ -158,6 +158,8 @@ __global__ void __launch_bounds__(128, 5)
 ln_warp_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
              const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps,
              float* __restrict__ mean_out, float* __restrict__ rstd_out) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -174,6 +176,8 @@ ln_block_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __r
               const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps,
               float* __restrict__ mean_out, float* __restrict__ rstd_out) {
   __shared__ float red[33];
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t row = blockIdx.x;
   ln_row<T, VPT, kExact, kFuse>(x + row * cols, gamma, beta, kFuse ? res + row * cols : nullptr, y + row * cols,
                                 threadIdx.x, blockDim.x,
@@ -285,7 +289,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
   if (vec_ok && nvec <= 32 * g_warp_row_max_vecs) {
     const unsigned grid = static_cast<unsigned>((rows + 3) / 4);
     const int vpt = static_cast<int>((nvec + 31) / 32);
-#define KCG_LN_LAUNCH(V, E, F) ln_warp_rows<T, V, E, F><<<grid, 128, 0, stream>>>(x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
+#define KCG_LN_LAUNCH(V, E, F) launch_overlapped(ln_warp_rows<T, V, E, F>, dim3(grid), dim3(128), 0, stream, x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
 #define KCG_LN_WARP(V)                                                          \
   do {                                                                          \
     const bool exact = nvec == 32 * V;                                          \
@@ -307,7 +311,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
     threads = (threads + 31) / 32 * 32;
     const int vpt = static_cast<int>((nvec + threads - 1) / threads);
     const unsigned grid = static_cast<unsigned>(rows);
-#define KCG_LN_LAUNCH(V, E, F) ln_block_rows<T, V, E, F><<<grid, threads, 0, stream>>>(x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
+#define KCG_LN_LAUNCH(V, E, F) launch_overlapped(ln_block_rows<T, V, E, F>, dim3(grid), dim3(threads), 0, stream, x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
 #define KCG_LN_BLOCK(V)                                                         \
   do {                                                                          \
     const bool exact = nvec == static_cast<int64_t>(threads) * V;               \

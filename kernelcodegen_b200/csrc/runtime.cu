@@ -2,6 +2,7 @@
 // buffer, and the small entry points that launch nothing.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -36,6 +37,14 @@ int fail(int code, const char* fmt, ...) {
 }
 
 void clear_error() { g_error[0] = 0; }
+
+bool overlap_launch_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("KCG_OVERLAP_LAUNCH");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 
 int sm_count() {
   const int d = current_device();
