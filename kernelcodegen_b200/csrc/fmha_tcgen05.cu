@@ -472,6 +472,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int n_blk1 = kv_end1 > 0 ? (kv_end1 + BN - 1) / BN : 0;
   const int n_max = max(n_blk0, n_blk1);  // == n_blk1: the later rows see at least as many keys
 
+  grid_launch_dependents();
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
@@ -498,6 +499,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();  // set-up done; global memory only after the previous kernel has finished
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA loader
@@ -796,7 +798,7 @@ int launch_fmha2(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorM
   const uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, BM, BN);
   const uint32_t idesc_pv = make_idesc(fmt, fmt, 0, 1, BM, D);
   dim3 grid((p.q_tiles + 1) / 2, p.B * p.H);
-  kern<<<grid, V2_THREADS, SMEM, stream>>>(tmQ, tmK, tmV, p, idesc_qk, idesc_pv);
+  launch_overlapped(kern, grid, dim3(V2_THREADS), SMEM, stream, tmQ, tmK, tmV, p, idesc_qk, idesc_pv);
   return check_launch("fmha_fwd_kernel2");
 }
 

@@ -168,6 +168,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  grid_launch_dependents();   // the next kernel's prologue may overlap this kernel (see launch_overlapped)
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmA);
@@ -192,6 +193,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Barriers, tensor memory and descriptors are set up; operands and the output may be touched
+  // only when the kernel before this one in the stream has finished.
+  grid_dependency_wait();
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -406,7 +410,7 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
     const int64_t batch = p.total_tiles / (static_cast<int64_t>(p.m_tiles) * p.n_tiles);
     const int64_t pair_tiles = static_cast<int64_t>((p.m_tiles + 1) / 2) * p.n_tiles * batch;
     const int64_t clusters = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
-    kern<<<static_cast<int>(clusters * 2), NUM_THREADS, PSMEM_BYTES, stream>>>(tmA, tmB_pair, p, idescs.pair);
+    launch_overlapped(kern, dim3(static_cast<unsigned>(clusters * 2)), dim3(NUM_THREADS), PSMEM_BYTES, stream, tmA, tmB_pair, p, idescs.pair);
     return check_launch("gemm_tcgen05_pair_kernel");
   }
   if (tiling == kNarrow) {
@@ -418,14 +422,14 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     const int grid = static_cast<int>(q.total_tiles < sms ? q.total_tiles : sms);
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB_pair, q, idescs.narrow);
+    launch_overlapped(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tmA, tmB_pair, q, idescs.narrow);
     return check_launch("gemm_tcgen05_kernel (128x128)");
   }
   auto kern = gemm_tcgen05_kernel<kKind, kElemBytes, kAMn, kBMn, TOut, 256>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   const int grid = static_cast<int>(p.total_tiles < sms ? p.total_tiles : sms);
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p, idescs.wide);
+  launch_overlapped(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tmA, tmB, p, idescs.wide);
   return check_launch("gemm_tcgen05_kernel");
 }
 
