@@ -43,6 +43,7 @@ inline int check_launch(const char* what) {
 // Rule: every kernel launched this way calls grid_dependency_wait() in all threads before its
 // first global access and calls grid_launch_dependents() once.  (A kernel that skipped the wait
 // could finish before its predecessor and release its own successor too early.)
+// KCG_OVERLAP_LAUNCH=0 in the environment launches the same kernels without the attribute, for A/B timing.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 bool overlap_launch_enabled();
