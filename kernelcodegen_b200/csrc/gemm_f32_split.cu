@@ -64,6 +64,8 @@ template <int kOrder>
 __global__ void __launch_bounds__(256)
 split_k_contiguous(const float* __restrict__ src, int64_t rows, int64_t K, int64_t ld, int64_t src_batch,
                    float* __restrict__ dst, int64_t Kp, int64_t kc, int64_t chunks) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t k = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t r = blockIdx.y;
   if (k >= Kp) return;
@@ -78,6 +80,8 @@ __global__ void __launch_bounds__(256)
 split_r_contiguous(const float* __restrict__ src, int64_t rows, int64_t K, int64_t ld, int64_t src_batch,
                    float* __restrict__ dst, int64_t Kp, int64_t kc, int64_t chunks) {
   __shared__ float tile[32][33];
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int64_t r0 = static_cast<int64_t>(blockIdx.x) * 32, k0 = static_cast<int64_t>(blockIdx.y) * 32;
   const float* s = src + blockIdx.z * src_batch;
@@ -99,6 +103,8 @@ __global__ void __launch_bounds__(256)
 reduce_partials(const float* __restrict__ part, int64_t chunks, int64_t M, int64_t N, float* __restrict__ C, int64_t ldc,
                 int64_t stride_c, const float* __restrict__ scale_a, const float* __restrict__ scale_b,
                 const float* __restrict__ bias, int act) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t n4 = (N + 3) / 4;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (t >= M * n4) return;
@@ -133,12 +139,12 @@ int launch_split(const float* src, bool k_contiguous, int64_t rows, int64_t K, i
   if (k_contiguous) {
     if (rows > 65535) return fail(KCG_ERR_UNSUPPORTED, "fp32 gemm (tensor path): more than 65535 rows");
     dim3 grid(static_cast<unsigned>((Kp + 255) / 256), static_cast<unsigned>(rows), static_cast<unsigned>(batch));
-    split_k_contiguous<kOrder><<<grid, 256, 0, stream>>>(src, rows, K, ld, src_batch, dst, Kp, kc, chunks);
+    launch_overlapped(split_k_contiguous<kOrder>, grid, dim3(256), 0, stream, src, rows, K, ld, src_batch, dst, Kp, kc, chunks);
   } else {
     const int64_t gy = (Kp + 31) / 32;
     if (gy > 65535) return fail(KCG_ERR_UNSUPPORTED, "fp32 gemm (tensor path): K too large");
     dim3 grid(static_cast<unsigned>((rows + 31) / 32), static_cast<unsigned>(gy), static_cast<unsigned>(batch));
-    split_r_contiguous<kOrder><<<grid, 256, 0, stream>>>(src, rows, K, ld, src_batch, dst, Kp, kc, chunks);
+    launch_overlapped(split_r_contiguous<kOrder>, grid, dim3(256), 0, stream, src, rows, K, ld, src_batch, dst, Kp, kc, chunks);
   }
   return check_launch("split_tf32");
 }
@@ -187,7 +193,7 @@ int gemm_f32_tensor(int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
     if (rc) return rc;
     const int64_t threads = M * ((np + 3) / 4);
     dim3 grid(static_cast<unsigned>((threads + 255) / 256), static_cast<unsigned>(batch));
-    reduce_partials<<<grid, 256, 0, stream>>>(part, chunks, M, np, C + n0, ldc, stride_c, scale_a, scale_b,
+    launch_overlapped(reduce_partials, grid, dim3(256), 0, stream, part, chunks, M, np, C + n0, ldc, stride_c, scale_a, scale_b,
                                               bias ? bias + n0 : nullptr, act);
     rc = check_launch("reduce_partials");
     if (rc) return rc;
