@@ -39,7 +39,7 @@ FALLBACK_BF16_TFLOPS = 1590.0
 
 CONFIG = {"workload": f"LayerNorm(last dim)+GELU(tanh)+add on [{ROWS},{COLS}] bf16 per GPU",
           "l2": f"inputs rotate over {BUFFER_SETS} buffer sets (1.8 GB) so reads miss the 126 MB L2",
-          "launch": f"steps captured in a CUDA graph ({GRAPH_STEPS} steps per replay)",
+          "launch": f"steps captured in a CUDA graph ({GRAPH_STEPS} steps per replay); each kernel is a programmatic dependent of the one before",
           "sharding": "rows per rank, no collective"}
 
 
