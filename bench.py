@@ -8,8 +8,14 @@ over one batch of synthetic data: LayerNorm over the last dim of [8192, 4096] bf
 (fp32 statistics), GELU(tanh) on [8192, 4096] bf16 and the elementwise add of two
 [8192, 4096] bf16 tensors.  The metric is algorithmic HBM bytes per second summed over all
 ranks (weak scaling: every rank owns its own rows; no collective is on the data path).
-The tensor-core operators of the same library (GEMM, FMHA) and the fp32 variants are timed
-after the headline and reported under "workloads" in the same JSON line.
+
+The tensor-core operators of the same library are timed after the headline.  Their results are
+reported twice in the one JSON line: in full under "workloads", and inside "roofline" —
+"roofline.tensor" (bf16 / FP8 GEMM 8192^3 and attention S = 4096, each with median and best over
+at least 50 launches, the SM clock seen, the DRAM traffic of the matching profile and the CPU
+loop nests beside it), "roofline.sweep" (the other GEMM / attention sizes next to cuBLAS on the
+same GPU) and "roofline.sharded" (the fixed-size 8-GPU workloads split over the ranks of this run,
+compute only and with the gather of the outputs).
 
 `--impl reference` times the reference's CPU arithmetic for the same step (the fp32 loop
 nests of oracle/kcg_oracle.c on all host threads; the reference's own MLIR->LLVM CPU
@@ -21,7 +27,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -33,13 +38,17 @@ sys.path.insert(0, str(ROOT))
 ROWS, COLS = 8192, 4096
 BUFFER_SETS = 4           # inputs rotate so that no read is served from the 126 MB L2
 GRAPH_STEPS = 20          # steps captured per CUDA graph replay
+HEADLINE_REPLAYS = 10     # timed replays of the captured steps; the median replay is reported
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
+NOMINAL_BF16_TFLOPS = 2250.0
+NOMINAL_FP8_TFLOPS = 4500.0
 
 
 CONFIG = {"workload": f"LayerNorm(last dim)+GELU(tanh)+add on [{ROWS},{COLS}] bf16 per GPU",
           "l2": f"inputs rotate over {BUFFER_SETS} buffer sets (1.8 GB) so reads miss the 126 MB L2",
-          "launch": f"steps captured in a CUDA graph ({GRAPH_STEPS} steps per replay); each kernel is a programmatic dependent of the one before",
+          "launch": f"steps captured in a CUDA graph ({GRAPH_STEPS} steps per replay, {HEADLINE_REPLAYS} timed replays, "
+                    "median replay reported); each kernel is a programmatic dependent of the one before",
           "sharding": "rows per rank, no collective"}
 
 
@@ -75,6 +84,13 @@ def ncu_traffic(kernel: str):
         except Exception:
             return None
     return None
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 class ClockSampler:
@@ -133,6 +149,43 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def bind_to_gpu_numa_node(local_rank: int) -> dict:
+    """Restrict this process to the CPUs of the NUMA node its GPU hangs off, so that pinned host
+    buffers allocated afterwards (first touch) and the copy threads sit next to the GPU's PCIe
+    root.  Reads sysfs only; nothing about the GPU or the driver is changed.  Returns what was done."""
+    info = {"numa_node": None, "cpus": None}
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        index = local_rank
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        if visible and all(v.strip().isdigit() for v in visible.split(",")):
+            index = int(visible.split(",")[local_rank])
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        bus = pynvml.nvmlDeviceGetPciInfo(h).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        dev = Path("/sys/bus/pci/devices") / bus.lower()[-12:]
+        if not dev.exists():
+            dev = Path("/sys/bus/pci/devices") / ("0000:" + bus.lower().split(":", 1)[1])
+        node = int((dev / "numa_node").read_text().strip())
+        info["numa_node"] = node
+        cpulist = (dev / "local_cpulist").read_text().strip()
+        cpus = set()
+        for part in cpulist.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                cpus.update(range(int(a), int(b) + 1))
+            elif part:
+                cpus.add(int(part))
+        allowed = cpus & set(os.sched_getaffinity(0))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            info["cpus"] = len(allowed)
+    except Exception as exc:   # noqa: BLE001 - affinity is an optimisation, never a requirement
+        info["note"] = str(exc)[:120]
+    return info
+
+
 # ------------------------------------------------------------------------------ reference arm
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
@@ -142,10 +195,7 @@ def run_reference(args) -> None:
     from oracle import oracle as O
 
     # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core it may run on
-    try:
-        threads = len(os.sched_getaffinity(0))
-    except AttributeError:
-        threads = os.cpu_count() or 1
+    threads = host_threads()
     rng = np.random.default_rng(0xC0DE)
     x = rng.standard_normal((ROWS, COLS), dtype=np.float32)
     g = (1.0 + 0.1 * rng.standard_normal(COLS)).astype(np.float32)
@@ -160,19 +210,21 @@ def run_reference(args) -> None:
         O.ref32.unary("Gelu", u, threads=threads)
         O.ref32.binary_same("Add", a1, a2, threads=threads)
 
-    for _ in range(max(1, min(args.warmup, 2))):
+    # bounded: a step of the loop nests takes ~50 ms on 16 cores, so the caps only matter for huge K / W
+    warmup = max(1, min(args.warmup, 50))
+    steps = max(1, min(args.steps, 200))
+    for _ in range(warmup):
         step()
-    steps = max(1, min(args.steps, 20))
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
     dt = (time.perf_counter() - t0) / steps
     val = nbytes / dt / 1e9
-    sample = (f"full [{ROWS},{COLS}] step in fp32 (LayerNorm + GELU + add loop nests), {steps} steps, "
-              "bytes counted as the bf16 workload's algorithmic bytes")
+    sample = (f"full [{ROWS},{COLS}] step in fp32 (LayerNorm + GELU + add loop nests), {steps} steps after {warmup} "
+              "warm-up steps, bytes counted as the bf16 workload's algorithmic bytes")
     print(json.dumps({
         "impl": "reference", "metric": "hbm_gbs_ln_gelu_add", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": CONFIG,
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
@@ -185,10 +237,7 @@ def cpu_side_by_side(workloads: dict) -> None:
     the same shape, in fp32, on every host core this process may run on."""
     import numpy as np
     from oracle import oracle as O
-    try:
-        threads = len(os.sched_getaffinity(0))
-    except AttributeError:
-        threads = os.cpu_count() or 1
+    threads = host_threads()
     rng = np.random.default_rng(0xC0DE)
 
     def note(key, flops, dtc, sample):
@@ -233,20 +282,26 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM/FMHA/fp32 side measurements")
-    ap.add_argument("--only", default="", help="comma list of extras to run (bw,fp32,bw2,gemm,sgemm,fmha,move,sweep,gather)")
+    ap.add_argument("--only", default="",
+                    help="comma list of extras to run (bw,fp32,bw2,gemm,sgemm,fmha,move,sweep,gather,sharded)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
         return
     args.warmup = max(args.warmup, 3)
 
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    # before torch allocates anything pinned: sit on the CPUs next to this rank's GPU (undone after
+    # the end-to-end section, so that the CPU legs may use every core again)
+    affinity_before = os.sched_getaffinity(0) if hasattr(os, "sched_getaffinity") else None
+    numa = bind_to_gpu_numa_node(local_rank)
+
     import torch
     import torch.distributed as dist
     from kernelcodegen_b200 import _lib, host, ops
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
     torch.cuda.set_device(local_rank)
@@ -272,6 +327,16 @@ def main() -> None:
     def rnd(shape, dtype=dt, mean=0.0, std=1.0):
         return (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * std + mean).to(dtype)
 
+    def rnd_big(shape, dtype=dt, std=1.0):
+        """N(0, std) in `dtype` without a full-size fp32 temporary (tensors of several GiB)."""
+        out = torch.empty(shape, dtype=dtype, device="cuda")
+        flat = out.view(-1)
+        piece = 1 << 27
+        for s in range(0, flat.numel(), piece):
+            e = min(flat.numel(), s + piece)
+            flat[s:e] = (torch.randn(e - s, generator=gen, device="cuda", dtype=torch.float32) * std).to(dtype)
+        return out
+
     sets = []
     for _ in range(BUFFER_SETS):
         sets.append({
@@ -290,16 +355,16 @@ def main() -> None:
     bytes_step = step_bytes(2)
     total_step_bytes = sum(bytes_step.values())
 
-    # The steps are captured once into a CUDA graph (GRAPH_STEPS steps over rotating buffers)
-    # and replayed, so that the ~10 us of host work per launch does not sit between 25 us kernels.
+    # The K steps are captured once into a CUDA graph (over rotating buffers) so that the ~10 us of
+    # host work per launch does not sit between 25 us kernels.  The graph is then replayed
+    # HEADLINE_REPLAYS times, each replay between its own pair of events; the reported time per
+    # step is the median replay divided by K (the mean and the best are reported beside it).
     cap_stream = torch.cuda.Stream()
     with torch.cuda.stream(cap_stream):
         for i in range(args.warmup):
             step(i)
     torch.cuda.synchronize()
-    graph_steps = min(GRAPH_STEPS, args.steps)
-    replays = (args.steps + graph_steps - 1) // graph_steps
-    args.steps = replays * graph_steps
+    graph_steps = max(1, args.steps)
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=cap_stream):
         for i in range(graph_steps):
@@ -315,32 +380,40 @@ def main() -> None:
     graph.replay()
     ln_graph.replay()
     sampler = ClockSampler(local_rank).start()
+    replays = HEADLINE_REPLAYS
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(replays):
+    evs[0].record()
+    for r in range(replays):
         graph.replay()
-    e1.record()
+        evs[r + 1].record()
     barrier()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
-    ms_per_step = ms_total / args.steps
+    replay_ms = [evs[r].elapsed_time(evs[r + 1]) for r in range(replays)]
+    ms_median = max_over_ranks(statistics.median(replay_ms)) / graph_steps
+    ms_mean = max_over_ranks(sum(replay_ms) / replays) / graph_steps
+    ms_best = max_over_ranks(min(replay_ms)) / graph_steps
+    ms_per_step = ms_median
     value = world * total_step_bytes / (ms_per_step * 1e-3) / 1e9
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    # ---- roofline of the dominant kernel (LayerNorm): n_roof launches on distinct inputs,
-    # timed with CUDA events on the stream they run on
+    # ---- roofline of the dominant kernel (LayerNorm): n_roof launches on distinct inputs per
+    # replay, each replay timed with CUDA events on the stream it runs on
     peaks = measured_peaks()
-    roof_reps = max(3, min(50, args.steps // n_roof))
-    e0.record()
-    for _ in range(roof_reps):
+    roof_reps = 8
+    revs = [torch.cuda.Event(enable_timing=True) for _ in range(roof_reps + 1)]
+    revs[0].record()
+    for r in range(roof_reps):
         ln_graph.replay()
-    e1.record()
+        revs[r + 1].record()
     torch.cuda.synchronize()
-    ln_ms = e0.elapsed_time(e1) / (roof_reps * n_roof)
+    rms = [revs[r].elapsed_time(revs[r + 1]) / n_roof for r in range(roof_reps)]
+    ln_ms = sum(rms) / roof_reps
     clocks = sampler.stop()
     ln_gbs = bytes_step["layernorm"] / (ln_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "ln_block_rows<bf16,8>", "achieved": ln_gbs, "peak": peaks["hbm_gbs"],
+    roofline = {"bound": "hbm", "kernel": "ln_rows<bf16> (LayerNorm row kernel)", "achieved": ln_gbs, "peak": peaks["hbm_gbs"],
                 "unit": "GB/s", "frac": ln_gbs / peaks["hbm_gbs"], "traffic": ncu_traffic("ln_block_rows_bf16_8192x4096"),
                 "algorithmic_bytes_per_launch": bytes_step["layernorm"], "avg_launch_ms": ln_ms,
+                "median_launch_ms": statistics.median(rms), "best_launch_ms": min(rms),
                 "launches_timed": roof_reps * n_roof, "peak_source": peaks["source"]}
     if _lib.device_status() != 0:
         raise SystemExit("a kernel reported a timed-out device-side wait")
@@ -369,34 +442,31 @@ def main() -> None:
     h2d = (hx.numel() + hu.numel() + ha.numel() + hb.numel() + hg.numel() + hbt.numel()) * 2
     d2h = 3 * ROWS * COLS * 2
     e2e = {"value": world * total_step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
-           "steps": e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+           "steps": e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           # what limits it: the PCIe copies of one rank (both directions overlap on two copy streams)
+           "h2d_gbs_per_rank": h2d / (e2e_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (e2e_ms * 1e-3) / 1e9,
+           "host_numa": numa}
     host.clear_staging()
     del hx, hu, ha, hb, oy, ov, oc
+    if affinity_before is not None:
+        os.sched_setaffinity(0, affinity_before)
 
-    # ---- the other operators of the library, each timed on its BASELINE configuration
-    pending_clock = []
-
-    class Workloads(dict):
-        """Each entry gets the SM clock sampled while its timed region ran (see time_op)."""
-
-        def __setitem__(self, key, entry):
-            if pending_clock and isinstance(entry, dict):
-                c = pending_clock.pop()
-                entry = dict(entry, sm_mhz=c["sm_mhz"], throttle_reasons=c["reasons"])
-            super().__setitem__(key, entry)
-
-    workloads = Workloads()
+    # ---- the other operators of the library, each timed on its own configuration
+    workloads = {}
     only = set(filter(None, args.only.split(",")))
 
     def want(name):
         return not args.no_extras and (not only or name in only)
 
-    def time_op(fn, iters, warm=3):
-        """Average device time of `fn`: `iters` calls captured in a CUDA graph, replayed once timed.
-        A short idle gap first lets the power-capped SM clock recover from the previous workload,
-        so every entry is a burst figure from the same starting state."""
+    def time_op(fn, iters, replays=1, warm=3, idle=0.25):
+        """Device time of one call of `fn`: `iters` calls captured in a CUDA graph that is replayed
+        `replays` times, each replay between its own pair of events on the launching stream.
+        Returns a dict with the median, best and mean time per call over the replays
+        (iters x replays launches) and the SM clock sampled meanwhile.  A short idle gap first lets
+        the power-capped SM clock recover from the previous workload, so every entry starts from
+        the same state; with many replays the later ones run at the sustained clock."""
         torch.cuda.synchronize()
-        time.sleep(0.25)
+        time.sleep(idle)
         with torch.cuda.stream(cap_stream):
             for _ in range(warm):
                 fn()
@@ -407,14 +477,32 @@ def main() -> None:
                 fn()
         g.replay()
         barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
         smp = ClockSampler(local_rank, interval=0.001).start()
-        e0.record()
-        g.replay()
-        e1.record()
+        ev[0].record()
+        for r in range(replays):
+            g.replay()
+            ev[r + 1].record()
         barrier()
-        del pending_clock[:]
-        pending_clock.append(smp.stop())
-        return max_over_ranks(e0.elapsed_time(e1)) / iters
+        clk = smp.stop()
+        per = [ev[r].elapsed_time(ev[r + 1]) / iters for r in range(replays)]
+        return {"ms": max_over_ranks(statistics.median(per)), "best_ms": max_over_ranks(min(per)),
+                "mean_ms": max_over_ranks(sum(per) / len(per)), "launches": iters * replays,
+                "sm_mhz": clk["sm_mhz"], "throttle_reasons": clk["reasons"]}
+
+    def entry(t, work, unit, **extra):
+        """Workload record from a time_op() result: value from the median time, best beside it."""
+        scale = 1e12 if unit == "TFLOP/s" else 1e9
+        e = {"ms": t["ms"], "best_ms": t["best_ms"], "launches": t["launches"],
+             "value": world * work / (t["ms"] * 1e-3) / scale, "best": world * work / (t["best_ms"] * 1e-3) / scale,
+             "unit": unit, "sm_mhz": t["sm_mhz"], "throttle_reasons": t["throttle_reasons"]}
+        e.update(extra)
+        return e
+
+    def cublas_tflops(A, B, C, iters, replays):
+        """torch.matmul (cuBLAS) on the same operands, same timing: the library figure beside ours."""
+        t = time_op(lambda: torch.matmul(A, B, out=C), iters, replays)
+        return t
 
     for op_name in ("layernorm", "gelu", "add"):
         # per-op split of the headline step, from the same buffers
@@ -426,23 +514,23 @@ def main() -> None:
                 ops.elementwise(s["u"], "Gelu", out=s["v"])
             else:
                 ops.binary(s["a"], s["b"], "Add", out=s["c"])
-        ms = time_op(one, 40)
-        gbs = world * bytes_step[op_name] / (ms * 1e-3) / 1e9
-        workloads[f"{op_name}_bf16_{ROWS}x{COLS}"] = {"ms": ms, "value": gbs, "unit": "GB/s",
-                                                     "frac_of_hbm_peak": gbs / world / peaks["hbm_gbs"]}
+        t = time_op(one, 40, 3)
+        e = entry(t, bytes_step[op_name], "GB/s")
+        e["frac_of_hbm_peak"] = e["value"] / world / peaks["hbm_gbs"]
+        workloads[f"{op_name}_bf16_{ROWS}x{COLS}"] = e
     if not args.no_extras:
         # the same three operators as one fused pass (x and the residual in, y out: 3 tensor passes, not 7)
         def fused(i=[0]):
             s = sets[i[0] % BUFFER_SETS]; i[0] += 1
             ops.layernorm_gelu_add(s["x"], gamma, beta, s["a"], 1e-5, out=s["y"])
-        ms = time_op(fused, 40)
+        t = time_op(fused, 40, 3)
         fb = 3 * ROWS * COLS * 2 + 2 * COLS * 2
-        workloads[f"layernorm_gelu_add_fused_bf16_{ROWS}x{COLS}"] = {
-            "ms": ms, "value": world * fb / (ms * 1e-3) / 1e9, "unit": "GB/s",
-            "frac_of_hbm_peak": fb / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-            "speedup_vs_three_kernels": (workloads[f"layernorm_bf16_{ROWS}x{COLS}"]["ms"] +
+        e = entry(t, fb, "GB/s")
+        e["frac_of_hbm_peak"] = e["value"] / world / peaks["hbm_gbs"]
+        e["speedup_vs_three_kernels"] = (workloads[f"layernorm_bf16_{ROWS}x{COLS}"]["ms"] +
                                          workloads[f"gelu_bf16_{ROWS}x{COLS}"]["ms"] +
-                                         workloads[f"add_bf16_{ROWS}x{COLS}"]["ms"]) / ms}
+                                         workloads[f"add_bf16_{ROWS}x{COLS}"]["ms"]) / t["ms"]
+        workloads[f"layernorm_gelu_add_fused_bf16_{ROWS}x{COLS}"] = e
     del sets
     torch.cuda.empty_cache()
 
@@ -466,26 +554,48 @@ def main() -> None:
             ops.binary(xs[cnt[0] % BUFFER_SETS], xs[(cnt[0] + 1) % BUFFER_SETS], "Add", out=ys[cnt[0] % 2])
 
         for name, fn, key in (("layernorm", ln32, "layernorm"), ("gelu", gelu32, "gelu"), ("add", add32, "add")):
-            ms = time_op(fn, 40)
-            gbs = world * fb[key] / (ms * 1e-3) / 1e9
-            workloads[f"{name}_f32_{ROWS}x{COLS}"] = {"ms": ms, "value": gbs, "unit": "GB/s",
-                                                     "frac_of_hbm_peak": gbs / world / peaks["hbm_gbs"]}
+            t = time_op(fn, 40, 3)
+            e = entry(t, fb[key], "GB/s")
+            e["frac_of_hbm_peak"] = e["value"] / world / peaks["hbm_gbs"]
+            workloads[f"{name}_f32_{ROWS}x{COLS}"] = e
         del xs, ys
         torch.cuda.empty_cache()
+
+    tensor = {}   # the tensor-core targets, kept inside "roofline"
+
+    def tensor_entry(key, kernel, e, flops, nominal, traffic_key, cublas=None):
+        per_gpu = e["value"] / world
+        r = {"kernel": kernel, "flops_per_launch": flops, "launches": e["launches"], "median_ms": e["ms"],
+             "best_ms": e["best_ms"], "achieved": per_gpu, "best": e["best"] / world, "unit": "TFLOP/s per GPU",
+             "peak": peaks["bf16_tflops"] * (nominal / NOMINAL_BF16_TFLOPS), "peak_source": peaks["source"] +
+             (" bf16 cuBLAS burst" if nominal == NOMINAL_BF16_TFLOPS else " bf16 cuBLAS burst x 2 (no FP8 peak was measured)"),
+             "frac": per_gpu / (peaks["bf16_tflops"] * (nominal / NOMINAL_BF16_TFLOPS)),
+             "frac_of_sustained": per_gpu / (peaks["bf16_tflops_sustained"] * (nominal / NOMINAL_BF16_TFLOPS)),
+             "frac_of_nominal": per_gpu / nominal, "nominal_peak": nominal,
+             "sm_mhz": e["sm_mhz"], "throttle_reasons": e["throttle_reasons"], "traffic": ncu_traffic(traffic_key)}
+        if cublas is not None:
+            r["cublas_tflops"] = cublas
+        tensor[key] = r
 
     if want("gemm"):
         n = 8192
         A = rnd((n, n), std=n ** -0.5); B = rnd((n, n)); C = torch.empty((n, n), dtype=dt, device="cuda")
-        ms = time_op(lambda: ops.matmul(A, B, out=C), 20)
-        tf = world * 2 * n ** 3 / (ms * 1e-3) / 1e12
-        workloads["gemm_bf16_8192"] = {"ms": ms, "value": tf, "unit": "TFLOP/s",
-                                       "frac_of_measured_bf16_peak": tf / world / peaks["bf16_tflops"],
-                                       "frac_of_nominal_2250": tf / world / 2250.0}
+        fl = 2 * n ** 3
+        e = entry(time_op(lambda: ops.matmul(A, B, out=C), 10, 6), fl, "TFLOP/s")
+        tc = cublas_tflops(A, B, C, 10, 6)
+        e["cublas_tflops"] = fl / (tc["ms"] * 1e-3) / 1e12
+        e["frac_of_measured_bf16_peak"] = e["value"] / world / peaks["bf16_tflops"]
+        e["frac_of_nominal_2250"] = e["value"] / world / NOMINAL_BF16_TFLOPS
+        workloads["gemm_bf16_8192"] = e
+        tensor_entry("gemm_bf16_8192", "gemm_tcgen05_pair_kernel<f16 kind, bf16>", e, fl, NOMINAL_BF16_TFLOPS,
+                     "gemm_tcgen05_pair_bf16_8192", e["cublas_tflops"])
         A8 = A.to(torch.float8_e4m3fn); B8 = B.to(torch.float8_e4m3fn)
         one = torch.ones(1, device="cuda")
-        ms = time_op(lambda: ops.matmul(A8, B8, out_dtype=dt, scale_a=one, scale_b=one, out=C), 20)
-        tf = world * 2 * n ** 3 / (ms * 1e-3) / 1e12
-        workloads["gemm_fp8_8192"] = {"ms": ms, "value": tf, "unit": "TFLOP/s", "frac_of_nominal_4500": tf / world / 4500.0}
+        e = entry(time_op(lambda: ops.matmul(A8, B8, out_dtype=dt, scale_a=one, scale_b=one, out=C), 10, 6), fl, "TFLOP/s")
+        e["frac_of_nominal_4500"] = e["value"] / world / NOMINAL_FP8_TFLOPS
+        workloads["gemm_fp8_8192"] = e
+        tensor_entry("gemm_fp8_8192", "gemm_tcgen05_pair_kernel<f8f6f4 kind, e4m3 -> bf16>", e, fl, NOMINAL_FP8_TFLOPS,
+                     "gemm_tcgen05_pair_fp8_8192")
         del A, B, C, A8, B8
         torch.cuda.empty_cache()
 
@@ -493,29 +603,30 @@ def main() -> None:
         n = 1024
         A = (torch.rand((n, n), generator=gen, device="cuda") * 2 - 1); B = (torch.rand((n, n), generator=gen, device="cuda") * 2 - 1)
         C = torch.empty((n, n), device="cuda")
-        ms = time_op(lambda: ops.matmul(A, B, out=C), 20)
-        workloads["gemm_f32_1024"] = {"ms": ms, "value": world * 2 * n ** 3 / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                                      "path": "tensor cores: three tf32 products of hi/lo-split operands, K in chunks of 256"}
+        e = entry(time_op(lambda: ops.matmul(A, B, out=C), 20, 3), 2 * n ** 3, "TFLOP/s")
+        e["path"] = "tensor cores: three tf32 products of hi/lo-split operands, K in chunks of 256"
+        workloads["gemm_f32_1024"] = e
         _lib.load().kcg_gemm_set_fp32_mode(0)
         try:
-            ms = time_op(lambda: ops.matmul(A, B, out=C), 20)
+            e = entry(time_op(lambda: ops.matmul(A, B, out=C), 20, 3), 2 * n ** 3, "TFLOP/s")
         finally:
             _lib.load().kcg_gemm_set_fp32_mode(-1)
-        workloads["gemm_f32_1024_cuda_cores"] = {"ms": ms, "value": world * 2 * n ** 3 / (ms * 1e-3) / 1e12,
-                                                 "unit": "TFLOP/s", "path": "FFMA kernel, reference accumulation order"}
+        e["path"] = "FFMA kernel, reference accumulation order"
+        workloads["gemm_f32_1024_cuda_cores"] = e
 
     if want("fmha"):
         Bq, H, S, D = 8, 32, 4096, 128
         Q, K, V = rnd((Bq, H, S, D)), rnd((Bq, H, S, D)), rnd((Bq, H, S, D))
         Oo = torch.empty_like(Q)
         for causal in (False, True):
-            ms = time_op(lambda: ops.fmha(Q, K, V, D ** -0.5, causal, out=Oo), 10)
             fl = 4 * Bq * H * S * S * D if not causal else 2 * Bq * H * S * (S + 1) * D
-            tf = world * fl / (ms * 1e-3) / 1e12
-            workloads[f"fmha_bf16_s4096_{'causal' if causal else 'full'}"] = {
-                "ms": ms, "value": tf, "unit": "TFLOP/s",
-                "frac_of_measured_bf16_peak": tf / world / peaks["bf16_tflops"],
-                "frac_of_nominal_2250": tf / world / 2250.0}
+            e = entry(time_op(lambda: ops.fmha(Q, K, V, D ** -0.5, causal, out=Oo), 10, 5), fl, "TFLOP/s")
+            e["frac_of_measured_bf16_peak"] = e["value"] / world / peaks["bf16_tflops"]
+            e["frac_of_nominal_2250"] = e["value"] / world / NOMINAL_BF16_TFLOPS
+            key = f"fmha_bf16_s4096_{'causal' if causal else 'full'}"
+            workloads[key] = e
+            tensor_entry(key, "fmha_fwd_kernel2<bf16, D=128>", e, fl, NOMINAL_BF16_TFLOPS,
+                         "fmha_fwd_bf16_b8_h32_s4096_d128" + ("_causal" if causal else ""))
         del Q, K, V, Oo
         torch.cuda.empty_cache()
     if want("bw2"):
@@ -542,10 +653,9 @@ def main() -> None:
         for name, fn, nbytes in (("softmax_inplace", sm, 2 * ROWS * COLS * esz),
                                  ("broadcast_add_row", badd, 2 * ROWS * COLS * esz + COLS * esz),
                                  ("cast_bf16_to_f32", cast, ROWS * COLS * (esz + 4))):
-            ms = time_op(fn, 40)
-            gbs = world * nbytes / (ms * 1e-3) / 1e9
-            workloads[f"{name}_bf16_{ROWS}x{COLS}"] = {"ms": ms, "value": gbs, "unit": "GB/s",
-                                                       "frac_of_hbm_peak": gbs / world / peaks["hbm_gbs"]}
+            e = entry(time_op(fn, 40, 3), nbytes, "GB/s")
+            e["frac_of_hbm_peak"] = e["value"] / world / peaks["hbm_gbs"]
+            workloads[f"{name}_bf16_{ROWS}x{COLS}"] = e
         del xs2, outs2, wide
         torch.cuda.empty_cache()
     if want("move"):
@@ -554,18 +664,17 @@ def main() -> None:
         table = rnd((rows_t, width))
         idx = torch.randint(0, rows_t, (n_idx,), generator=gen, device="cuda")
         out = torch.empty((n_idx, width), dtype=dt, device="cuda")
-        ms = time_op(lambda: ops.gather(table, idx, 0, out=out), 20)
-        gbs = world * 2 * out.numel() * 2 / (ms * 1e-3) / 1e9
-        workloads["gather_rows_bf16_131072x4096"] = {"ms": ms, "value": gbs, "unit": "GB/s",
-                                                     "frac_of_hbm_peak": gbs / world / peaks["hbm_gbs"]}
+        e = entry(time_op(lambda: ops.gather(table, idx, 0, out=out), 20, 3), 2 * out.numel() * 2, "GB/s")
+        e["frac_of_hbm_peak"] = e["value"] / world / peaks["hbm_gbs"]
+        workloads["gather_rows_bf16_131072x4096"] = e
         del table, idx, out
         x = rnd((4, 8192, 8192)); y = torch.empty((4, 8192, 8192), dtype=dt, device="cuda")
-        ms = time_op(lambda: ops.transpose(x, out=y), 20)
-        gbs = world * 2 * x.numel() * 2 / (ms * 1e-3) / 1e9
-        workloads["transpose_bf16_4x8192x8192"] = {"ms": ms, "value": gbs, "unit": "GB/s",
-                                                   "frac_of_hbm_peak": gbs / world / peaks["hbm_gbs"]}
+        e = entry(time_op(lambda: ops.transpose(x, out=y), 20, 3), 2 * x.numel() * 2, "GB/s")
+        e["frac_of_hbm_peak"] = e["value"] / world / peaks["hbm_gbs"]
+        workloads["transpose_bf16_4x8192x8192"] = e
         del x, y
         torch.cuda.empty_cache()
+    sweep = {}    # compact copy kept inside "roofline": name -> [median, best, cuBLAS median] TFLOP/s per GPU
     if want("sweep"):
         # the other sizes of the GEMM and FMHA configurations (per GPU; N ranks run N copies)
         Bq, H, D = 8, 32, 128
@@ -573,31 +682,40 @@ def main() -> None:
             Q, K, V = rnd((Bq, H, S, D)), rnd((Bq, H, S, D)), rnd((Bq, H, S, D))
             Oo = torch.empty_like(Q)
             for causal in (False, True):
-                ms = time_op(lambda: ops.fmha(Q, K, V, D ** -0.5, causal, out=Oo), 20)
                 fl = 4 * Bq * H * S * S * D if not causal else 2 * Bq * H * S * (S + 1) * D
-                tf = world * fl / (ms * 1e-3) / 1e12
-                workloads[f"fmha_bf16_s{S}_{'causal' if causal else 'full'}"] = {
-                    "ms": ms, "value": tf, "unit": "TFLOP/s", "frac_of_nominal_2250": tf / world / 2250.0}
+                e = entry(time_op(lambda: ops.fmha(Q, K, V, D ** -0.5, causal, out=Oo), 20, 3), fl, "TFLOP/s")
+                e["frac_of_nominal_2250"] = e["value"] / world / NOMINAL_BF16_TFLOPS
+                key = f"fmha_bf16_s{S}_{'causal' if causal else 'full'}"
+                workloads[key] = e
+                sweep[key] = [round(e["value"] / world, 1), round(e["best"] / world, 1), None]
             del Q, K, V, Oo
         torch.cuda.empty_cache()
         for n in (1024, 2048, 4096, 16384):
+            iters, reps = (20, 3) if n <= 4096 else (5, 10)
             for tdt, tag in ((torch.bfloat16, "bf16"), (torch.float16, "f16")):
                 A = rnd((n, n), tdt, std=n ** -0.5); B = rnd((n, n), tdt)
                 C = torch.empty((n, n), dtype=tdt, device="cuda")
-                ms = time_op(lambda: ops.matmul(A, B, out=C), 20 if n <= 4096 else 8)
-                tf = world * 2 * n ** 3 / (ms * 1e-3) / 1e12
-                workloads[f"gemm_{tag}_{n}"] = {"ms": ms, "value": tf, "unit": "TFLOP/s",
-                                                "frac_of_nominal_2250": tf / world / 2250.0}
+                fl = 2 * n ** 3
+                e = entry(time_op(lambda: ops.matmul(A, B, out=C), iters, reps), fl, "TFLOP/s")
+                tc = cublas_tflops(A, B, C, iters, reps)
+                e["cublas_tflops"] = fl / (tc["ms"] * 1e-3) / 1e12
+                e["frac_of_cublas"] = e["value"] / world / e["cublas_tflops"]
+                e["frac_of_nominal_2250"] = e["value"] / world / NOMINAL_BF16_TFLOPS
                 if n <= 4096:
-                    workloads[f"gemm_{tag}_{n}"]["note"] = "operands fit the 126 MB L2 (compute-bound shape)"
+                    e["note"] = "operands fit the 126 MB L2 (compute-bound shape)"
+                workloads[f"gemm_{tag}_{n}"] = e
+                sweep[f"gemm_{tag}_{n}"] = [round(e["value"] / world, 1), round(e["best"] / world, 1),
+                                            round(e["cublas_tflops"], 1)]
                 del A, B, C
             A8 = rnd((n, n), torch.float32, std=n ** -0.5).to(torch.float8_e4m3fn)
             B8 = rnd((n, n), torch.float32).to(torch.float8_e4m3fn)
             C = torch.empty((n, n), dtype=dt, device="cuda")
             one = torch.ones(1, device="cuda")
-            ms = time_op(lambda: ops.matmul(A8, B8, out_dtype=dt, scale_a=one, scale_b=one, out=C), 20 if n <= 4096 else 8)
-            tf = world * 2 * n ** 3 / (ms * 1e-3) / 1e12
-            workloads[f"gemm_fp8_{n}"] = {"ms": ms, "value": tf, "unit": "TFLOP/s", "frac_of_nominal_4500": tf / world / 4500.0}
+            e = entry(time_op(lambda: ops.matmul(A8, B8, out_dtype=dt, scale_a=one, scale_b=one, out=C), iters, reps),
+                      2 * n ** 3, "TFLOP/s")
+            e["frac_of_nominal_4500"] = e["value"] / world / NOMINAL_FP8_TFLOPS
+            workloads[f"gemm_fp8_{n}"] = e
+            sweep[f"gemm_fp8_{n}"] = [round(e["value"] / world, 1), round(e["best"] / world, 1), None]
             del A8, B8, C
             torch.cuda.empty_cache()
     if world > 1 and not args.no_extras:
@@ -619,6 +737,21 @@ def main() -> None:
             workloads[name] = {"ms": ms, "value": recv / (ms * 1e-3) / 1e9, "unit": "GB/s received per GPU"}
             del loc, out
         torch.cuda.empty_cache()
+
+    def timed_loop(fn, iters, warm=3):
+        """Eager launches between two events, max over ranks (collectives cannot sit in one graph
+        with IPC-mapped stores on every NCCL version, and these steps take a millisecond or more)."""
+        for _ in range(warm):
+            fn()
+        barrier()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)) / iters
+
+    bufs = None
     if world > 1 and want("gather"):
         # replicated C from a row-sharded GEMM, two ways: the epilogue that stores every tile into
         # all ranks' buffers (peer stores over NVLink) against the plain kernel followed by an
@@ -644,15 +777,7 @@ def main() -> None:
             dist.all_gather_into_tensor(Cg, Cl)
 
         for name, fn in (("gemm_allgather_fused_epilogue", fused_iter), ("gemm_then_nccl_allgather", nccl_iter)):
-            for _ in range(3):
-                fn()
-            barrier()
-            e0.record()
-            for _ in range(10):
-                fn()
-            e1.record()
-            barrier()
-            ms = max_over_ranks(e0.elapsed_time(e1)) / 10
+            ms = timed_loop(fn, 10)
             workloads[name] = {"ms": ms, "value": world * 2 * n ** 3 / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                                "bytes_sent_per_gpu": (world - 1) * n * n * 2,
                                "link_gbs_per_gpu": (world - 1) * n * n * 2 / (ms * 1e-3) / 1e9}
@@ -677,15 +802,7 @@ def main() -> None:
 
         fl = 2 * Bq * H * S * (S + 1) * D
         for name, fn in (("fmha_allgather_fused_epilogue", fused_attn), ("fmha_then_nccl_allgather", nccl_attn)):
-            for _ in range(3):
-                fn()
-            barrier()
-            e0.record()
-            for _ in range(5):
-                fn()
-            e1.record()
-            barrier()
-            ms = max_over_ranks(e0.elapsed_time(e1)) / 5
+            ms = timed_loop(fn, 5)
             workloads[name] = {"ms": ms, "value": world * fl / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                                "bytes_sent_per_gpu": (world - 1) * Q.numel() * 2,
                                "link_gbs_per_gpu": (world - 1) * Q.numel() * 2 / (ms * 1e-3) / 1e9}
@@ -694,8 +811,112 @@ def main() -> None:
         del Q, K, V, Ol, Og
         fb.close()
         torch.cuda.empty_cache()
+
+    # ---- the fixed-size sharded workloads (strong scaling): the whole problem is split over the
+    # ranks of this run; "compute" is every rank's kernel on its shard, "gather" adds the exchange
+    # that leaves the full output on every rank (fused into the epilogue where the kernel has one,
+    # NCCL all-gather otherwise).  Times are the max over ranks; values count the whole problem.
+    sharded = {}
+    if want("sharded"):
+        from kernelcodegen_b200 import shard
+        # GEMM M = 65536, N = K = 8192, bf16: rows of A / C split, B replicated
+        Mt, n = 65536, 8192
+        b0, cnt = _lib.shard_range(Mt, world, rank, shard.GEMM_ROW_GRANULE)
+        A = rnd_big((cnt, n), std=n ** -0.5); B = rnd((n, n))
+        Cl = torch.empty((cnt, n), dtype=dt, device="cuda")
+        fl = 2 * Mt * n * n
+        ms = timed_loop(lambda: ops.matmul(A, B, out=Cl), 5)
+        rec = {"shape": f"M={Mt} N=K={n} bf16, {cnt} rows per rank", "compute_ms": ms,
+               "compute_tflops": fl / (ms * 1e-3) / 1e12}
+        if world > 1:
+            gb = None
+            try:
+                gb = shard.GatherBuffers(Mt, n, dt)
+            except RuntimeError as exc:
+                rec["gather_error"] = str(exc)[:200]
+            if gb is not None:
+                def fused_g():
+                    shard.matmul_allgather(A, B, gb, sync=False)
+                    shard.stream_barrier()
+                ms = timed_loop(fused_g, 5)
+                rec["gather_fused_ms"] = ms
+                rec["gather_fused_tflops"] = fl / (ms * 1e-3) / 1e12
+                Cg = torch.empty((Mt, n), dtype=dt, device="cuda")
+
+                def nccl_g():
+                    ops.matmul(A, B, out=Cl)
+                    dist.all_gather_into_tensor(Cg, Cl)
+                ms = timed_loop(nccl_g, 5)
+                rec["gather_nccl_ms"] = ms
+                rec["gather_fused_bit_identical_to_nccl"] = bool(torch.equal(gb.local, Cg))
+                del Cg
+                gb.close()
+        sharded["gemm_bf16_m65536"] = rec
+        del A, B, Cl
+        torch.cuda.empty_cache()
+        # attention B = 64, H = 32, S = 4096, D = 128, causal: whole batches split
+        Bt, H, S, D = 64, 32, 4096, 128
+        b0, cnt = _lib.shard_range(Bt, world, rank, 1)
+        Q, K, V = rnd_big((cnt, H, S, D)), rnd_big((cnt, H, S, D)), rnd_big((cnt, H, S, D))
+        Ol = torch.empty_like(Q)
+        fl = 2 * Bt * H * S * (S + 1) * D
+        ms = timed_loop(lambda: ops.fmha(Q, K, V, D ** -0.5, True, out=Ol), 3)
+        rec = {"shape": f"B={Bt} H={H} S={S} D={D} causal bf16, {cnt} batches per rank", "compute_ms": ms,
+               "compute_tflops": fl / (ms * 1e-3) / 1e12}
+        if world > 1:
+            gb = None
+            try:
+                gb = shard.GatherBuffers(Bt * H * S, D, dt)
+            except RuntimeError as exc:
+                rec["gather_error"] = str(exc)[:200]
+            if gb is not None:
+                def fused_a():
+                    shard.fmha_allgather(Q, K, V, gb, Bt, D ** -0.5, True, sync=False)
+                    shard.stream_barrier()
+                ms = timed_loop(fused_a, 3)
+                rec["gather_fused_ms"] = ms
+                rec["gather_fused_tflops"] = fl / (ms * 1e-3) / 1e12
+                Og = torch.empty((Bt, H, S, D), dtype=dt, device="cuda")
+
+                def nccl_a():
+                    ops.fmha(Q, K, V, D ** -0.5, True, out=Ol)
+                    dist.all_gather_into_tensor(Og, Ol)
+                ms = timed_loop(nccl_a, 3)
+                rec["gather_nccl_ms"] = ms
+                rec["gather_fused_bit_identical_to_nccl"] = bool(torch.equal(gb.local.view(Bt, H, S, D), Og))
+                del Og
+                gb.close()
+        sharded["fmha_bf16_b64_s4096_causal"] = rec
+        del Q, K, V, Ol
+        torch.cuda.empty_cache()
+        # LayerNorm over [262144, 8192] bf16: rows split
+        Rt, Ct = 262144, 8192
+        b0, cnt = _lib.shard_range(Rt, world, rank, 1)
+        x = rnd_big((cnt, Ct)); y = torch.empty_like(x)
+        g2, b2 = rnd((Ct,), mean=1.0, std=0.1), rnd((Ct,), std=0.1)
+        nb = Rt * Ct * 2 * 2 + 2 * Ct * 2
+        ms = timed_loop(lambda: ops.layernorm(x, g2, b2, 1, 1e-5, out=y), 5)
+        rec = {"shape": f"[{Rt},{Ct}] bf16, {cnt} rows per rank", "compute_ms": ms, "compute_gbs": nb / (ms * 1e-3) / 1e9,
+               "frac_of_hbm_peak_per_gpu": nb / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        if world > 1:
+            yg = torch.empty((Rt, Ct), dtype=dt, device="cuda")
+
+            def nccl_l():
+                ops.layernorm(x, g2, b2, 1, 1e-5, out=y)
+                dist.all_gather_into_tensor(yg, y)
+            ms = timed_loop(nccl_l, 3)
+            rec["gather_nccl_ms"] = ms
+            del yg
+        sharded["layernorm_bf16_262144x8192"] = rec
+        del x, y
+        torch.cuda.empty_cache()
+        workloads["sharded"] = sharded
+
     if rank == 0 and world == 1 and not args.no_extras:
         cpu_side_by_side(workloads)
+        for key, r in tensor.items():
+            if "cpu" in workloads.get(key, {}):
+                r["cpu"] = workloads[key]["cpu"]
     if _lib.device_status() != 0:
         raise SystemExit("a kernel reported a timed-out device-side wait")
 
@@ -716,14 +937,26 @@ def main() -> None:
                         "sample": f"one full [{ROWS},{COLS}] step of the fp32 loop nests on one core ({dtc:.2f} s); "
                                   "bytes counted as the bf16 workload's algorithmic bytes"}
 
+    if tensor:
+        roofline["tensor"] = tensor
+    if sweep:
+        roofline["sweep"] = {"columns": ["median TFLOP/s", "best TFLOP/s", "cuBLAS median TFLOP/s"], **sweep}
+    if sharded:
+        roofline["sharded"] = sharded
     if rank == 0:
+        # a compact copy of the tensor-core figures goes last so that it is what a truncated log keeps
+        summary = {k: [round(v["achieved"], 1), round(v["frac"], 3)] for k, v in tensor.items()}
+        summary.update({k: v[0] for k, v in sweep.items()})
         print(json.dumps({
-            "metric": "hbm_gbs_ln_gelu_add", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "metric": "hbm_gbs_ln_gelu_add", "value": value, "unit": "GB/s", "n_gpus": world, "steps": graph_steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": CONFIG,
-            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": 3 * args.steps,
-            "clocks": clocks, "workloads": workloads,
+            "timing": {"replays": replays, "ms_per_step_median": ms_median, "ms_per_step_mean": ms_mean,
+                       "ms_per_step_best": ms_best},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": 3 * graph_steps * replays,
+            "clocks": clocks, "workloads": workloads, "summary_tflops": summary,
         }))
     if world > 1:
         dist.destroy_process_group()

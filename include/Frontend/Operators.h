@@ -85,7 +85,7 @@ struct LayerNorm : Operator<LayerNorm> {
 
 struct Gather : Operator<Gather> {
   static Value build(ComputeDAG* graph, Value input, Value indices, const std::int64_t& axis = 0,
-                     const std::string& dtype_ = {""});  // not on the accelerated path: rejected
+                     const std::string& dtype_ = {""});  // out = take(input, indices, axis); runs kcg_gather
 };
 
 }  // namespace KernelCodeGen

@@ -18,9 +18,18 @@
  *   - every function returns a kcg_status (0 = success) and never aborts;
  *   - tensors are dense row-major unless a leading dimension / stride is given;
  *   - element counts and strides are in ELEMENTS, not bytes;
- *   - functions are re-entrant; kernels launched on different streams do not
- *     share state, except the per-device scratch buffer documented at
- *     kcg_layernorm().
+ *   - functions are re-entrant: they may be called from several host threads at
+ *     once.  The tuning switches (kcg_*_set_*) are settings of the CALLING THREAD
+ *     only: they affect the launches that thread makes afterwards and nothing else,
+ *     so two threads can tune, or autotune, side by side;
+ *   - kernels launched on different streams do not share state, except the
+ *     per-device scratch buffers documented at kcg_layernorm() and
+ *     kcg_gemm_set_fp32_mode().  Scratch rules: a scratch buffer that has been handed
+ *     to a launch is never freed before the process exits (a larger request gets a
+ *     new buffer and the old one is parked), so CUDA graphs captured earlier stay
+ *     valid; a call that would have to GROW a scratch buffer while its stream is
+ *     being captured returns KCG_ERR_UNSUPPORTED instead of allocating inside the
+ *     capture — make one call of that size before capturing.
  */
 #ifndef KCG_KERNELS_H_
 #define KCG_KERNELS_H_
@@ -131,7 +140,8 @@ KCG_API int kcg_layernorm(int dtype, int64_t rows, int64_t cols, const void* x,
  * kernels would store it, so the result is bit-identical to calling kcg_layernorm,
  * kcg_eltwise(Gelu) and kcg_binary(Add) in turn, at 3 instead of 7 tensor passes.  y may
  * alias x or residual.  Rows the one-pass kernels do not take (longer than 32768 bf16 /
- * 16384 fp32 elements, or not 16-byte vectorisable) run as those three launches.
+ * 16384 fp32 elements, or not 16-byte vectorisable) run as those three launches, in place in
+ * y: for such rows y may still alias x but must not overlap residual (KCG_ERR_UNSUPPORTED).
  */
 KCG_API int kcg_layernorm_gelu_add(int dtype, int64_t rows, int64_t cols, const void* x,
                                    const void* gamma, const void* beta, float eps,
@@ -165,7 +175,9 @@ KCG_API int kcg_layernorm_gelu_add(int dtype, int64_t rows, int64_t cols, const 
  * array and it keeps the previous call's contents; that is harmless because every entry
  * read is first rewritten by the same call, so nothing needs clearing — but two calls that
  * overlap on the GPU (different streams, or different host threads on one device) race on
- * it: serialise them.
+ * it: serialise them.  The cached address belongs to the device's current primary context:
+ * after a cudaDeviceReset() in the process it is stale and this entry point must not be
+ * called again.
  */
 KCG_API int kcg_layernorm_split_static(int dtype, int64_t rows, int64_t cols, const void* x,
                                        const void* gamma, const void* beta, float eps, void* y,
@@ -189,7 +201,7 @@ KCG_API int kcg_layernorm_stats(int dtype, int64_t rows, int64_t cols, const voi
 /*
  * Tuning switch with no counterpart in the reference: rows of up to 32 * vecs_per_lane
  * 16-byte vectors are normalised by one warp each (no block barrier); longer rows get one
- * thread block each.  Range 0..16, default 8.  Process-wide, not thread-safe.
+ * thread block each.  Range 0..16, default 8.  A setting of the calling thread.
  */
 KCG_API void kcg_layernorm_set_warp_row_limit(int vecs_per_lane);
 
@@ -254,8 +266,10 @@ KCG_API int kcg_softmax(int dtype, int64_t rows, int64_t cols, float scale, int 
  *     KCG_BF16 -> KCG_BF16 | KCG_F32, KCG_F16 -> KCG_F16 | KCG_F32
  *         tcgen05 tensor-core kernel, fp32 accumulation in tensor memory;
  *     KCG_F8E4M3 -> KCG_BF16 | KCG_F32   tcgen05 kind::f8f6f4, fp32 accumulation;
- *     KCG_F32 -> KCG_F32   CUDA-core FFMA kernel, sequential-k fp32 accumulation
- *         (the reference's own arithmetic; tensor cores cannot hold 1e-5).
+ *     KCG_F32 -> KCG_F32   by default (M N K >= 256^3) the tensor cores, as three tf32
+ *         products of hi/lo-split operands with K cut into chunks of 256 (within ~3e-6 of
+ *         a float64 product); smaller problems, or kcg_gemm_set_fp32_mode(0), take the
+ *         CUDA-core FFMA kernel with the reference's sequential-k fp32 accumulation.
  *   Tensor-core paths need 16-byte aligned base pointers and leading dimensions
  *   / batch strides that are multiples of 16 bytes; M, N, K are arbitrary.
  */
@@ -286,7 +300,7 @@ KCG_API int kcg_gemm_fused(int dtype_in, int dtype_out, int64_t M, int64_t N, in
  * GEMM: -1 (default) picks, per problem, whichever of the three shapes below fills the SMs most
  * evenly (large problems get CTA pairs); 0 forces 128x256 tiles on single CTAs; 1 forces CTA
  * pairs (tcgen05 cta_group::2, one 256x256 tile per two SMs) whenever M > 128; 2 forces 128x128
- * tiles on single CTAs.  Results are identical.  Process-wide, not thread-safe.
+ * tiles on single CTAs.  Results are identical.  A setting of the calling thread.
  */
 KCG_API void kcg_gemm_set_pair_mode(int mode);
 
@@ -317,7 +331,7 @@ KCG_API int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Sk
  *    1            one query tile per CTA, P through tensor memory;
  *    0            one query tile per CTA, P through a swizzled shared-memory tile.
  * All variants give results within the same tolerance; kept so the data paths can be compared
- * on one build.  Process-wide, not thread-safe.
+ * on one build.  A setting of the calling thread.
  */
 KCG_API void kcg_fmha_set_p_in_tmem(int variant);
 
@@ -357,8 +371,8 @@ KCG_API int kcg_transpose(int dtype, int64_t batch, int64_t rows, int64_t cols, 
  * within ~1e-6 relative of a float64 product, several times faster; uses a cached per-device
  * scratch buffer of 12 (M + N) K bytes per batch entry plus up to 1 GiB of partial products,
  * shared by all float32 GEMMs of a device: serialise float32 GEMMs that could overlap on one
- * device from different streams); -1 (default) = 1 when M N K >= 256^3, else 0.  Process-wide,
- * not thread-safe.
+ * device from different streams); -1 (default) = 1 when M N K >= 256^3, else 0.  A setting of
+ * the calling thread.
  */
 KCG_API void kcg_gemm_set_fp32_mode(int mode);
 

@@ -43,6 +43,12 @@ inline int check_launch(const char* what) {
 // Rule: every kernel launched this way calls grid_dependency_wait() in all threads before its
 // first global access and calls grid_launch_dependents() once.  (A kernel that skipped the wait
 // could finish before its predecessor and release its own successor too early.)
+// Rule for kernels that allocate tensor memory: grid_launch_dependents() comes AFTER tcgen05.alloc
+// has returned in the CTA.  A dependent grid starts only when every CTA of this grid has issued the
+// trigger, so by then every resident CTA already holds its columns; if the trigger came first, a
+// dependent CTA could become resident beside a CTA that has not allocated yet, take all 512
+// columns and park in grid_dependency_wait(), and that CTA's tcgen05.alloc (a wait no time budget
+// covers) would never return.
 // KCG_OVERLAP_LAUNCH=0 in the environment launches the same kernels without the attribute, for A/B timing.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

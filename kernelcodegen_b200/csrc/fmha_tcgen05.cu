@@ -472,7 +472,6 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int n_blk1 = kv_end1 > 0 ? (kv_end1 + BN - 1) / BN : 0;
   const int n_max = max(n_blk0, n_blk1);  // == n_blk1: the later rows see at least as many keys
 
-  grid_launch_dependents();
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
@@ -499,6 +498,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_launch_dependents();  // after the tensor-memory allocation (the rule in common.cuh)
   grid_dependency_wait();  // set-up done; global memory only after the previous kernel has finished
 
   if (warp == 8) {
@@ -817,7 +817,7 @@ int launch_fmha(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMa
   return check_launch("fmha_fwd_kernel");
 }
 
-int g_p_in_tmem = -1;  // -1: choose by shape
+thread_local int g_p_in_tmem = -1;  // per calling thread; -1: choose by shape
 
 }  // namespace
 

@@ -17,7 +17,7 @@ int gemm_f32_tensor(int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
                     int64_t ldc, int64_t stride_c, const float* scale_a, const float* scale_b, const float* bias,
                     int act, cudaStream_t stream);
 namespace {
-int g_fp32_mode = -1;  // -1: by size; 0: CUDA-core kernel; 1: tensor cores (three tf32 products)
+thread_local int g_fp32_mode = -1;  // per calling thread; -1: by size; 0: CUDA-core kernel; 1: tensor cores (three tf32 products)
 }
 }  // namespace kcg
 

@@ -25,7 +25,7 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
                  int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
                  const float* scale_b, const void* bias, int act, cudaStream_t stream, void* const* extra_c,
                  int n_extra);
-void* device_scratch(size_t bytes, int slot);  // runtime.cu
+void* device_scratch(size_t bytes, int slot, cudaStream_t stream, int* why);  // runtime.cu
 
 namespace {
 
@@ -172,8 +172,9 @@ int gemm_f32_tensor(int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
   const size_t part_floats = chunks > 1 ? static_cast<size_t>(batch) * chunks * M * panel : 0;
   const size_t bytes = (op_floats + part_floats) * sizeof(float);
   if (bytes > (6ull << 30) || M > 65535 || N > 65535 || batch * chunks > 65535) return KCG_ERR_UNSUPPORTED;
-  float* scratch = static_cast<float*>(device_scratch(bytes, 1));
-  if (!scratch) return fail(KCG_ERR_CUDA, "fp32 gemm: could not allocate %zu bytes for the split operands", bytes);
+  int why = KCG_ERR_CUDA;
+  float* scratch = static_cast<float*>(device_scratch(bytes, 1, stream, &why));
+  if (!scratch) return why;   // the message says why (allocation failed, or growth refused during a stream capture)
   float* As = scratch;
   float* Bs = As + static_cast<size_t>(batch) * M * 3 * Kp;
   float* part = Bs + static_cast<size_t>(batch) * N * 3 * Kp;

@@ -63,7 +63,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const int m_pairs = (p.m_tiles + 1) / 2;
   const int64_t total = static_cast<int64_t>(m_pairs) * p.n_tiles * (p.total_tiles / (static_cast<int64_t>(p.m_tiles) * p.n_tiles));
 
-  grid_launch_dependents();
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
@@ -87,6 +86,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   cluster_sync_all();  // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_launch_dependents();  // after the tensor-memory allocation (the rule in common.cuh)
   grid_dependency_wait();  // set-up done; global memory only after the previous kernel has finished
 
   if (warp == 0) {

@@ -168,7 +168,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  grid_launch_dependents();   // the next kernel's prologue may overlap this kernel (see launch_overlapped)
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmA);
@@ -193,6 +192,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // The next kernel's prologue may overlap this kernel from here on (see launch_overlapped), and
+  // only from here: this CTA holds its tensor memory now (the rule in common.cuh).
+  grid_launch_dependents();
   // Barriers, tensor memory and descriptors are set up; operands and the output may be touched
   // only when the kernel before this one in the stream has finished.
   grid_dependency_wait();
@@ -373,7 +375,9 @@ int encode_tmap_sw128(CUtensorMap* out, int dtype, const void* base, int rank, c
 
 namespace {
 
-int g_pair_mode = -1;  // -1: pick_tiling(); 0: 128x256 single CTA; 1: CTA pairs when M > 128; 2: 128x128 single CTA
+// Per calling thread, so that two host threads (two generators, or a generator and a direct
+// caller of the C ABI) never see each other's setting.
+thread_local int g_pair_mode = -1;  // -1: pick_tiling(); 0: 128x256 single CTA; 1: CTA pairs when M > 128; 2: 128x128 single CTA
 
 enum Tiling { kWide = 0, kPair = 1, kNarrow = 2 };
 struct Idescs { uint32_t wide, pair, narrow; };

@@ -19,12 +19,13 @@
 
 namespace kcg {
 
-void* device_scratch(size_t bytes, int slot);  // runtime.cu
+void* device_scratch(size_t bytes, int slot, cudaStream_t stream, int* why);  // runtime.cu
 
 namespace {
 
-// Longest row (in 16-byte vectors per lane) that is given to the warp-per-row kernel.
-int g_warp_row_max_vecs = 8;
+// Longest row (in 16-byte vectors per lane) that is given to the warp-per-row kernel (a setting
+// of the calling thread).
+thread_local int g_warp_row_max_vecs = 8;
 
 // Loads, normalises and stores one row held by `nthr` cooperating threads (a warp or a
 // block); `reduce` sums a float over those threads.  kExact: the row is exactly
@@ -334,9 +335,9 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
                 "%lld columns (got %lld)",
                 static_cast<long long>(rows), 65535LL * 32 * kChunk, static_cast<long long>(cols));
   const int chunks = static_cast<int>(chunks64);
-  float* stats = static_cast<float*>(device_scratch(static_cast<size_t>(rows) * chunks * 2 * sizeof(float), 0));
-  if (!stats) return fail(KCG_ERR_CUDA, "layernorm: could not allocate %zu bytes of scratch",
-                          static_cast<size_t>(rows) * chunks * 2 * sizeof(float));
+  int why = KCG_ERR_CUDA;
+  float* stats = static_cast<float*>(device_scratch(static_cast<size_t>(rows) * chunks * 2 * sizeof(float), 0, stream, &why));
+  if (!stats) return why;
   dim3 grid(chunks, static_cast<unsigned>(rows));
   ln_chunk_stats<T><<<grid, kChunkThreads, 0, stream>>>(x, stats, cols, chunks);
   int rc = check_launch("ln_chunk_stats");
@@ -460,8 +461,18 @@ extern "C" int kcg_layernorm_gelu_add(int dtype, int64_t rows, int64_t cols, con
   }
   if (rc != KCG_ERR_UNSUPPORTED) return rc;
   // Rows the one-pass kernels do not take (too long or not vectorisable): the same three
-  // operators back to back, in place in y.
+  // operators back to back, in place in y.  That order overwrites y before the residual is
+  // read, so here (unlike in the one-pass kernels) y must not overlap the residual.
   clear_error();
+  {
+    const size_t nbytes = static_cast<size_t>(rows) * static_cast<size_t>(cols) * kcg_dtype_size(dtype);
+    const char* yb = static_cast<const char*>(y);
+    const char* rb = static_cast<const char*>(residual);
+    if (yb < rb + nbytes && rb < yb + nbytes)
+      return fail(KCG_ERR_UNSUPPORTED,
+                  "layernorm_gelu_add: rows of %lld elements run as three launches in place in y, which must then "
+                  "not overlap the residual", static_cast<long long>(cols));
+  }
   rc = kcg_layernorm(dtype, rows, cols, x, gamma, beta, eps, y, stream);
   if (rc) return rc;
   rc = kcg_eltwise(KCG_UNARY_GELU, dtype, dtype, rows * cols, y, y, stream);
@@ -526,7 +537,11 @@ const T* const_vector(int dtype_slot, int which, int64_t n, cudaStream_t stream)
   std::lock_guard<std::mutex> lock(g_const_mutex);
   ConstVec& cv = g_const_vec[dev][dtype_slot][which];
   if (cv.n < n) {
-    if (cv.ptr) cudaFree(cv.ptr);  // waits for kernels that still read the old vector
+    // A shorter vector handed out earlier is left allocated (launches in flight and captured
+    // graphs may still read it); growing allocates, which a stream capture does not allow.
+    cudaStreamCaptureStatus cap_state = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap_state) != cudaSuccess) cudaGetLastError();
+    if (cap_state != cudaStreamCaptureStatusNone) return nullptr;
     cv.ptr = nullptr; cv.n = 0;
     const int64_t cap = (n + 4095) / 4096 * 4096;
     if (cudaMalloc(&cv.ptr, static_cast<size_t>(cap) * sizeof(T)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
@@ -545,7 +560,9 @@ int layernorm_stats_t(int slot, int64_t rows, int64_t cols, const void* x, const
   const T* b = static_cast<const T*>(beta);
   if (!g) g = const_vector<T>(slot, 0, cols, s);
   if (!b) b = const_vector<T>(slot, 1, cols, s);
-  if (!g || !b) return fail(KCG_ERR_CUDA, "layernorm_stats: could not allocate the default scale / bias vector");
+  if (!g || !b)
+    return fail(KCG_ERR_CUDA, "layernorm_stats: could not allocate the default scale / bias vector (it cannot be "
+                              "allocated while the stream is being captured: call once before the capture)");
   return launch_ln<T>(rows, cols, static_cast<const T*>(x), g, b, eps, static_cast<T*>(y), s, nullptr, mean, inv_std);
 }
 

@@ -5,6 +5,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 namespace kcg {
 
@@ -16,6 +17,9 @@ struct DeviceState {
   int sms = 0;
   void* scratch[kScratchSlots] = {nullptr, nullptr};
   size_t scratch_bytes[kScratchSlots] = {0, 0};
+  // buffers a larger request has replaced: launches already queued, and CUDA graphs captured
+  // earlier, may still name them, so they stay allocated until the process exits
+  std::vector<void*> retired;
 };
 constexpr int kMaxDevices = 64;
 DeviceState g_dev[kMaxDevices];
@@ -58,25 +62,35 @@ int sm_count() {
   return g_dev[d].sms;
 }
 
-// Returns a device buffer of at least `bytes` bytes that stays valid until a larger request
-// for the same slot replaces it (cudaFree of the old buffer waits for work in flight).
-void* device_scratch(size_t bytes, int slot) {
+// Returns a device buffer of at least `bytes` bytes for `slot`, or nullptr with *why set to a
+// kcg_status.  A buffer that has been handed out is never freed: when a larger request replaces
+// it, the old one is parked until the process exits, because launches in flight and CUDA graphs
+// captured earlier still hold its address.  Growth allocates (cudaMalloc), which is not allowed
+// while `stream` is being captured: that request is refused with KCG_ERR_UNSUPPORTED and the
+// capture stays valid.
+void* device_scratch(size_t bytes, int slot, cudaStream_t stream, int* why) {
+  auto refuse = [&](int code, const char* fmt, size_t n) -> void* {
+    if (why) *why = fail(code, fmt, n);
+    return nullptr;
+  };
   const int d = current_device();
-  if (d < 0 || slot < 0 || slot >= kScratchSlots) return nullptr;
+  if (d < 0 || slot < 0 || slot >= kScratchSlots) return refuse(KCG_ERR_CUDA, "scratch: no current device (%zu bytes)", bytes);
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState& st = g_dev[d];
   if (st.scratch_bytes[slot] >= bytes && st.scratch[slot]) return st.scratch[slot];
-  if (st.scratch[slot]) {
-    cudaFree(st.scratch[slot]);
-    st.scratch[slot] = nullptr;
-    st.scratch_bytes[slot] = 0;
-  }
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cudaGetLastError();
+  if (cap != cudaStreamCaptureStatusNone)
+    return refuse(KCG_ERR_UNSUPPORTED,
+                  "the library's scratch buffer would have to grow to %zu bytes while the stream is being captured; "
+                  "make one call of this size before starting the capture", bytes);
   size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
   void* p = nullptr;
   if (cudaMalloc(&p, want) != cudaSuccess) {
     cudaGetLastError();
-    return nullptr;
+    return refuse(KCG_ERR_CUDA, "could not allocate %zu bytes of scratch memory", want);
   }
+  if (st.scratch[slot]) st.retired.push_back(st.scratch[slot]);
   st.scratch[slot] = p;
   st.scratch_bytes[slot] = want;
   return p;

@@ -207,6 +207,12 @@ bool KernelFusionOptimizer::applicable(Module& module) {
       const int other = add.inputs[0] == g.ops[ge].output ? add.inputs[1] : add.inputs[0];
       if (other == g.ops[ge].output) continue;  // y + y
       if (g.tensors[other].shape != x.shape || g.tensors[other].dtype != x.dtype) continue;
+      // Rows the one-pass kernel does not take (not a whole number of 16-byte vectors, or more
+      // than 4096 of them) run as three launches in place in the output, which then must not be
+      // the residual's own storage (an inplace Add on the residual): leave that chain unfused.
+      const int64_t vw = 16 / static_cast<int64_t>(dtypeSize(x.dtype));
+      const bool one_pass = cols % vw == 0 && cols / vw <= 4096;
+      if (!one_pass && g.root(add.output) == g.root(other)) continue;
       ln_chains.push_back({i, ge, ad});
     }
   }

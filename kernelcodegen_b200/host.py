@@ -41,6 +41,14 @@ def _down(d: torch.Tensor, out: torch.Tensor | None) -> torch.Tensor:
 
 
 def clear_staging() -> None:
+    """Drop the cached device staging tensors.  They were allocated on the current stream but are
+    also read and written by the two copy streams, so those streams (and the current one) are
+    drained first: the caching allocator may then hand the memory to anyone."""
+    if torch.cuda.is_available():
+        for up, down in _copy_streams.values():
+            up.synchronize()
+            down.synchronize()
+        torch.cuda.current_stream().synchronize()
     _stage.clear()
     _last_reader.clear()
 

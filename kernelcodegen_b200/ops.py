@@ -53,6 +53,27 @@ def _need_cuda(*ts: torch.Tensor) -> None:
             raise ValueError("operands must be contiguous")
 
 
+def _check_out(out, shape, dtype, like, what: str) -> None:
+    """An ``out=`` tensor is written through its raw pointer with the strides of a dense tensor,
+    so anything else (wrong shape or dtype, a view with gaps, another device) must stop here."""
+    if out is None:
+        return
+    if tuple(out.shape) != tuple(shape):
+        raise ValueError(f"{what}: out has shape {tuple(out.shape)}, the result has {tuple(shape)}")
+    if out.dtype != dtype:
+        raise ValueError(f"{what}: out has dtype {out.dtype}, the result has {dtype}")
+    if out.device != like.device:
+        raise ValueError(f"{what}: out is on {out.device}, the operands are on {like.device}")
+    if not out.is_contiguous():
+        raise ValueError(f"{what}: out must be contiguous")
+
+
+def _same_dtype(what: str, *ts) -> None:
+    for t in ts[1:]:
+        if t.dtype != ts[0].dtype:
+            raise TypeError(f"{what}: operands must share a dtype (got {ts[0].dtype} and {t.dtype})")
+
+
 def _i64arr(v):
     return (ctypes.c_int64 * len(v))(*[int(x) for x in v])
 
@@ -71,6 +92,8 @@ def _broadcast_shape(sa, sb):
 
 def layernorm(x, scale, bias, axis: int, eps: float = 1e-5, inplace: bool = False, out=None):
     """LayerNorm over dims [axis..] (reference: LayerNorm::build, Operators.h:125-128)."""
+    _same_dtype("layernorm", x, scale, bias)
+    _check_out(out, x.shape, x.dtype, x, "layernorm")
     _need_cuda(x, scale, bias)
     nd = x.dim()
     if axis >= nd or axis <= -nd:
@@ -94,6 +117,8 @@ def layernorm_with_stats(x, scale, bias, axis: int, eps: float = 1e-5, out=None)
     """(Y, mean, invStdDev): LayerNorm over dims [axis..] that also returns the fp32 row mean and
     1/sqrt(var + eps), shaped like x with the normalised dims removed — the result tuple the
     reference's design notes plan (doc/pass.md:789-791).  ``scale`` / ``bias`` may be None."""
+    _same_dtype("layernorm_with_stats", x, *[t for t in (scale, bias) if t is not None])
+    _check_out(out, x.shape, x.dtype, x, "layernorm_with_stats")
     _need_cuda(x, *[t for t in (scale, bias) if t is not None])
     nd = x.dim()
     if axis >= nd or axis <= -nd:
@@ -121,9 +146,11 @@ def layernorm_with_stats(x, scale, bias, axis: int, eps: float = 1e-5, out=None)
 def layernorm_gelu_add(x, scale, bias, residual, eps: float = 1e-5, out=None):
     """Gelu(LayerNorm(x over the last dim)) + residual in one kernel; bit-identical to the chain
     layernorm -> elementwise("Gelu") -> binary("Add")."""
-    _need_cuda(x, scale, bias, residual)
     if tuple(residual.shape) != tuple(x.shape) or residual.dtype != x.dtype:
         raise ValueError("residual must match x in shape and dtype")
+    _same_dtype("layernorm_gelu_add", x, scale, bias)
+    _check_out(out, x.shape, x.dtype, x, "layernorm_gelu_add")
+    _need_cuda(x, scale, bias, residual)
     cols = x.shape[-1]
     if tuple(scale.shape) != (cols,) or tuple(bias.shape) != (cols,):
         raise ValueError("scale and bias must have the length of the last dim")
@@ -137,10 +164,11 @@ def layernorm_gelu_add(x, scale, bias, residual, eps: float = 1e-5, out=None):
 
 def elementwise(x, operation: str, dtype=None, inplace: bool = False, out=None):
     """Unary map (reference: ElementWise::build, Operators.h:114-123)."""
-    _need_cuda(x)
     if operation not in _lib.UNARY_OPS:
         raise KeyError(operation)
     out_dtype = x.dtype if dtype is None else (DTYPE_NAMES[dtype] if isinstance(dtype, str) else dtype)
+    _check_out(None if inplace else out, x.shape, out_dtype, x, "elementwise")
+    _need_cuda(x)
     if inplace:
         y = x
     else:
@@ -157,12 +185,13 @@ def relu(x, inplace: bool = False):
 
 def binary(a, b, operation: str, inplace: bool = False, out=None):
     """Broadcasting binary map (reference: Binary::build, Operators.h:101-112)."""
-    _need_cuda(a, b)
     if operation not in _lib.BINARY_OPS:
         raise KeyError(operation)
     if a.dtype != b.dtype:
         raise TypeError("binary: operands must share a dtype")
     oshape = _broadcast_shape(a.shape, b.shape)
+    _check_out(None if inplace else out, oshape, a.dtype, a, "binary")
+    _need_cuda(a, b)
     if inplace:
         if tuple(a.shape) != tuple(oshape):
             raise ValueError("inplace needs the left operand to have the output shape")
@@ -204,9 +233,10 @@ def batched_matmul(A, B, trans_a: bool = False, trans_b: bool = False, out_dtype
                    scale_b=None, out=None, bias=None, activation=None):
     """C = op(A) op(B) over leading batch dims (reference: BatchedMatmul::build with
     Layout::rowMajor / Layout::colMajor, Operators.h:87-89; trans_x=True is colMajor)."""
-    _need_cuda(A, B)
     if A.dim() < 2 or A.dim() != B.dim():
         raise ValueError("BatchedMatmul: A, B dim not matched.")
+    # the kernel reads both operands with A's element size: a narrower B would be read past its end
+    _same_dtype("BatchedMatmul", A, B)
     m, k1 = (A.shape[-1], A.shape[-2]) if trans_a else (A.shape[-2], A.shape[-1])
     n, k2 = (B.shape[-2], B.shape[-1]) if trans_b else (B.shape[-1], B.shape[-2])
     if k1 != k2:
@@ -215,7 +245,12 @@ def batched_matmul(A, B, trans_a: bool = False, trans_b: bool = False, out_dtype
         raise ValueError("BatchedMatmul: batch dims differ")
     batch = math.prod(A.shape[:-2])
     if out_dtype is None:
-        out_dtype = torch.bfloat16 if A.dtype == getattr(torch, "float8_e4m3fn", None) else A.dtype
+        if out is not None:
+            out_dtype = out.dtype
+        else:
+            out_dtype = torch.bfloat16 if A.dtype == getattr(torch, "float8_e4m3fn", None) else A.dtype
+    _check_out(out, tuple(A.shape[:-2]) + (m, n), out_dtype, A, "BatchedMatmul")
+    _need_cuda(A, B)
     C = out if out is not None else torch.empty(tuple(A.shape[:-2]) + (m, n), dtype=out_dtype, device=A.device)
     if bias is not None and (not bias.is_cuda or bias.dtype != C.dtype or bias.numel() != n):
         raise ValueError("bias holds N values of the output dtype on the device")
@@ -249,7 +284,6 @@ def gather(x, indices, axis: int = 0, out=None):
     """out = take(x, indices, axis) (reference: Gather::build, Operators.cc:1253-1352): the dim
     ``axis`` of x is replaced by the shape of ``indices`` — or dropped when ``indices`` has
     shape [1], as the reference does."""
-    _need_cuda(x, indices)
     if indices.dtype not in (torch.int32, torch.int64):
         raise TypeError("gather: indices must be int32 or int64")
     if axis >= x.dim() or axis < 0:
@@ -258,6 +292,8 @@ def gather(x, indices, axis: int = 0, out=None):
     inner = math.prod(x.shape[axis + 1:])
     idx_shape = () if tuple(indices.shape) == (1,) else tuple(indices.shape)
     shape = tuple(x.shape[:axis]) + idx_shape + tuple(x.shape[axis + 1:])
+    _check_out(out, shape, x.dtype, x, "gather")
+    _need_cuda(x, indices)
     if out is None:
         out = torch.empty(shape, dtype=x.dtype, device=x.device)
     check(_lib.load().kcg_gather(_move_dt(x), _lib.I32 if indices.dtype == torch.int32 else _lib.I64, outer,
@@ -269,11 +305,12 @@ def gather(x, indices, axis: int = 0, out=None):
 def transpose(x, out=None):
     """Swap the two innermost dims (reference: Transpose::build is declared with a single operand
     and an empty body, Operators.h:97-99)."""
-    _need_cuda(x)
     if x.dim() < 2:
         raise ValueError("Transpose takes an operand of rank 2 or more")
     r, c = x.shape[-2], x.shape[-1]
     batch = math.prod(x.shape[:-2])
+    _check_out(out, tuple(x.shape[:-2]) + (c, r), x.dtype, x, "transpose")
+    _need_cuda(x)
     if out is None:
         out = torch.empty(tuple(x.shape[:-2]) + (c, r), dtype=x.dtype, device=x.device)
     check(_lib.load().kcg_transpose(_move_dt(x), batch, r, c, x.data_ptr(), out.data_ptr(), _stream()),
@@ -281,17 +318,39 @@ def transpose(x, out=None):
     return out
 
 
+def check_attention_operands(Q, K, V) -> None:
+    """Q [B,H,Sq,D], K and V [B,H,Skv,D] of one dtype, head dimension contiguous.  The kernel builds
+    the K and V tensor maps from K's shape, so a shorter V (or a narrower dtype) would be read
+    past its end: anything that does not match stops here."""
+    for t in (Q, K, V):
+        if t.dim() != 4 or t.stride(-1) != 1:
+            raise ValueError("fmha takes [B,H,S,D] tensors with a contiguous head dimension")
+    if K.dtype != Q.dtype or V.dtype != Q.dtype:
+        raise TypeError(f"fmha: Q, K and V must share a dtype (got {Q.dtype}, {K.dtype}, {V.dtype})")
+    B, H, _, D = Q.shape
+    for name, t in (("K", K), ("V", V)):
+        if t.shape[0] != B or t.shape[1] != H or t.shape[3] != D:
+            raise ValueError(f"fmha: {name} has shape {tuple(t.shape)}; batch, heads and head dimension must match "
+                             f"Q's {tuple(Q.shape)}")
+    if K.shape[2] != V.shape[2]:
+        raise ValueError(f"fmha: K has {K.shape[2]} keys, V has {V.shape[2]}")
+
+
 def fmha(Q, K, V, softmax_scale: float = 1.0, causal: bool = False, out_layout: str = "bhsd", out=None):
     """Fused attention forward on [B,H,S,D] tensors: softmax(scale * Q K^T [+ causal mask]) V,
     the chain BatchedMatmul(NT) -> Softmax -> BatchedMatmul(NN) the reference fuses
     (test/test.cc:128-130).  ``out_layout`` "bshd" returns O as [B,S,H,D]."""
+    check_attention_operands(Q, K, V)
+    B, H, Sq, D = Q.shape
+    Skv = K.shape[2]
+    if out is not None:
+        # out may be a strided view (e.g. a [B,S,H,D] buffer seen as [B,H,S,D]); its strides are passed on
+        if tuple(out.shape) != (B, H, Sq, D) or out.dtype != Q.dtype or out.device != Q.device or out.stride(-1) != 1:
+            raise ValueError(f"fmha: out must be a [B,H,Sq,D] = {(B, H, Sq, D)} {Q.dtype} tensor on {Q.device} with a "
+                             "contiguous head dimension")
     for t in (Q, K, V):
         if not t.is_cuda:
             raise ValueError("operands must be CUDA tensors (there is no CPU path)")
-        if t.dim() != 4 or t.stride(-1) != 1:
-            raise ValueError("fmha takes [B,H,S,D] tensors with a contiguous head dimension")
-    B, H, Sq, D = Q.shape
-    Skv = K.shape[2]
     if out is None:
         if out_layout == "bhsd":
             out = torch.empty((B, H, Sq, D), dtype=Q.dtype, device=Q.device)

@@ -243,6 +243,10 @@ def matmul_allgather(A_local: torch.Tensor, B: torch.Tensor, bufs: GatherBuffers
     from . import ops
     if not (A_local.is_cuda and B.is_cuda and A_local.is_contiguous() and B.is_contiguous()):
         raise ValueError("operands must be contiguous CUDA tensors")
+    if A_local.dim() != 2 or B.dim() != 2:
+        raise ValueError("Matmul takes rank-2 operands")
+    if A_local.dtype != B.dtype:
+        raise TypeError(f"operands must share a dtype (got {A_local.dtype} and {B.dtype})")
     M, K = A_local.shape
     N = B.shape[0] if trans_b else B.shape[1]
     if (B.shape[1] if trans_b else B.shape[0]) != K:
@@ -274,8 +278,11 @@ def fmha_allgather(Q_local: torch.Tensor, K_local: torch.Tensor, V_local: torch.
     rows of D columns; returns the local buffer viewed as [total_batches, H, S, D]."""
     import ctypes
     from . import ops
+    ops.check_attention_operands(Q_local, K_local, V_local)
     Bl, H, Sq, D = Q_local.shape
     Skv = K_local.shape[2]
+    if bufs.dtype != Q_local.dtype:
+        raise TypeError(f"buffer dtype {bufs.dtype} does not match the operands' {Q_local.dtype}")
     if bufs.cols != D or bufs.total_rows != total_batches * H * Sq:
         raise ValueError("buffer shape does not match [total_batches*H*S, D]")
     begin, count = _lib.shard_range(total_batches, bufs.world, bufs.rank, 1)

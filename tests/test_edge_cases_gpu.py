@@ -104,3 +104,55 @@ def test_bounded_wait_gives_up_and_context_survives():
     x = torch.randn(64, 256, device="cuda").bfloat16()
     assert torch.equal(ops.elementwise(x, "Relu"), torch.relu(x))
     assert l.kcg_selftest_bounded_wait(0, waited.data_ptr(), None) == L.ERR_INVALID_ARG
+
+
+_SCRATCH_SCRIPT = r"""
+import sys, torch
+sys.path.insert(0, sys.argv[1])
+from kernelcodegen_b200 import _lib, ops
+lib = _lib.load()
+dt = torch.bfloat16
+def ln(x, g, b, y):
+    return lib.kcg_layernorm(_lib.BF16, x.shape[0], x.shape[1], x.data_ptr(), g.data_ptr(), b.data_ptr(), 1e-5,
+                             y.data_ptr(), torch.cuda.current_stream().cuda_stream)
+# rows of 1001 elements are not a whole number of 16-byte vectors: the split-row kernels run and
+# keep per-chunk statistics in the library's scratch buffer (1 MiB is the smallest it allocates)
+xs = torch.randn(64, 1001, device="cuda").to(dt); gs = torch.ones(1001, device="cuda", dtype=dt); bs = torch.zeros_like(gs)
+ys = torch.empty_like(xs)
+assert ln(xs, gs, bs, ys) == 0                       # first call: allocates the buffer
+want_small = ys.clone()
+side = torch.cuda.Stream()
+g1 = torch.cuda.CUDAGraph()
+with torch.cuda.graph(g1, stream=side):
+    assert ln(xs, gs, bs, ys) == 0                   # fits the buffer: may be captured
+# 65535 rows of two chunks need more than 1 MiB of statistics
+xb = torch.randn(65535, 8195, device="cuda", dtype=dt); gb = torch.ones(8195, device="cuda", dtype=dt); bb = torch.zeros_like(gb)
+yb = torch.empty_like(xb)
+g2 = torch.cuda.CUDAGraph()
+with torch.cuda.graph(g2, stream=side):
+    rc = ln(xb, gb, bb, yb)                          # would have to grow inside the capture: refused
+    msg = lib.kcg_last_error().decode()
+    assert ln(xs, gs, bs, ys) == 0                   # the capture itself is still valid
+assert rc == _lib.ERR_UNSUPPORTED and "captured" in msg, (rc, msg)
+assert ln(xb, gb, bb, yb) == 0                       # outside a capture the buffer grows
+torch.cuda.synchronize()
+ref = torch.nn.functional.layer_norm(xb[:64].float(), (8195,), gb.float(), bb.float(), 1e-5)
+assert (yb[:64].float() - ref).norm() / ref.norm() < 1e-2
+# the graph captured before the growth still names the old buffer, which must still exist
+ys.zero_()
+g1.replay(); g2.replay()
+torch.cuda.synchronize()
+assert torch.equal(ys, want_small)
+assert _lib.device_status() == 0
+print("scratch rules ok")
+"""
+
+
+def test_scratch_buffer_is_never_freed_and_never_grows_inside_a_capture():
+    """Run in a fresh process so that the library's scratch buffer starts unallocated."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    r = subprocess.run([sys.executable, "-c", _SCRATCH_SCRIPT, str(root)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "scratch rules ok" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]

@@ -1,5 +1,7 @@
-"""Fused kernels against the chains they replace: the result must be bit-identical to the
-separate operators (and therefore within the same tolerance of the float64 oracle)."""
+"""Fused kernels against the chains they replace.  The criterion is bit-equality with the
+separate operators (the fused kernels round to the storage dtype exactly where the chain would
+store); the comparison with the float64 oracle is held to the operators' own tolerance
+(relative Frobenius 1e-5 for fp32, 1e-2 for 16-bit storage)."""
 import numpy as np
 import pytest
 import torch
@@ -28,7 +30,7 @@ def test_layernorm_gelu_add_equals_chain(shape, dtype):
     sync_ok()
     assert torch.equal(fused, chain)
     want = O.binary_f64("Add", O.unary_f64("Gelu", O.layernorm_f64(f64(x), f64(g), f64(b), -1)), f64(r))
-    assert rel_fro(fused, want) <= TOL[dtype] * 2  # three roundings to the storage dtype
+    assert rel_fro(fused, want) <= TOL[dtype]
 
 
 def test_layernorm_gelu_add_in_place():
@@ -40,6 +42,31 @@ def test_layernorm_gelu_add_in_place():
     got = ops().layernorm_gelu_add(x, g, b, r, out=x)
     sync_ok()
     assert got.data_ptr() == x.data_ptr() and torch.equal(got, want)
+
+
+def test_layernorm_gelu_add_in_place_on_the_residual():
+    """y may be the residual's own storage where the one-pass kernel runs; rows that fall back to
+    three in-place launches (1001 columns: not a whole number of 16-byte vectors) would read the
+    residual after it has been overwritten, so that combination is refused, not computed wrongly."""
+    from kernelcodegen_b200 import _lib
+    for cols, fused_ok in ((2048, True), (1001, False)):
+        x = randn((16, cols), torch.bfloat16, 715).cuda()
+        r = randn((16, cols), torch.bfloat16, 716).cuda()
+        g = randn((cols,), torch.bfloat16, 717, mean=1.0, std=0.1).cuda()
+        b = randn((cols,), torch.bfloat16, 718, std=0.1).cuda()
+        want = ops().layernorm_gelu_add(x, g, b, r)
+        sync_ok()
+        if fused_ok:
+            got = ops().layernorm_gelu_add(x, g, b, r, out=r)
+            sync_ok()
+            assert torch.equal(got, want)
+        else:
+            keep = r.clone()
+            with pytest.raises(_lib.KcgError) as e:
+                ops().layernorm_gelu_add(x, g, b, r, out=r)
+            assert e.value.status == _lib.ERR_UNSUPPORTED
+            sync_ok()
+            assert torch.equal(r, keep)   # refused before anything was launched
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
@@ -64,7 +91,7 @@ def test_gemm_fused_epilogue_equals_chain(m, n, k, with_bias, act, dtype):
         want = want + f64(bias)
     if act:
         want = O.unary_f64(act, want)
-    assert rel_fro(fused, want) <= TOL[dtype] * 2
+    assert rel_fro(fused, want) <= TOL[dtype]
 
 
 def test_gemm_fused_rejects_bad_activation():

@@ -16,7 +16,7 @@ def ops():
 
 
 def test_fp32_config_1024_cubed():
-    # BASELINE config 1: A, B uniform[-1,1], row-major, 1024^3
+    # the fp32 reference workload: A, B uniform[-1,1], row-major, 1024^3
     A = uniform((1024, 1024), torch.float32, 500)
     B = uniform((1024, 1024), torch.float32, 501)
     C = ops().matmul(A.cuda(), B.cuda())

@@ -48,6 +48,37 @@ def test_matches_allocating_entry_point_twice_in_a_row(dtype):
     assert torch.equal(again, got)
 
 
+def test_device_memory_in_use_does_not_change():
+    """After the first call on the device (which only looks up the array's address), further calls
+    must leave the amount of free device memory exactly as it was: the outputs are allocated here,
+    before the measurement, and the entry point itself must not allocate or free anything."""
+    from kernelcodegen_b200 import _lib
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    shapes = [(3, 40000), (200, 9000), (1, 100000)]
+    bufs = []
+    for i, (rows, cols) in enumerate(shapes):
+        x = randn((rows, cols), torch.float32, 930 + i).cuda()
+        g = randn((cols,), torch.float32, 940 + i, mean=1.0, std=0.1).cuda()
+        b = randn((cols,), torch.float32, 950 + i, std=0.1).cuda()
+        bufs.append((rows, cols, x, g, b, torch.empty_like(x)))
+    rows, cols, x, g, b, y = bufs[0]
+    _lib.check(lib.kcg_layernorm_split_static(0, rows, cols, x.data_ptr(), g.data_ptr(), b.data_ptr(), 1e-5,
+                                              y.data_ptr(), stream), "first call")
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        for rows, cols, x, g, b, y in bufs:
+            _lib.check(lib.kcg_layernorm_split_static(0, rows, cols, x.data_ptr(), g.data_ptr(), b.data_ptr(), 1e-5,
+                                                      y.data_ptr(), stream), "kcg_layernorm_split_static")
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    sync_ok()
+    for rows, cols, x, g, b, y in bufs:
+        assert rel_fro(y, O.layernorm_f64(f64(x), f64(g), f64(b), 1)) <= 1e-5
+
+
 def test_rejects_sizes_beyond_the_builtin_scratch():
     from kernelcodegen_b200 import _lib
     lib = _lib.load()
