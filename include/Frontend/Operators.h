@@ -35,7 +35,12 @@ struct Operator {
 };
 
 struct PlaceHolder : Operator<PlaceHolder> {
-  static Value build(ComputeDAG* graph, const std::vector<int64_t>& shapes, const std::string& dtype);
+  // `strides` (extension; elements, one per dim, innermost must be 1) declares a tensor that is
+  // not dense row-major, e.g. shape [B,H,S,D] with strides {S*H*D, D, H*D, 1} for data stored as
+  // [B,S,H,D].  Empty (the default) is the reference's dense layout.  Strided tensors are
+  // accepted by BatchedMatmul only (the attention chain); every other operator refuses them.
+  static Value build(ComputeDAG* graph, const std::vector<int64_t>& shapes, const std::string& dtype,
+                     const std::vector<int64_t>& strides = {});
 };
 
 struct Matmul : Operator<Matmul> {
@@ -51,8 +56,11 @@ struct Relu : Operator<Relu> {
 };
 
 struct BatchedMatmul : Operator<BatchedMatmul> {
+  // `out` (extension): a PlaceHolder of the result's shape and element type to write into, which
+  // is how a result gets a layout of its own (the reference allocates C itself, dense).  The
+  // returned handle names out's storage.
   static Value build(ComputeDAG* graph, Value A, Layout layoutA, Value B, Layout layoutB,
-                     const std::string& dtype = {""});
+                     const std::string& dtype = {""}, Value out = {});
 };
 
 // Softmax over the last dim, always in place (the reference returns its input buffer).

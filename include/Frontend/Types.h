@@ -52,6 +52,8 @@ struct Value {
   explicit operator bool() const { return id >= 0; }
   bool operator==(const Value& o) const { return id == o.id && owner == o.owner; }
   const std::vector<int64_t>& shape() const;
+  // element strides, one per dim; the dense row-major strides unless the PlaceHolder gave others
+  std::vector<int64_t> strides() const;
   DType dtype() const;
   int64_t numel() const;
   size_t bytes() const;
@@ -59,6 +61,11 @@ struct Value {
 
 struct TensorInfo {
   std::vector<int64_t> shape;
+  // Element strides per dim; empty = dense row-major (the only layout the reference has).
+  // Extension: a PlaceHolder may declare others, e.g. a [B,H,S,D] view of a [B,S,H,D] buffer.
+  std::vector<int64_t> strides;
+  bool dense() const;                        // strides are absent or equal to the row-major ones
+  std::vector<int64_t> effective_strides() const;
   DType dtype = DType::f32;
   MemorySpace space = MemorySpace::global;
   int producer = -1;       // index into GraphData::ops, -1 for a PlaceHolder

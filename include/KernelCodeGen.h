@@ -54,6 +54,23 @@ struct Bindings {
   std::map<int, void*> ptrs;
 };
 
+// How run() splits a module over the GPUs of one node (one process per GPU; extension, the
+// reference is single-GPU).  Every operator is cut along its independent units — Matmul rows of
+// A / C in granules of 128, BatchedMatmul and attention batches, LayerNorm / Softmax / elementwise
+// rows — by kcg_shard_range; rank `rank` of `world` launches the ordinary kernel on its block
+// only.  Buffers are bound at FULL size on every rank (inputs replicated).  With `gather` the
+// output of each sharded operator is all-gathered in place over `nccl_comm` (an ncclComm_t) on
+// the same stream, so every rank ends with the whole tensor and later operators may read all of
+// it; without it a rank's buffer holds its own block only (enough for a chain of row-wise
+// operators, which all cut the rows the same way).  Operators with no row-like unit (Gather,
+// a 2-D Transpose, a Binary that broadcasts along dim 0) run whole on every rank.
+struct ShardSpec {
+  int world = 1;
+  int rank = 0;
+  void* nccl_comm = nullptr;
+  bool gather = false;
+};
+
 class KernelCodeGenerator {
  public:
   KernelCodeGenerator(const std::string& platform_ = {"CUDA"});
@@ -90,6 +107,9 @@ class KernelCodeGenerator {
   // launch touches must be bound.  Returns a kcg_status; functions no optimizer selected
   // are an error (there is no CPU execution path).
   int run(Module& module, const Bindings& bindings, void* stream = nullptr);
+  // The same, sharded over the ranks `shard` describes (see ShardSpec).  Collective when
+  // shard.gather is set: every rank calls it with the same module.
+  int run(Module& module, const Bindings& bindings, const ShardSpec& shard, void* stream = nullptr);
 
   // Time every candidate config on the device inside optimize() (see evaluate()).
   bool autotune = false;
@@ -107,7 +127,8 @@ class KernelCodeGenerator {
   ComputeDAG graph;
   std::string platform;
   float minLatency = FLT_MAX;
-  int runSelected(Module& module, const Bindings& bindings, void* stream, bool skipUnselected);
+  int runSelected(Module& module, const Bindings& bindings, void* stream, bool skipUnselected,
+                  const ShardSpec* shard = nullptr);
   std::vector<std::map<std::string, int>> matmulConfigs, fmhaConfigs, binaryConfigs, elementWiseConfigs,
       gatherConfigs, layerNormConfigs, batchMatmulConfigs, softmaxConfigs, fusionConfigs;
 };

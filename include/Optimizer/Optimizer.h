@@ -3,7 +3,8 @@
 // schedules are the hand-written sm_100a kernels, so an optimizer only SELECTS: `applicable`
 // finds the functions of its family that are still tagged "cpu", `applyOptimzer` tags them
 // "gpu" and records the kernel that will run them.  The static tile-config maps are kept
-// (KernelCodeGenerator fills them from its tables) and recorded with the selection.
+// (KernelCodeGenerator fills them from its tables) and recorded with the selection; they are
+// per host thread, so generators on different threads can optimize at the same time.
 #pragma once
 
 #include <map>
@@ -36,7 +37,7 @@ struct Optimizer {
     Class() { this->name = Name; }                                       \
     bool applicable(Module& module) override;                            \
     void applyOptimzer(Module& module, OpBuilder& builder) override;     \
-    static std::map<std::string, int> configMember;                      \
+    static thread_local std::map<std::string, int> configMember;         \
   }
 
 KCG_DECLARE_OPTIMIZER(MatmulOptimizer, "Matmul", matmulConfig);
@@ -57,7 +58,7 @@ struct FMHAOptimizer : Optimizer {
   FMHAOptimizer() { this->name = "FMHA"; }
   bool applicable(Module& module) override;
   void applyOptimzer(Module& module, OpBuilder& builder) override;
-  static std::map<std::string, int> fmhaConfig;
+  static thread_local std::map<std::string, int> fmhaConfig;
 
  private:
   struct Chain { int qk, softmax, pv; };
@@ -75,7 +76,7 @@ struct KernelFusionOptimizer : Optimizer {
   KernelFusionOptimizer() { this->name = "KernelFusion"; }
   bool applicable(Module& module) override;
   void applyOptimzer(Module& module, OpBuilder& builder) override;
-  static std::map<std::string, int> fusionConfig;
+  static thread_local std::map<std::string, int> fusionConfig;
 
  private:
   struct GemmChain { int gemm, add, act; };     // op indices, -1 where absent

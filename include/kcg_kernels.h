@@ -458,6 +458,32 @@ KCG_API int kcg_selftest_bounded_wait(uint64_t budget_ns, unsigned long long* wa
 KCG_API int kcg_shard_range(int64_t total, int world, int rank, int64_t granule,
                             int64_t* begin, int64_t* count);
 
+/*
+ * The optional exchange after a sharded operator: an in-place all-gather over NCCL.  `buffer`
+ * holds the whole output, `total_units` units of `unit_bytes` bytes each (GEMM / LayerNorm /
+ * elementwise rows, attention batches); on entry the block kcg_shard_range(total_units, world,
+ * rank, granule) assigns to this rank is valid, and once the work queued on `stream` has run,
+ * every rank's block is.  Blocks of equal size go through one in-place ncclAllGather, ragged
+ * ones through one ncclBroadcast per owner inside a group.  `nccl_comm` is an ncclComm_t of
+ * `world` ranks in which this process is rank `rank` (checked).  Collective: every rank calls it
+ * with the same sizes.  No counterpart in the reference (which has no multi-GPU code); NCCL is
+ * looked up at run time in the libnccl.so.2 already loaded in the process, not linked.
+ */
+KCG_API int kcg_shard_allgather(void* buffer, int64_t total_units, int64_t unit_bytes,
+                                int64_t granule, int world, int rank, void* nccl_comm,
+                                void* stream);
+
+/*
+ * Thin wrappers for host code that does not include nccl.h itself (the C++ front end's tests, a
+ * ctypes caller): kcg_nccl_unique_id fills the 128-byte ncclUniqueId that rank 0 hands to the
+ * others by its own means; kcg_nccl_comm_create is ncclCommInitRank on the current device
+ * (collective); kcg_nccl_comm_destroy is ncclCommDestroy.  A communicator created elsewhere with
+ * the same NCCL library works just as well.
+ */
+KCG_API int kcg_nccl_unique_id(unsigned char id[128]);
+KCG_API int kcg_nccl_comm_create(int world, int rank, const unsigned char id[128], void** comm);
+KCG_API int kcg_nccl_comm_destroy(void* comm);
+
 #ifdef __cplusplus
 }
 #endif

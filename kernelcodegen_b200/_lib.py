@@ -65,6 +65,10 @@ SIGNATURES = {
     "kcg_timer_end": ([_vp, _vp, ctypes.POINTER(_fp)], _ci),
     "kcg_selftest_bounded_wait": ([ctypes.c_uint64, _vp, _vp], _ci),
     "kcg_shard_range": ([_i64, _ci, _ci, _i64, _i64p, _i64p], _ci),
+    "kcg_shard_allgather": ([_vp, _i64, _i64, _i64, _ci, _ci, _vp, _vp], _ci),
+    "kcg_nccl_unique_id": ([ctypes.c_char_p], _ci),
+    "kcg_nccl_comm_create": ([_ci, _ci, ctypes.c_char_p, ctypes.POINTER(_vp)], _ci),
+    "kcg_nccl_comm_destroy": ([_vp], _ci),
 }
 
 _lib = None

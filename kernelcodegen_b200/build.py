@@ -76,7 +76,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
             list(pool.map(_run, jobs))
     out = LIB / "libkcg_kernels.so"
     if jobs or not out.exists():
-        _run([nvcc, "-shared", "-cudart", "static", "-o", str(out)] + [str(o) for o in objs])
+        _run([nvcc, "-shared", "-cudart", "static", "-o", str(out)] + [str(o) for o in objs] + ["-ldl"])
     return out
 
 

@@ -313,9 +313,48 @@ int KernelCodeGenerator::run(Module& module, const Bindings& bindings, void* str
   return runSelected(module, bindings, stream, false);
 }
 
-int KernelCodeGenerator::runSelected(Module& module, const Bindings& bindings, void* stream, bool skipUnselected) {
+int KernelCodeGenerator::run(Module& module, const Bindings& bindings, const ShardSpec& shard, void* stream) {
+  if (shard.world < 1 || shard.rank < 0 || shard.rank >= shard.world) {
+    std::cerr << "run: ShardSpec with world " << shard.world << ", rank " << shard.rank << ".\n";
+    return KCG_ERR_INVALID_ARG;
+  }
+  if (shard.gather && shard.world > 1 && !shard.nccl_comm) {
+    std::cerr << "run: ShardSpec::gather needs an NCCL communicator.\n";
+    return KCG_ERR_INVALID_ARG;
+  }
+  return runSelected(module, bindings, stream, false, &shard);
+}
+
+namespace {
+
+// This rank's block of `total` units (all of them when the run is not sharded).
+struct Cut {
+  int64_t begin = 0, count = 0;
+  bool on = false;
+};
+
+// Leading dimension and batch stride of a tensor used as a (batched) GEMM operand: the innermost
+// stride must be 1 and the batch dims must collapse to one stride.
+bool gemm_view(const TensorInfo& t, int64_t& ld, int64_t& batch_stride) {
+  const auto st = t.effective_strides();
+  const size_t r = st.size();
+  if (r < 2 || st[r - 1] != 1) return false;
+  ld = st[r - 2];
+  batch_stride = r > 2 ? st[r - 3] : 0;
+  for (size_t d = 0; d + 3 < r; ++d)
+    if (st[d] != st[d + 1] * t.shape[d + 1]) return false;
+  return true;
+}
+
+char* shifted(void* p, int64_t elements, size_t esize) { return static_cast<char*>(p) + elements * static_cast<int64_t>(esize); }
+
+}  // namespace
+
+int KernelCodeGenerator::runSelected(Module& module, const Bindings& bindings, void* stream, bool skipUnselected,
+                                     const ShardSpec* shard) {
   if (!module.graph) return KCG_ERR_INVALID_ARG;
   const auto& g = *module.graph;
+  const bool sharded = shard && shard->world > 1;
   auto ptr = [&](int id) -> void* {
     for (int t = id; t >= 0; t = g.tensors[t].alias_of)
       if (void* p = bindings.get(t)) return p;
@@ -325,6 +364,17 @@ int KernelCodeGenerator::runSelected(Module& module, const Bindings& bindings, v
     int64_t n = 1;
     for (auto d : g.tensors[id].shape) n *= d;
     return n;
+  };
+  auto cut = [&](int64_t total, int64_t granule) {
+    Cut c;
+    c.count = total;
+    if (sharded && kcg_shard_range(total, shard->world, shard->rank, granule, &c.begin, &c.count) == KCG_OK) c.on = true;
+    return c;
+  };
+  // all-gather of a sharded output, in place, on the same stream (only when the spec asks for it)
+  auto gather = [&](const Cut& c, void* out, int64_t units, int64_t unit_bytes, int64_t granule) -> int {
+    if (!c.on || !shard->gather) return KCG_OK;
+    return kcg_shard_allgather(out, units, unit_bytes, granule, shard->world, shard->rank, shard->nccl_comm, stream);
   };
   for (const auto& c : module.calls) {
     const auto& op = g.ops[c.op];
@@ -351,6 +401,7 @@ int KernelCodeGenerator::runSelected(Module& module, const Bindings& bindings, v
     }
     const auto& t0 = g.tensors[op.inputs[0]];
     const auto& to = g.tensors[op.output];
+    const size_t es_in = dtypeSize(t0.dtype), es_out = dtypeSize(to.dtype);
     int rc = KCG_OK;
     apply_knobs(op.kind, info.config, false);
     switch (op.kind) {
@@ -358,29 +409,74 @@ int KernelCodeGenerator::runSelected(Module& module, const Bindings& bindings, v
         const int64_t m = t0.shape[0], k = t0.shape[1], n = g.tensors[op.inputs[1]].shape[1];
         const float* sa = op.scale_a >= 0 ? static_cast<const float*>(ptr(op.scale_a)) : nullptr;
         const float* sb = op.scale_b >= 0 ? static_cast<const float*>(ptr(op.scale_b)) : nullptr;
-        rc = kcg_gemm_fused(static_cast<int>(t0.dtype), static_cast<int>(to.dtype), m, n, k, 1, 0, 0, in[0], k, 0, in[1], n,
-                            0, out, n, 0, sa, sb, op.bias >= 0 ? ptr(op.bias) : nullptr, act_code(op.activation), stream);
+        const Cut r = cut(m, 128);   // rows of A and C; B is replicated
+        if (r.count > 0)
+          rc = kcg_gemm_fused(static_cast<int>(t0.dtype), static_cast<int>(to.dtype), r.count, n, k, 1, 0, 0,
+                              shifted(in[0], r.begin * k, es_in), k, 0, in[1], n, 0, shifted(out, r.begin * n, es_out), n, 0,
+                              sa, sb, op.bias >= 0 ? ptr(op.bias) : nullptr, act_code(op.activation), stream);
+        if (rc == KCG_OK) rc = gather(r, out, m, n * static_cast<int64_t>(es_out), 128);
         break;
       }
       case OpKind::BatchedMatmul: {
+        const auto& tb = g.tensors[op.inputs[1]];
         const auto& sa = t0.shape;
-        const auto& sb = g.tensors[op.inputs[1]].shape;
+        const auto& sb = tb.shape;
         const size_t r = sa.size();
-        const bool ta = op.layoutA == Layout::colMajor, tb = op.layoutB == Layout::colMajor;
+        const bool ta = op.layoutA == Layout::colMajor, tbt = op.layoutB == Layout::colMajor;
         const int64_t m = ta ? sa[r - 1] : sa[r - 2], k = ta ? sa[r - 2] : sa[r - 1];
-        const int64_t n = tb ? sb[r - 2] : sb[r - 1];
+        const int64_t n = tbt ? sb[r - 2] : sb[r - 1];
         int64_t batch = 1;
         for (size_t d = 0; d + 2 < r; ++d) batch *= sa[d];
-        rc = kcg_gemm_fused(static_cast<int>(t0.dtype), static_cast<int>(to.dtype), m, n, k, batch, ta, tb, in[0],
-                            sa[r - 1], sa[r - 1] * sa[r - 2], in[1], sb[r - 1], sb[r - 1] * sb[r - 2], out, n, m * n,
-                            nullptr, nullptr, op.bias >= 0 ? ptr(op.bias) : nullptr, act_code(op.activation), stream);
+        int64_t lda, ldb, ldc, stride_a, stride_b, stride_c;
+        if (!gemm_view(t0, lda, stride_a) || !gemm_view(tb, ldb, stride_b) || !gemm_view(to, ldc, stride_c)) {
+          std::cerr << "run: @" << op.func << " has a strided operand the GEMM kernel cannot address (one leading "
+                       "dimension and one batch stride); such layouts run only as part of the fused attention chain.\n";
+          return KCG_ERR_UNSUPPORTED;
+        }
+        const void* bias = op.bias >= 0 ? ptr(op.bias) : nullptr;
+        if (batch > 1) {
+          const Cut bc = cut(batch, 1);   // whole matrices per rank
+          if (bc.count > 0)
+            rc = kcg_gemm_fused(static_cast<int>(t0.dtype), static_cast<int>(to.dtype), m, n, k, bc.count, ta, tbt,
+                                shifted(in[0], bc.begin * stride_a, es_in), lda, stride_a,
+                                shifted(in[1], bc.begin * stride_b, es_in), ldb, stride_b,
+                                shifted(out, bc.begin * stride_c, es_out), ldc, stride_c, nullptr, nullptr, bias,
+                                act_code(op.activation), stream);
+          if (rc == KCG_OK && bc.on && shard->gather) {
+            if (!to.dense()) {
+              std::cerr << "run: the gather of @" << op.func << " needs a dense result.\n";
+              return KCG_ERR_UNSUPPORTED;
+            }
+            rc = gather(bc, out, batch, m * n * static_cast<int64_t>(es_out), 1);
+          }
+        } else {
+          const Cut rc_rows = cut(m, 128);
+          if (rc_rows.count > 0)
+            rc = kcg_gemm_fused(static_cast<int>(t0.dtype), static_cast<int>(to.dtype), rc_rows.count, n, k, 1, ta, tbt,
+                                shifted(in[0], ta ? rc_rows.begin : rc_rows.begin * lda, es_in), lda, 0, in[1], ldb, 0,
+                                shifted(out, rc_rows.begin * ldc, es_out), ldc, 0, nullptr, nullptr, bias,
+                                act_code(op.activation), stream);
+          if (rc == KCG_OK && rc_rows.on && shard->gather) {
+            if (!to.dense()) {
+              std::cerr << "run: the gather of @" << op.func << " needs a dense result.\n";
+              return KCG_ERR_UNSUPPORTED;
+            }
+            rc = gather(rc_rows, out, m, n * static_cast<int64_t>(es_out), 128);
+          }
+        }
         break;
       }
       case OpKind::Softmax: {
         const int64_t cols = t0.shape.back();
         const int64_t rows = cols ? numel(op.inputs[0]) / cols : 0;
         const int64_t q_len = t0.shape.size() >= 2 ? t0.shape[t0.shape.size() - 2] : 1;
-        rc = kcg_softmax(static_cast<int>(t0.dtype), rows, cols, op.scale, op.causal, q_len, in[0], out, stream);
+        // a causal mask depends on the row's position inside its [q_len, cols] matrix: keep matrices whole
+        const int64_t gran = op.causal && q_len > 0 ? q_len : 1;
+        const Cut r = cut(rows, gran);
+        if (r.count > 0)
+          rc = kcg_softmax(static_cast<int>(t0.dtype), r.count, cols, op.scale, op.causal, q_len,
+                           shifted(in[0], r.begin * cols, es_in), shifted(out, r.begin * cols, es_out), stream);
+        if (rc == KCG_OK) rc = gather(r, out, rows, cols * static_cast<int64_t>(es_out), gran);
         break;
       }
       case OpKind::LayerNorm: {
@@ -392,21 +488,52 @@ int KernelCodeGenerator::runSelected(Module& module, const Bindings& bindings, v
                        "normalised shape.\n";
           return KCG_ERR_UNSUPPORTED;
         }
-        rc = kcg_layernorm(static_cast<int>(t0.dtype), rows, cols, in[0], in[1], in[2], op.eps, out, stream);
+        const Cut r = cut(rows, 1);
+        if (r.count > 0)
+          rc = kcg_layernorm(static_cast<int>(t0.dtype), r.count, cols, shifted(in[0], r.begin * cols, es_in), in[1], in[2],
+                             op.eps, shifted(out, r.begin * cols, es_out), stream);
+        if (rc == KCG_OK) rc = gather(r, out, rows, cols * static_cast<int64_t>(es_out), 1);
         break;
       }
       case OpKind::ElementWise: {
         const int opi = index_of(ElementWise::operations(), op.operation);
-        rc = kcg_eltwise(opi, static_cast<int>(t0.dtype), static_cast<int>(to.dtype), numel(op.inputs[0]), in[0], out,
-                         stream);
+        const int64_t n_all = numel(op.inputs[0]);
+        const int64_t units = !t0.shape.empty() && t0.shape[0] > 0 ? t0.shape[0] : 1;
+        const int64_t inner = n_all / units;
+        const Cut r = cut(units, 1);
+        if (r.count * inner > 0)
+          rc = kcg_eltwise(opi, static_cast<int>(t0.dtype), static_cast<int>(to.dtype), r.count * inner,
+                           shifted(in[0], r.begin * inner, es_in), shifted(out, r.begin * inner, es_out), stream);
+        if (rc == KCG_OK && n_all > 0) rc = gather(r, out, units, inner * static_cast<int64_t>(es_out), 1);
         break;
       }
       case OpKind::Binary: {
-        const auto& sa = t0.shape;
-        const auto& sb = g.tensors[op.inputs[1]].shape;
-        rc = kcg_binary(index_of(Binary::operations(), op.operation), static_cast<int>(t0.dtype),
-                        static_cast<int>(sa.size()), sa.data(), static_cast<int>(sb.size()), sb.data(), in[0], in[1], out,
-                        stream);
+        std::vector<int64_t> sa = t0.shape, sb = g.tensors[op.inputs[1]].shape;
+        // Rows can be split when A already has the output's shape and B either has it too or does
+        // not extend along dim 0 (a bias-like operand); any other broadcast runs whole on every rank.
+        const bool b_same = sb == sa;
+        const bool b_fixed = sb.size() < sa.size() || (sb.size() == sa.size() && !sb.empty() && sb[0] == 1 && sa[0] != 1);
+        const bool splittable = sharded && to.shape == sa && !sa.empty() && sa[0] > 0 && (b_same || b_fixed);
+        void* a_ptr = in[0];
+        void* b_ptr = in[1];
+        void* c_ptr = out;
+        Cut r;
+        r.count = sa.empty() ? 1 : sa[0];
+        if (splittable) {
+          r = cut(sa[0], 1);
+          const int64_t inner = numel(op.inputs[0]) / sa[0];
+          a_ptr = shifted(in[0], r.begin * inner, es_in);
+          c_ptr = shifted(out, r.begin * inner, es_out);
+          if (b_same) b_ptr = shifted(in[1], r.begin * inner, es_in);
+          sa[0] = r.count;
+          if (b_same) sb[0] = r.count;
+        }
+        if (!splittable || r.count > 0)
+          rc = kcg_binary(index_of(Binary::operations(), op.operation), static_cast<int>(t0.dtype),
+                          static_cast<int>(sa.size()), sa.data(), static_cast<int>(sb.size()), sb.data(), a_ptr, b_ptr, c_ptr,
+                          stream);
+        if (rc == KCG_OK && splittable)
+          rc = gather(r, out, t0.shape[0], numel(op.inputs[0]) / t0.shape[0] * static_cast<int64_t>(es_out), 1);
         break;
       }
       case OpKind::Gather: {
@@ -422,25 +549,54 @@ int KernelCodeGenerator::runSelected(Module& module, const Bindings& bindings, v
         const size_t r = t0.shape.size();
         const int64_t rows = t0.shape[r - 2], cols = t0.shape[r - 1];
         const int64_t batch = (rows != 0 && cols != 0) ? numel(op.inputs[0]) / (rows * cols) : 0;
-        rc = kcg_transpose(static_cast<int>(t0.dtype), batch, rows, cols, in[0], out, stream);
+        Cut bc;
+        bc.count = batch;
+        if (batch > 1) bc = cut(batch, 1);
+        if (bc.count > 0)
+          rc = kcg_transpose(static_cast<int>(t0.dtype), bc.count, rows, cols, shifted(in[0], bc.begin * rows * cols, es_in),
+                             shifted(out, bc.begin * rows * cols, es_out), stream);
+        if (rc == KCG_OK && batch > 1) rc = gather(bc, out, batch, rows * cols * static_cast<int64_t>(es_out), 1);
         break;
       }
       case OpKind::FusedLayerNormGeluAdd: {
         const int64_t cols = t0.shape.back();
         const int64_t rows = cols ? numel(op.inputs[0]) / cols : 0;
-        rc = kcg_layernorm_gelu_add(static_cast<int>(t0.dtype), rows, cols, in[0], in[1], in[2], op.eps, in[3], out,
-                                    stream);
+        const Cut r = cut(rows, 1);
+        if (r.count > 0)
+          rc = kcg_layernorm_gelu_add(static_cast<int>(t0.dtype), r.count, cols, shifted(in[0], r.begin * cols, es_in), in[1],
+                                      in[2], op.eps, shifted(in[3], r.begin * cols, es_in),
+                                      shifted(out, r.begin * cols, es_out), stream);
+        if (rc == KCG_OK) rc = gather(r, out, rows, cols * static_cast<int64_t>(es_out), 1);
         break;
       }
       case OpKind::FusedAttention: {
+        const auto& tk = g.tensors[op.inputs[1]];
+        const auto& tv = g.tensors[op.inputs[2]];
         const auto& q = t0.shape;
-        const auto& k = g.tensors[op.inputs[1]].shape;
         const size_t r = q.size();
-        const int64_t D = q[r - 1], Sq = q[r - 2], Skv = k[r - 2];
+        const int64_t D = q[r - 1], Sq = q[r - 2], Skv = tk.shape[r - 2];
         const int64_t H = r == 4 ? q[1] : 1, B = q[0];
-        const int64_t qs[3] = {H * Sq * D, Sq * D, D}, ks[3] = {H * Skv * D, Skv * D, D};
-        rc = kcg_fmha_fwd(static_cast<int>(t0.dtype), B, H, Sq, Skv, D, op.scale, op.causal, in[0], qs, in[1], ks, in[2],
-                          ks, out, qs, stream);
+        // (batch, head, sequence) element strides of each tensor, whatever layout it was declared with
+        auto bhs = [&](const TensorInfo& t, int64_t (&st)[3]) {
+          const auto e = t.effective_strides();
+          st[0] = e[0];
+          st[1] = r == 4 ? e[1] : e[0];
+          st[2] = e[r - 2];
+        };
+        int64_t qs[3], ks[3], vs[3], os[3];
+        bhs(t0, qs); bhs(tk, ks); bhs(tv, vs); bhs(to, os);
+        const Cut bc = cut(B, 1);   // whole batches per rank
+        if (bc.count > 0)
+          rc = kcg_fmha_fwd(static_cast<int>(t0.dtype), bc.count, H, Sq, Skv, D, op.scale, op.causal,
+                            shifted(in[0], bc.begin * qs[0], es_in), qs, shifted(in[1], bc.begin * ks[0], es_in), ks,
+                            shifted(in[2], bc.begin * vs[0], es_in), vs, shifted(out, bc.begin * os[0], es_out), os, stream);
+        if (rc == KCG_OK && bc.on && shard->gather) {
+          if (os[0] != H * Sq * D) {
+            std::cerr << "run: the gather of @" << op.func << " needs each batch of the result to be one contiguous block.\n";
+            return KCG_ERR_UNSUPPORTED;
+          }
+          rc = gather(bc, out, B, os[0] * static_cast<int64_t>(es_out), 1);
+        }
         break;
       }
     }

@@ -47,6 +47,21 @@ size_t dtypeSize(DType type) {
 
 // ---- handles and graph queries -----------------------------------------------------------
 const std::vector<int64_t>& Value::shape() const { return owner->tensors[id].shape; }
+std::vector<int64_t> Value::strides() const { return owner->tensors[id].effective_strides(); }
+
+std::vector<int64_t> TensorInfo::effective_strides() const {
+  if (!strides.empty()) return strides;
+  std::vector<int64_t> st(shape.size(), 1);
+  for (int d = static_cast<int>(shape.size()) - 2; d >= 0; --d) st[d] = st[d + 1] * shape[d + 1];
+  return st;
+}
+
+bool TensorInfo::dense() const {
+  if (strides.empty()) return true;
+  TensorInfo plain;
+  plain.shape = shape;
+  return strides == plain.effective_strides();
+}
 DType Value::dtype() const { return owner->tensors[id].dtype; }
 int64_t Value::numel() const {
   int64_t n = 1;
@@ -78,13 +93,28 @@ std::string dims(const std::vector<int64_t>& shape, const char* sep = "_") {
   return s;
 }
 
-bool valid(ComputeDAG* graph, Value v, const char* what) {
+// The reference names a function after its operator and shapes only, so two calls that differ in
+// element type would share one function (and one optimizer decision).  All-float32 functions keep
+// the reference's exact name; any other element type is appended ("_bfloat16"), and a result type
+// that differs from the operand type as well ("_float32_to_int32").
+std::string dtype_suffix(DType in, DType out) {
+  if (in == DType::f32 && out == DType::f32) return "";
+  std::string s = "_" + toStr(in);
+  if (out != in) s += "_to_" + toStr(out);
+  return s;
+}
+
+bool valid(ComputeDAG* graph, Value v, const char* what, bool allow_strided = false) {
   if (!graph || !graph->data) {
     std::cerr << "No graph: call KernelCodeGenerator::createGraph first.\n";
     return false;
   }
   if (!v || v.owner != graph->data.get()) {
     std::cerr << what;
+    return false;
+  }
+  if (!allow_strided && !graph->data->tensors[v.id].dense()) {
+    std::cerr << "This operator takes dense row-major tensors; strided PlaceHolders are accepted by BatchedMatmul only.\n";
     return false;
   }
   return true;
@@ -160,7 +190,8 @@ void ComputeDAG::dump(const std::string& info) {
 }
 
 // ---- PlaceHolder (reference: Operators.cc:112-118) ------------------------------------------
-Value PlaceHolder::build(ComputeDAG* graph, const std::vector<int64_t>& shapes, const std::string& dtype) {
+Value PlaceHolder::build(ComputeDAG* graph, const std::vector<int64_t>& shapes, const std::string& dtype,
+                         const std::vector<int64_t>& strides) {
   if (!graph || !graph->data) {
     std::cerr << "No graph: call KernelCodeGenerator::createGraph first.\n";
     return {};
@@ -175,7 +206,18 @@ Value PlaceHolder::build(ComputeDAG* graph, const std::vector<int64_t>& shapes, 
       std::cerr << "PlaceHolder needs static non-negative dims.\n";
       return {};
     }
-  return new_tensor(graph, shapes, dt, MemorySpace::global, -1);
+  if (!strides.empty()) {
+    bool ok = strides.size() == shapes.size() && strides.back() == 1;
+    for (auto s : strides) ok = ok && s > 0;
+    if (!ok) {
+      std::cerr << "PlaceHolder strides: one positive element stride per dim, the innermost equal to 1.\n";
+      return {};
+    }
+  }
+  Value v = new_tensor(graph, shapes, dt, MemorySpace::global, -1);
+  graph->data->tensors[v.id].strides = strides;
+  if (graph->data->tensors[v.id].dense()) graph->data->tensors[v.id].strides.clear();
+  return v;
 }
 
 // ---- Matmul (reference: Operators.cc:120-220) ------------------------------------------------
@@ -197,7 +239,8 @@ Value Matmul::build(ComputeDAG* graph, Value A, Value B, const std::string& dtyp
   if (!resolve_dtype(dtype_, fallback, dt, "Matmul")) return {};
   OpNode node;
   node.kind = OpKind::Matmul;
-  node.func = "Matmul_m" + std::to_string(m) + "n" + std::to_string(n) + "k" + std::to_string(k1);
+  node.func = "Matmul_m" + std::to_string(m) + "n" + std::to_string(n) + "k" + std::to_string(k1) +
+              dtype_suffix(A.dtype(), dt);
   node.inputs = {A.id, B.id};
   return add_op(graph, node, {m, n}, dt, MemorySpace::global, -1);
 }
@@ -231,17 +274,17 @@ Value Relu::build(ComputeDAG* graph, Value input, MemorySpace ms, const std::str
   OpNode node;
   node.kind = OpKind::ElementWise;
   node.operation = "Relu";
-  node.func = "Relu_Elementwise" + dims(input.shape());
+  const DType out_dt = ms == MemorySpace::inplace ? input.dtype() : dt;
+  node.func = "Relu_Elementwise" + dims(input.shape()) + dtype_suffix(input.dtype(), out_dt);
   node.inputs = {input.id};
-  return add_op(graph, node, input.shape(), ms == MemorySpace::inplace ? input.dtype() : dt, ms,
-                ms == MemorySpace::inplace ? input.id : -1);
+  return add_op(graph, node, input.shape(), out_dt, ms, ms == MemorySpace::inplace ? input.id : -1);
 }
 
 // ---- BatchedMatmul (reference: Operators.cc:291-457) ------------------------------------------
 Value BatchedMatmul::build(ComputeDAG* graph, Value A, Layout layoutA, Value B, Layout layoutB,
-                           const std::string& dtype_) {
-  if (!valid(graph, A, "Type of left operand of BatchedMatmul is not Memref.\n")) return {};
-  if (!valid(graph, B, "Type of right operand of BatchedMatmul is not Memref.\n")) return {};
+                           const std::string& dtype_, Value out) {
+  if (!valid(graph, A, "Type of left operand of BatchedMatmul is not Memref.\n", true)) return {};
+  if (!valid(graph, B, "Type of right operand of BatchedMatmul is not Memref.\n", true)) return {};
   const auto& sa = A.shape();
   const auto& sb = B.shape();
   const int total = static_cast<int>(sa.size());
@@ -277,12 +320,25 @@ Value BatchedMatmul::build(ComputeDAG* graph, Value A, Layout layoutA, Value B, 
   name += "_m" + std::to_string(m) + "_n" + std::to_string(n) + "_k" + std::to_string(k1) + "_";
   name += layoutA == Layout::rowMajor ? 'N' : 'T';
   name += layoutB == Layout::rowMajor ? 'N' : 'T';
+  name += dtype_suffix(A.dtype(), dt);
   OpNode node;
   node.kind = OpKind::BatchedMatmul;
   node.func = name;
   node.inputs = {A.id, B.id};
   node.layoutA = layoutA;
   node.layoutB = layoutB;
+  if (out) {
+    if (!valid(graph, out, "BatchedMatmul: out is not a tensor of this graph.\n", true)) return {};
+    const auto& ot = graph->data->tensors[out.id];
+    if (ot.producer >= 0 || ot.shape != sc || ot.dtype != dt) {
+      std::cerr << "BatchedMatmul: out must be a PlaceHolder with the result's shape and element type.\n";
+      return {};
+    }
+    const std::vector<int64_t> out_strides = ot.strides;
+    Value c = add_op(graph, node, sc, dt, MemorySpace::global, out.id);
+    graph->data->tensors[c.id].strides = out_strides;
+    return c;
+  }
   return add_op(graph, node, sc, dt, MemorySpace::global, -1);
 }
 
@@ -308,7 +364,7 @@ Value Softmax::build(ComputeDAG* graph, Value input, int axis, MemorySpace, cons
   if (!resolve_dtype(dtype_, input.dtype(), dt, "Softmax")) return {};
   OpNode node;
   node.kind = OpKind::Softmax;
-  node.func = "Softmax" + dims(input.shape()) + "_axis" + std::to_string(start);
+  node.func = "Softmax" + dims(input.shape()) + "_axis" + std::to_string(start) + dtype_suffix(input.dtype(), input.dtype());
   node.inputs = {input.id};
   node.axis = start;
   node.scale = scale;
@@ -330,7 +386,7 @@ Value Transpose::build(ComputeDAG* graph, Value input) {
   std::swap(out[out.size() - 1], out[out.size() - 2]);
   OpNode node;
   node.kind = OpKind::Transpose;
-  node.func = "Transpose" + dims(in);
+  node.func = "Transpose" + dims(in) + dtype_suffix(input.dtype(), input.dtype());
   node.inputs = {input.id};
   return add_op(graph, node, out, input.dtype(), MemorySpace::global, -1);
 }
@@ -373,7 +429,8 @@ Value Binary::build(ComputeDAG* graph, Value A, Value B, std::string operation, 
   OpNode node;
   node.kind = OpKind::Binary;
   node.operation = operation;
-  node.func = operation + "_Binary" + dims(A.shape()) + "_" + operation + dims(B.shape());
+  node.func = operation + "_Binary" + dims(A.shape()) + "_" + operation + dims(B.shape()) +
+              dtype_suffix(A.dtype(), ms == MemorySpace::inplace ? A.dtype() : dt);
   node.inputs = {A.id, B.id};
   int alias = -1;
   if (ms == MemorySpace::inplace) {
@@ -413,7 +470,7 @@ Value ElementWise::build(ComputeDAG* graph, Value input, std::string operation, 
   OpNode node;
   node.kind = OpKind::ElementWise;
   node.operation = operation;
-  node.func = operation + "_Elementwise" + dims(input.shape());
+  node.func = operation + "_Elementwise" + dims(input.shape()) + dtype_suffix(input.dtype(), dt);
   node.inputs = {input.id};
   return add_op(graph, node, input.shape(), dt, ms, ms == MemorySpace::inplace ? input.id : -1);
 }
@@ -452,7 +509,7 @@ Value LayerNorm::build(ComputeDAG* graph, Value input, Value scale, Value bias, 
   }
   OpNode node;
   node.kind = OpKind::LayerNorm;
-  node.func = "LayerNorm" + dims(in) + "_axis_" + std::to_string(axis);
+  node.func = "LayerNorm" + dims(in) + "_axis_" + std::to_string(axis) + dtype_suffix(input.dtype(), input.dtype());
   node.inputs = {input.id, scale.id, bias.id};
   node.axis = axis;
   node.eps = eps;
@@ -490,6 +547,8 @@ Value Gather::build(ComputeDAG* graph, Value input, Value indices, const std::in
   name += "_indices";
   for (auto d : idx) name += "_" + std::to_string(d);
   name += "_axis_" + std::to_string(axis);
+  name += dtype_suffix(input.dtype(), input.dtype());
+  if (indices.dtype() == DType::i32) name += "_idx32";   // the reference's indices are `index` (64-bit)
   node.func = name;
   node.inputs = {input.id, indices.id};
   node.axis = axis;

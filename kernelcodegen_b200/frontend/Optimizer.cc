@@ -8,15 +8,15 @@
 
 namespace KernelCodeGen {
 
-std::map<std::string, int> MatmulOptimizer::matmulConfig;
-std::map<std::string, int> FMHAOptimizer::fmhaConfig;
-std::map<std::string, int> BinaryOptimizer::binaryConfig;
-std::map<std::string, int> ElementWiseOptimizer::elementWiseConfig;
-std::map<std::string, int> LayerNormOptimizer::layerNormConfig;
-std::map<std::string, int> GatherOptimizer::gatherConfig;
-std::map<std::string, int> TransposeOptimizer::transposeConfig;
-std::map<std::string, int> BatchMatmulOptimizer::batchMatmulConfig;
-std::map<std::string, int> SoftmaxOptimizer::softmaxConfig;
+thread_local std::map<std::string, int> MatmulOptimizer::matmulConfig;
+thread_local std::map<std::string, int> FMHAOptimizer::fmhaConfig;
+thread_local std::map<std::string, int> BinaryOptimizer::binaryConfig;
+thread_local std::map<std::string, int> ElementWiseOptimizer::elementWiseConfig;
+thread_local std::map<std::string, int> LayerNormOptimizer::layerNormConfig;
+thread_local std::map<std::string, int> GatherOptimizer::gatherConfig;
+thread_local std::map<std::string, int> TransposeOptimizer::transposeConfig;
+thread_local std::map<std::string, int> BatchMatmulOptimizer::batchMatmulConfig;
+thread_local std::map<std::string, int> SoftmaxOptimizer::softmaxConfig;
 
 std::vector<std::string> Optimizer::collect(Module& module, const std::string& needle, const std::string& exclude) {
   std::vector<std::string> out;
@@ -87,9 +87,18 @@ bool FMHAOptimizer::applicable(Module& module) {
     for (size_t d = 0; d + 2 < r; ++d) same = same && q.shape[d] == k.shape[d] && q.shape[d] == v.shape[d];
     if (!same || k.shape[r - 2] != v.shape[r - 2]) continue;
     const int64_t hd = q.shape[r - 1];
+    // the kernel addresses each tensor as base + b*s0 + h*s1 + s*s2 + d: any strides whose
+    // innermost is 1 and whose others are multiples of 8 elements (16-byte rows for TMA)
+    auto strides_ok = [](const TensorInfo& t) {
+      for (size_t d = 0; d + 1 < t.strides.size(); ++d)
+        if (t.strides[d] % 8 != 0) return false;
+      return true;
+    };
+    const auto& o = g.tensors[pv.output];
     const bool kernel_ok = (q.dtype == DType::bf16 || q.dtype == DType::f16) && k.dtype == q.dtype &&
                            v.dtype == q.dtype && (hd == 64 || hd == 128) && v.shape[r - 1] == hd &&
-                           g.tensors[pv.output].dtype == q.dtype;
+                           o.dtype == q.dtype && strides_ok(q) && strides_ok(k) && strides_ok(v) && strides_ok(o) &&
+                           g.tensors[qk.output].dense() && g.tensors[g.ops[si].output].dense();
     if (!kernel_ok) {
       if (KCGLog::level == Log::Debug)
         std::cerr << "FMHA: chain at @" << qk.func << " left unfused (the fused kernel takes bfloat16/float16 with "
@@ -113,7 +122,7 @@ void FMHAOptimizer::applyOptimzer(Module& module, OpBuilder&) {
     fused.kind = OpKind::FusedAttention;
     fused.func = "Fused_Multi_Head_Attention";
     for (size_t d = 0; d + 2 < r; ++d) fused.func += "_" + std::to_string(q.shape[d]);
-    fused.func += "_SL" + std::to_string(q.shape[r - 2]) + "_HD" + std::to_string(q.shape[r - 1]);
+    fused.func += "_SL" + std::to_string(q.shape[r - 2]) + "_HD" + std::to_string(q.shape[r - 1]) + "_" + toStr(q.dtype);
     fused.inputs = {qk.inputs[0], qk.inputs[1], pv.inputs[1]};
     fused.output = pv.output;
     fused.scale = sm.scale;
@@ -146,7 +155,7 @@ void FMHAOptimizer::applyOptimzer(Module& module, OpBuilder&) {
 // ---------------------------------------------------------------------------- KernelFusion
 namespace KernelCodeGen {
 
-std::map<std::string, int> KernelFusionOptimizer::fusionConfig;
+thread_local std::map<std::string, int> KernelFusionOptimizer::fusionConfig;
 
 namespace {
 // The single live op that reads `tensor` as its first input, or -1 (also -1 when the tensor has

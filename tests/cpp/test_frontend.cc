@@ -41,10 +41,10 @@ static void test_operators_cast() {  // test/test.cc:8-49, the live sequence
   auto module = generator.optimize(graph);
   generator.dump(module);
   auto&& sourceCode = generator.codegen(module);
-  CHECK(has(sourceCode, "launch kcg_eltwise") && has(sourceCode, "@Cast_Elementwise_2_768_768"));
-  CHECK(module.graph->funcs.at("Cast_Elementwise_2_768_768").state == "gpu");
+  CHECK(has(sourceCode, "launch kcg_eltwise") && has(sourceCode, "@Cast_Elementwise_2_768_768_float32_to_int32"));
+  CHECK(module.graph->funcs.at("Cast_Elementwise_2_768_768_float32_to_int32").state == "gpu");
   // the graph the user holds is untouched by optimize (the reference optimizes a clone)
-  CHECK(graph.data->funcs.at("Cast_Elementwise_2_768_768").state == "cpu");
+  CHECK(graph.data->funcs.at("Cast_Elementwise_2_768_768_float32_to_int32").state == "cpu");
 }
 
 static void test_commented_sequences() {  // test/test.cc:26-46, the commented-out variants
@@ -125,15 +125,17 @@ static void test_flash_attention_graph() {  // test/test.cc:107-147
     auto P = graph.create<Softmax>(S, -1, MemorySpace::inplace);
     auto O = graph.create<BatchedMatmul>(P, Layout::rowMajor, V, Layout::rowMajor);
     CHECK(bool(O) && O.shape() == Q.shape());
-    CHECK(graph.data->funcs.count("BatchMatmul_8_32_m2048_n2048_k64_NT"));
-    CHECK(graph.data->funcs.count("Softmax_8_32_2048_2048_axis3"));
-    CHECK(graph.data->funcs.count("BatchMatmul_8_32_m2048_n64_k2048_NN"));
+    // float32 functions carry the reference's exact names; other element types are appended
+    const std::string sfx = std::string(dtype) == "float32" ? "" : "_" + std::string(dtype);
+    CHECK(graph.data->funcs.count("BatchMatmul_8_32_m2048_n2048_k64_NT" + sfx));
+    CHECK(graph.data->funcs.count("Softmax_8_32_2048_2048_axis3" + sfx));
+    CHECK(graph.data->funcs.count("BatchMatmul_8_32_m2048_n64_k2048_NN" + sfx));
     auto module = generator.optimize(graph);
     auto plan = generator.codegen(module);
     if (std::string(dtype) == "bfloat16") {
       CHECK(module.calls.size() == 1);
-      CHECK(has(plan, "launch kcg_fmha_fwd") && has(plan, "@Fused_Multi_Head_Attention_8_32_SL2048_HD64"));
-      CHECK(!module.graph->funcs.count("Softmax_8_32_2048_2048_axis3"));
+      CHECK(has(plan, "launch kcg_fmha_fwd") && has(plan, "@Fused_Multi_Head_Attention_8_32_SL2048_HD64_bfloat16"));
+      CHECK(!module.graph->funcs.count("Softmax_8_32_2048_2048_axis3_bfloat16"));
     } else {
       // the fused kernel is a 16-bit tensor-core kernel: the fp32 chain stays three calls
       CHECK(module.calls.size() == 3 && !has(plan, "kcg_fmha_fwd"));
@@ -183,10 +185,10 @@ static void test_kernel_fusion() {
   auto module = generator.optimize(graph);
   auto plan = generator.codegen(module);
   CHECK(module.calls.size() == 6);  // fused gemm+bias+gelu, fused gemm+relu, fused LN chain, gemm, gelu, tanh
-  CHECK(has(plan, "@Fused_Matmul_m512n256k128_Bias_Gelu"));
-  CHECK(has(plan, "@Fused_Matmul_m512n256k128_Relu"));
-  CHECK(has(plan, "launch kcg_layernorm_gelu_add") && has(plan, "@Fused_LayerNorm_64_256_axis_1_Gelu_Add"));
-  CHECK(has(plan, "@Gelu_Elementwise_512_256") && has(plan, "@Tanh_Elementwise_512_256"));
+  CHECK(has(plan, "@Fused_Matmul_m512n256k128_bfloat16_Bias_Gelu"));
+  CHECK(has(plan, "@Fused_Matmul_m512n256k128_bfloat16_Relu"));
+  CHECK(has(plan, "launch kcg_layernorm_gelu_add") && has(plan, "@Fused_LayerNorm_64_256_axis_1_bfloat16_Gelu_Add"));
+  CHECK(has(plan, "@Gelu_Elementwise_512_256_bfloat16") && has(plan, "@Tanh_Elementwise_512_256_bfloat16"));
   for (const auto& kv : module.graph->funcs) CHECK(kv.second.state == "gpu");
 }
 
@@ -208,7 +210,7 @@ static void test_gather_transpose_graph() {  // test/test.cc:17-23 (the commente
   CHECK(bool(G0) && G0.shape() == (std::vector<int64_t>{3, 2, 9, 6}));
   CHECK(bool(T) && T.shape() == (std::vector<int64_t>{4, 3, 6, 2}));
   const auto& f = graph.data->funcs;
-  CHECK(f.count("Gather_4_9_6_indices_3_2_axis_1") && f.count("Gather_4_9_6_indices_1_axis_1"));
+  CHECK(f.count("Gather_4_9_6_indices_3_2_axis_1") && f.count("Gather_4_9_6_indices_1_axis_1_idx32"));
   CHECK(f.count("Transpose_4_3_2_6"));
   auto module = generator.optimize(graph);
   for (const auto& kv : module.graph->funcs) CHECK(kv.second.state == "gpu");
@@ -232,8 +234,8 @@ static void test_config_candidates_without_autotune() {
   auto Y = graph.create<LayerNorm>(C, gm, gm, int64_t(1), 1e-5f);
   auto module = generator.optimize(graph);
   CHECK(generator.evaluate(module) == 0.0f && generator.bestLatency() == 0.0f);
-  CHECK(module.graph->funcs.at("Matmul_m512n512k256").config.at("CTA_PAIR") == generator.configs("Matmul")->front().at("CTA_PAIR"));
-  CHECK(module.graph->funcs.at("LayerNorm_512_512_axis_1").config.at("WARP_ROW_VECS") == 8);
+  CHECK(module.graph->funcs.at("Matmul_m512n512k256_bfloat16").config.at("CTA_PAIR") == generator.configs("Matmul")->front().at("CTA_PAIR"));
+  CHECK(module.graph->funcs.at("LayerNorm_512_512_axis_1_bfloat16").config.at("WARP_ROW_VECS") == 8);
   auto plan = generator.codegen(module);
   CHECK(has(plan, "CTA_PAIR=1") && has(plan, "WARP_ROW_VECS=8"));   // the choice is part of the saved plan
   (void)Y;
@@ -271,6 +273,97 @@ static void test_errors() {
   auto g2 = rocm.createGraph("x");
   auto m2 = rocm.optimize(g2);
   CHECK(rocm.codegen(m2).empty());
+}
+
+static void test_dtype_is_part_of_the_function_key() {
+  // The reference names functions by operator and shape only; two calls that differ in element
+  // type must still be two functions here (own state, optimizer decision, autotuned config).
+  KernelCodeGenerator generator("CUDA");
+  generator.opts.push_back(std::make_unique<LayerNormOptimizer>());
+  auto graph = generator.createGraph("keys");
+  Value y[2];
+  int i = 0;
+  for (const char* dtype : {"float32", "bfloat16"}) {
+    auto X = graph.create<PlaceHolder>(std::vector<int64_t>{64, 512}, std::string{dtype});
+    auto G = graph.create<PlaceHolder>(std::vector<int64_t>{512}, std::string{dtype});
+    y[i++] = graph.create<LayerNorm>(X, G, G, int64_t(1));
+  }
+  CHECK(bool(y[0]) && bool(y[1]));
+  const auto& f = graph.data->funcs;
+  CHECK(f.size() == 2 && f.count("LayerNorm_64_512_axis_1") && f.count("LayerNorm_64_512_axis_1_bfloat16"));
+  // same shape and type again: the existing function is reused (the reference's dedup)
+  auto X = graph.create<PlaceHolder>(std::vector<int64_t>{64, 512}, std::string{"bfloat16"});
+  auto G = graph.create<PlaceHolder>(std::vector<int64_t>{512}, std::string{"bfloat16"});
+  CHECK(bool(graph.create<LayerNorm>(X, G, G, int64_t(1))) && graph.data->funcs.size() == 2);
+  // a Cast is keyed by both types
+  auto c1 = graph.create<ElementWise>(X, "Cast", MemorySpace::global, "float32");
+  auto c2 = graph.create<ElementWise>(X, "Cast", MemorySpace::global, "float16");
+  CHECK(bool(c1) && bool(c2) && f.count("Cast_Elementwise_64_512_bfloat16_to_float32") &&
+        f.count("Cast_Elementwise_64_512_bfloat16_to_float16"));
+}
+
+static void test_strided_placeholders() {
+  // Q, K, V stored [B,S,H,D] and declared as [B,H,S,D] views; O written into a [B,S,H,D] buffer
+  KernelCodeGenerator generator("CUDA");
+  generator.opts.push_back(std::make_unique<FMHAOptimizer>());
+  generator.opts.push_back(std::make_unique<BatchMatmulOptimizer>());
+  generator.opts.push_back(std::make_unique<SoftmaxOptimizer>());
+  auto graph = generator.createGraph("bshd");
+  const int64_t B = 2, H = 4, S = 256, D = 128;
+  const std::vector<int64_t> shape{B, H, S, D}, bshd{S * H * D, D, H * D, 1};
+  auto Q = graph.create<PlaceHolder>(shape, std::string{"bfloat16"}, bshd);
+  auto K = graph.create<PlaceHolder>(shape, std::string{"bfloat16"}, bshd);
+  auto V = graph.create<PlaceHolder>(shape, std::string{"bfloat16"}, bshd);
+  auto Obuf = graph.create<PlaceHolder>(shape, std::string{"bfloat16"}, bshd);
+  CHECK(bool(Q) && Q.strides() == bshd && !graph.data->tensors[Q.id].dense());
+  auto dense = graph.create<PlaceHolder>(shape, std::string{"bfloat16"}, std::vector<int64_t>{H * S * D, S * D, D, 1});
+  CHECK(bool(dense) && graph.data->tensors[dense.id].dense());       // row-major strides are the default layout
+  CHECK(!graph.create<PlaceHolder>(shape, std::string{"bfloat16"}, std::vector<int64_t>{1, 2, 3}));      // one per dim
+  CHECK(!graph.create<PlaceHolder>(shape, std::string{"bfloat16"}, std::vector<int64_t>{8, 8, 8, 2}));   // innermost 1
+  auto Sc = graph.create<BatchedMatmul>(Q, Layout::rowMajor, K, Layout::colMajor);
+  auto P = graph.create<Softmax>(Sc, -1, MemorySpace::inplace, "", 0.0883883f, true);
+  auto O = graph.create<BatchedMatmul>(P, Layout::rowMajor, V, Layout::rowMajor, "", Obuf);
+  CHECK(bool(O) && O.strides() == bshd && graph.data->root(O.id) == Obuf.id);
+  // every other operator takes dense tensors only
+  CHECK(!graph.create<ElementWise>(Q, "Gelu", MemorySpace::global));
+  CHECK(!graph.create<Binary>(Q, Q, "Add"));
+  // out must be a PlaceHolder of the result's shape and type
+  CHECK(!graph.create<BatchedMatmul>(P, Layout::rowMajor, V, Layout::rowMajor, "", Sc));
+  auto module = generator.optimize(graph);
+  auto plan = generator.codegen(module);
+  CHECK(module.calls.size() == 1 && module.calls[0].entry == "kcg_fmha_fwd");
+  // unfused, the strided operands have no single batch stride: run() must refuse, not mis-address
+  KernelCodeGenerator plain("CUDA");
+  plain.opts.push_back(std::make_unique<BatchMatmulOptimizer>());
+  plain.opts.push_back(std::make_unique<SoftmaxOptimizer>());
+  auto m2 = plain.optimize(graph);
+  CHECK(m2.calls.size() == 3);
+  Bindings bind;
+  int dummy[4];
+  for (int t = 0; t < static_cast<int>(graph.data->tensors.size()); ++t) bind.ptrs[t] = dummy;
+  CHECK(plain.run(m2, bind) == KCG_ERR_UNSUPPORTED);
+}
+
+static void test_shard_spec_validation() {
+  KernelCodeGenerator generator("CUDA");
+  generator.opts.push_back(std::make_unique<ElementWiseOptimizer>());
+  auto graph = generator.createGraph("shard");
+  auto A = graph.create<PlaceHolder>(std::vector<int64_t>{4, 5}, std::string{"float32"});
+  auto C = graph.create<ElementWise>(A, "Gelu", MemorySpace::global);
+  (void)C;
+  auto module = generator.optimize(graph);
+  Bindings bind;
+  ShardSpec bad;
+  bad.world = 2; bad.rank = 2;
+  CHECK(generator.run(module, bind, bad) == KCG_ERR_INVALID_ARG);
+  ShardSpec no_comm;
+  no_comm.world = 2; no_comm.rank = 0; no_comm.gather = true;
+  CHECK(generator.run(module, bind, no_comm) == KCG_ERR_INVALID_ARG);
+  // the C entry refuses bad arguments before it looks for NCCL
+  CHECK(kcg_shard_allgather(nullptr, 8, 4, 1, 2, 0, nullptr, nullptr) == KCG_ERR_INVALID_ARG);
+  CHECK(kcg_shard_allgather(nullptr, 8, 0, 1, 2, 0, nullptr, nullptr) == KCG_ERR_INVALID_ARG);
+  CHECK(kcg_shard_allgather(nullptr, 0, 4, 1, 2, 0, nullptr, nullptr) == KCG_OK);   // nothing to exchange
+  CHECK(kcg_shard_allgather(nullptr, 8, 4, 1, 1, 0, nullptr, nullptr) == KCG_OK);   // one rank
 }
 
 // ---------------------------------------------------------------------------------- gpu mode
@@ -541,12 +634,12 @@ static void gpu_autotune() {  // every candidate timed on the device; any choice
     auto module = generator.optimize(graph);
     if (tuned) {
       CHECK(generator.bestLatency() > 0.0f && generator.bestLatency() < 1e3f);   // a measured time, in ms
-      const auto& cfg = module.graph->funcs.at("LayerNorm_1024_2048_axis_1").config;
+      const auto& cfg = module.graph->funcs.at("LayerNorm_1024_2048_axis_1_bfloat16").config;
       bool known = false;
       for (const auto& cand : *generator.configs("LayerNorm")) known = known || cand == cfg;
       CHECK(known);
       std::printf("autotune kept CTA_PAIR=%d WARP_ROW_VECS=%d, %.4f ms\n",
-                  module.graph->funcs.at("Matmul_m1024n2048k512").config.at("CTA_PAIR"), cfg.at("WARP_ROW_VECS"),
+                  module.graph->funcs.at("Matmul_m1024n2048k512_bfloat16").config.at("CTA_PAIR"), cfg.at("WARP_ROW_VECS"),
                   generator.bestLatency());
     }
     Bindings bind;
@@ -566,8 +659,244 @@ static void gpu_autotune() {  // every candidate timed on the device; any choice
   CHECK(results[0] == results[1]);
 }
 
+static void gpu_fused_attention_bshd() {
+  // The attention benchmark's layout through the graph API: Q, K, V held as [B,S,H,D], O written
+  // as [B,S,H,D], all declared as [B,H,S,D] views with strides; bf16, D = 128, causal, scaled.
+  KernelCodeGenerator generator("CUDA");
+  generator.opts.push_back(std::make_unique<FMHAOptimizer>());
+  auto graph = generator.createGraph("attn_bshd");
+  const int64_t B = 2, H = 4, S = 384, D = 128;
+  const std::vector<int64_t> shape{B, H, S, D}, bshd{S * H * D, D, H * D, 1};
+  auto Q = graph.create<PlaceHolder>(shape, std::string{"bfloat16"}, bshd);
+  auto K = graph.create<PlaceHolder>(shape, std::string{"bfloat16"}, bshd);
+  auto V = graph.create<PlaceHolder>(shape, std::string{"bfloat16"}, bshd);
+  auto Ob = graph.create<PlaceHolder>(shape, std::string{"bfloat16"}, bshd);
+  const float scale = 1.0f / std::sqrt(float(D));
+  auto Sc = graph.create<BatchedMatmul>(Q, Layout::rowMajor, K, Layout::colMajor);
+  auto P = graph.create<Softmax>(Sc, -1, MemorySpace::inplace, "", scale, true);
+  auto O = graph.create<BatchedMatmul>(P, Layout::rowMajor, V, Layout::rowMajor, "", Ob);
+  auto module = generator.optimize(graph);
+  CHECK(bool(O) && module.calls.size() == 1 && module.calls[0].entry == "kcg_fmha_fwd");
+  const size_t n = size_t(B) * H * S * D;
+  auto fq = randn(n, 71), fk = randn(n, 72), fv = randn(n, 73);
+  std::vector<uint16_t> hq(n), hk(n), hv(n);
+  for (size_t i = 0; i < n; ++i) {
+    hq[i] = to_bf16(fq[i]); hk[i] = to_bf16(fk[i]); hv[i] = to_bf16(fv[i]);
+    fq[i] = from_bf16(hq[i]); fk[i] = from_bf16(hk[i]); fv[i] = from_bf16(hv[i]);
+  }
+  Bindings bind;
+  void* dO = upload(nullptr, n * 2);
+  bind.set(Q, upload(hq.data(), n * 2));
+  bind.set(K, upload(hk.data(), n * 2));
+  bind.set(V, upload(hv.data(), n * 2));
+  bind.set(Ob, dO);   // O names Ob's storage
+  CHECK(generator.run(module, bind) == KCG_OK);
+  cudaDeviceSynchronize();
+  CHECK(kcg_device_status() == KCG_OK);
+  std::vector<uint16_t> ho(n);
+  cudaMemcpy(ho.data(), dO, n * 2, 2);
+  std::vector<float> got(n), want(n);
+  for (size_t i = 0; i < n; ++i) got[i] = from_bf16(ho[i]);
+  const int64_t st[3] = {S * H * D, D, H * D};   // (batch, head, sequence) strides of a [B,S,H,D] buffer
+  oracle_attention_f32(fq.data(), fk.data(), fv.data(), want.data(), B, H, S, S, D, scale, 1, st, st, st, st, 0, B * H, 0);
+  CHECK(rel_fro(got, want) <= 1e-2);
+}
+
+// One generator per "rank" on one GPU, no collective: rank r of `world` writes only its block of
+// each output, so running the ranks one after the other on the same full-size buffers must
+// reproduce the unsharded run bit for bit.  This checks every operator's pointer arithmetic.
+static void gpu_sharded_run_matches_unsharded() {
+  const int64_t rows = 1000, cols = 512, n = 384;   // 1000 rows: ragged GEMM blocks (granule 128)
+  auto build = [&](KernelCodeGenerator& generator, Value (&v)[9]) {
+    generator.opts.push_back(std::make_unique<LayerNormOptimizer>());
+    generator.opts.push_back(std::make_unique<ElementWiseOptimizer>());
+    generator.opts.push_back(std::make_unique<BinaryOptimizer>());
+    generator.opts.push_back(std::make_unique<MatmulOptimizer>());
+    generator.opts.push_back(std::make_unique<SoftmaxOptimizer>());
+    auto graph = generator.createGraph("sharded");
+    v[0] = graph.create<PlaceHolder>(std::vector<int64_t>{rows, cols}, std::string{"bfloat16"});   // X
+    v[1] = graph.create<PlaceHolder>(std::vector<int64_t>{cols}, std::string{"bfloat16"});         // gamma / beta / bias
+    v[2] = graph.create<PlaceHolder>(std::vector<int64_t>{cols, n}, std::string{"bfloat16"});      // W
+    v[3] = graph.create<LayerNorm>(v[0], v[1], v[1], int64_t(1));
+    v[4] = graph.create<ElementWise>(v[3], "Gelu", MemorySpace::global);
+    v[5] = graph.create<Binary>(v[4], v[0], "Add");            // same-shape add
+    v[6] = graph.create<Binary>(v[5], v[1], "Mul");            // row-broadcast operand
+    v[7] = graph.create<Matmul>(v[6], v[2]);                   // rows of A and C
+    v[8] = graph.create<Softmax>(v[7]);                        // in place in the GEMM result
+    return graph;
+  };
+  auto hx32 = randn(rows * cols, 81), hg32 = randn(cols, 82, 0.1f, 1.f), hw32 = randn(cols * n, 83, 0.05f);
+  std::vector<uint16_t> hx(hx32.size()), hg(hg32.size()), hw(hw32.size());
+  for (size_t i = 0; i < hx.size(); ++i) hx[i] = to_bf16(hx32[i]);
+  for (size_t i = 0; i < hg.size(); ++i) hg[i] = to_bf16(hg32[i]);
+  for (size_t i = 0; i < hw.size(); ++i) hw[i] = to_bf16(hw32[i]);
+  std::vector<std::vector<uint16_t>> outs;
+  for (int world : {1, 3}) {
+    KernelCodeGenerator generator("CUDA");
+    Value v[9];
+    auto graph = build(generator, v);
+    auto module = generator.optimize(graph);
+    Bindings bind;
+    bind.set(v[0], upload(hx.data(), hx.size() * 2));
+    bind.set(v[1], upload(hg.data(), hg.size() * 2));
+    bind.set(v[2], upload(hw.data(), hw.size() * 2));
+    for (int t = 3; t <= 6; ++t) {
+      void* p = upload(nullptr, rows * cols * 2);
+      kcg_device_memset(p, 0xFF, rows * cols * 2, nullptr);
+      bind.set(v[t], p);
+    }
+    void* dOut = upload(nullptr, rows * n * 2);
+    kcg_device_memset(dOut, 0xFF, rows * n * 2, nullptr);
+    bind.set(v[7], dOut);
+    for (int r = 0; r < world; ++r) {
+      ShardSpec spec;
+      spec.world = world; spec.rank = r;
+      CHECK(generator.run(module, bind, spec) == KCG_OK);
+    }
+    cudaDeviceSynchronize();
+    CHECK(kcg_device_status() == KCG_OK);
+    std::vector<uint16_t> out(rows * n);
+    cudaMemcpy(out.data(), dOut, out.size() * 2, 2);
+    outs.push_back(out);
+  }
+  CHECK(outs[0] == outs[1]);
+  // and the unsharded result is a softmax: rows sum to one
+  double s = 0;
+  for (int64_t j = 0; j < n; ++j) s += from_bf16(outs[0][j]);
+  CHECK(std::fabs(s - 1.0) < 2e-2);
+}
+
+// Two host threads, each with its own generator whose optimizer picked a different GEMM tile
+// (a setting of the calling thread in the kernel library), run at the same time on their own
+// streams: neither may see the other's setting, and both must give the bits of a lone run.
+extern "C" {
+int cudaStreamCreate(void**);
+int cudaStreamSynchronize(void*);
+}
+#include <thread>
+static void gpu_two_generators_two_threads() {
+  const int m = 1024, n = 1024, k = 512;
+  auto hA32 = randn(size_t(m) * k, 91, 0.05f), hB32 = randn(size_t(k) * n, 92);
+  std::vector<uint16_t> hA(hA32.size()), hB(hB32.size());
+  for (size_t i = 0; i < hA.size(); ++i) hA[i] = to_bf16(hA32[i]);
+  for (size_t i = 0; i < hB.size(); ++i) hB[i] = to_bf16(hB32[i]);
+  void* dA = upload(hA.data(), hA.size() * 2);
+  void* dB = upload(hB.data(), hB.size() * 2);
+  std::vector<uint16_t> out[2];
+  int status[2] = {-1, -1};
+  auto worker = [&](int which) {
+    KernelCodeGenerator generator("CUDA");
+    generator.opts.push_back(std::make_unique<MatmulOptimizer>());
+    // thread 0 keeps the first candidate (CTA pairs), thread 1 only has the 128x128 single-CTA tile
+    if (which == 1) {
+      auto* table = generator.configs("Matmul");
+      auto narrow = table->back();
+      table->clear();
+      table->push_back(narrow);
+    }
+    auto graph = generator.createGraph("mt");
+    auto A = graph.create<PlaceHolder>(std::vector<int64_t>{m, k}, std::string{"bfloat16"});
+    auto B = graph.create<PlaceHolder>(std::vector<int64_t>{k, n}, std::string{"bfloat16"});
+    auto C = graph.create<Matmul>(A, B);
+    auto module = generator.optimize(graph);
+    void* stream = nullptr;
+    cudaStreamCreate(&stream);
+    void* dC = upload(nullptr, size_t(m) * n * 2);
+    Bindings bind;
+    bind.set(A, dA); bind.set(B, dB); bind.set(C, dC);
+    int rc = KCG_OK;
+    for (int i = 0; i < 200 && rc == KCG_OK; ++i) rc = generator.run(module, bind, stream);
+    cudaStreamSynchronize(stream);
+    status[which] = rc;
+    out[which].resize(size_t(m) * n);
+    cudaMemcpy(out[which].data(), dC, out[which].size() * 2, 2);
+  };
+  std::thread t0(worker, 0), t1(worker, 1);
+  t0.join();
+  t1.join();
+  CHECK(status[0] == KCG_OK && status[1] == KCG_OK && kcg_device_status() == KCG_OK);
+  CHECK(out[0] == out[1]);   // every tile shape accumulates in the same order
+}
+
+// Run by two (or more) processes, one per GPU: `test_frontend shard <world> <rank> <id file>`.
+// Each builds the same graph, runs it sharded with the in-place NCCL gather after every operator,
+// and compares every rank's full result with an unsharded run on its own GPU, bit for bit.
+extern "C" int cudaSetDevice(int);
+#include <chrono>
+#include <fstream>
+static int shard_main(int world, int rank, const std::string& id_file) {
+  if (cudaSetDevice(rank) != 0) { std::fprintf(stderr, "cudaSetDevice(%d) failed\n", rank); return 2; }
+  unsigned char id[128];
+  if (rank == 0) {
+    if (kcg_nccl_unique_id(id) != KCG_OK) { std::fprintf(stderr, "%s\n", kcg_last_error()); return 2; }
+    std::ofstream w(id_file + ".tmp", std::ios::binary);
+    w.write(reinterpret_cast<const char*>(id), 128);
+    w.close();
+    std::rename((id_file + ".tmp").c_str(), id_file.c_str());
+  } else {
+    bool got = false;
+    for (int i = 0; i < 600 && !got; ++i) {
+      std::ifstream r(id_file, std::ios::binary);
+      if (r && r.read(reinterpret_cast<char*>(id), 128)) got = true;
+      else std::this_thread::sleep_for(std::chrono::milliseconds(100));
+    }
+    if (!got) { std::fprintf(stderr, "rank %d: no NCCL id\n", rank); return 2; }
+  }
+  void* comm = nullptr;
+  if (kcg_nccl_comm_create(world, rank, id, &comm) != KCG_OK) { std::fprintf(stderr, "%s\n", kcg_last_error()); return 2; }
+  const int64_t rows = 1000, cols = 512, n = 384;
+  auto hx32 = randn(rows * cols, 81), hg32 = randn(cols, 82, 0.1f, 1.f), hw32 = randn(cols * n, 83, 0.05f);
+  std::vector<uint16_t> hx(hx32.size()), hg(hg32.size()), hw(hw32.size());
+  for (size_t i = 0; i < hx.size(); ++i) hx[i] = to_bf16(hx32[i]);
+  for (size_t i = 0; i < hg.size(); ++i) hg[i] = to_bf16(hg32[i]);
+  for (size_t i = 0; i < hw.size(); ++i) hw[i] = to_bf16(hw32[i]);
+  std::vector<uint16_t> outs[2];
+  for (int pass = 0; pass < 2; ++pass) {   // 0: unsharded, 1: sharded with gather
+    KernelCodeGenerator generator("CUDA");
+    generator.opts.push_back(std::make_unique<LayerNormOptimizer>());
+    generator.opts.push_back(std::make_unique<MatmulOptimizer>());
+    generator.opts.push_back(std::make_unique<ElementWiseOptimizer>());
+    auto graph = generator.createGraph("sharded");
+    auto X = graph.create<PlaceHolder>(std::vector<int64_t>{rows, cols}, std::string{"bfloat16"});
+    auto G = graph.create<PlaceHolder>(std::vector<int64_t>{cols}, std::string{"bfloat16"});
+    auto W = graph.create<PlaceHolder>(std::vector<int64_t>{cols, n}, std::string{"bfloat16"});
+    auto Y = graph.create<LayerNorm>(X, G, G, int64_t(1));
+    auto C = graph.create<Matmul>(Y, W);              // rows cut in granules of 128: ragged blocks
+    auto Z = graph.create<ElementWise>(C, "Gelu", MemorySpace::global);   // rows cut evenly
+    auto module = generator.optimize(graph);
+    Bindings bind;
+    bind.set(X, upload(hx.data(), hx.size() * 2));
+    bind.set(G, upload(hg.data(), hg.size() * 2));
+    bind.set(W, upload(hw.data(), hw.size() * 2));
+    bind.set(Y, upload(nullptr, rows * cols * 2));
+    bind.set(C, upload(nullptr, rows * n * 2));
+    void* dZ = upload(nullptr, rows * n * 2);
+    kcg_device_memset(dZ, 0xFF, rows * n * 2, nullptr);
+    bind.set(Z, dZ);
+    int rc;
+    if (pass == 0) {
+      rc = generator.run(module, bind);
+    } else {
+      ShardSpec spec;
+      spec.world = world; spec.rank = rank; spec.nccl_comm = comm; spec.gather = true;
+      rc = generator.run(module, bind, spec);
+    }
+    CHECK(rc == KCG_OK);
+    cudaDeviceSynchronize();
+    CHECK(kcg_device_status() == KCG_OK);
+    outs[pass].resize(rows * n);
+    cudaMemcpy(outs[pass].data(), dZ, outs[pass].size() * 2, 2);
+  }
+  CHECK(outs[0] == outs[1]);
+  CHECK(kcg_nccl_comm_destroy(comm) == KCG_OK);
+  if (failures) return 1;
+  std::printf("frontend shard rank %d of %d passed\n", rank, world);
+  return 0;
+}
+
 int main(int argc, char** argv) {
   const std::string mode = argc > 1 ? argv[1] : "cpu";
+  if (mode == "shard" && argc == 5) return shard_main(std::atoi(argv[2]), std::atoi(argv[3]), argv[4]);
   if (mode == "cpu") {
     test_operators_cast();
     test_commented_sequences();
@@ -576,11 +905,17 @@ int main(int argc, char** argv) {
     test_gather_transpose_graph();
     test_config_candidates_without_autotune();
     test_errors();
+    test_dtype_is_part_of_the_function_key();
+    test_strided_placeholders();
+    test_shard_spec_validation();
   } else {
     gpu_matmul_relu();
     gpu_layernorm_gelu_add();
     gpu_kernel_fusion();
     gpu_fused_attention();
+    gpu_fused_attention_bshd();
+    gpu_sharded_run_matches_unsharded();
+    gpu_two_generators_two_threads();
     gpu_gather_transpose();
     gpu_autotune();
   }

@@ -64,3 +64,14 @@ def test_shard_range_partitions(total, world, granule):
 def test_shard_range_rejects_bad_rank(lib):
     b, c = ctypes.c_int64(), ctypes.c_int64()
     assert lib.kcg_shard_range(10, 4, 4, 1, ctypes.byref(b), ctypes.byref(c)) == _lib.ERR_INVALID_ARG
+
+
+def test_shard_allgather_argument_errors_without_device(lib):
+    # refused before NCCL is even looked for
+    assert lib.kcg_shard_allgather(None, 8, 4, 1, 2, 0, None, None) == _lib.ERR_INVALID_ARG
+    assert b"null" in lib.kcg_last_error()
+    assert lib.kcg_shard_allgather(None, 8, 4, 0, 2, 0, None, None) == _lib.ERR_INVALID_ARG
+    assert lib.kcg_shard_allgather(None, 8, 4, 1, 2, 2, None, None) == _lib.ERR_INVALID_ARG
+    assert lib.kcg_shard_allgather(None, 0, 4, 1, 2, 0, None, None) == _lib.OK
+    assert lib.kcg_nccl_comm_create(0, 0, None, None) == _lib.ERR_INVALID_ARG
+    assert lib.kcg_nccl_comm_destroy(None) == _lib.OK

@@ -125,8 +125,8 @@ side = torch.cuda.Stream()
 g1 = torch.cuda.CUDAGraph()
 with torch.cuda.graph(g1, stream=side):
     assert ln(xs, gs, bs, ys) == 0                   # fits the buffer: may be captured
-# 65535 rows of two chunks need more than 1 MiB of statistics
-xb = torch.randn(65535, 8195, device="cuda", dtype=dt); gb = torch.ones(8195, device="cuda", dtype=dt); bb = torch.zeros_like(gb)
+# 65535 rows of three chunks need more than 1 MiB of statistics
+xb = torch.randn(65535, 16387, device="cuda", dtype=dt); gb = torch.ones(16387, device="cuda", dtype=dt); bb = torch.zeros_like(gb)
 yb = torch.empty_like(xb)
 g2 = torch.cuda.CUDAGraph()
 with torch.cuda.graph(g2, stream=side):
@@ -136,7 +136,7 @@ with torch.cuda.graph(g2, stream=side):
 assert rc == _lib.ERR_UNSUPPORTED and "captured" in msg, (rc, msg)
 assert ln(xb, gb, bb, yb) == 0                       # outside a capture the buffer grows
 torch.cuda.synchronize()
-ref = torch.nn.functional.layer_norm(xb[:64].float(), (8195,), gb.float(), bb.float(), 1e-5)
+ref = torch.nn.functional.layer_norm(xb[:64].float(), (16387,), gb.float(), bb.float(), 1e-5)
 assert (yb[:64].float() - ref).norm() / ref.norm() < 1e-2
 # the graph captured before the growth still names the old buffer, which must still exist
 ys.zero_()

@@ -58,6 +58,32 @@ def _worker(rank, world, port, results):
             ok = ok and torch.equal(out, ops.fmha(Q, K, V, 128 ** -0.5, True))
         finally:
             fb.close()
+        # the C entry a host program without Python uses: an NCCL communicator made through the
+        # library's own wrappers (the id travels by other means, here torch's object broadcast),
+        # then the in-place gather of a row-sharded buffer, with even and with ragged blocks
+        import ctypes
+        lib = _lib.load()
+        uid = ctypes.create_string_buffer(128)
+        if rank == 0:
+            _lib.check(lib.kcg_nccl_unique_id(uid), "kcg_nccl_unique_id")
+        box = [bytes(uid.raw)]
+        dist.broadcast_object_list(box, src=0)
+        comm = ctypes.c_void_p()
+        _lib.check(lib.kcg_nccl_comm_create(world, rank, ctypes.create_string_buffer(box[0], 128), ctypes.byref(comm)),
+                   "kcg_nccl_comm_create")
+        stream = torch.cuda.current_stream().cuda_stream
+        for total, granule in ((4096, 1), (1000, 128)):
+            want = torch.arange(total * 64, device="cuda", dtype=torch.float32).view(total, 64)
+            buf = torch.full_like(want, -1.0)
+            b1, c1 = _lib.shard_range(total, world, rank, granule)
+            buf[b1:b1 + c1] = want[b1:b1 + c1]
+            _lib.check(lib.kcg_shard_allgather(buf.data_ptr(), total, 64 * 4, granule, world, rank, comm, stream),
+                       "kcg_shard_allgather")
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(buf, want)
+        # a communicator of another size is refused
+        ok = ok and lib.kcg_shard_allgather(buf.data_ptr(), 16, 4, 1, world + 1, rank, comm, stream) == _lib.ERR_INVALID_ARG
+        _lib.check(lib.kcg_nccl_comm_destroy(comm), "kcg_nccl_comm_destroy")
         torch.cuda.synchronize()
         ok = ok and _lib.device_status() == 0
         results[rank] = bool(ok)
