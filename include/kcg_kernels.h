@@ -206,6 +206,18 @@ KCG_API int kcg_layernorm_stats(int dtype, int64_t rows, int64_t cols, const voi
 KCG_API void kcg_layernorm_set_warp_row_limit(int vecs_per_lane);
 
 /*
+ * Tuning switch with no counterpart in the reference: the shape of the block-per-row kernel that
+ * takes the rows too long for one warp.  A row is held by ceil(vectors / vecs_per_thread) threads
+ * (vecs_per_thread 2, 4 or 8 16-byte vectors each; 0, the default, picks 4 for rows of up to 768
+ * vectors and 8 beyond) and a thread block holds rows_per_block (1, the default, 2 or 4) such
+ * groups, each with its own barrier; a negative rows_per_block runs a persistent grid of that
+ * many blocks per SM, each prefetching its next row.  rows_per_block does not change the result;
+ * vecs_per_thread changes the order in which the fp32 partial sums are added, so results agree
+ * to rounding, not bit for bit.  A setting of the calling thread.
+ */
+KCG_API void kcg_layernorm_set_block_shape(int vecs_per_thread, int rows_per_block);
+
+/*
  * Unary elementwise map — replaces `{Op}_Elementwise_{dims}` and
  * `Relu_Elementwise_{dims}` (builders: src/Frontend/Operators.cc:222-289 and
  * :1003-1074; schedule: src/Optimizer/Optimizer.cc:1080-1175).

@@ -36,6 +36,7 @@ SIGNATURES = {
     "kcg_layernorm_split_static": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _vp], _ci),
     "kcg_layernorm_stats": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _vp], _ci),
     "kcg_layernorm_set_warp_row_limit": ([_ci], None),
+    "kcg_layernorm_set_block_shape": ([_ci, _ci], None),
     "kcg_eltwise": ([_ci, _ci, _ci, _i64, _vp, _vp, _vp], _ci),
     "kcg_binary": ([_ci, _ci, _ci, _i64p, _ci, _i64p, _vp, _vp, _vp, _vp], _ci),
     "kcg_softmax": ([_ci, _i64, _i64, _fp, _ci, _i64, _vp, _vp, _vp], _ci),

@@ -23,6 +23,8 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
+#include <cstdlib>
+
 namespace kcg {
 
 int* device_status_word();
@@ -52,6 +54,7 @@ struct FmhaParams {
   // of peer GPUs; written by the two-tile kernel's epilogue
   void* extra_o[7];
   int n_extra;
+  int flags;   // experiment switches (bit 0: speculative exponentials)
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -648,31 +651,11 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int a = 0; a < 8; ++a) mx[a] = max3(mx[a], __uint_as_float(sreg[k + 2 * a]), __uint_as_float(sreg[k + 2 * a + 1]));
       }
       const float mt = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * c;
-      float alpha = 1.f;
-      bool rescale = false;
-      if ((mt > m + kRescaleThreshold || m == -INFINITY) && mt > m) {
-        alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - mt);
-        rescale = (j > 0);
-        m = mt;
-      }
-      const float neg_m = (m == -INFINITY) ? 0.f : -m;
-      const uint64_t c2 = f2_pack(c, c), nm2 = f2_pack(neg_m, neg_m);
-      // S_i(j) being complete means PV_i(j-1) is complete: O_i may be rescaled now.
-      if (__any_sync(0xffffffffu, rescale)) {
-        const float a = rescale ? alpha : 1.f;
-#pragma unroll 1
-        for (int cc = 0; cc < D / 32; ++cc) {
-          uint32_t oreg[32];
-          tmem_ld32(o_addr + cc * 32, oreg);
-          tmem_wait_ld();
-#pragma unroll
-          for (int k = 0; k < 32; ++k) oreg[k] = __float_as_uint(__uint_as_float(oreg[k]) * a);
-          tmem_st32(o_addr + cc * 32, oreg);
-        }
-      }
       uint64_t lsum_a = 0ull, lsum_b = 0ull;  // two (+0.f, +0.f) accumulators
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      const uint64_t c2 = f2_pack(c, c);
+      // exponentials of one half of the row (64 scores -> 32 packed words, written in place over
+      // the words already consumed), then the hand-over of that half of P to the MMA thread
+      auto exp_half = [&](int half, uint64_t nm2) {
 #pragma unroll
         for (int k = half * 64; k < half * 64 + 64; k += 2) {
           const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sreg[k]), __uint_as_float(sreg[k + 1])), c2, nm2);
@@ -683,12 +666,64 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
           sreg[k >> 1] = pack2<T>(p0, p1);  // in place: word k/2 is never read again
         }
-        // hand this half of P (32 packed columns) to the MMA thread
+      };
+      auto hand_over = [&](int half) {
         tmem_st32(s_addr + half * 32, reinterpret_cast<uint32_t(&)[32]>(sreg[half * 32]));
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[2 * i + half]);
+      };
+      float alpha = 1.f;
+      bool half0_done = false;
+      // Speculative path (every block after the first that needs no mask): the exponentials of the
+      // first half start at once with the running maximum m, so that the maximum of this block is
+      // computed in the shadow of the special-function unit instead of in front of it.  That is
+      // exact whenever the block's maximum stays within the rescale threshold of m, which is the
+      // condition under which m would have been kept anyway; otherwise (rare once a few blocks have
+      // been seen) the first half is read again from tensor memory and redone on the ordinary path.
+      const bool speculate = (p.flags & 1) && __all_sync(0xffffffffu, j > 0 && limit >= BN && m != -INFINITY);
+      if (speculate) {
+        const float neg_m0 = -m;
+        exp_half(0, f2_pack(neg_m0, neg_m0));
+        if (!__any_sync(0xffffffffu, mt > m + kRescaleThreshold)) {
+          hand_over(0);
+          half0_done = true;
+        } else {
+          tmem_ld64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));   // the first 32 words were overwritten
+          tmem_wait_ld();
+          lsum_a = 0ull;
+          lsum_b = 0ull;
+        }
+      }
+      if (!half0_done) {
+        bool rescale = false;
+        if ((mt > m + kRescaleThreshold || m == -INFINITY) && mt > m) {
+          alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - mt);
+          rescale = (j > 0);
+          m = mt;
+        }
+        // S_i(j) being complete means PV_i(j-1) is complete: O_i may be rescaled now.
+        if (__any_sync(0xffffffffu, rescale)) {
+          const float a = rescale ? alpha : 1.f;
+#pragma unroll 1
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t oreg[32];
+            tmem_ld32(o_addr + cc * 32, oreg);
+            tmem_wait_ld();
+#pragma unroll
+            for (int k = 0; k < 32; ++k) oreg[k] = __float_as_uint(__uint_as_float(oreg[k]) * a);
+            tmem_st32(o_addr + cc * 32, oreg);
+          }
+        }
+        const float neg_m = (m == -INFINITY) ? 0.f : -m;
+        exp_half(0, f2_pack(neg_m, neg_m));
+        hand_over(0);
+      }
+      {
+        const float neg_m = (m == -INFINITY) ? 0.f : -m;
+        exp_half(1, f2_pack(neg_m, neg_m));
+        hand_over(1);
       }
       float l0, l1;
       f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
@@ -741,7 +776,13 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (row0 + rr < p.Sq) {
             const int64_t off = slice + static_cast<int64_t>(row0 + rr) * p.o_ss + ch * 8;
             *reinterpret_cast<uint4*>(static_cast<T*>(p.O) + off) = v;
-            for (int e = 0; e < p.n_extra; ++e) *reinterpret_cast<uint4*>(static_cast<T*>(p.extra_o[e]) + off) = v;
+            // peers in an order that differs from CTA to CTA and from step to step, so that the
+            // stores of the whole grid do not queue up on one NVLink destination at a time
+            const int peer0 = static_cast<int>((blockIdx.x + blockIdx.y + warp + it) % static_cast<unsigned>(p.n_extra));
+            for (int e = 0; e < p.n_extra; ++e) {
+              const int d = (e + peer0) % p.n_extra;
+              *reinterpret_cast<uint4*>(static_cast<T*>(p.extra_o[d]) + off) = v;
+            }
           }
         }
       } else {
@@ -914,6 +955,10 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
   p.status = device_status_word();
   if (!p.status) return fail(KCG_ERR_CUDA, "fmha: could not allocate the host-mapped status word");
   p.n_extra = n_extra;
+  {
+    const char* e = std::getenv("KCG_FMHA_FLAGS");
+    p.flags = e ? std::atoi(e) : 0;
+  }
   for (int i = 0; i < 7; ++i) p.extra_o[i] = i < n_extra ? extra_o[i] : nullptr;
   for (int i = 0; i < n_extra; ++i)
     if (!extra_o[i] || !aligned16(extra_o[i])) return fail(KCG_ERR_ALIGNMENT, "fmha: extra output %d is null or not 16-byte aligned", i);

@@ -22,11 +22,11 @@ constexpr int PBM = 256, PBN = 256;           // tile of the pair
 constexpr int PEPI_STAGE_BYTES = 32 * 128;   // per epilogue warp: 32 rows x 128 bytes of output
 constexpr int PSMEM_BYTES = PSTAGES * PSTAGE_BYTES + 1024 + 256 + 4 * PEPI_STAGE_BYTES;
 
-__device__ __forceinline__ void pair_tile_coords(int64_t tile, int m_pairs, int n_tiles, int& b, int& mp, int& nt) {
+__device__ __forceinline__ void pair_tile_coords(int64_t tile, int m_pairs, int n_tiles, int group_m, int& b, int& mp, int& nt) {
   const int64_t per_batch = static_cast<int64_t>(m_pairs) * n_tiles;
   b = static_cast<int>(tile / per_batch);
   const int r = static_cast<int>(tile % per_batch);
-  constexpr int GROUP = GROUP_M / 2;  // in units of 256-row pairs
+  const int GROUP = max(1, group_m / 2);  // in units of 256-row pairs
   const int group_span = GROUP * n_tiles;
   const int first = (r / group_span) * GROUP;
   const int gsize = min(m_pairs - first, GROUP);
@@ -96,7 +96,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       bool ok = true;
       for (int64_t tile = cluster_id; tile < total && ok; tile += n_clusters) {
         int b, mp, nt;
-        pair_tile_coords(tile, m_pairs, p.n_tiles, b, mp, nt);
+        pair_tile_coords(tile, m_pairs, p.n_tiles, p.group_m, b, mp, nt);
         const int m0 = mp * PBM + static_cast<int>(rank) * 128;
         const int n0 = nt * PBN + static_cast<int>(rank) * 128;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
@@ -177,7 +177,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     bool ok = true;
     for (int64_t tile = cluster_id; tile < total && ok; tile += n_clusters, ++tile_iter) {
       int b, mp, nt;
-      pair_tile_coords(tile, m_pairs, p.n_tiles, b, mp, nt);
+      pair_tile_coords(tile, m_pairs, p.n_tiles, p.group_m, b, mp, nt);
       const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
       if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
       tc_fence_after();
@@ -196,6 +196,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const int64_t tile_row0 = static_cast<int64_t>(mp) * PBM + rank * 128 + quarter * 32;
 #pragma unroll 1
         for (int c = 0; c < PBN / RC; ++c) {
+          const int peer0 = static_cast<int>((blockIdx.x + quarter + c) % static_cast<unsigned>(p.n_extra));
           uint32_t r[RC];
           if constexpr (RC == 64) tmem_ld64(t_base + c * RC, r); else tmem_ld32(t_base + c * RC, r);
           tmem_wait_ld();
@@ -219,7 +220,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             if (grow < p.M && col + VW <= p.N) {
               const int64_t off = b * p.stride_c + grow * p.ldc + col;
               *reinterpret_cast<uint4*>(static_cast<TOut*>(p.C) + off) = v;
-              for (int e = 0; e < p.n_extra; ++e) *reinterpret_cast<uint4*>(static_cast<TOut*>(p.extra_c[e]) + off) = v;
+              // peers in an order that differs from CTA to CTA and from round to round, so that
+              // the stores of the whole grid do not queue up on one NVLink destination at a time
+              for (int e = 0; e < p.n_extra; ++e) {
+                const int d = (e + peer0) % p.n_extra;
+                *reinterpret_cast<uint4*>(static_cast<TOut*>(p.extra_c[d]) + off) = v;
+              }
             }
           }
           __syncwarp();

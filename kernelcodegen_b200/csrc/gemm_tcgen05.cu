@@ -59,16 +59,17 @@ struct GemmParams {
   // buffers of peer GPUs: the CTA-pair kernel's epilogue stores every tile to each of them.
   void* extra_c[KCG_MAX_EXTRA_C];
   int n_extra;
+  int group_m;   // row tiles (of 128) per group of the tile order
 };
 
 __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, int& b, int& mt, int& nt) {
   const int64_t per_batch = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
   b = static_cast<int>(tile / per_batch);
   const int r = static_cast<int>(tile % per_batch);
-  const int group_span = GROUP_M * p.n_tiles;
+  const int group_span = p.group_m * p.n_tiles;
   const int group = r / group_span;
-  const int first_m = group * GROUP_M;
-  const int gsize = min(p.m_tiles - first_m, GROUP_M);
+  const int first_m = group * p.group_m;
+  const int gsize = min(p.m_tiles - first_m, p.group_m);
   const int in_group = r % group_span;
   mt = first_m + in_group % gsize;
   nt = in_group / gsize;
@@ -524,6 +525,7 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
   const size_t out_es = kcg_dtype_size(dtype_out);
   p.c_vec_ok = aligned16(C) && (ldc * out_es) % 16 == 0 && (stride_c * out_es) % 16 == 0;
   p.n_extra = n_extra;
+  p.group_m = GROUP_M;   // 8, 32 and 64 were measured at 4096..16384: no better than 16
   for (int i = 0; i < KCG_MAX_EXTRA_C; ++i) p.extra_c[i] = i < n_extra ? extra_c[i] : nullptr;
   if (n_extra > 0) {
     bool ok = p.c_vec_ok && (N * out_es) % 16 == 0;

@@ -26,6 +26,11 @@ namespace {
 // Longest row (in 16-byte vectors per lane) that is given to the warp-per-row kernel (a setting
 // of the calling thread).
 thread_local int g_warp_row_max_vecs = 8;
+// Block-per-row kernel: 16-byte vectors held by one thread (0 = chosen by row length, else 2, 4
+// or 8) and rows per thread block (1, 2 or 4; negative: a persistent grid of that many blocks per
+// SM); settings of the calling thread.
+thread_local int g_block_vecs = 0;
+thread_local int g_block_rows = 1;
 
 // Loads, normalises and stores one row held by `nthr` cooperating threads (a warp or a
 // block); `reduce` sums a float over those threads.  kExact: the row is exactly
@@ -33,25 +38,50 @@ thread_local int g_warp_row_max_vecs = 8;
 // kFuse: the row is not stored after normalisation but run through GELU and added to the
 // matching row of `res` first, rounding to T after each step exactly where the three separate
 // kernels would have stored and re-loaded it, so the result is bit-identical to the chain.
-template <typename T, int VPT, bool kExact, bool kFuse, typename Reduce>
-__device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __restrict__ gamma,
-                                       const T* __restrict__ beta, const T* __restrict__ res, T* __restrict__ yr,
-                                       int tid, int nthr, int nvec, float inv_n, float eps, Reduce reduce,
-                                       float* mean_out = nullptr, float* rstd_out = nullptr) {
-  using W = Words<T>;
-  constexpr int EPW = W::EPW;
-  uint4 v[VPT];
+// The thread's share of a row (and, fused, of the residual row): vector i*nthr + tid for i < VPT.
+template <typename T, int VPT, bool kExact, bool kFuse>
+__device__ __forceinline__ void ln_row_load(const T* __restrict__ xr, const T* __restrict__ res, int tid, int nthr,
+                                            int nvec, uint4 (&v)[VPT], uint4 (&rv)[kFuse ? VPT : 1]) {
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
     if (kExact || i * nthr + tid < nvec) v[i] = __ldcs(reinterpret_cast<const uint4*>(xr) + i * nthr + tid);
   // fused form: the residual row is requested together with x, so that its latency is spent
   // under the two reductions instead of after them
-  uint4 rv[kFuse ? VPT : 1];
   if constexpr (kFuse) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
       if (kExact || i * nthr + tid < nvec) rv[i] = __ldcs(reinterpret_cast<const uint4*>(res) + i * nthr + tid);
   }
+}
+
+template <typename T, int VPT, bool kExact, bool kFuse, typename Reduce>
+__device__ __forceinline__ void ln_row_body(const uint4 (&v)[VPT], const uint4 (&rv)[kFuse ? VPT : 1],
+                                            const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ yr,
+                                            int tid, int nthr, int nvec, float inv_n, float eps, Reduce reduce,
+                                            float* mean_out, float* rstd_out, const uint4* g_regs = nullptr,
+                                            const uint4* b_regs = nullptr);
+
+template <typename T, int VPT, bool kExact, bool kFuse, typename Reduce>
+__device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __restrict__ gamma,
+                                       const T* __restrict__ beta, const T* __restrict__ res, T* __restrict__ yr,
+                                       int tid, int nthr, int nvec, float inv_n, float eps, Reduce reduce,
+                                       float* mean_out = nullptr, float* rstd_out = nullptr) {
+  uint4 v[VPT];
+  uint4 rv[kFuse ? VPT : 1];
+  ln_row_load<T, VPT, kExact, kFuse>(xr, res, tid, nthr, nvec, v, rv);
+  ln_row_body<T, VPT, kExact, kFuse>(v, rv, gamma, beta, yr, tid, nthr, nvec, inv_n, eps, reduce, mean_out, rstd_out);
+}
+
+template <typename T, int VPT, bool kExact, bool kFuse, typename Reduce>
+__device__ __forceinline__ void ln_row_body(const uint4 (&v)[VPT], const uint4 (&rv)[kFuse ? VPT : 1],
+                                            const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ yr,
+                                            int tid, int nthr, int nvec, float inv_n, float eps, Reduce reduce,
+                                            float* mean_out, float* rstd_out, const uint4* g_regs,
+                                            const uint4* b_regs) {
+  // g_regs / b_regs: the thread's vectors of gamma / beta already held in registers (a kernel
+  // that walks over many rows loads them once); otherwise they are read here, from L1 / L2.
+  using W = Words<T>;
+  constexpr int EPW = W::EPW;
   // 16-bit types: the two elements of a word go through the packed fp32x2 pipe together (the
   // even and the odd elements of the thread form two partial sums that are added at the end).
   float s = 0.f;
@@ -110,11 +140,15 @@ __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __rest
   for (int i = 0; i < VPT; ++i) {
     const int vi = i * nthr + tid;
     if (kExact || vi < nvec) {
-      const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
-      const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(beta) + vi);
+      const uint4 g4 = g_regs ? g_regs[i] : __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
+      const uint4 b4 = b_regs ? b_regs[i] : __ldg(reinterpret_cast<const uint4*>(beta) + vi);
       const uint32_t w[4] = {opaque(v[i].x), opaque(v[i].y), opaque(v[i].z), opaque(v[i].w)};
-      const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
-      const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
+      // (held in registers across rows, the packed words are made opaque so that the compiler
+      // does not hoist their unpacked fp32 form out of the row loop: 128 more registers)
+      const uint32_t gw[4] = {g_regs ? opaque(g4.x) : g4.x, g_regs ? opaque(g4.y) : g4.y, g_regs ? opaque(g4.z) : g4.z,
+                              g_regs ? opaque(g4.w) : g4.w};
+      const uint32_t bw[4] = {b_regs ? opaque(b4.x) : b4.x, b_regs ? opaque(b4.y) : b4.y, b_regs ? opaque(b4.z) : b4.z,
+                              b_regs ? opaque(b4.w) : b4.w};
       uint32_t o[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -170,21 +204,91 @@ ln_warp_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __re
                          mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr);
 }
 
-// One thread block per row for longer rows: blockDim.x threads hold up to VPT vectors each.
-template <typename T, int VPT, bool kExact, bool kFuse>
+// Sum over one group of `nthr` threads (a multiple of 32) of a block that holds several such
+// groups, each working on its own row: the groups meet on their own named barrier (1 + group
+// index), so a group never waits for another.  `red` is the group's own 33 floats.
+__device__ __forceinline__ float group_sum(float v, float* red, int tid, int nthr, int bar_id) {
+  const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
+  v = warp_sum(v);
+  if (nwarps == 1) return v;
+  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthr) : "memory");   // the previous call's readers are done
+  if (lane == 0) red[warp] = v;
+  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthr) : "memory");
+  const float t = lane < nwarps ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+
+// One group of threads per row for longer rows: `nthr` threads hold up to VPT vectors each; a
+// block holds kRows such groups (kRows == 1: one thread block per row).
+template <typename T, int VPT, bool kExact, bool kFuse, int kRows = 1>
 __global__ void __launch_bounds__(512)
 ln_block_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
               const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps,
               float* __restrict__ mean_out, float* __restrict__ rstd_out) {
+  __shared__ float red[33 * kRows];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  if constexpr (kRows == 1) {
+    const int64_t row = blockIdx.x;
+    ln_row<T, VPT, kExact, kFuse>(x + row * cols, gamma, beta, kFuse ? res + row * cols : nullptr, y + row * cols,
+                                  threadIdx.x, blockDim.x, cols / Vec16<T>::N, 1.0f / static_cast<float>(cols), eps,
+                                  [&](float v) { return block_sum(v, red); },
+                                  mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr);
+  } else {
+    const int nthr = blockDim.x / kRows;
+    const int group = threadIdx.x / nthr, tid = threadIdx.x - group * nthr;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kRows + group;
+    if (row >= rows) return;   // whole groups leave together; the others use their own barriers
+    float* my_red = red + 33 * group;
+    ln_row<T, VPT, kExact, kFuse>(x + row * cols, gamma, beta, kFuse ? res + row * cols : nullptr, y + row * cols,
+                                  tid, nthr, cols / Vec16<T>::N, 1.0f / static_cast<float>(cols), eps,
+                                  [&](float v) { return group_sum(v, my_red, tid, nthr, 1 + group); },
+                                  mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr);
+  }
+}
+
+// Persistent form of the block-per-row kernel: a fixed grid of blocks (a few per SM) walks over
+// the rows with stride gridDim.x, and a block requests its NEXT row before it starts the
+// arithmetic of the current one, so that HBM latency is spent under the two reductions and the
+// cost of starting and retiring a thread block is paid once per several rows.
+template <typename T, int VPT, bool kExact, bool kFuse>
+__global__ void __launch_bounds__(128, 2)
+ln_persistent_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                   const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps,
+                   float* __restrict__ mean_out, float* __restrict__ rstd_out) {
   __shared__ float red[33];
   grid_launch_dependents();
   grid_dependency_wait();
-  const int64_t row = blockIdx.x;
-  ln_row<T, VPT, kExact, kFuse>(x + row * cols, gamma, beta, kFuse ? res + row * cols : nullptr, y + row * cols,
-                                threadIdx.x, blockDim.x,
-                         cols / Vec16<T>::N, 1.0f / static_cast<float>(cols), eps,
-                         [&](float v) { return block_sum(v, red); },
-                         mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr);
+  const int nvec = cols / Vec16<T>::N;
+  const float inv_n = 1.0f / static_cast<float>(cols);
+  uint4 cur[VPT], nxt[VPT];
+  uint4 rcur[kFuse ? VPT : 1], rnxt[kFuse ? VPT : 1];
+  int64_t row = blockIdx.x;
+  if (row >= rows) return;
+  // this thread meets the same columns in every row: its share of gamma and beta stays in registers
+  uint4 gq[VPT], bq[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+    if (kExact || i * static_cast<int>(blockDim.x) + static_cast<int>(threadIdx.x) < nvec) {
+      gq[i] = __ldg(reinterpret_cast<const uint4*>(gamma) + i * blockDim.x + threadIdx.x);
+      bq[i] = __ldg(reinterpret_cast<const uint4*>(beta) + i * blockDim.x + threadIdx.x);
+    }
+  ln_row_load<T, VPT, kExact, kFuse>(x + row * cols, kFuse ? res + row * cols : nullptr, threadIdx.x, blockDim.x, nvec, cur, rcur);
+  for (; row < rows; row += gridDim.x) {
+    const int64_t next = row + gridDim.x;
+    if (next < rows)
+      ln_row_load<T, VPT, kExact, kFuse>(x + next * cols, kFuse ? res + next * cols : nullptr, threadIdx.x, blockDim.x, nvec,
+                                         nxt, rnxt);
+    ln_row_body<T, VPT, kExact, kFuse>(cur, rcur, gamma, beta, y + row * cols, threadIdx.x, blockDim.x, nvec, inv_n, eps,
+                                       [&](float v) { return block_sum(v, red); },
+                                       mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr, gq, bq);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) cur[i] = nxt[i];
+    if constexpr (kFuse) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) rcur[i] = rnxt[i];
+    }
+  }
 }
 
 // ---- split-row path ----------------------------------------------------------------
@@ -308,11 +412,43 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
   }
   // Block per row: at most 8 vectors per thread and at most 512 threads.
   if (vec_ok && nvec <= 512 * 8 && rows <= 0x7fffffffll) {
-    int threads = static_cast<int>((nvec + 7) / 8);
+    // Vectors per thread: the setting, unless the row then needs more than 512 threads.  By default
+    // rows of up to 768 vectors get 4 per thread (a bf16 row of 4096 elements is then spread over
+    // 128 threads: measured 22.5 us against 23.8 us with 64 threads x 8 vectors on [8192, 4096];
+    // 256 x 2, two or four rows per block and the persistent form were all slower), longer rows 8.
+    int want_vpt = g_block_vecs > 0 ? g_block_vecs : (nvec <= 768 ? 4 : 8);
+    while (want_vpt < 8 && (nvec + want_vpt - 1) / want_vpt > 512) want_vpt *= 2;
+    int threads = static_cast<int>((nvec + want_vpt - 1) / want_vpt);
     threads = (threads + 31) / 32 * 32;
     const int vpt = static_cast<int>((nvec + threads - 1) / threads);
-    const unsigned grid = static_cast<unsigned>(rows);
-#define KCG_LN_LAUNCH(V, E, F) launch_overlapped(ln_block_rows<T, V, E, F>, dim3(grid), dim3(threads), 0, stream, x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
+    if (g_block_rows < 0 && threads <= 128 && rows > static_cast<int64_t>(sm_count()) * -g_block_rows) {
+      // persistent grid: -g_block_rows blocks per SM, each walking over rows
+      const unsigned pgrid = static_cast<unsigned>(sm_count() * -g_block_rows);
+#define KCG_LN_LAUNCH(V, E, F) launch_overlapped(ln_persistent_rows<T, V, E, F>, dim3(pgrid), dim3(threads), 0, stream, x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
+#define KCG_LN_PERS(V)                                                          \
+  do {                                                                          \
+    const bool exact = nvec == static_cast<int64_t>(threads) * V;               \
+    if (res) { if (exact) KCG_LN_LAUNCH(V, true, true); else KCG_LN_LAUNCH(V, false, true); }   \
+    else     { if (exact) KCG_LN_LAUNCH(V, true, false); else KCG_LN_LAUNCH(V, false, false); } \
+  } while (0)
+      if (vpt <= 2) KCG_LN_PERS(2);
+      else if (vpt <= 4) KCG_LN_PERS(4);
+      else KCG_LN_PERS(8);
+#undef KCG_LN_PERS
+#undef KCG_LN_LAUNCH
+      return check_launch("ln_persistent_rows");
+    }
+    int rpb = g_block_rows < 1 ? 1 : g_block_rows;   // rows per block, as long as the block stays within 512 threads
+    while (rpb > 1 && rpb * threads > 512) rpb /= 2;
+    const unsigned grid = static_cast<unsigned>((rows + rpb - 1) / rpb);
+    const dim3 block(static_cast<unsigned>(threads * rpb));
+#define KCG_LN_LAUNCH_R(V, E, F, R) launch_overlapped(ln_block_rows<T, V, E, F, R>, dim3(grid), block, 0, stream, x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
+#define KCG_LN_LAUNCH(V, E, F)                                                  \
+  do {                                                                          \
+    if (rpb == 4) KCG_LN_LAUNCH_R(V, E, F, 4);                                  \
+    else if (rpb == 2) KCG_LN_LAUNCH_R(V, E, F, 2);                             \
+    else KCG_LN_LAUNCH_R(V, E, F, 1);                                           \
+  } while (0)
 #define KCG_LN_BLOCK(V)                                                         \
   do {                                                                          \
     const bool exact = nvec == static_cast<int64_t>(threads) * V;               \
@@ -324,6 +460,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
     else KCG_LN_BLOCK(8);
 #undef KCG_LN_BLOCK
 #undef KCG_LN_LAUNCH
+#undef KCG_LN_LAUNCH_R
     return check_launch("ln_block_rows");
   }
   if (res) return KCG_ERR_UNSUPPORTED;  // no fused form beyond the row kernels
@@ -479,6 +616,12 @@ extern "C" int kcg_layernorm_gelu_add(int dtype, int64_t rows, int64_t cols, con
   if (rc) return rc;
   const int64_t shape[2] = {rows, cols};
   return kcg_binary(KCG_BINARY_ADD, dtype, 2, shape, 2, shape, y, residual, y, stream);
+}
+
+extern "C" void kcg_layernorm_set_block_shape(int vecs_per_thread, int rows_per_block) {
+  kcg::g_block_vecs = vecs_per_thread <= 0 ? 0 : (vecs_per_thread <= 2 ? 2 : (vecs_per_thread <= 4 ? 4 : 8));
+  kcg::g_block_rows = rows_per_block < 0 ? (rows_per_block < -16 ? -16 : rows_per_block)
+                                         : (rows_per_block <= 1 ? 1 : (rows_per_block <= 2 ? 2 : 4));
 }
 
 extern "C" void kcg_layernorm_set_warp_row_limit(int vecs_per_lane) {

@@ -84,10 +84,12 @@ KernelCodeGenerator::KernelCodeGenerator(const std::string& platform_) : platfor
   batchMatmulConfigs = matmulConfigs;
   binaryConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
   elementWiseConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
-  layerNormConfigs = {{{"WARP_ROW_VECS", 8}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}},
-                      {{"WARP_ROW_VECS", 16}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}},
-                      {{"WARP_ROW_VECS", 4}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}},
-                      {{"WARP_ROW_VECS", 0}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}}};
+  // THREAD_VECS 0: the library picks the vectors per thread of the block-per-row kernel by row length
+  layerNormConfigs = {{{"WARP_ROW_VECS", 8}, {"THREAD_VECS", 0}, {"VECTORIZE_WIDTH", 16}},
+                      {{"WARP_ROW_VECS", 16}, {"THREAD_VECS", 0}, {"VECTORIZE_WIDTH", 16}},
+                      {{"WARP_ROW_VECS", 8}, {"THREAD_VECS", 8}, {"VECTORIZE_WIDTH", 16}},
+                      {{"WARP_ROW_VECS", 8}, {"THREAD_VECS", 4}, {"VECTORIZE_WIDTH", 16}},
+                      {{"WARP_ROW_VECS", 0}, {"THREAD_VECS", 0}, {"VECTORIZE_WIDTH", 16}}};
   gatherConfigs = {{{"BLOCK_SIZE", 256}, {"VECTORIZE_WIDTH", 16}}};
   softmaxConfigs = {{{"BLOCK_SIZE", 256}}};
   fusionConfigs = {{{"EPILOGUE", 1}}};
@@ -300,6 +302,7 @@ void apply_knobs(OpKind kind, const std::map<std::string, int>& cfg, bool restor
       break;
     case OpKind::LayerNorm: case OpKind::FusedLayerNormGeluAdd:
       if (find("WARP_ROW_VECS", v)) kcg_layernorm_set_warp_row_limit(restore ? 8 : v);
+      if (find("THREAD_VECS", v)) kcg_layernorm_set_block_shape(restore ? 0 : v, 1);
       break;
     case OpKind::FusedAttention:
       if (find("VARIANT", v)) kcg_fmha_set_p_in_tmem(restore ? -1 : v);
