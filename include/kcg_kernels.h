@@ -338,7 +338,10 @@ KCG_API int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Sk
 
 /*
  * Tuning switch with no counterpart in the reference: which attention kernel runs.
- *   -1 (default)  chosen by shape: two query tiles per CTA when Sq > 128, else one;
+ *   -1 (default)  chosen by shape: a CTA pair on four query tiles when Sq > 256 and D = 128, two
+ *                 query tiles per CTA when Sq > 128, else one;
+ *    3            CTA pair (tcgen05 cta_group::2): four 128-query tiles per two SMs, each SM staging
+ *                 half of every K and V tile (D = 128 only; other head dimensions run variant 2);
  *    2            two 128-query tiles per CTA, P handed to the second MMA through tensor memory;
  *    1            one query tile per CTA, P through tensor memory;
  *    0            one query tile per CTA, P through a swizzled shared-memory tile.

@@ -100,13 +100,11 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // 2^x for a pair of values on the FMA and integer pipes instead of the special-function unit:
 // n = round(x) by the magic-number addition, f = x - n in [-0.5, 0.5], 2^f by a cubic (relative
 // error 1.1e-4, far below the rounding of a 16-bit P), and n added into the exponent field.
-// x is clamped at -126 so that a vanishing term comes out as 2^-126 * p ~ 1e-38 instead of wrapping.
+// Arguments below -126 (masked scores are -inf) give exactly 0, like the flushing ex2.approx.ftz.
 __device__ __forceinline__ void exp2_pair_fma(uint64_t x2, float& p0, float& p1) {
   float x0, x1;
   f2_unpack(x2, x0, x1);
-  x0 = x0 < -126.f ? -126.f : x0;   // (a NaN stays a NaN)
-  x1 = x1 < -126.f ? -126.f : x1;
-  const uint64_t xc = f2_pack(x0, x1);
+  const uint64_t xc = x2;
   const uint64_t magic = f2_pack(12582912.f, 12582912.f), nmagic = f2_pack(-12582912.f, -12582912.f);
   const uint64_t t = f2_add(xc, magic);                 // low mantissa bits = n
   const uint64_t n = f2_add(t, nmagic);                 // n as a float
@@ -117,8 +115,8 @@ __device__ __forceinline__ void exp2_pair_fma(uint64_t x2, float& p0, float& p1)
   float t0, t1, q0, q1;
   f2_unpack(t, t0, t1);
   f2_unpack(p, q0, q1);
-  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
-  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+  p0 = x0 < -126.f ? 0.f : __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+  p1 = x1 < -126.f ? 0.f : __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
 }
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -446,6 +444,317 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// One key block of the online softmax for the calling thread's query row.  The 128 scores of the
+// row sit in tensor memory at s_addr (this thread's lane); columns >= limit are masked.  On return
+// P (16-bit, 64 columns) has replaced the first half of the scores, handed to the MMA thread in
+// two halves through arrive(half) (called by lane 0 after the warp's stores are complete), the
+// output accumulator at o_addr has been rescaled if the running maximum m moved by more than the
+// threshold, and m and the running row sum l are up to date.  All 32 lanes of the warp call it.
+template <typename T, int D, typename Arrive>
+__device__ __forceinline__ void softmax_block(uint32_t s_addr, uint32_t o_addr, int j, int limit, float c, float& m,
+                                              float& l, int lane, Arrive arrive) {
+  uint32_t sreg[BN];
+  tmem_ld64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));
+  tmem_ld64(s_addr + 64, reinterpret_cast<uint32_t(&)[64]>(sreg[64]));
+  tmem_wait_ld();
+  if (limit < BN) {
+#pragma unroll
+    for (int k = 0; k < BN; ++k)
+      if (k >= limit) sreg[k] = 0xff800000u;  // -inf
+  }
+  // eight independent chains of 3-input max (8 dependent steps instead of 16)
+  float mx[8];
+#pragma unroll
+  for (int a = 0; a < 8; ++a) mx[a] = fmaxf(__uint_as_float(sreg[2 * a]), __uint_as_float(sreg[2 * a + 1]));
+#pragma unroll
+  for (int k = 16; k < BN; k += 16) {
+#pragma unroll
+    for (int a = 0; a < 8; ++a) mx[a] = max3(mx[a], __uint_as_float(sreg[k + 2 * a]), __uint_as_float(sreg[k + 2 * a + 1]));
+  }
+  const float mt = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * c;
+  uint64_t lsum_a = 0ull, lsum_b = 0ull;  // two (+0.f, +0.f) accumulators
+  const uint64_t c2 = f2_pack(c, c);
+  // exponentials of one half of the row (64 scores -> 32 packed words, written in place over
+  // the words already consumed), then the hand-over of that half of P to the MMA thread
+  auto exp_half = [&](int half, uint64_t nm2) {
+#pragma unroll
+    for (int k = half * 64; k < half * 64 + 64; k += 2) {
+      const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sreg[k]), __uint_as_float(sreg[k + 1])), c2, nm2);
+      float p0, p1;
+      if (KCG_FMHA_EMU_MASK != 0 && ((k >> 1) & KCG_FMHA_EMU_MASK) == KCG_FMHA_EMU_MASK) {
+        exp2_pair_fma(x2, p0, p1);
+      } else {
+        float x0, x1;
+        f2_unpack(x2, x0, x1);
+        p0 = fast_exp2(x0);
+        p1 = fast_exp2(x1);
+      }
+      if ((k >> 1) & 1) lsum_b = f2_add(lsum_b, f2_pack(p0, p1));
+      else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
+      sreg[k >> 1] = pack2<T>(p0, p1);  // in place: word k/2 is never read again
+    }
+  };
+  auto hand_over = [&](int half) {
+    tmem_st32(s_addr + half * 32, reinterpret_cast<uint32_t(&)[32]>(sreg[half * 32]));
+    tmem_wait_st();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) arrive(half);
+  };
+  float alpha = 1.f;
+  bool half0_done = false;
+  // Speculative path (every block after the first that needs no mask): the exponentials of the
+  // first half start at once with the running maximum m, so that the maximum of this block is
+  // computed in the shadow of the special-function unit instead of in front of it.  That is
+  // exact whenever the block's maximum stays within the rescale threshold of m, which is the
+  // condition under which m would have been kept anyway; otherwise (rare once a few blocks have
+  // been seen) the first half is read again from tensor memory and redone on the ordinary path.
+  const bool speculate = __all_sync(0xffffffffu, j > 0 && limit >= BN && m != -INFINITY);
+  if (speculate) {
+    const float neg_m0 = -m;
+    exp_half(0, f2_pack(neg_m0, neg_m0));
+    if (!__any_sync(0xffffffffu, mt > m + kRescaleThreshold)) {
+      hand_over(0);
+      half0_done = true;
+    } else {
+      tmem_ld64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));   // the first 32 words were overwritten
+      tmem_wait_ld();
+      lsum_a = 0ull;
+      lsum_b = 0ull;
+    }
+  }
+  if (!half0_done) {
+    bool rescale = false;
+    if ((mt > m + kRescaleThreshold || m == -INFINITY) && mt > m) {
+      alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - mt);
+      rescale = (j > 0);
+      m = mt;
+    }
+    // S_i(j) being complete means PV_i(j-1) is complete: O_i may be rescaled now.
+    if (__any_sync(0xffffffffu, rescale)) {
+      const float a = rescale ? alpha : 1.f;
+#pragma unroll 1
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t oreg[32];
+        tmem_ld32(o_addr + cc * 32, oreg);
+        tmem_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) oreg[k] = __float_as_uint(__uint_as_float(oreg[k]) * a);
+        tmem_st32(o_addr + cc * 32, oreg);
+      }
+    }
+    const float neg_m = (m == -INFINITY) ? 0.f : -m;
+    exp_half(0, f2_pack(neg_m, neg_m));
+    hand_over(0);
+  }
+  {
+    const float neg_m = (m == -INFINITY) ? 0.f : -m;
+    exp_half(1, f2_pack(neg_m, neg_m));
+    hand_over(1);
+  }
+  float l0, l1;
+  f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
+  l = l * alpha + (l0 + l1);
+}
+
+// The same key-block step with P handed over through shared memory instead of tensor memory.
+// The score row leaves tensor memory for good as soon as it has been read (release_s() is called
+// by lane 0 right after the load), so the MMA thread can compute the NEXT block's scores while
+// this block's exponentials run: the softmax of a tile then runs back to back instead of waiting
+// for "P -> PV -> next S".  P (16-bit) is written to this row of a K-major, 128-byte swizzled
+// shared-memory tile p_tile (two blocks of 64 keys, 16 KB each) in two halves, arrive(half) after
+// each.  wait_pv() must return once the previous block's PV MMA has finished (it reads the same P
+// tile and writes the accumulator that a rescale touches); it returns false on a timed-out wait.
+template <typename T, int D, typename ReleaseS, typename WaitPV, typename Arrive>
+__device__ __forceinline__ bool softmax_block_smem(uint32_t s_addr, uint32_t o_addr, uint8_t* p_tile, int row, int j,
+                                                   int limit, float c, float& m, float& l, int lane, ReleaseS release_s,
+                                                   WaitPV wait_pv, Arrive arrive) {
+  uint32_t sreg[BN];
+  tmem_ld64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));
+  tmem_ld64(s_addr + 64, reinterpret_cast<uint32_t(&)[64]>(sreg[64]));
+  tmem_wait_ld();
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) release_s();
+  if (limit < BN) {
+#pragma unroll
+    for (int k = 0; k < BN; ++k)
+      if (k >= limit) sreg[k] = 0xff800000u;  // -inf
+  }
+  float mx[8];
+#pragma unroll
+  for (int a = 0; a < 8; ++a) mx[a] = fmaxf(__uint_as_float(sreg[2 * a]), __uint_as_float(sreg[2 * a + 1]));
+#pragma unroll
+  for (int k = 16; k < BN; k += 16) {
+#pragma unroll
+    for (int a = 0; a < 8; ++a) mx[a] = max3(mx[a], __uint_as_float(sreg[k + 2 * a]), __uint_as_float(sreg[k + 2 * a + 1]));
+  }
+  const float mt = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * c;
+  uint64_t lsum_a = 0ull, lsum_b = 0ull;
+  const uint64_t c2 = f2_pack(c, c);
+  uint32_t pk[32];   // one half of the row's P, packed
+  auto exp_half = [&](int half, uint64_t nm2) {
+#pragma unroll
+    for (int k = half * 64; k < half * 64 + 64; k += 2) {
+      const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sreg[k]), __uint_as_float(sreg[k + 1])), c2, nm2);
+      float p0, p1;
+      if (KCG_FMHA_EMU_MASK != 0 && ((k >> 1) & KCG_FMHA_EMU_MASK) == KCG_FMHA_EMU_MASK) {
+        exp2_pair_fma(x2, p0, p1);
+      } else {
+        float x0, x1;
+        f2_unpack(x2, x0, x1);
+        p0 = fast_exp2(x0);
+        p1 = fast_exp2(x1);
+      }
+      if ((k >> 1) & 1) lsum_b = f2_add(lsum_b, f2_pack(p0, p1));
+      else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
+      pk[(k >> 1) & 31] = pack2<T>(p0, p1);
+    }
+  };
+  auto hand_over = [&](int half) {
+    uint8_t* dst = p_tile + half * TILE16K + row * 128;
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+      *reinterpret_cast<uint4*>(dst + ((t ^ (row & 7)) << 4)) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
+    fence_proxy_async_smem();   // generic-proxy writes -> visible to the MMA's async-proxy reads
+    __syncwarp();
+    if (lane == 0) arrive(half);
+  };
+  float alpha = 1.f;
+  bool half0_done = false, ok = true;
+  const bool speculate = __all_sync(0xffffffffu, j > 0 && limit >= BN && m != -INFINITY);
+  if (speculate) {   // exponentials first, the block's maximum in their shadow (see softmax_block)
+    const float neg_m0 = -m;
+    exp_half(0, f2_pack(neg_m0, neg_m0));
+    if (!__any_sync(0xffffffffu, mt > m + kRescaleThreshold)) {
+      ok = wait_pv();
+      hand_over(0);
+      half0_done = true;
+    } else {
+      lsum_a = 0ull;   // the scores are still in registers: redo the half on the ordinary path
+      lsum_b = 0ull;
+    }
+  }
+  if (!half0_done) {
+    bool rescale = false;
+    if ((mt > m + kRescaleThreshold || m == -INFINITY) && mt > m) {
+      alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - mt);
+      rescale = (j > 0);
+      m = mt;
+    }
+    if (j > 0) ok = wait_pv();
+    if (__any_sync(0xffffffffu, rescale)) {
+      tc_fence_after();
+      const float a = rescale ? alpha : 1.f;
+#pragma unroll 1
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t oreg[32];
+        tmem_ld32(o_addr + cc * 32, oreg);
+        tmem_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) oreg[k] = __float_as_uint(__uint_as_float(oreg[k]) * a);
+        tmem_st32(o_addr + cc * 32, oreg);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+    }
+    const float neg_m = (m == -INFINITY) ? 0.f : -m;
+    exp_half(0, f2_pack(neg_m, neg_m));
+    hand_over(0);
+  }
+  {
+    const float neg_m = (m == -INFINITY) ? 0.f : -m;
+    exp_half(1, f2_pack(neg_m, neg_m));
+    hand_over(1);
+  }
+  float l0, l1;
+  f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
+  l = l * alpha + (l0 + l1);
+  return ok;
+}
+
+// Stores the calling thread's finished output row: O / l, rounded to T.  With extra outputs
+// (copies of O in other GPUs' memory) the warp's 32 rows are staged through `stg` (32 rows x D
+// elements of shared memory that is idle by now) and leave as whole rows to every destination.
+template <typename T, int D>
+__device__ __forceinline__ void store_output(const FmhaParams& p, uint32_t o_addr, bool have_o, float l, int b, int h,
+                                             int row0, int lane, uint8_t* stg, int peer_seed) {
+  const int qi = row0 + lane;   // this thread's query row; row0 is the first row of the warp
+  const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+  T* orow = static_cast<T*>(p.O) + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh +
+            static_cast<int64_t>(qi) * p.o_ss;
+  if (p.n_extra > 0) {
+    // Staged stores for remote destinations: this warp's 32 output rows pass through idle shared
+    // memory, swizzled, and leave as whole rows of D elements (256 bytes at D = 128), so that a
+    // store to another GPU's memory carries full lines; every destination receives the same registers.
+    constexpr int ROWB = D * 2;          // bytes per output row
+    constexpr int CH = ROWB / 16;        // 16-byte chunks per row
+    constexpr int RPI = 32 / CH;         // rows per store instruction
+#pragma unroll 1
+    for (int cc = 0; cc < D / 32; ++cc) {
+      uint32_t oreg[32];
+      if (have_o) {
+        tmem_ld32(o_addr + cc * 32, oreg);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) oreg[k] = 0u;
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 o;
+        o.x = pack2<T>(__uint_as_float(oreg[g * 8 + 0]) * inv_l, __uint_as_float(oreg[g * 8 + 1]) * inv_l);
+        o.y = pack2<T>(__uint_as_float(oreg[g * 8 + 2]) * inv_l, __uint_as_float(oreg[g * 8 + 3]) * inv_l);
+        o.z = pack2<T>(__uint_as_float(oreg[g * 8 + 4]) * inv_l, __uint_as_float(oreg[g * 8 + 5]) * inv_l);
+        o.w = pack2<T>(__uint_as_float(oreg[g * 8 + 6]) * inv_l, __uint_as_float(oreg[g * 8 + 7]) * inv_l);
+        const int gc = cc * 4 + g;
+        *reinterpret_cast<uint4*>(stg + lane * ROWB + ((gc ^ (lane & (CH - 1))) << 4)) = o;
+      }
+    }
+    __syncwarp();
+    const int64_t slice = static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh;
+#pragma unroll
+    for (int it = 0; it < 32 / RPI; ++it) {
+      const int rr = it * RPI + lane / CH, ch = lane % CH;
+      const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * ROWB + ((ch ^ (rr & (CH - 1))) << 4));
+      if (row0 + rr < p.Sq) {
+        const int64_t off = slice + static_cast<int64_t>(row0 + rr) * p.o_ss + ch * 8;
+        *reinterpret_cast<uint4*>(static_cast<T*>(p.O) + off) = v;
+        // peers in an order that differs from CTA to CTA and from step to step, so that the
+        // stores of the whole grid do not queue up on one NVLink destination at a time
+        const int peer0 = static_cast<int>(static_cast<unsigned>(peer_seed + it) % static_cast<unsigned>(p.n_extra));
+        for (int e = 0; e < p.n_extra; ++e) {
+          const int d = (e + peer0) % p.n_extra;
+          *reinterpret_cast<uint4*>(static_cast<T*>(p.extra_o[d]) + off) = v;
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int cc = 0; cc < D / 32; ++cc) {
+      uint32_t oreg[32];
+      if (have_o) {
+        tmem_ld32(o_addr + cc * 32, oreg);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) oreg[k] = 0u;
+      }
+      if (qi < p.Sq) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 o;
+          o.x = pack2<T>(__uint_as_float(oreg[g * 8 + 0]) * inv_l, __uint_as_float(oreg[g * 8 + 1]) * inv_l);
+          o.y = pack2<T>(__uint_as_float(oreg[g * 8 + 2]) * inv_l, __uint_as_float(oreg[g * 8 + 3]) * inv_l);
+          o.z = pack2<T>(__uint_as_float(oreg[g * 8 + 4]) * inv_l, __uint_as_float(oreg[g * 8 + 5]) * inv_l);
+          o.w = pack2<T>(__uint_as_float(oreg[g * 8 + 6]) * inv_l, __uint_as_float(oreg[g * 8 + 7]) * inv_l);
+          *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) = o;
+        }
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Version 2: two 128-query tiles per CTA.
 //
@@ -659,192 +968,18 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int j = 0; j < n_mine; ++j) {
       if (!mbar_wait(&s_full[i], j & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sreg[BN];
-      tmem_ld64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));
-      tmem_ld64(s_addr + 64, reinterpret_cast<uint32_t(&)[64]>(sreg[64]));
-      tmem_wait_ld();
       const int kv0 = j * BN;
       int limit = p.Skv - kv0;
       if (p.causal) limit = min(limit, qi + off + 1 - kv0);
-      if (limit < BN) {
-#pragma unroll
-        for (int k = 0; k < BN; ++k)
-          if (k >= limit) sreg[k] = 0xff800000u;  // -inf
-      }
-      // eight independent chains of 3-input max (8 dependent steps instead of 16)
-      float mx[8];
-#pragma unroll
-      for (int a = 0; a < 8; ++a) mx[a] = fmaxf(__uint_as_float(sreg[2 * a]), __uint_as_float(sreg[2 * a + 1]));
-#pragma unroll
-      for (int k = 16; k < BN; k += 16) {
-#pragma unroll
-        for (int a = 0; a < 8; ++a) mx[a] = max3(mx[a], __uint_as_float(sreg[k + 2 * a]), __uint_as_float(sreg[k + 2 * a + 1]));
-      }
-      const float mt = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * c;
-      uint64_t lsum_a = 0ull, lsum_b = 0ull;  // two (+0.f, +0.f) accumulators
-      const uint64_t c2 = f2_pack(c, c);
-      // exponentials of one half of the row (64 scores -> 32 packed words, written in place over
-      // the words already consumed), then the hand-over of that half of P to the MMA thread
-      auto exp_half = [&](int half, uint64_t nm2) {
-#pragma unroll
-        for (int k = half * 64; k < half * 64 + 64; k += 2) {
-          const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sreg[k]), __uint_as_float(sreg[k + 1])), c2, nm2);
-          float p0, p1;
-          if (KCG_FMHA_EMU_MASK != 0 && ((k >> 1) & KCG_FMHA_EMU_MASK) == KCG_FMHA_EMU_MASK) {
-            exp2_pair_fma(x2, p0, p1);
-          } else {
-            float x0, x1;
-            f2_unpack(x2, x0, x1);
-            p0 = fast_exp2(x0);
-            p1 = fast_exp2(x1);
-          }
-          if ((k >> 1) & 1) lsum_b = f2_add(lsum_b, f2_pack(p0, p1));
-          else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
-          sreg[k >> 1] = pack2<T>(p0, p1);  // in place: word k/2 is never read again
-        }
-      };
-      auto hand_over = [&](int half) {
-        tmem_st32(s_addr + half * 32, reinterpret_cast<uint32_t(&)[32]>(sreg[half * 32]));
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[2 * i + half]);
-      };
-      float alpha = 1.f;
-      bool half0_done = false;
-      // Speculative path (every block after the first that needs no mask): the exponentials of the
-      // first half start at once with the running maximum m, so that the maximum of this block is
-      // computed in the shadow of the special-function unit instead of in front of it.  That is
-      // exact whenever the block's maximum stays within the rescale threshold of m, which is the
-      // condition under which m would have been kept anyway; otherwise (rare once a few blocks have
-      // been seen) the first half is read again from tensor memory and redone on the ordinary path.
-      const bool speculate = __all_sync(0xffffffffu, j > 0 && limit >= BN && m != -INFINITY);
-      if (speculate) {
-        const float neg_m0 = -m;
-        exp_half(0, f2_pack(neg_m0, neg_m0));
-        if (!__any_sync(0xffffffffu, mt > m + kRescaleThreshold)) {
-          hand_over(0);
-          half0_done = true;
-        } else {
-          tmem_ld64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));   // the first 32 words were overwritten
-          tmem_wait_ld();
-          lsum_a = 0ull;
-          lsum_b = 0ull;
-        }
-      }
-      if (!half0_done) {
-        bool rescale = false;
-        if ((mt > m + kRescaleThreshold || m == -INFINITY) && mt > m) {
-          alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - mt);
-          rescale = (j > 0);
-          m = mt;
-        }
-        // S_i(j) being complete means PV_i(j-1) is complete: O_i may be rescaled now.
-        if (__any_sync(0xffffffffu, rescale)) {
-          const float a = rescale ? alpha : 1.f;
-#pragma unroll 1
-          for (int cc = 0; cc < D / 32; ++cc) {
-            uint32_t oreg[32];
-            tmem_ld32(o_addr + cc * 32, oreg);
-            tmem_wait_ld();
-#pragma unroll
-            for (int k = 0; k < 32; ++k) oreg[k] = __float_as_uint(__uint_as_float(oreg[k]) * a);
-            tmem_st32(o_addr + cc * 32, oreg);
-          }
-        }
-        const float neg_m = (m == -INFINITY) ? 0.f : -m;
-        exp_half(0, f2_pack(neg_m, neg_m));
-        hand_over(0);
-      }
-      {
-        const float neg_m = (m == -INFINITY) ? 0.f : -m;
-        exp_half(1, f2_pack(neg_m, neg_m));
-        hand_over(1);
-      }
-      float l0, l1;
-      f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
-      l = l * alpha + (l0 + l1);
+      softmax_block<T, D>(s_addr, o_addr, j, limit, c, m, l, lane, [&](int half) { mbar_arrive(&p_full[2 * i + half]); });
     }
     // epilogue: the commit after the last PV arrives on s_full once more
     if (ok && n_mine > 0) ok = mbar_wait(&s_full[i], n_mine & 1u, abort_flag);
     if (ok) {
       tc_fence_after();
-      const float inv_l = l > 0.f ? 1.0f / l : 0.f;
-      T* orow = static_cast<T*>(p.O) + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh +
-                static_cast<int64_t>(qi) * p.o_ss;
-      if (p.n_extra > 0) {
-        // Staged stores for remote destinations: this warp's 32 output rows pass through the
-        // (now idle) shared memory of its Q tile, swizzled, and leave as whole rows of D
-        // elements (256 bytes at D = 128), so that a store to another GPU's memory carries full
-        // lines; every destination receives the same registers.
-        constexpr int ROWB = D * 2;          // bytes per output row
-        constexpr int CH = ROWB / 16;        // 16-byte chunks per row
-        constexpr int RPI = 32 / CH;         // rows per store instruction
-        uint8_t* stg = q_smem + i * TILE + quarter * (32 * ROWB);
-#pragma unroll 1
-        for (int cc = 0; cc < D / 32; ++cc) {
-          uint32_t oreg[32];
-          if (n_mine > 0) {
-            tmem_ld32(o_addr + cc * 32, oreg);
-            tmem_wait_ld();
-          } else {
-#pragma unroll
-            for (int k = 0; k < 32; ++k) oreg[k] = 0u;
-          }
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 o;
-            o.x = pack2<T>(__uint_as_float(oreg[g * 8 + 0]) * inv_l, __uint_as_float(oreg[g * 8 + 1]) * inv_l);
-            o.y = pack2<T>(__uint_as_float(oreg[g * 8 + 2]) * inv_l, __uint_as_float(oreg[g * 8 + 3]) * inv_l);
-            o.z = pack2<T>(__uint_as_float(oreg[g * 8 + 4]) * inv_l, __uint_as_float(oreg[g * 8 + 5]) * inv_l);
-            o.w = pack2<T>(__uint_as_float(oreg[g * 8 + 6]) * inv_l, __uint_as_float(oreg[g * 8 + 7]) * inv_l);
-            const int gc = cc * 4 + g;
-            *reinterpret_cast<uint4*>(stg + lane * ROWB + ((gc ^ (lane & (CH - 1))) << 4)) = o;
-          }
-        }
-        __syncwarp();
-        const int64_t slice = static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh;
-        const int row0 = q0 + i * BM + quarter * 32;
-#pragma unroll
-        for (int it = 0; it < 32 / RPI; ++it) {
-          const int rr = it * RPI + lane / CH, ch = lane % CH;
-          const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * ROWB + ((ch ^ (rr & (CH - 1))) << 4));
-          if (row0 + rr < p.Sq) {
-            const int64_t off = slice + static_cast<int64_t>(row0 + rr) * p.o_ss + ch * 8;
-            *reinterpret_cast<uint4*>(static_cast<T*>(p.O) + off) = v;
-            // peers in an order that differs from CTA to CTA and from step to step, so that the
-            // stores of the whole grid do not queue up on one NVLink destination at a time
-            const int peer0 = static_cast<int>((blockIdx.x + blockIdx.y + warp + it) % static_cast<unsigned>(p.n_extra));
-            for (int e = 0; e < p.n_extra; ++e) {
-              const int d = (e + peer0) % p.n_extra;
-              *reinterpret_cast<uint4*>(static_cast<T*>(p.extra_o[d]) + off) = v;
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-      for (int cc = 0; cc < D / 32; ++cc) {
-        uint32_t oreg[32];
-        if (n_mine > 0) {
-          tmem_ld32(o_addr + cc * 32, oreg);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int k = 0; k < 32; ++k) oreg[k] = 0u;
-        }
-        if (qi < p.Sq) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 o;
-            o.x = pack2<T>(__uint_as_float(oreg[g * 8 + 0]) * inv_l, __uint_as_float(oreg[g * 8 + 1]) * inv_l);
-            o.y = pack2<T>(__uint_as_float(oreg[g * 8 + 2]) * inv_l, __uint_as_float(oreg[g * 8 + 3]) * inv_l);
-            o.z = pack2<T>(__uint_as_float(oreg[g * 8 + 4]) * inv_l, __uint_as_float(oreg[g * 8 + 5]) * inv_l);
-            o.w = pack2<T>(__uint_as_float(oreg[g * 8 + 6]) * inv_l, __uint_as_float(oreg[g * 8 + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) = o;
-          }
-        }
-      }
-      }
+      store_output<T, D>(p, o_addr, n_mine > 0, l, b, h, q0 + i * BM + quarter * 32, lane,
+                         q_smem + i * TILE + quarter * (32 * D * 2),
+                         static_cast<int>(blockIdx.x + blockIdx.y) + warp);
     } else if (lane == 0 && !*abort_flag) {
       *abort_flag = 1;
       *p.status = KCG_ERR_TIMEOUT;
@@ -861,6 +996,8 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
+
+#include "fmha_pair_kernel.cuh"
 
 template <typename T, int D>
 int launch_fmha2(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FmhaParams& p,
@@ -899,7 +1036,7 @@ thread_local int g_p_in_tmem = -1;  // per calling thread; -1: choose by shape
 }  // namespace
 
 // Kernel variant: -1 (default) picks by shape; 0 / 1 = one query tile per CTA with P through
-// shared / tensor memory; 2 = two query tiles per CTA.
+// shared / tensor memory; 2 = two query tiles per CTA; 3 = a CTA pair on four query tiles.
 extern "C" __attribute__((visibility("default"))) void kcg_fmha_set_p_in_tmem(int v) { g_p_in_tmem = v; }
 
 }  // namespace kcg
@@ -912,6 +1049,15 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
                   int n_extra);
 }
 }  // namespace kcg
+
+#ifdef KCG_FMHA_TRACE
+extern "C" __attribute__((visibility("default"))) int kcg_debug_fmha_trace(long long* out, int reset) {
+  long long zero[32] = {0};
+  if (out) cudaMemcpyFromSymbol(out, kcg::g_fmha_trace, sizeof(zero));
+  if (reset) cudaMemcpyToSymbol(kcg::g_fmha_trace, zero, sizeof(zero));
+  return 0;
+}
+#endif
 
 extern "C" int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int64_t D,
                             float softmax_scale, int causal, const void* Q, const int64_t q_strides[3],
@@ -971,15 +1117,16 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
         return fail(KCG_ERR_ALIGNMENT, "fmha: strides must be positive multiples of 8 elements (tensor %d stride %d = %lld)",
                     t, i, static_cast<long long>(strides[t][i]));
   }
-  CUtensorMap tm[3];
-  const int64_t seq[3] = {Sq, Skv, Skv};
-  for (int t = 0; t < 3; ++t) {
+  CUtensorMap tm[4];   // Q, K, V with 128-row boxes; K again with 64-row boxes (the CTA-pair kernel's halves)
+  const int64_t seq[4] = {Sq, Skv, Skv, Skv};
+  const int src[4] = {0, 1, 2, 1};
+  for (int t = 0; t < 4; ++t) {
     uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(seq[t]), static_cast<uint64_t>(H),
                         static_cast<uint64_t>(B)};
-    uint64_t st[3] = {static_cast<uint64_t>(strides[t][2]) * 2, static_cast<uint64_t>(strides[t][1]) * 2,
-                      static_cast<uint64_t>(strides[t][0]) * 2};
-    uint32_t box[4] = {64, 128, 1, 1};
-    int rc = encode_tmap_sw128(&tm[t], dtype, ptrs[t], 4, dims, st, box);
+    uint64_t st[3] = {static_cast<uint64_t>(strides[src[t]][2]) * 2, static_cast<uint64_t>(strides[src[t]][1]) * 2,
+                      static_cast<uint64_t>(strides[src[t]][0]) * 2};
+    uint32_t box[4] = {64, t == 3 ? 64u : 128u, 1, 1};
+    int rc = encode_tmap_sw128(&tm[t], dtype, ptrs[src[t]], 4, dims, st, box);
     if (rc) return rc;
   }
   FmhaParams p;
@@ -996,9 +1143,18 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
     if (!extra_o[i] || !aligned16(extra_o[i])) return fail(KCG_ERR_ALIGNMENT, "fmha: extra output %d is null or not 16-byte aligned", i);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const uint32_t fmt = dtype == KCG_BF16 ? 1u : 0u;
-  // Two query tiles per CTA pay off once there is more than one tile of queries; only that
-  // kernel writes extra outputs.
-  const int variant = n_extra > 0 ? 2 : (g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? 2 : 1));
+  // By shape: a CTA pair on four query tiles once there are more than two tiles of queries (head
+  // dimension 128), two query tiles per CTA when there is more than one, else one tile.  Extra
+  // outputs are written by the two-tile and the pair kernel only.
+  int variant = g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? 2 : 1);
+  if (variant >= 3 && D != 128) variant = 2;
+  if (n_extra > 0 && variant < 2) variant = 2;
+  if (variant == 3)
+    return dtype == KCG_BF16 ? launch_fmha_pair<__nv_bfloat16, false>(tm[0], tm[3], tm[2], p, fmt, s)
+                             : launch_fmha_pair<__half, false>(tm[0], tm[3], tm[2], p, fmt, s);
+  if (variant == 4)
+    return dtype == KCG_BF16 ? launch_fmha_pair<__nv_bfloat16, true>(tm[0], tm[3], tm[2], p, fmt, s)
+                             : launch_fmha_pair<__half, true>(tm[0], tm[3], tm[2], p, fmt, s);
 #define KCG_FMHA(TT, DD)                                                                      \
   (variant == 2   ? launch_fmha2<TT, DD>(tm[0], tm[1], tm[2], p, fmt, s)                      \
    : variant == 1 ? launch_fmha<TT, DD, true>(tm[0], tm[1], tm[2], p, fmt, s)                 \

@@ -273,6 +273,12 @@ __device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// The same arrival without release semantics: for hand-overs whose data is in tensor memory (ordered
+// by tcgen05.wait + tcgen05.fence::before_thread_sync, not by the memory model).  A releasing arrive
+// at cluster scope was measured at about 800 clocks in the arriving thread.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 // TMA load whose completion bytes are counted on the mbarrier at cluster address `bar_addr`
 // (the leader CTA's barrier); the data lands in this CTA's shared memory.  No multicast.
 __device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* m, uint32_t bar_addr, int x, int y, int z) {
@@ -280,6 +286,37 @@ __device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* m
       "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_addr), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(void* dst, const CUtensorMap* m, uint32_t bar_addr, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_addr), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+// Wait on a barrier of this CTA that CTAs of the whole cluster arrive on: the acquire has cluster
+// scope, so that what the remote arriver released (its tensor-memory stores) is visible afterwards.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint64_t budget_ns = kWaitBudgetNs) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((i & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > budget_ns) return false;
+    }
+  }
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols)
@@ -316,6 +353,16 @@ __device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, ui
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
   }
+}
+// D(tmem) (+)= A(tmem) * B(smem) on a CTA pair: each CTA's 128 rows of A come from its own tensor memory.
+__device__ __forceinline__ void mma_ts_f16_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "setp.ne.b32 P, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, P;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 // One arrival on the mbarrier at the same shared-memory offset in every CTA of `cta_mask`
 // once all MMAs issued so far by this thread have finished (barrier signalling only; no data

@@ -93,7 +93,10 @@ KernelCodeGenerator::KernelCodeGenerator(const std::string& platform_) : platfor
   gatherConfigs = {{{"BLOCK_SIZE", 256}, {"VECTORIZE_WIDTH", 16}}};
   softmaxConfigs = {{{"BLOCK_SIZE", 256}}};
   fusionConfigs = {{{"EPILOGUE", 1}}};
-  fmhaConfigs = {{{"BLOCK_SIZE", 320}, {"Br", 256}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}, {"VARIANT", 2}},
+  // VARIANT -1: the library picks the attention kernel by shape (CTA pair, two tiles, one tile)
+  fmhaConfigs = {{{"BLOCK_SIZE", 384}, {"Br", 512}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}, {"VARIANT", -1}},
+                 {{"BLOCK_SIZE", 384}, {"Br", 512}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}, {"VARIANT", 3}},
+                 {{"BLOCK_SIZE", 384}, {"Br", 256}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}, {"VARIANT", 2}},
                  {{"BLOCK_SIZE", 192}, {"Br", 128}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}, {"VARIANT", 1}}};
 }
 

@@ -25,6 +25,7 @@ CASES = [
     (1, 2, 128, 520, 128),    # more keys than queries
     (1, 1, 1, 300, 128),      # a single query (decode-like)
     (1, 2, 1024, 1024, 128),  # 8 key blocks: both score buffers and both ring stages wrap
+    (2, 2, 700, 900, 128),    # six query tiles (the second group of four half empty), ragged keys
 ]
 
 
@@ -55,8 +56,9 @@ def variant(request):
 
 # Every kernel the library ships is held to the same parity bar, not only the one the default
 # picks for a shape: 0 / 1 = one query tile per CTA with P through shared / tensor memory (also
-# for long sequences), 2 = two query tiles per CTA (also for a single, partly empty tile pair).
-@pytest.mark.parametrize("variant", [0, 1, 2], indirect=True)
+# for long sequences), 2 = two query tiles per CTA (also for a single, partly empty tile pair),
+# 3 = a CTA pair on four query tiles (also when most of the four are empty; D = 64 runs variant 2).
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4], indirect=True)
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("B,H,Sq,Skv,D", CASES)
