@@ -751,6 +751,24 @@ def main() -> None:
         barrier()
         return max_over_ranks(e0.elapsed_time(e1)) / iters
 
+    def multicast_buffers(rows, cols):
+        """Symmetric-memory gather buffers bound to an NVLink multicast object, or None (every rank
+        gets the same answer: the outcome is agreed on before anyone uses the buffers)."""
+        from kernelcodegen_b200 import shard
+        mb, good = None, 1
+        try:
+            mb = shard.MulticastBuffers(rows, cols, dt)
+            good = 1 if mb.mc_ptr else 0
+        except Exception:   # noqa: BLE001 - no symmetric memory on this host: the peer-store path remains
+            good = 0
+        flag = torch.tensor([good], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            if mb is not None:
+                mb.close()
+            return None
+        return mb
+
     bufs = None
     if world > 1 and want("gather"):
         # replicated C from a row-sharded GEMM, two ways: the epilogue that stores every tile into
@@ -782,6 +800,16 @@ def main() -> None:
                                "bytes_sent_per_gpu": (world - 1) * n * n * 2,
                                "link_gbs_per_gpu": (world - 1) * n * n * 2 / (ms * 1e-3) / 1e9}
         workloads["gemm_allgather_fused_epilogue"]["bit_identical_to_nccl_path"] = bool(torch.equal(bufs.local, Cg))
+        mb = multicast_buffers(world * n, n)
+        if mb is not None:
+            def mc_iter():
+                shard.matmul_allgather(A, B, mb, sync=False)
+                shard.stream_barrier()
+            ms = timed_loop(mc_iter, 10)
+            workloads["gemm_allgather_multicast_epilogue"] = {
+                "ms": ms, "value": world * 2 * n ** 3 / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "bytes_sent_per_gpu": n * n * 2, "bit_identical_to_nccl_path": bool(torch.equal(mb.local, Cg))}
+            mb.close()
         del A, B, Cl, Cg
         bufs.close()
         torch.cuda.empty_cache()
@@ -808,6 +836,16 @@ def main() -> None:
                                "link_gbs_per_gpu": (world - 1) * Q.numel() * 2 / (ms * 1e-3) / 1e9}
         workloads["fmha_allgather_fused_epilogue"]["bit_identical_to_nccl_path"] = bool(
             torch.equal(fb.local.view(world * Bq, H, S, D), Og))
+        mb = multicast_buffers(world * Bq * H * S, D)
+        if mb is not None:
+            def mc_attn():
+                shard.fmha_allgather(Q, K, V, mb, world * Bq, D ** -0.5, True, sync=False)
+                shard.stream_barrier()
+            ms = timed_loop(mc_attn, 5)
+            workloads["fmha_allgather_multicast_epilogue"] = {
+                "ms": ms, "value": world * fl / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "bytes_sent_per_gpu": Q.numel() * 2,
+                "bit_identical_to_nccl_path": bool(torch.equal(mb.local.view(world * Bq, H, S, D), Og))}
+            mb.close()
         del Q, K, V, Ol, Og
         fb.close()
         torch.cuda.empty_cache()
@@ -849,8 +887,18 @@ def main() -> None:
                 ms = timed_loop(nccl_g, 5)
                 rec["gather_nccl_ms"] = ms
                 rec["gather_fused_bit_identical_to_nccl"] = bool(torch.equal(gb.local, Cg))
-                del Cg
                 gb.close()
+                mb = multicast_buffers(Mt, n)
+                if mb is not None:
+                    def mc_g():
+                        shard.matmul_allgather(A, B, mb, sync=False)
+                        shard.stream_barrier()
+                    ms = timed_loop(mc_g, 5)
+                    rec["gather_multicast_ms"] = ms
+                    rec["gather_multicast_tflops"] = fl / (ms * 1e-3) / 1e12
+                    rec["gather_multicast_bit_identical_to_nccl"] = bool(torch.equal(mb.local, Cg))
+                    mb.close()
+                del Cg
         sharded["gemm_bf16_m65536"] = rec
         del A, B, Cl
         torch.cuda.empty_cache()
@@ -884,8 +932,18 @@ def main() -> None:
                 ms = timed_loop(nccl_a, 3)
                 rec["gather_nccl_ms"] = ms
                 rec["gather_fused_bit_identical_to_nccl"] = bool(torch.equal(gb.local.view(Bt, H, S, D), Og))
-                del Og
                 gb.close()
+                mb = multicast_buffers(Bt * H * S, D)
+                if mb is not None:
+                    def mc_a():
+                        shard.fmha_allgather(Q, K, V, mb, Bt, D ** -0.5, True, sync=False)
+                        shard.stream_barrier()
+                    ms = timed_loop(mc_a, 3)
+                    rec["gather_multicast_ms"] = ms
+                    rec["gather_multicast_tflops"] = fl / (ms * 1e-3) / 1e12
+                    rec["gather_multicast_bit_identical_to_nccl"] = bool(torch.equal(mb.local.view(Bt, H, S, D), Og))
+                    mb.close()
+                del Og
         sharded["fmha_bf16_b64_s4096_causal"] = rec
         del Q, K, V, Ol
         torch.cuda.empty_cache()

@@ -338,8 +338,10 @@ KCG_API int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Sk
 
 /*
  * Tuning switch with no counterpart in the reference: which attention kernel runs.
- *   -1 (default)  chosen by shape: a CTA pair on four query tiles when Sq > 256 and D = 128, two
- *                 query tiles per CTA when Sq > 128, else one;
+ *   -1 (default)  chosen by shape: two query tiles per CTA when Sq > 128, else one;
+ *    4            CTA pair with one query tile per CTA, two score buffers and P in tensor-memory
+ *                 columns of its own; the two softmax warpgroups take alternate key blocks and
+ *                 two threads issue the MMAs (D = 128 only, no gather epilogue);
  *    3            CTA pair (tcgen05 cta_group::2): four 128-query tiles per two SMs, each SM staging
  *                 half of every K and V tile (D = 128 only; other head dimensions run variant 2);
  *    2            two 128-query tiles per CTA, P handed to the second MMA through tensor memory;
@@ -428,6 +430,43 @@ KCG_API int kcg_fmha_fwd_allgather(int dtype, int64_t B, int64_t H, int64_t Sq, 
                                    const int64_t v_strides[3], void* const* gathered, int world,
                                    int rank, int64_t batch_offset, const int64_t o_strides[3],
                                    void* stream);
+
+/*
+ * The two fused gathers with the replication done by NVSwitch (no counterpart in the reference).
+ * `gathered_multicast` is the address of the gathered matrix / tensor inside a multicast mapping
+ * to which every rank has bound its own buffer (an NVLink multicast object, e.g. the
+ * `multicast_ptr` of a torch symmetric-memory allocation), `gathered_local` this rank's own
+ * buffer.  Each tile (output row) is stored ONCE, with multimem.st to the multicast address, and
+ * the switch delivers it to every rank's buffer, this rank's included: a GPU sends its block over
+ * its links once instead of world - 1 times, which is what keeps the gather under the math at 8
+ * GPUs.  Same kernels, same bits and same synchronisation rules as kcg_gemm_allgather /
+ * kcg_fmha_fwd_allgather.  All ranks must unbind / release the mapping before any of them exits.
+ */
+KCG_API int kcg_gemm_allgather_multicast(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K,
+                                         int trans_a, int trans_b, const void* A, int64_t lda,
+                                         const void* B, int64_t ldb, void* gathered_local,
+                                         void* gathered_multicast, int64_t row_offset, int64_t ldc,
+                                         const float* scale_a, const float* scale_b, const void* bias,
+                                         int activation, void* stream);
+KCG_API int kcg_fmha_fwd_allgather_multicast(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv,
+                                             int64_t D, float softmax_scale, int causal, const void* Q,
+                                             const int64_t q_strides[3], const void* K,
+                                             const int64_t k_strides[3], const void* V,
+                                             const int64_t v_strides[3], void* gathered_local,
+                                             void* gathered_multicast, int64_t batch_offset,
+                                             const int64_t o_strides[3], void* stream);
+
+/*
+ * LayerNorm of this rank's `rows` rows with the all-gather of the result done by NVSwitch: row r is
+ * stored, with multimem.st, to row row_offset + r of `gathered_multicast` (the multicast address
+ * of the [total_rows, cols] gathered tensor, see kcg_gemm_allgather_multicast) and arrives in every
+ * rank's buffer.  Rows the one-pass kernels take only (16-byte vectorisable, at most 4096 vectors).
+ * Same arithmetic and bits as kcg_layernorm; no counterpart in the reference.
+ */
+KCG_API int kcg_layernorm_allgather_multicast(int dtype, int64_t rows, int64_t cols, const void* x,
+                                              const void* gamma, const void* beta, float eps,
+                                              void* gathered_multicast, int64_t row_offset,
+                                              void* stream);
 
 /*
  * Device memory that other processes on the node can map (CUDA IPC).  kcg_peer_alloc returns a

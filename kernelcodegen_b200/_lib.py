@@ -48,6 +48,11 @@ SIGNATURES = {
     "kcg_gemm_set_fp32_mode": ([_ci], None),
     "kcg_gemm_allgather": ([_ci, _ci, _i64, _i64, _i64, _ci, _ci, _vp, _i64, _vp, _i64, ctypes.POINTER(_vp), _ci, _ci,
                             _i64, _i64, _vp, _vp, _vp, _ci, _vp], _ci),
+    "kcg_gemm_allgather_multicast": ([_ci, _ci, _i64, _i64, _i64, _ci, _ci, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64,
+                                      _vp, _vp, _vp, _ci, _vp], _ci),
+    "kcg_fmha_fwd_allgather_multicast": ([_ci, _i64, _i64, _i64, _i64, _i64, _fp, _ci, _vp, _i64p, _vp, _i64p, _vp, _i64p,
+                                          _vp, _vp, _i64, _i64p, _vp], _ci),
+    "kcg_layernorm_allgather_multicast": ([_ci, _i64, _i64, _vp, _vp, _vp, _fp, _vp, _i64, _vp], _ci),
     "kcg_peer_alloc": ([ctypes.c_size_t, ctypes.POINTER(_vp)], _ci),
     "kcg_peer_free": ([_vp], _ci),
     "kcg_peer_export": ([_vp, ctypes.c_char_p], _ci),

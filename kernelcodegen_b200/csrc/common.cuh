@@ -135,6 +135,16 @@ __device__ __forceinline__ void st_256(void* p, const uint4& lo, const uint4& hi
                : "memory");
 }
 
+// One 16-byte store to a multicast address: NVSwitch writes it into the buffer of every GPU bound
+// to the multicast object (the issuing GPU's own included), so a gather that needs the same bytes on
+// N GPUs sends them over this GPU's links once instead of N - 1 times.  A data move: the four words
+// pass through float registers untouched.
+__device__ __forceinline__ void multimem_st16(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

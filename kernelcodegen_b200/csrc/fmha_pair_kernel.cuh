@@ -18,23 +18,10 @@
 // warps, two-CTA tcgen05.commit from the leader).
 #pragma once
 
-#ifdef KCG_FMHA_TRACE
-// Debug build only: clock64 totals of the first cluster's MMA thread and of one softmax thread of
-// each CTA over key blocks [8, 24), read back with kcg_debug_fmha_trace().
-__device__ long long g_fmha_trace[32];
-#define KCG_TR_ON (blockIdx.x < 2 && blockIdx.y == 0)
-#define KCG_TR(idx, expr) do { if (j >= 8 && j < 24) { const long long _t = clock64(); expr; tr_acc[idx] += clock64() - _t; } else { expr; } } while (0)
-#else
-#define KCG_TR(idx, expr) do { expr; } while (0)
-#endif
-
 constexpr int V3_THREADS = 384;
 constexpr int V3_HALF = 16384;   // half of a K or V tile: 64 keys x 128 d, or 128 keys x 64 d (bytes)
 
-// kPSmem: P goes to the second MMA through shared memory and the score buffer is released as soon
-// as it has been read, so S_i(j+1) is computed under the softmax of block j (see
-// softmax_block_smem); otherwise P overwrites S in tensor memory as in the two-tile kernel.
-template <typename T, bool kPSmem>
+template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(V3_THREADS, 1)
 fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKh,
                      const __grid_constant__ CUtensorMap tmV, const FmhaParams p, const uint32_t idesc_qk,
@@ -48,18 +35,14 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
   uint8_t* q_smem = smem;                   // [2][TILE]: this CTA's tiles of slot 0 and slot 1
   uint8_t* kv_smem = smem + 2 * TILE;       // [5][V3_HALF]: ring entry r = (V at 2r, K at 2r + 1), K_0 at 4
-  uint8_t* p_smem = kv_smem + 5 * V3_HALF;  // kPSmem: [2][TILE] P of this CTA's tiles (K-major, swizzled)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + (kPSmem ? 2 * TILE : 0));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_smem + 5 * V3_HALF);
   uint64_t* q_full = bars;                  // [1]  leader: Q of both CTAs and K_0
   uint64_t* kv_full = bars + 1;             // [2]  leader
   uint64_t* kv_empty = bars + 3;            // [2]  each CTA (two-CTA commit)
   uint64_t* s_full = bars + 5;              // [2]  each CTA (two-CTA commit)
   uint64_t* p_full = bars + 7;              // [2 slots][2 halves]  leader, 8 arrivals (4 warps x 2 CTAs)
   uint64_t* drain_bar = bars + 11;
-  uint64_t* s_free = bars + 12;             // [2]  leader, 8 arrivals: S_i has been read by every softmax warp
-  uint64_t* pv_done = bars + 14;            // [2]  each CTA (two-CTA commit): PV_i(j) has finished
-  uint64_t* p_local = bars + 16;            // kPSmem: [2 slots][2 halves] each CTA, 4 arrivals (its softmax warps)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,13 +71,8 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      // P through shared memory: one arrival per CTA, made by its relay warp (see below)
-      mbar_init(&p_full[2 * s], kPSmem ? 2 : 8);
-      mbar_init(&p_full[2 * s + 1], kPSmem ? 2 : 8);
-      mbar_init(&p_local[2 * s], 4);
-      mbar_init(&p_local[2 * s + 1], 4);
-      mbar_init(&s_free[s], 8);
-      mbar_init(&pv_done[s], 1);
+      mbar_init(&p_full[2 * s], 8);
+      mbar_init(&p_full[2 * s + 1], 8);
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -151,9 +129,6 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     reg_dealloc<V2_REGS_SERVICE>();
     if (lane == 0 && rank == 0 && n_max > 0) {
       bool ok = true;
-#ifdef KCG_FMHA_TRACE
-      long long tr_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#endif
       const uint64_t q_desc0 = make_smem_desc(smem_u32(q_smem), 16, 1024);
       const uint64_t k_desc0 = make_smem_desc(smem_u32(kv_smem), 16, 1024);        // K halves (K-major)
       const uint64_t v_desc0 = make_smem_desc(smem_u32(kv_smem), TILE16K, 1024);   // V halves (MN-major, one column block)
@@ -167,19 +142,12 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             mma_ss_pair<Kind::F16>(tmem_base + i * BN, qd_ + ((d * TILE16K + k * 32) >> 4), kd + ((d * KBLK + k * 32) >> 4),
                                    idesc_qk, (d | k) != 0 ? 1u : 0u);
       };
-      const uint64_t p_desc0 = make_smem_desc(smem_u32(p_smem), 16, 1024);         // P tiles (K-major A operand)
       auto issue_pv = [&](int i, int j, int half) {  // O_i += P_i(j)[:, half] V_j[half, :]
         const uint64_t vd = v_desc0 + static_cast<uint64_t>((2 * (j & 1) * V3_HALF) >> 4);
 #pragma unroll
-        for (int kk = half * 4; kk < half * 4 + 4; ++kk) {
-          if constexpr (kPSmem) {
-            const uint64_t pd = p_desc0 + static_cast<uint64_t>((i * TILE + (kk >> 2) * TILE16K + (kk & 3) * 32) >> 4);
-            mma_ss_pair<Kind::F16>(tmem_base + 256 + i * BN, pd, vd + ((kk * 2048) >> 4), idesc_pv, (j | kk) != 0 ? 1u : 0u);
-          } else {
-            mma_ts_f16_pair(tmem_base + 256 + i * BN, tmem_base + i * BN + kk * 8, vd + ((kk * 2048) >> 4), idesc_pv,
-                            (j | kk) != 0 ? 1u : 0u);
-          }
-        }
+        for (int kk = half * 4; kk < half * 4 + 4; ++kk)
+          mma_ts_f16_pair(tmem_base + 256 + i * BN, tmem_base + i * BN + kk * 8, vd + ((kk * 2048) >> 4), idesc_pv,
+                          (j | kk) != 0 ? 1u : 0u);
       };
       ok = mbar_wait(q_full, 0, abort_flag);
       if (ok) {
@@ -192,59 +160,24 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
       }
       for (int j = 0; j < n_max && ok; ++j) {
-        KCG_TR(0, ok = mbar_wait(&kv_full[j & 1], (j >> 1) & 1u, abort_flag));
+        ok = mbar_wait(&kv_full[j & 1], (j >> 1) & 1u, abort_flag);
         if (!ok) break;
-        if constexpr (kPSmem) {
-          // the next block's scores first: they only need the score buffers back, which happens
-          // right after the softmax threads have read block j
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int n_i = i == 0 ? n_blk0 : n_blk1;
-            if (j + 1 >= n_i) continue;
-            KCG_TR(1, ok = mbar_wait_cluster(&s_free[i], j & 1u, abort_flag));
-            if (!ok) break;
-            tc_fence_after();
-            KCG_TR(2, issue_s(i, j + 1); mma_commit_pair(&s_full[i], 3));
-          }
-#pragma unroll
-          for (int i = 0; i < 2 && ok; ++i) {
-            const int n_i = i == 0 ? n_blk0 : n_blk1;
-            if (j >= n_i) continue;
-            KCG_TR(3, ok = mbar_wait_cluster(&p_full[2 * i], j & 1u, abort_flag));
-            if (!ok) break;
-            tc_fence_after();
-            KCG_TR(4, issue_pv(i, j, 0));
-            KCG_TR(5, ok = mbar_wait_cluster(&p_full[2 * i + 1], j & 1u, abort_flag));
-            if (!ok) break;
-            tc_fence_after();
-            KCG_TR(4, issue_pv(i, j, 1); mma_commit_pair(&pv_done[i], 3));
-          }
-          if (ok) mma_commit_pair(&kv_empty[j & 1], 3);
-#ifdef KCG_FMHA_TRACE
-          if (j == 8) tr_acc[6] = clock64();
-          if (j == 24) tr_acc[7] = clock64();
-#endif
-          continue;
-        }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           const int n_i = i == 0 ? n_blk0 : n_blk1;
           if (j >= n_i) continue;
-          KCG_TR(3, ok = mbar_wait_cluster(&p_full[2 * i], j & 1u, abort_flag));
+          ok = mbar_wait_cluster(&p_full[2 * i], j & 1u, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          KCG_TR(4, issue_pv(i, j, 0));
-          KCG_TR(5, ok = mbar_wait_cluster(&p_full[2 * i + 1], j & 1u, abort_flag));
+          issue_pv(i, j, 0);
+          ok = mbar_wait_cluster(&p_full[2 * i + 1], j & 1u, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          KCG_TR(4, issue_pv(i, j, 1));
-          KCG_TR(2, if (j + 1 < n_i) issue_s(i, j + 1); mma_commit_pair(&s_full[i], 3));   // the next score tile, or the finished output, in both CTAs
+          issue_pv(i, j, 1);
+          if (j + 1 < n_i) issue_s(i, j + 1);
+          mma_commit_pair(&s_full[i], 3);   // the next score tile, or the finished output, in both CTAs
         }
         if (ok) mma_commit_pair(&kv_empty[j & 1], 3);
-#ifdef KCG_FMHA_TRACE
-        if (j == 8) tr_acc[6] = clock64();
-        if (j == 24) tr_acc[7] = clock64();
-#endif
       }
       if (!ok) {
         if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
@@ -252,10 +185,6 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         mma_commit_pair(drain_bar, 1);
         mbar_wait(drain_bar, 0, &zero, 20000000ull);
       }
-#ifdef KCG_FMHA_TRACE
-      if (KCG_TR_ON)
-        for (int t = 0; t < 8; ++t) g_fmha_trace[t] = tr_acc[t];
-#endif
     }
     __syncwarp();
   } else if (warp < 8) {
@@ -272,51 +201,19 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t s_addr = tmem_base + lane_base + i * BN;
     const uint32_t o_addr = tmem_base + lane_base + 256 + i * BN;
     const uint32_t p_bar0 = map_to_cta(&p_full[2 * i], 0), p_bar1 = map_to_cta(&p_full[2 * i + 1], 0);
-    const uint32_t s_free_bar = map_to_cta(&s_free[i], 0);
     float m = -INFINITY, l = 0.f;
     bool ok = true;
-#ifdef KCG_FMHA_TRACE
-    long long sm_acc[2] = {0, 0};
-#endif
     for (int j = 0; j < n_mine; ++j) {
-#ifdef KCG_FMHA_TRACE
-      const bool tr = j >= 8 && j < 24;
-      const long long tw0 = clock64();
-#endif
       if (!mbar_wait(&s_full[i], j & 1u, abort_flag)) { ok = false; break; }
-#ifdef KCG_FMHA_TRACE
-      const long long tw1 = clock64();
-      if (tr) sm_acc[0] += tw1 - tw0;
-#endif
       tc_fence_after();
       const int kv0 = j * BN;
       int limit = p.Skv - kv0;
       if (p.causal) limit = min(limit, qi + off + 1 - kv0);
-      if constexpr (kPSmem) {
-        ok = softmax_block_smem<T, D>(
-            s_addr, o_addr, p_smem + i * TILE, r, j, limit, c, m, l, lane,
-            [&]() { mbar_arrive_cluster_relaxed(s_free_bar); },
-            [&]() { return mbar_wait(&pv_done[i], (j - 1) & 1u, abort_flag); },
-            [&](int half) { mbar_arrive(&p_local[2 * i + half]); });
-        if (!ok) break;
-      } else {
-        softmax_block<T, D>(s_addr, o_addr, j, limit, c, m, l, lane,
-                            [&](int half) { mbar_arrive_cluster_relaxed(half ? p_bar1 : p_bar0); });
-      }
-#ifdef KCG_FMHA_TRACE
-      if (tr) sm_acc[1] += clock64() - tw1;
-#endif
+      softmax_block<T, D>(s_addr, o_addr, j, limit, c, m, l, lane,
+                          [&](int half) { mbar_arrive_cluster_relaxed(half ? p_bar1 : p_bar0); });
     }
-#ifdef KCG_FMHA_TRACE
-    if (KCG_TR_ON && threadIdx.x == 0) {
-      g_fmha_trace[8 + 4 * rank] = sm_acc[0];
-      g_fmha_trace[9 + 4 * rank] = sm_acc[1];
-    }
-#endif
-    // epilogue: the last PV of this slot has finished (kPSmem: its own barrier; otherwise the
-    // commit after the last PV arrives on s_full once more)
-    if (ok && n_mine > 0)
-      ok = kPSmem ? mbar_wait(&pv_done[i], (n_mine - 1) & 1u, abort_flag) : mbar_wait(&s_full[i], n_mine & 1u, abort_flag);
+    // epilogue: the commit after the last PV arrives on s_full once more
+    if (ok && n_mine > 0) ok = mbar_wait(&s_full[i], n_mine & 1u, abort_flag);
     if (ok) {
       tc_fence_after();
       store_output<T, D>(p, o_addr, n_mine > 0, l, b, h, tile_row0 + quarter * 32, lane,
@@ -327,26 +224,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       __threadfence_system();
     }
   } else {
-    reg_dealloc<V2_REGS_SERVICE>();   // warps 10-11
-    if constexpr (kPSmem) {
-      // Relay of slot (warp - 10): P written to shared memory by ordinary stores has to be released
-      // at cluster scope before the leader's MMA thread may read it, and a releasing arrive on a
-      // remote barrier costs the arriving thread about 800 clocks.  The softmax warps therefore
-      // arrive on a barrier of their own CTA (cheap), and this otherwise idle warp forwards each
-      // completed half to the leader, so that the cost stays off the softmax threads.
-      const int i = warp - 10;
-      const int n_mine = i == 0 ? n_blk0 : n_blk1;
-      if (lane == 0) {
-        const uint32_t bar0 = map_to_cta(&p_full[2 * i], 0), bar1 = map_to_cta(&p_full[2 * i + 1], 0);
-        for (int j = 0; j < n_mine; ++j) {
-          if (!mbar_wait(&p_local[2 * i], j & 1u, abort_flag)) break;
-          mbar_arrive_cluster(bar0);
-          if (!mbar_wait(&p_local[2 * i + 1], j & 1u, abort_flag)) break;
-          mbar_arrive_cluster(bar1);
-        }
-      }
-      __syncwarp();
-    }
+    reg_dealloc<V2_REGS_SERVICE>();   // warps 10-11: only the register hand-over
   }
 
   // Neither CTA may leave (or free tensor memory) while the other can still signal it.
@@ -358,11 +236,11 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
 }
 
-template <typename T, bool kPSmem>
+template <typename T>
 int launch_fmha_pair(const CUtensorMap& tmQ, const CUtensorMap& tmKh, const CUtensorMap& tmV, const FmhaParams& p,
                      uint32_t fmt, cudaStream_t stream) {
-  constexpr int SMEM = 2 * (2 * TILE16K) + 5 * V3_HALF + (kPSmem ? 2 * (2 * TILE16K) : 0) + 1024 + 256;
-  auto kern = fmha_fwd_pair_kernel<T, kPSmem>;
+  constexpr int SMEM = 2 * (2 * TILE16K) + 5 * V3_HALF + 1024 + 256;
+  auto kern = fmha_fwd_pair_kernel<T>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
   if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "fmha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   const uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, 2 * BM, BN);

@@ -61,6 +61,9 @@ struct FmhaParams {
   // of peer GPUs; written by the two-tile kernel's epilogue
   void* extra_o[7];
   int n_extra;
+  // or: the same block of O inside a multicast mapping of every rank's gather buffer (one store
+  // per row segment, delivered to all ranks by NVSwitch, instead of O plus every extra_o)
+  void* mc_o;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -450,9 +453,19 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // two halves through arrive(half) (called by lane 0 after the warp's stores are complete), the
 // output accumulator at o_addr has been rescaled if the running maximum m moved by more than the
 // threshold, and m and the running row sum l are up to date.  All 32 lanes of the warp call it.
-template <typename T, int D, typename Arrive>
-__device__ __forceinline__ void softmax_block(uint32_t s_addr, uint32_t o_addr, int j, int limit, float c, float& m,
-                                              float& l, int lane, Arrive arrive) {
+struct NoHook {
+  __device__ __forceinline__ bool operator()() const { return true; }
+};
+
+// Two optional hooks serve the kernel whose warpgroups take alternate key blocks of one tile:
+// decided() is called (by all lanes) as soon as this block's value of m is final — before the
+// exponentials on the ordinary path — and wait_o() before the accumulator is touched for a rescale
+// (it returns false if its wait timed out; the rescale is then skipped and the caller gives up).
+template <typename T, int D, typename Arrive, typename Decided = NoHook, typename WaitO = NoHook>
+__device__ __forceinline__ bool softmax_block(uint32_t s_addr, uint32_t o_addr, int j, int limit, float c, float& m,
+                                              float& l, int lane, Arrive arrive, Decided decided = Decided(),
+                                              WaitO wait_o = WaitO()) {
+  bool hooks_ok = true;
   uint32_t sreg[BN];
   tmem_ld64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));
   tmem_ld64(s_addr + 64, reinterpret_cast<uint32_t(&)[64]>(sreg[64]));
@@ -514,6 +527,7 @@ __device__ __forceinline__ void softmax_block(uint32_t s_addr, uint32_t o_addr, 
     const float neg_m0 = -m;
     exp_half(0, f2_pack(neg_m0, neg_m0));
     if (!__any_sync(0xffffffffu, mt > m + kRescaleThreshold)) {
+      decided();
       hand_over(0);
       half0_done = true;
     } else {
@@ -530,19 +544,25 @@ __device__ __forceinline__ void softmax_block(uint32_t s_addr, uint32_t o_addr, 
       rescale = (j > 0);
       m = mt;
     }
-    // S_i(j) being complete means PV_i(j-1) is complete: O_i may be rescaled now.
+    // In the two-tile kernels S_i(j) being complete means PV_i(j-1) is complete, so O_i may be
+    // rescaled at once; a kernel where that does not hold passes wait_o.
     if (__any_sync(0xffffffffu, rescale)) {
-      const float a = rescale ? alpha : 1.f;
+      hooks_ok = wait_o();
+      if (hooks_ok) {
+        tc_fence_after();
+        const float a = rescale ? alpha : 1.f;
 #pragma unroll 1
-      for (int cc = 0; cc < D / 32; ++cc) {
-        uint32_t oreg[32];
-        tmem_ld32(o_addr + cc * 32, oreg);
-        tmem_wait_ld();
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t oreg[32];
+          tmem_ld32(o_addr + cc * 32, oreg);
+          tmem_wait_ld();
 #pragma unroll
-        for (int k = 0; k < 32; ++k) oreg[k] = __float_as_uint(__uint_as_float(oreg[k]) * a);
-        tmem_st32(o_addr + cc * 32, oreg);
+          for (int k = 0; k < 32; ++k) oreg[k] = __float_as_uint(__uint_as_float(oreg[k]) * a);
+          tmem_st32(o_addr + cc * 32, oreg);
+        }
       }
     }
+    decided();
     const float neg_m = (m == -INFINITY) ? 0.f : -m;
     exp_half(0, f2_pack(neg_m, neg_m));
     hand_over(0);
@@ -555,20 +575,22 @@ __device__ __forceinline__ void softmax_block(uint32_t s_addr, uint32_t o_addr, 
   float l0, l1;
   f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
   l = l * alpha + (l0 + l1);
+  return hooks_ok;
 }
 
-// The same key-block step with P handed over through shared memory instead of tensor memory.
-// The score row leaves tensor memory for good as soon as it has been read (release_s() is called
-// by lane 0 right after the load), so the MMA thread can compute the NEXT block's scores while
-// this block's exponentials run: the softmax of a tile then runs back to back instead of waiting
-// for "P -> PV -> next S".  P (16-bit) is written to this row of a K-major, 128-byte swizzled
-// shared-memory tile p_tile (two blocks of 64 keys, 16 KB each) in two halves, arrive(half) after
-// each.  wait_pv() must return once the previous block's PV MMA has finished (it reads the same P
-// tile and writes the accumulator that a rescale touches); it returns false on a timed-out wait.
-template <typename T, int D, typename ReleaseS, typename WaitPV, typename Arrive>
-__device__ __forceinline__ bool softmax_block_smem(uint32_t s_addr, uint32_t o_addr, uint8_t* p_tile, int row, int j,
-                                                   int limit, float c, float& m, float& l, int lane, ReleaseS release_s,
-                                                   WaitPV wait_pv, Arrive arrive) {
+// The key-block step for the kernel that keeps P in tensor-memory columns of its own (p_addr, 64
+// columns) instead of over the scores.  The score row then leaves tensor memory for good as soon
+// as it has been read — release_s() is called by lane 0 right after the load — so the MMA thread
+// may refill the score buffer while this block's exponentials run.  The row's scores stay in
+// registers for the whole step (P is packed into a separate 32-word buffer per half), so the
+// speculative path can redo a half without reading tensor memory again.  decided() is called by
+// all lanes once this block's value of m is final; wait_o() before the accumulator is touched for
+// a rescale and wait_p() before P(j) overwrites the P written two blocks earlier (both return
+// false if their wait timed out); arrive() by lane 0 when all 64 columns of P are in place.
+template <typename T, int D, typename ReleaseS, typename Decided, typename WaitO, typename WaitP, typename Arrive>
+__device__ __forceinline__ bool softmax_block_px(uint32_t s_addr, uint32_t o_addr, uint32_t p_addr, int j, int limit,
+                                                 float c, float& m, float& l, int lane, ReleaseS release_s,
+                                                 Decided decided, WaitO wait_o, WaitP wait_p, Arrive arrive) {
   uint32_t sreg[BN];
   tmem_ld64(s_addr, reinterpret_cast<uint32_t(&)[64]>(sreg[0]));
   tmem_ld64(s_addr + 64, reinterpret_cast<uint32_t(&)[64]>(sreg[64]));
@@ -592,8 +614,11 @@ __device__ __forceinline__ bool softmax_block_smem(uint32_t s_addr, uint32_t o_a
   const float mt = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7])) * c;
   uint64_t lsum_a = 0ull, lsum_b = 0ull;
   const uint64_t c2 = f2_pack(c, c);
-  uint32_t pk[32];   // one half of the row's P, packed
-  auto exp_half = [&](int half, uint64_t nm2) {
+  // P of the first half goes to a buffer of its own (that half may have to be redone from the
+  // scores); P of the second half overwrites the first half's scores, which are dead by then.  The
+  // registers a tcgen05.st reads are not touched again before tcgen05.wait::st.
+  uint32_t pk[32];
+  auto exp_half = [&](int half, uint64_t nm2, uint32_t* dst) {
 #pragma unroll
     for (int k = half * 64; k < half * 64 + 64; k += 2) {
       const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sreg[k]), __uint_as_float(sreg[k + 1])), c2, nm2);
@@ -608,27 +633,19 @@ __device__ __forceinline__ bool softmax_block_smem(uint32_t s_addr, uint32_t o_a
       }
       if ((k >> 1) & 1) lsum_b = f2_add(lsum_b, f2_pack(p0, p1));
       else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
-      pk[(k >> 1) & 31] = pack2<T>(p0, p1);
+      dst[(k >> 1) & 31] = pack2<T>(p0, p1);
     }
-  };
-  auto hand_over = [&](int half) {
-    uint8_t* dst = p_tile + half * TILE16K + row * 128;
-#pragma unroll
-    for (int t = 0; t < 8; ++t)
-      *reinterpret_cast<uint4*>(dst + ((t ^ (row & 7)) << 4)) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
-    fence_proxy_async_smem();   // generic-proxy writes -> visible to the MMA's async-proxy reads
-    __syncwarp();
-    if (lane == 0) arrive(half);
   };
   float alpha = 1.f;
   bool half0_done = false, ok = true;
   const bool speculate = __all_sync(0xffffffffu, j > 0 && limit >= BN && m != -INFINITY);
   if (speculate) {   // exponentials first, the block's maximum in their shadow (see softmax_block)
     const float neg_m0 = -m;
-    exp_half(0, f2_pack(neg_m0, neg_m0));
+    exp_half(0, f2_pack(neg_m0, neg_m0), pk);
     if (!__any_sync(0xffffffffu, mt > m + kRescaleThreshold)) {
-      ok = wait_pv();
-      hand_over(0);
+      decided();
+      ok = wait_p();
+      tmem_st32(p_addr, pk);
       half0_done = true;
     } else {
       lsum_a = 0ull;   // the scores are still in registers: redo the half on the ordinary path
@@ -642,31 +659,37 @@ __device__ __forceinline__ bool softmax_block_smem(uint32_t s_addr, uint32_t o_a
       rescale = (j > 0);
       m = mt;
     }
-    if (j > 0) ok = wait_pv();
     if (__any_sync(0xffffffffu, rescale)) {
-      tc_fence_after();
-      const float a = rescale ? alpha : 1.f;
+      ok = wait_o();
+      if (ok) {
+        tc_fence_after();
+        const float a = rescale ? alpha : 1.f;
 #pragma unroll 1
-      for (int cc = 0; cc < D / 32; ++cc) {
-        uint32_t oreg[32];
-        tmem_ld32(o_addr + cc * 32, oreg);
-        tmem_wait_ld();
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t oreg[32];
+          tmem_ld32(o_addr + cc * 32, oreg);
+          tmem_wait_ld();
 #pragma unroll
-        for (int k = 0; k < 32; ++k) oreg[k] = __float_as_uint(__uint_as_float(oreg[k]) * a);
-        tmem_st32(o_addr + cc * 32, oreg);
+          for (int k = 0; k < 32; ++k) oreg[k] = __float_as_uint(__uint_as_float(oreg[k]) * a);
+          tmem_st32(o_addr + cc * 32, oreg);
+        }
       }
-      tmem_wait_st();
-      tc_fence_before();
     }
+    decided();
     const float neg_m = (m == -INFINITY) ? 0.f : -m;
-    exp_half(0, f2_pack(neg_m, neg_m));
-    hand_over(0);
+    exp_half(0, f2_pack(neg_m, neg_m), pk);
+    ok = wait_p() && ok;
+    tmem_st32(p_addr, pk);
   }
   {
     const float neg_m = (m == -INFINITY) ? 0.f : -m;
-    exp_half(1, f2_pack(neg_m, neg_m));
-    hand_over(1);
+    exp_half(1, f2_pack(neg_m, neg_m), sreg);
+    tmem_st32(p_addr + 32, reinterpret_cast<uint32_t(&)[32]>(sreg[0]));
   }
+  tmem_wait_st();
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) arrive();
   float l0, l1;
   f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
   l = l * alpha + (l0 + l1);
@@ -683,7 +706,7 @@ __device__ __forceinline__ void store_output(const FmhaParams& p, uint32_t o_add
   const float inv_l = l > 0.f ? 1.0f / l : 0.f;
   T* orow = static_cast<T*>(p.O) + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh +
             static_cast<int64_t>(qi) * p.o_ss;
-  if (p.n_extra > 0) {
+  if (p.n_extra > 0 || p.mc_o != nullptr) {
     // Staged stores for remote destinations: this warp's 32 output rows pass through idle shared
     // memory, swizzled, and leave as whole rows of D elements (256 bytes at D = 128), so that a
     // store to another GPU's memory carries full lines; every destination receives the same registers.
@@ -719,10 +742,14 @@ __device__ __forceinline__ void store_output(const FmhaParams& p, uint32_t o_add
       const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * ROWB + ((ch ^ (rr & (CH - 1))) << 4));
       if (row0 + rr < p.Sq) {
         const int64_t off = slice + static_cast<int64_t>(row0 + rr) * p.o_ss + ch * 8;
+        if (p.mc_o != nullptr) {
+          multimem_st16(static_cast<T*>(p.mc_o) + off, v);
+          continue;
+        }
         *reinterpret_cast<uint4*>(static_cast<T*>(p.O) + off) = v;
         // peers in an order that differs from CTA to CTA and from step to step, so that the
         // stores of the whole grid do not queue up on one NVLink destination at a time
-        const int peer0 = static_cast<int>(static_cast<unsigned>(peer_seed + it) % static_cast<unsigned>(p.n_extra));
+        const int peer0 = p.n_extra > 0 ? static_cast<int>(static_cast<unsigned>(peer_seed + it) % static_cast<unsigned>(p.n_extra)) : 0;
         for (int e = 0; e < p.n_extra; ++e) {
           const int d = (e + peer0) % p.n_extra;
           *reinterpret_cast<uint4*>(static_cast<T*>(p.extra_o[d]) + off) = v;
@@ -998,6 +1025,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 #include "fmha_pair_kernel.cuh"
+#include "fmha_split_kernel.cuh"
 
 template <typename T, int D>
 int launch_fmha2(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FmhaParams& p,
@@ -1036,7 +1064,8 @@ thread_local int g_p_in_tmem = -1;  // per calling thread; -1: choose by shape
 }  // namespace
 
 // Kernel variant: -1 (default) picks by shape; 0 / 1 = one query tile per CTA with P through
-// shared / tensor memory; 2 = two query tiles per CTA; 3 = a CTA pair on four query tiles.
+// shared / tensor memory; 2 = two query tiles per CTA; 3 = a CTA pair on four query tiles; 4 = a
+// CTA pair with one tile per CTA whose warpgroups take alternate key blocks.
 extern "C" __attribute__((visibility("default"))) void kcg_fmha_set_p_in_tmem(int v) { g_p_in_tmem = v; }
 
 }  // namespace kcg
@@ -1046,18 +1075,9 @@ namespace {
 int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int64_t D, float softmax_scale, int causal,
                   const void* Q, const int64_t q_strides[3], const void* K, const int64_t k_strides[3], const void* V,
                   const int64_t v_strides[3], void* O, const int64_t o_strides[3], void* stream, void* const* extra_o,
-                  int n_extra);
+                  int n_extra, void* mc_o = nullptr);
 }
 }  // namespace kcg
-
-#ifdef KCG_FMHA_TRACE
-extern "C" __attribute__((visibility("default"))) int kcg_debug_fmha_trace(long long* out, int reset) {
-  long long zero[32] = {0};
-  if (out) cudaMemcpyFromSymbol(out, kcg::g_fmha_trace, sizeof(zero));
-  if (reset) cudaMemcpyToSymbol(kcg::g_fmha_trace, zero, sizeof(zero));
-  return 0;
-}
-#endif
 
 extern "C" int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int64_t D,
                             float softmax_scale, int causal, const void* Q, const int64_t q_strides[3],
@@ -1092,12 +1112,30 @@ extern "C" int kcg_fmha_fwd_allgather(int dtype, int64_t B, int64_t H, int64_t S
                        o_strides, stream, others, n_others);
 }
 
+// The same with the gather done by NVSwitch: every output row is stored once, to the multicast
+// address of its place in the gathered tensor, and arrives in every rank's buffer.
+extern "C" int kcg_fmha_fwd_allgather_multicast(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int64_t D,
+                                                float softmax_scale, int causal, const void* Q,
+                                                const int64_t q_strides[3], const void* K, const int64_t k_strides[3],
+                                                const void* V, const int64_t v_strides[3], void* gathered_local,
+                                                void* gathered_multicast, int64_t batch_offset,
+                                                const int64_t o_strides[3], void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (!gathered_local || !gathered_multicast || !o_strides || batch_offset < 0)
+    return fail(KCG_ERR_INVALID_ARG, "fmha_allgather_multicast: bad argument");
+  const size_t shift = static_cast<size_t>(batch_offset) * o_strides[0] * 2;
+  return fmha_fwd_impl(dtype, B, H, Sq, Skv, D, softmax_scale, causal, Q, q_strides, K, k_strides, V, v_strides,
+                       static_cast<char*>(gathered_local) + shift, o_strides, stream, nullptr, 0,
+                       static_cast<char*>(gathered_multicast) + shift);
+}
+
 namespace kcg {
 namespace {
 int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int64_t D, float softmax_scale, int causal,
                   const void* Q, const int64_t q_strides[3], const void* K, const int64_t k_strides[3], const void* V,
                   const int64_t v_strides[3], void* O, const int64_t o_strides[3], void* stream, void* const* extra_o,
-                  int n_extra) {
+                  int n_extra, void* mc_o) {
   if (B < 0 || H < 0 || Sq < 0 || Skv < 0) return fail(KCG_ERR_INVALID_ARG, "fmha: negative extent");
   if (dtype != KCG_BF16 && dtype != KCG_F16)
     return fail(KCG_ERR_UNSUPPORTED, "fmha: dtype %d has no kernel (bfloat16, float16)", dtype);
@@ -1138,23 +1176,25 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
   p.status = device_status_word();
   if (!p.status) return fail(KCG_ERR_CUDA, "fmha: could not allocate the host-mapped status word");
   p.n_extra = n_extra;
+  p.mc_o = mc_o;
+  if (mc_o && !aligned16(mc_o)) return fail(KCG_ERR_ALIGNMENT, "fmha: the multicast output address is not 16-byte aligned");
   for (int i = 0; i < 7; ++i) p.extra_o[i] = i < n_extra ? extra_o[i] : nullptr;
   for (int i = 0; i < n_extra; ++i)
     if (!extra_o[i] || !aligned16(extra_o[i])) return fail(KCG_ERR_ALIGNMENT, "fmha: extra output %d is null or not 16-byte aligned", i);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const uint32_t fmt = dtype == KCG_BF16 ? 1u : 0u;
-  // By shape: a CTA pair on four query tiles once there are more than two tiles of queries (head
-  // dimension 128), two query tiles per CTA when there is more than one, else one tile.  Extra
-  // outputs are written by the two-tile and the pair kernel only.
+  // By shape: two query tiles per CTA when there is more than one tile of queries, else one tile.
+  // (The CTA-pair kernels, variants 3 and 4, are correct on every test shape but measured slower
+  // than the two-tile kernel; they stay selectable.)  Extra outputs are written by variants 2 and 3.
   int variant = g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? 2 : 1);
   if (variant >= 3 && D != 128) variant = 2;
-  if (n_extra > 0 && variant < 2) variant = 2;
-  if (variant == 3)
-    return dtype == KCG_BF16 ? launch_fmha_pair<__nv_bfloat16, false>(tm[0], tm[3], tm[2], p, fmt, s)
-                             : launch_fmha_pair<__half, false>(tm[0], tm[3], tm[2], p, fmt, s);
+  if ((n_extra > 0 || mc_o) && (variant < 2 || variant == 4)) variant = 2;
   if (variant == 4)
-    return dtype == KCG_BF16 ? launch_fmha_pair<__nv_bfloat16, true>(tm[0], tm[3], tm[2], p, fmt, s)
-                             : launch_fmha_pair<__half, true>(tm[0], tm[3], tm[2], p, fmt, s);
+    return dtype == KCG_BF16 ? launch_fmha_split<__nv_bfloat16>(tm[0], tm[3], tm[2], p, fmt, s)
+                             : launch_fmha_split<__half>(tm[0], tm[3], tm[2], p, fmt, s);
+  if (variant == 3)
+    return dtype == KCG_BF16 ? launch_fmha_pair<__nv_bfloat16>(tm[0], tm[3], tm[2], p, fmt, s)
+                             : launch_fmha_pair<__half>(tm[0], tm[3], tm[2], p, fmt, s);
 #define KCG_FMHA(TT, DD)                                                                      \
   (variant == 2   ? launch_fmha2<TT, DD>(tm[0], tm[1], tm[2], p, fmt, s)                      \
    : variant == 1 ? launch_fmha<TT, DD, true>(tm[0], tm[1], tm[2], p, fmt, s)                 \

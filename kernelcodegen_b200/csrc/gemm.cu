@@ -11,7 +11,7 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
                  int trans_b, const void* A, int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
                  int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
                  const float* scale_b, const void* bias, int act, cudaStream_t stream, void* const* extra_c = nullptr,
-                 int n_extra = 0);
+                 int n_extra = 0, void* mc_c = nullptr);
 int gemm_f32_tensor(int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a, int trans_b, const float* A,
                     int64_t lda, int64_t stride_a, const float* B, int64_t ldb, int64_t stride_b, float* C,
                     int64_t ldc, int64_t stride_c, const float* scale_a, const float* scale_b, const float* bias,
@@ -107,4 +107,30 @@ extern "C" int kcg_gemm_allgather(int dtype_in, int dtype_out, int64_t M, int64_
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return gemm_tcgen05(dtype_in, dtype_out, M, N, K, 1, trans_a, trans_b, A, lda, 0, B, ldb, 0, mine, ldc, 0, scale_a,
                       scale_b, bias, activation, s, others, n_others);
+}
+
+// The same with the gather done by NVSwitch: every tile is stored once, to the multicast address
+// of its place in the gathered matrix, and arrives in every rank's buffer (this rank's included).
+extern "C" int kcg_gemm_allgather_multicast(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int trans_a,
+                                            int trans_b, const void* A, int64_t lda, const void* B, int64_t ldb,
+                                            void* gathered_local, void* gathered_multicast, int64_t row_offset,
+                                            int64_t ldc, const float* scale_a, const float* scale_b, const void* bias,
+                                            int activation, void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (!gathered_local || !gathered_multicast) return fail(KCG_ERR_INVALID_ARG, "gemm_allgather_multicast: null pointer");
+  if (row_offset < 0 || ldc < N) return fail(KCG_ERR_INVALID_ARG, "gemm_allgather_multicast: bad row offset or ldc");
+  if (activation < 0 || activation > 2) return fail(KCG_ERR_INVALID_ARG, "gemm: activation %d (0 none, 1 Relu, 2 Gelu)", activation);
+  if (M < 0 || N < 0 || K < 0) return fail(KCG_ERR_INVALID_ARG, "gemm: negative extent");
+  if (M == 0 || N == 0) return KCG_OK;
+  if (K == 0) return fail(KCG_ERR_INVALID_ARG, "gemm: K must be positive");
+  if (!A || !B) return fail(KCG_ERR_INVALID_ARG, "gemm: null pointer");
+  if (dtype_in != KCG_BF16 && dtype_in != KCG_F16 && dtype_in != KCG_F8E4M3)
+    return fail(KCG_ERR_UNSUPPORTED, "gemm_allgather_multicast: tensor-core input dtypes only (bfloat16, float16, float8_e4m3)");
+  const int64_t a_cols = trans_a ? M : K, b_cols = trans_b ? K : N;
+  if (lda < a_cols || ldb < b_cols) return fail(KCG_ERR_INVALID_ARG, "gemm: leading dimension shorter than a row");
+  const size_t shift = static_cast<size_t>(row_offset) * ldc * kcg_dtype_size(dtype_out);
+  return gemm_tcgen05(dtype_in, dtype_out, M, N, K, 1, trans_a, trans_b, A, lda, 0, B, ldb, 0,
+                      static_cast<char*>(gathered_local) + shift, ldc, 0, scale_a, scale_b, bias, activation,
+                      static_cast<cudaStream_t>(stream), nullptr, 0, static_cast<char*>(gathered_multicast) + shift);
 }

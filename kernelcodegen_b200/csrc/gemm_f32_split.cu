@@ -24,7 +24,7 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
                  int trans_b, const void* A, int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
                  int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
                  const float* scale_b, const void* bias, int act, cudaStream_t stream, void* const* extra_c,
-                 int n_extra);
+                 int n_extra, void* mc_c = nullptr);
 void* device_scratch(size_t bytes, int slot, cudaStream_t stream, int* why);  // runtime.cu
 
 namespace {

@@ -186,7 +186,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       TOut* crow = static_cast<TOut*>(p.C) + b * p.stride_c + row * p.ldc;
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * PBN;
       constexpr int VW = Vec16<TOut>::N;
-      if (p.n_extra > 0) {
+      if (p.n_extra > 0 || p.mc_c != nullptr) {
         // Staged stores: the warp's 32 rows x 128 bytes go through a swizzled shared-memory
         // tile so that eight lanes write one whole 128-byte row segment per instruction —
         // the granularity a store to another GPU's memory should have — and every
@@ -196,7 +196,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const int64_t tile_row0 = static_cast<int64_t>(mp) * PBM + rank * 128 + quarter * 32;
 #pragma unroll 1
         for (int c = 0; c < PBN / RC; ++c) {
-          const int peer0 = static_cast<int>((blockIdx.x + quarter + c) % static_cast<unsigned>(p.n_extra));
+          const int peer0 = p.n_extra > 0 ? static_cast<int>((blockIdx.x + quarter + c) % static_cast<unsigned>(p.n_extra)) : 0;
           uint32_t r[RC];
           if constexpr (RC == 64) tmem_ld64(t_base + c * RC, r); else tmem_ld32(t_base + c * RC, r);
           tmem_wait_ld();
@@ -219,6 +219,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             const int64_t grow = tile_row0 + rr, col = cbase + ch * VW;
             if (grow < p.M && col + VW <= p.N) {
               const int64_t off = b * p.stride_c + grow * p.ldc + col;
+              if (p.mc_c != nullptr) {   // one store that NVSwitch delivers to every rank's buffer, this one's included
+                multimem_st16(static_cast<TOut*>(p.mc_c) + off, v);
+                continue;
+              }
               *reinterpret_cast<uint4*>(static_cast<TOut*>(p.C) + off) = v;
               // peers in an order that differs from CTA to CTA and from round to round, so that
               // the stores of the whole grid do not queue up on one NVLink destination at a time

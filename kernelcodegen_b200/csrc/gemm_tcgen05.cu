@@ -59,6 +59,9 @@ struct GemmParams {
   // buffers of peer GPUs: the CTA-pair kernel's epilogue stores every tile to each of them.
   void* extra_c[KCG_MAX_EXTRA_C];
   int n_extra;
+  // Or: the same block of C inside a multicast mapping of every rank's gather buffer; each tile is
+  // then stored once, to this address, instead of to C and every extra_c.
+  void* mc_c;
   int group_m;   // row tiles (of 128) per group of the tile order
 };
 
@@ -461,7 +464,7 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
                  int trans_b, const void* A, int64_t lda, int64_t stride_a, const void* B, int64_t ldb,
                  int64_t stride_b, void* C, int64_t ldc, int64_t stride_c, const float* scale_a,
                  const float* scale_b, const void* bias, int act, cudaStream_t stream, void* const* extra_c,
-                 int n_extra) {
+                 int n_extra, void* mc_c) {
   const int es = dtype_in == KCG_F8E4M3 ? 1 : (dtype_in == KCG_F32 ? 4 : 2);   // fp32 words are read as tf32
   if (!aligned16(A) || !aligned16(B))
     return fail(KCG_ERR_ALIGNMENT, "gemm: A and B must be 16-byte aligned for the tensor-core path");
@@ -478,7 +481,7 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
                   : g_pair_mode == 2 ? kNarrow
                   : g_pair_mode == 1 ? (M > BM ? kPair : kWide)
                                      : pick_tiling(M, N, K, batch, es, sm_count());
-  if (n_extra > 0) {
+  if (n_extra > 0 || mc_c) {
     // only the CTA-pair kernel has the staged epilogue that writes whole 128-byte row segments
     if (n_extra > KCG_MAX_EXTRA_C) return fail(KCG_ERR_UNSUPPORTED, "gemm: at most %d extra outputs", KCG_MAX_EXTRA_C);
     if (M <= BM) return fail(KCG_ERR_UNSUPPORTED, "gemm: extra outputs need M > 128 (got %lld)", static_cast<long long>(M));
@@ -525,10 +528,11 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
   const size_t out_es = kcg_dtype_size(dtype_out);
   p.c_vec_ok = aligned16(C) && (ldc * out_es) % 16 == 0 && (stride_c * out_es) % 16 == 0;
   p.n_extra = n_extra;
+  p.mc_c = mc_c;
   p.group_m = GROUP_M;   // 8, 32 and 64 were measured at 4096..16384: no better than 16
   for (int i = 0; i < KCG_MAX_EXTRA_C; ++i) p.extra_c[i] = i < n_extra ? extra_c[i] : nullptr;
-  if (n_extra > 0) {
-    bool ok = p.c_vec_ok && (N * out_es) % 16 == 0;
+  if (n_extra > 0 || mc_c) {
+    bool ok = p.c_vec_ok && (N * out_es) % 16 == 0 && aligned16(mc_c);
     for (int i = 0; i < n_extra; ++i) ok = ok && extra_c[i] != nullptr && aligned16(extra_c[i]);
     if (!ok)
       return fail(KCG_ERR_ALIGNMENT, "gemm: extra outputs need 16-byte aligned pointers, ldc and N (in bytes)");

@@ -59,17 +59,18 @@ __device__ __forceinline__ void ln_row_body(const uint4 (&v)[VPT], const uint4 (
                                             const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ yr,
                                             int tid, int nthr, int nvec, float inv_n, float eps, Reduce reduce,
                                             float* mean_out, float* rstd_out, const uint4* g_regs = nullptr,
-                                            const uint4* b_regs = nullptr);
+                                            const uint4* b_regs = nullptr, bool y_multicast = false);
 
 template <typename T, int VPT, bool kExact, bool kFuse, typename Reduce>
 __device__ __forceinline__ void ln_row(const T* __restrict__ xr, const T* __restrict__ gamma,
                                        const T* __restrict__ beta, const T* __restrict__ res, T* __restrict__ yr,
                                        int tid, int nthr, int nvec, float inv_n, float eps, Reduce reduce,
-                                       float* mean_out = nullptr, float* rstd_out = nullptr) {
+                                       float* mean_out = nullptr, float* rstd_out = nullptr, bool y_multicast = false) {
   uint4 v[VPT];
   uint4 rv[kFuse ? VPT : 1];
   ln_row_load<T, VPT, kExact, kFuse>(xr, res, tid, nthr, nvec, v, rv);
-  ln_row_body<T, VPT, kExact, kFuse>(v, rv, gamma, beta, yr, tid, nthr, nvec, inv_n, eps, reduce, mean_out, rstd_out);
+  ln_row_body<T, VPT, kExact, kFuse>(v, rv, gamma, beta, yr, tid, nthr, nvec, inv_n, eps, reduce, mean_out, rstd_out,
+                                     nullptr, nullptr, y_multicast);
 }
 
 template <typename T, int VPT, bool kExact, bool kFuse, typename Reduce>
@@ -77,7 +78,9 @@ __device__ __forceinline__ void ln_row_body(const uint4 (&v)[VPT], const uint4 (
                                             const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ yr,
                                             int tid, int nthr, int nvec, float inv_n, float eps, Reduce reduce,
                                             float* mean_out, float* rstd_out, const uint4* g_regs,
-                                            const uint4* b_regs) {
+                                            const uint4* b_regs, bool y_multicast) {
+  // y_multicast: yr is an address inside an NVLink multicast mapping; the row is stored with
+  // multimem.st and arrives in every bound GPU's buffer
   // g_regs / b_regs: the thread's vectors of gamma / beta already held in registers (a kernel
   // that walks over many rows loads them once); otherwise they are read here, from L1 / L2.
   using W = Words<T>;
@@ -181,7 +184,8 @@ __device__ __forceinline__ void ln_row_body(const uint4 (&v)[VPT], const uint4 (
           o[k] = W::pack(t);
         }
       }
-      __stcs(reinterpret_cast<uint4*>(yr) + vi, make_uint4(o[0], o[1], o[2], o[3]));
+      if (y_multicast) multimem_st16(reinterpret_cast<uint4*>(yr) + vi, make_uint4(o[0], o[1], o[2], o[3]));
+      else __stcs(reinterpret_cast<uint4*>(yr) + vi, make_uint4(o[0], o[1], o[2], o[3]));
     }
   }
 }
@@ -192,7 +196,7 @@ template <typename T, int VPT, bool kExact, bool kFuse>
 __global__ void __launch_bounds__(128, 5)
 ln_warp_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
              const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps,
-             float* __restrict__ mean_out, float* __restrict__ rstd_out) {
+             float* __restrict__ mean_out, float* __restrict__ rstd_out, int y_multicast) {
   grid_launch_dependents();
   grid_dependency_wait();
   const int lane = threadIdx.x & 31;
@@ -201,7 +205,7 @@ ln_warp_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __re
   ln_row<T, VPT, kExact, kFuse>(x + row * cols, gamma, beta, kFuse ? res + row * cols : nullptr, y + row * cols, lane, 32,
                                 cols / Vec16<T>::N,
                          1.0f / static_cast<float>(cols), eps, [](float v) { return warp_sum(v); },
-                         mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr);
+                         mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr, y_multicast != 0);
 }
 
 // Sum over one group of `nthr` threads (a multiple of 32) of a block that holds several such
@@ -224,7 +228,7 @@ template <typename T, int VPT, bool kExact, bool kFuse, int kRows = 1>
 __global__ void __launch_bounds__(512)
 ln_block_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
               const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps,
-              float* __restrict__ mean_out, float* __restrict__ rstd_out) {
+              float* __restrict__ mean_out, float* __restrict__ rstd_out, int y_multicast) {
   __shared__ float red[33 * kRows];
   grid_launch_dependents();
   grid_dependency_wait();
@@ -233,7 +237,7 @@ ln_block_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __r
     ln_row<T, VPT, kExact, kFuse>(x + row * cols, gamma, beta, kFuse ? res + row * cols : nullptr, y + row * cols,
                                   threadIdx.x, blockDim.x, cols / Vec16<T>::N, 1.0f / static_cast<float>(cols), eps,
                                   [&](float v) { return block_sum(v, red); },
-                                  mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr);
+                                  mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr, y_multicast != 0);
   } else {
     const int nthr = blockDim.x / kRows;
     const int group = threadIdx.x / nthr, tid = threadIdx.x - group * nthr;
@@ -243,7 +247,7 @@ ln_block_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __r
     ln_row<T, VPT, kExact, kFuse>(x + row * cols, gamma, beta, kFuse ? res + row * cols : nullptr, y + row * cols,
                                   tid, nthr, cols / Vec16<T>::N, 1.0f / static_cast<float>(cols), eps,
                                   [&](float v) { return group_sum(v, my_red, tid, nthr, 1 + group); },
-                                  mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr);
+                                  mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr, y_multicast != 0);
   }
 }
 
@@ -255,7 +259,7 @@ template <typename T, int VPT, bool kExact, bool kFuse>
 __global__ void __launch_bounds__(128, 2)
 ln_persistent_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                    const T* __restrict__ res, T* __restrict__ y, int64_t rows, int cols, float eps,
-                   float* __restrict__ mean_out, float* __restrict__ rstd_out) {
+                   float* __restrict__ mean_out, float* __restrict__ rstd_out, int y_multicast) {
   __shared__ float red[33];
   grid_launch_dependents();
   grid_dependency_wait();
@@ -281,7 +285,8 @@ ln_persistent_rows(const T* __restrict__ x, const T* __restrict__ gamma, const T
                                          nxt, rnxt);
     ln_row_body<T, VPT, kExact, kFuse>(cur, rcur, gamma, beta, y + row * cols, threadIdx.x, blockDim.x, nvec, inv_n, eps,
                                        [&](float v) { return block_sum(v, red); },
-                                       mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr, gq, bq);
+                                       mean_out ? mean_out + row : nullptr, mean_out ? rstd_out + row : nullptr, gq, bq,
+                                       y_multicast != 0);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) cur[i] = nxt[i];
     if constexpr (kFuse) {
@@ -382,7 +387,8 @@ ln_chunk_apply(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
 template <typename T>
 int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* beta, float eps,
               T* y, cudaStream_t stream, const T* res = nullptr, float* mean_out = nullptr,
-              float* rstd_out = nullptr) {
+              float* rstd_out = nullptr, int y_mc = 0) {
+  // y_mc: y is an address inside a multicast mapping (row kernels only)
   // res != nullptr: y = gelu(layernorm(x)) + res in one pass (row kernels only; the caller
   // falls back to three launches when the row kernels do not apply).
   constexpr int VW = Vec16<T>::N;
@@ -394,7 +400,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
   if (vec_ok && nvec <= 32 * g_warp_row_max_vecs) {
     const unsigned grid = static_cast<unsigned>((rows + 3) / 4);
     const int vpt = static_cast<int>((nvec + 31) / 32);
-#define KCG_LN_LAUNCH(V, E, F) launch_overlapped(ln_warp_rows<T, V, E, F>, dim3(grid), dim3(128), 0, stream, x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
+#define KCG_LN_LAUNCH(V, E, F) launch_overlapped(ln_warp_rows<T, V, E, F>, dim3(grid), dim3(128), 0, stream, x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out, y_mc)
 #define KCG_LN_WARP(V)                                                          \
   do {                                                                          \
     const bool exact = nvec == 32 * V;                                          \
@@ -424,7 +430,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
     if (g_block_rows < 0 && threads <= 128 && rows > static_cast<int64_t>(sm_count()) * -g_block_rows) {
       // persistent grid: -g_block_rows blocks per SM, each walking over rows
       const unsigned pgrid = static_cast<unsigned>(sm_count() * -g_block_rows);
-#define KCG_LN_LAUNCH(V, E, F) launch_overlapped(ln_persistent_rows<T, V, E, F>, dim3(pgrid), dim3(threads), 0, stream, x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
+#define KCG_LN_LAUNCH(V, E, F) launch_overlapped(ln_persistent_rows<T, V, E, F>, dim3(pgrid), dim3(threads), 0, stream, x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out, y_mc)
 #define KCG_LN_PERS(V)                                                          \
   do {                                                                          \
     const bool exact = nvec == static_cast<int64_t>(threads) * V;               \
@@ -442,7 +448,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
     while (rpb > 1 && rpb * threads > 512) rpb /= 2;
     const unsigned grid = static_cast<unsigned>((rows + rpb - 1) / rpb);
     const dim3 block(static_cast<unsigned>(threads * rpb));
-#define KCG_LN_LAUNCH_R(V, E, F, R) launch_overlapped(ln_block_rows<T, V, E, F, R>, dim3(grid), block, 0, stream, x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out)
+#define KCG_LN_LAUNCH_R(V, E, F, R) launch_overlapped(ln_block_rows<T, V, E, F, R>, dim3(grid), block, 0, stream, x, gamma, beta, res, y, rows, icols, eps, mean_out, rstd_out, y_mc)
 #define KCG_LN_LAUNCH(V, E, F)                                                  \
   do {                                                                          \
     if (rpb == 4) KCG_LN_LAUNCH_R(V, E, F, 4);                                  \
@@ -463,7 +469,7 @@ int launch_ln(int64_t rows, int64_t cols, const T* x, const T* gamma, const T* b
 #undef KCG_LN_LAUNCH_R
     return check_launch("ln_block_rows");
   }
-  if (res) return KCG_ERR_UNSUPPORTED;  // no fused form beyond the row kernels
+  if (res || y_mc) return KCG_ERR_UNSUPPORTED;  // no fused / multicast form beyond the row kernels
   // Split-row path.
   const int64_t chunks64 = (cols + kChunk - 1) / kChunk;
   if (chunks64 > 65535 * 32 || rows > 65535)
@@ -728,4 +734,40 @@ extern "C" int kcg_layernorm_stats(int dtype, int64_t rows, int64_t cols, const 
     default:
       return fail(KCG_ERR_UNSUPPORTED, "layernorm_stats: dtype %d has no kernel (float32, bfloat16, float16)", dtype);
   }
+}
+
+// LayerNorm of a row block whose result is all-gathered by NVSwitch: every row is stored once, with
+// multimem.st, to its place in a multicast mapping of all ranks' gathered tensors.
+extern "C" int kcg_layernorm_allgather_multicast(int dtype, int64_t rows, int64_t cols, const void* x, const void* gamma,
+                                                 const void* beta, float eps, void* gathered_multicast,
+                                                 int64_t row_offset, void* stream) {
+  using namespace kcg;
+  clear_error();
+  if (rows < 0 || cols < 0 || row_offset < 0) return fail(KCG_ERR_INVALID_ARG, "layernorm_allgather_multicast: negative size");
+  if (rows == 0 || cols == 0) return KCG_OK;
+  if (!x || !gamma || !beta || !gathered_multicast) return fail(KCG_ERR_INVALID_ARG, "layernorm_allgather_multicast: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* y = static_cast<char*>(gathered_multicast) + static_cast<size_t>(row_offset) * cols * kcg_dtype_size(dtype);
+  int rc;
+  switch (dtype) {
+    case KCG_F32:
+      rc = launch_ln<float>(rows, cols, static_cast<const float*>(x), static_cast<const float*>(gamma),
+                            static_cast<const float*>(beta), eps, reinterpret_cast<float*>(y), s, nullptr, nullptr, nullptr, 1);
+      break;
+    case KCG_BF16:
+      rc = launch_ln<__nv_bfloat16>(rows, cols, static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma),
+                                    static_cast<const __nv_bfloat16*>(beta), eps, reinterpret_cast<__nv_bfloat16*>(y), s,
+                                    nullptr, nullptr, nullptr, 1);
+      break;
+    case KCG_F16:
+      rc = launch_ln<__half>(rows, cols, static_cast<const __half*>(x), static_cast<const __half*>(gamma),
+                             static_cast<const __half*>(beta), eps, reinterpret_cast<__half*>(y), s, nullptr, nullptr, nullptr, 1);
+      break;
+    default:
+      return fail(KCG_ERR_UNSUPPORTED, "layernorm_allgather_multicast: dtype %d has no kernel (float32, bfloat16, float16)", dtype);
+  }
+  if (rc == KCG_ERR_UNSUPPORTED && kcg_last_error()[0] == 0)
+    return fail(KCG_ERR_UNSUPPORTED, "layernorm_allgather_multicast: rows of %lld elements are beyond the one-pass kernels "
+                                     "(16-byte vectorisable rows of at most 4096 vectors)", static_cast<long long>(cols));
+  return rc;
 }

@@ -217,6 +217,44 @@ class GatherBuffers:
             self._own = None
 
 
+class MulticastBuffers:
+    """One [total_rows, cols] matrix per rank in symmetric memory that is also bound to an NVLink
+    multicast object, so that one store to ``mc_ptr + offset`` lands in every rank's matrix.
+
+    The allocation, the exchange of handles and the multicast binding are torch's
+    (``torch.distributed._symmetric_memory``): plumbing.  ``local`` is this rank's matrix, ``ptrs[r]``
+    rank r's matrix as seen from this process (usable for plain peer stores), ``mc_ptr`` the
+    multicast address of the matrix (0 when the fabric or the driver offers no multicast: the gather
+    epilogues then fall back to one peer store per rank).  Collective: every rank constructs it and
+    calls ``close()``; no rank may exit while its memory is still bound, so ``close()`` ends with a
+    barrier and drops the mapping on every rank before any of them moves on.
+    """
+
+    def __init__(self, total_rows: int, cols: int, dtype: torch.dtype, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.world, self.rank = world_and_rank(group)
+        self.group = group
+        self.total_rows, self.cols, self.dtype = int(total_rows), int(cols), dtype
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.local = symm_mem.empty((self.total_rows, self.cols), dtype=dtype, device=dev)
+        pg = group if group is not None else dist.group.WORLD
+        self._handle = symm_mem.rendezvous(self.local, pg)
+        off = int(getattr(self._handle, "offset", 0))
+        self.ptrs = [int(p) + off for p in self._handle.buffer_ptrs]
+        mc = int(self._handle.multicast_ptr or 0)
+        self.mc_ptr = mc + off if mc else 0
+
+    def close(self) -> None:
+        torch.cuda.synchronize()
+        if self.world > 1 and dist.is_initialized():
+            dist.barrier(group=self.group)
+        self._handle = None
+        self.local = None
+        self.mc_ptr = 0
+        if self.world > 1 and dist.is_initialized():
+            dist.barrier(group=self.group)
+
+
 _barrier_word = {}
 
 
@@ -260,12 +298,21 @@ def matmul_allgather(A_local: torch.Tensor, B: torch.Tensor, bufs: GatherBuffers
     stream = torch.cuda.current_stream().cuda_stream
     if sync and bufs.world > 1:
         stream_barrier(bufs.group)
-    arr = (ctypes.c_void_p * bufs.world)(*bufs.ptrs)
-    _lib.check(_lib.load().kcg_gemm_allgather(
-        ops._dt(A_local), ops._DT[bufs.dtype], M, N, K, 0, int(trans_b), A_local.data_ptr(), A_local.stride(0),
-        B.data_ptr(), B.stride(0), arr, bufs.world, bufs.rank, begin, bufs.cols,
-        scale_a.data_ptr() if scale_a is not None else None, scale_b.data_ptr() if scale_b is not None else None,
-        bias.data_ptr() if bias is not None else None, act, stream), "kcg_gemm_allgather")
+    sa = scale_a.data_ptr() if scale_a is not None else None
+    sb = scale_b.data_ptr() if scale_b is not None else None
+    bp = bias.data_ptr() if bias is not None else None
+    if getattr(bufs, "mc_ptr", 0):
+        # one multimem.st per tile segment; NVSwitch delivers it to every rank's matrix
+        _lib.check(_lib.load().kcg_gemm_allgather_multicast(
+            ops._dt(A_local), ops._DT[bufs.dtype], M, N, K, 0, int(trans_b), A_local.data_ptr(), A_local.stride(0),
+            B.data_ptr(), B.stride(0), bufs.ptrs[bufs.rank], bufs.mc_ptr, begin, bufs.cols, sa, sb, bp, act, stream),
+            "kcg_gemm_allgather_multicast")
+    else:
+        arr = (ctypes.c_void_p * bufs.world)(*bufs.ptrs)
+        _lib.check(_lib.load().kcg_gemm_allgather(
+            ops._dt(A_local), ops._DT[bufs.dtype], M, N, K, 0, int(trans_b), A_local.data_ptr(), A_local.stride(0),
+            B.data_ptr(), B.stride(0), arr, bufs.world, bufs.rank, begin, bufs.cols, sa, sb, bp, act, stream),
+            "kcg_gemm_allgather")
     if sync and bufs.world > 1:
         stream_barrier(bufs.group)
     return bufs.local
@@ -295,11 +342,17 @@ def fmha_allgather(Q_local: torch.Tensor, K_local: torch.Tensor, V_local: torch.
     ost = (ctypes.c_int64 * 3)(H * Sq * D, Sq * D, D)
     if sync and bufs.world > 1:
         stream_barrier(bufs.group)
-    arr = (ctypes.c_void_p * bufs.world)(*bufs.ptrs)
-    _lib.check(_lib.load().kcg_fmha_fwd_allgather(
-        ops._dt(Q_local), Bl, H, Sq, Skv, D, float(softmax_scale), int(causal), Q_local.data_ptr(), st(Q_local),
-        K_local.data_ptr(), st(K_local), V_local.data_ptr(), st(V_local), arr, bufs.world, bufs.rank, begin, ost,
-        torch.cuda.current_stream().cuda_stream), "kcg_fmha_fwd_allgather")
+    if getattr(bufs, "mc_ptr", 0):
+        _lib.check(_lib.load().kcg_fmha_fwd_allgather_multicast(
+            ops._dt(Q_local), Bl, H, Sq, Skv, D, float(softmax_scale), int(causal), Q_local.data_ptr(), st(Q_local),
+            K_local.data_ptr(), st(K_local), V_local.data_ptr(), st(V_local), bufs.ptrs[bufs.rank], bufs.mc_ptr, begin, ost,
+            torch.cuda.current_stream().cuda_stream), "kcg_fmha_fwd_allgather_multicast")
+    else:
+        arr = (ctypes.c_void_p * bufs.world)(*bufs.ptrs)
+        _lib.check(_lib.load().kcg_fmha_fwd_allgather(
+            ops._dt(Q_local), Bl, H, Sq, Skv, D, float(softmax_scale), int(causal), Q_local.data_ptr(), st(Q_local),
+            K_local.data_ptr(), st(K_local), V_local.data_ptr(), st(V_local), arr, bufs.world, bufs.rank, begin, ost,
+            torch.cuda.current_stream().cuda_stream), "kcg_fmha_fwd_allgather")
     if sync and bufs.world > 1:
         stream_barrier(bufs.group)
     return bufs.local.view(total_batches, H, Sq, D)

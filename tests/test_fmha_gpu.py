@@ -57,7 +57,8 @@ def variant(request):
 # Every kernel the library ships is held to the same parity bar, not only the one the default
 # picks for a shape: 0 / 1 = one query tile per CTA with P through shared / tensor memory (also
 # for long sequences), 2 = two query tiles per CTA (also for a single, partly empty tile pair),
-# 3 = a CTA pair on four query tiles (also when most of the four are empty; D = 64 runs variant 2).
+# 3 = a CTA pair on four query tiles (also when most of the four are empty), 4 = a CTA pair with one
+# tile per CTA whose warpgroups take alternate key blocks (D = 64 runs variant 2 for both).
 @pytest.mark.parametrize("variant", [0, 1, 2, 3, 4], indirect=True)
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("causal", [False, True])

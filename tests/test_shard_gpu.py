@@ -58,6 +58,32 @@ def _worker(rank, world, port, results):
             ok = ok and torch.equal(out, ops.fmha(Q, K, V, 128 ** -0.5, True))
         finally:
             fb.close()
+        # the same two gathers with the replication done by NVSwitch (multimem.st to a multicast
+        # mapping; torch's symmetric memory does the binding).  Where the fabric offers no multicast
+        # mc_ptr is 0 and the calls take the peer-store path over the same buffers.
+        mb = None
+        try:
+            mb = shard.MulticastBuffers(A.shape[0], B.shape[1], torch.bfloat16)
+        except Exception as exc:   # noqa: BLE001 - symmetric memory may be unavailable on a host
+            print(f"rank {rank}: symmetric memory unavailable: {exc}", flush=True)
+        if mb is not None:
+            try:
+                for _ in range(2):
+                    mb.local.zero_()
+                    out = shard.matmul_allgather(A[b0:b0 + c0].contiguous(), B, mb)
+                torch.cuda.synchronize()
+                ok = ok and torch.equal(out, full)
+                print(f"rank {rank}: multicast gather used: {bool(mb.mc_ptr)}", flush=True)
+            finally:
+                mb.close()
+            mf = shard.MulticastBuffers(6 * 2 * 256, 128, torch.bfloat16)
+            try:
+                out = shard.fmha_allgather(shard.shard_rows(Q).contiguous(), shard.shard_rows(K).contiguous(),
+                                           shard.shard_rows(V).contiguous(), mf, 6, 128 ** -0.5, True)
+                torch.cuda.synchronize()
+                ok = ok and torch.equal(out, ops.fmha(Q, K, V, 128 ** -0.5, True))
+            finally:
+                mf.close()
         # the C entry a host program without Python uses: an NCCL communicator made through the
         # library's own wrappers (the id travels by other means, here torch's object broadcast),
         # then the in-place gather of a row-sharded buffer, with even and with ragged blocks
