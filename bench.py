@@ -964,6 +964,15 @@ def main() -> None:
                 dist.all_gather_into_tensor(yg, y)
             ms = timed_loop(nccl_l, 3)
             rec["gather_nccl_ms"] = ms
+            mb = multicast_buffers(Rt, Ct)
+            if mb is not None:
+                def mc_l():
+                    shard.layernorm_allgather(x, g2, b2, mb, 1e-5, sync=False)
+                    shard.stream_barrier()
+                ms = timed_loop(mc_l, 3)
+                rec["gather_multicast_ms"] = ms
+                rec["gather_multicast_bit_identical_to_nccl"] = bool(torch.equal(mb.local, yg))
+                mb.close()
             del yg
         sharded["layernorm_bf16_262144x8192"] = rec
         del x, y

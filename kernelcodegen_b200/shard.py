@@ -356,3 +356,32 @@ def fmha_allgather(Q_local: torch.Tensor, K_local: torch.Tensor, V_local: torch.
     if sync and bufs.world > 1:
         stream_barrier(bufs.group)
     return bufs.local.view(total_batches, H, Sq, D)
+
+
+def layernorm_allgather(x_local: torch.Tensor, scale: torch.Tensor, bias: torch.Tensor, bufs: "MulticastBuffers",
+                        eps: float = 1e-5, sync: bool = True) -> torch.Tensor:
+    """Replicated LayerNorm (over the last dim) of a row-sharded [total_rows, cols] tensor: each rank
+    normalises its rows and stores every row once, to the multicast mapping of ``bufs``, so NVSwitch
+    places it in every rank's matrix.  Needs buffers with a multicast address (``bufs.mc_ptr``);
+    returns ``bufs.local``."""
+    from . import ops
+    if not getattr(bufs, "mc_ptr", 0):
+        raise ValueError("layernorm_allgather needs MulticastBuffers with a multicast mapping")
+    if x_local.dim() != 2 or x_local.shape[1] != bufs.cols or x_local.dtype != bufs.dtype:
+        raise ValueError("x_local must be [rows, cols] of the buffers' dtype and width")
+    if not (x_local.is_cuda and x_local.is_contiguous()):
+        raise ValueError("operands must be contiguous CUDA tensors")
+    for t in (scale, bias):
+        if tuple(t.shape) != (bufs.cols,) or t.dtype != x_local.dtype or not t.is_cuda:
+            raise ValueError("scale and bias hold one value per column, in the input's dtype, on the device")
+    begin, count = _lib.shard_range(bufs.total_rows, bufs.world, bufs.rank, 1)
+    if count != x_local.shape[0]:
+        raise ValueError(f"this rank owns {count} rows of the gathered tensor, x_local has {x_local.shape[0]}")
+    if sync and bufs.world > 1:
+        stream_barrier(bufs.group)
+    _lib.check(_lib.load().kcg_layernorm_allgather_multicast(
+        ops._dt(x_local), count, bufs.cols, x_local.data_ptr(), scale.data_ptr(), bias.data_ptr(), float(eps),
+        bufs.mc_ptr, begin, torch.cuda.current_stream().cuda_stream), "kcg_layernorm_allgather_multicast")
+    if sync and bufs.world > 1:
+        stream_barrier(bufs.group)
+    return bufs.local
