@@ -309,10 +309,11 @@ KCG_API int kcg_gemm_fused(int dtype_in, int dtype_out, int64_t M, int64_t N, in
 
 /*
  * Tuning switch with no counterpart in the reference, choosing the tile of the tensor-core
- * GEMM: -1 (default) picks, per problem, whichever of the three shapes below fills the SMs most
+ * GEMM: -1 (default) picks, per problem, whichever of the shapes below fills the SMs most
  * evenly (large problems get CTA pairs); 0 forces 128x256 tiles on single CTAs; 1 forces CTA
  * pairs (tcgen05 cta_group::2, one 256x256 tile per two SMs) whenever M > 128; 2 forces 128x128
- * tiles on single CTAs.  Results are identical.  A setting of the calling thread.
+ * and 3 forces 128x64 tiles on single CTAs (the latter for 16-bit inputs; 8-bit and tf32 inputs
+ * get 128x128).  Results are identical.  A setting of the calling thread.
  */
 KCG_API void kcg_gemm_set_pair_mode(int mode);
 

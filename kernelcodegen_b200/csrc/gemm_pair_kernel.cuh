@@ -11,7 +11,8 @@
 //   - TMA completion bytes of both CTAs are counted on the leader's (rank 0) full barrier;
 //   - one thread of the leader issues the MMAs and releases ring stages / publishes finished
 //     accumulators in both CTAs with a two-CTA tcgen05.commit;
-//   - the peer's epilogue warps hand accumulators back with a remote mbarrier arrive.
+//   - the epilogue warps of both CTAs (eight each, two per lane quarter) hand accumulators back
+//     with an mbarrier arrive on the leader's barrier.
 #pragma once
 
 constexpr int PSTAGES = 6;
@@ -19,8 +20,8 @@ constexpr int PA_BYTES = 128 * 128;           // 128 rows x 128 bytes of K
 constexpr int PB_BYTES = 128 * 128;           // this CTA's half of the B tile
 constexpr int PSTAGE_BYTES = PA_BYTES + PB_BYTES;
 constexpr int PBM = 256, PBN = 256;           // tile of the pair
-constexpr int PEPI_STAGE_BYTES = 32 * 128;   // per epilogue warp: 32 rows x 128 bytes of output
-constexpr int PSMEM_BYTES = PSTAGES * PSTAGE_BYTES + 1024 + 256 + 4 * PEPI_STAGE_BYTES;
+constexpr int PEPI_STAGE_BYTES = EPI_STAGE_BYTES;   // per epilogue warp: 32 rows x 128 bytes of output
+constexpr int PSMEM_BYTES = PSTAGES * PSTAGE_BYTES + 1024 + 256 + EPI_WARPS * PEPI_STAGE_BYTES;
 
 __device__ __forceinline__ void pair_tile_coords(int64_t tile, int m_pairs, int n_tiles, int group_m, int& b, int& mp, int& nt) {
   const int64_t per_batch = static_cast<int64_t>(m_pairs) * n_tiles;
@@ -38,7 +39,7 @@ __device__ __forceinline__ void pair_tile_coords(int64_t tile, int m_pairs, int 
 template <Kind kKind, int kElemBytes, bool kAMn, bool kBMn, typename TOut>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                         const GemmParams p, const uint32_t idesc) {
+                         const __grid_constant__ CUtensorMap tmC, const GemmParams p, const uint32_t idesc) {
   constexpr int BK = 128 / kElemBytes;
   constexpr int UMMA_K = 32 / kElemBytes;
   constexpr int MN_BOX = 128 / kElemBytes;
@@ -48,7 +49,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PSTAGES * PSTAGE_BYTES);
+  uint8_t* epi_stage = smem + PSTAGES * PSTAGE_BYTES;   // [EPI_WARPS] x 4 KB, 1024-byte aligned like the ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + EPI_WARPS * PEPI_STAGE_BYTES);
   uint64_t* full_bar = bars;                    // [PSTAGES]  used in the leader
   uint64_t* empty_bar = bars + PSTAGES;         // [PSTAGES]  one per CTA
   uint64_t* tfull_bar = bars + 2 * PSTAGES;     // [2]        one per CTA
@@ -66,13 +68,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    if (p.c_tma) prefetch_tmap(&tmC);
     for (int s = 0; s < PSTAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 8);
+      mbar_init(&tempty_bar[a], 2 * EPI_WARPS);
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -92,16 +95,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer (both CTAs)
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, s = 0, ph = 0;
       bool ok = true;
       for (int64_t tile = cluster_id; tile < total && ok; tile += n_clusters) {
         int b, mp, nt;
         pair_tile_coords(tile, m_pairs, p.n_tiles, p.group_m, b, mp, nt);
         const int m0 = mp * PBM + static_cast<int>(rank) * 128;
         const int n0 = nt * PBN + static_cast<int>(rank) * 128;
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % PSTAGES, ph = (it / PSTAGES) & 1u;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it, ph ^= (s + 1 == PSTAGES), s = (s + 1 == PSTAGES ? 0 : s + 1)) {
+          // the first pass over the ring finds every stage free without asking
+          if (it >= PSTAGES && !mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* a_dst = smem + s * PSTAGE_BYTES;
           uint8_t* b_dst = a_dst + PA_BYTES;
           // completion bytes of both CTAs go to the leader's barrier
@@ -110,6 +113,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const int k0 = kb * BK;
           if constexpr (!kAMn) {
             tma_load_3d_pair(a_dst, &tmA, bar, k0, m0, b);
+          } else if (p.a_blocked && PA_BYTES / MN_BOX_BYTES > 1) {
+            tma_load_4d_pair(a_dst, &tmA, bar, 0, k0, m0 / MN_BOX, b);   // all 128-byte column blocks in one copy
           } else {
 #pragma unroll
             for (int j = 0; j < PA_BYTES / MN_BOX_BYTES; ++j)
@@ -117,6 +122,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           }
           if constexpr (!kBMn) {
             tma_load_3d_pair(b_dst, &tmB, bar, k0, n0, b);
+          } else if (p.b_blocked && PB_BYTES / MN_BOX_BYTES > 1) {
+            tma_load_4d_pair(b_dst, &tmB, bar, 0, k0, n0 / MN_BOX, b);
           } else {
 #pragma unroll
             for (int j = 0; j < PB_BYTES / MN_BOX_BYTES; ++j)
@@ -133,7 +140,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader only)
     if (lane == 0 && rank == 0) {
-      uint32_t it = 0, tile_iter = 0;
+      uint32_t tile_iter = 0;
       bool ok = true;
       const uint32_t smem_base = smem_u32(smem);
       const uint64_t adesc0 = kAMn ? make_smem_desc(smem_base, MN_BOX_BYTES, 1024) : make_smem_desc(smem_base, 16, 1024);
@@ -141,20 +148,21 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                                    : make_smem_desc(smem_base + PA_BYTES, 16, 1024);
       constexpr uint32_t kStageStep = PSTAGE_BYTES >> 4;
       constexpr uint32_t kAStep = (kAMn ? MN_KSTEP : 32) >> 4, kBStep = (kBMn ? MN_KSTEP : 32) >> 4;
+      static_assert(BK / UMMA_K == 4, "mma_kblock issues four k-steps");
+      const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+      uint32_t s = 0, ph = 0;
+      bool ready = false;   // the stage about to be used was seen full by the test issued with the previous k-block
       for (int64_t tile = cluster_id; tile < total && ok; tile += n_clusters, ++tile_iter) {
         const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1u, abort_flag)) { ok = false; break; }
-        tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * PBN;
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % PSTAGES, ph = (it / PSTAGES) & 1u;
-          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!ready && !mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t adesc = adesc0 + s * kStageStep, bdesc = bdesc0 + s * kStageStep;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            mma_ss_pair<kKind>(d_tmem, adesc + k * kAStep, bdesc + k * kBStep, idesc, (kb | k) != 0 ? 1u : 0u);
-          mma_commit_pair(&empty_bar[s], 3);
+          const uint32_t s1 = s + 1 == PSTAGES ? 0u : s + 1, ph1 = s + 1 == PSTAGES ? ph ^ 1u : ph;
+          ready = mma_kblock<kKind, true>(d_tmem, adesc0 + s * kStageStep, bdesc0 + s * kStageStep, kAStep, kBStep, idesc,
+                                          kb != 0 ? 1u : 0u, empty0 + s * 8, 3, full0 + s1 * 8, ph1);
+          s = s1; ph = ph1;
         }
         if (ok) mma_commit_pair(&tfull_bar[acc], 3);
       }
@@ -168,7 +176,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- epilogue (both CTAs)
-    const int quarter = warp & 3;
+    const int quarter = warp & 3, col_half = (warp - 2) >> 2;
     float alpha = 1.f;
     if (p.scale_a) alpha *= *p.scale_a;
     if (p.scale_b) alpha *= *p.scale_b;
@@ -192,10 +200,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         // the granularity a store to another GPU's memory should have — and every
         // destination receives the same registers.
         constexpr int RC = 128 / static_cast<int>(sizeof(TOut));   // columns per round
-        uint8_t* stg = smem + PSTAGES * PSTAGE_BYTES + 256 + quarter * PEPI_STAGE_BYTES;
+        uint8_t* stg = epi_stage + (warp - 2) * PEPI_STAGE_BYTES;
         const int64_t tile_row0 = static_cast<int64_t>(mp) * PBM + rank * 128 + quarter * 32;
 #pragma unroll 1
-        for (int c = 0; c < PBN / RC; ++c) {
+        for (int c = col_half; c < PBN / RC; c += EPI_WARPS / 4) {
           const int peer0 = p.n_extra > 0 ? static_cast<int>((blockIdx.x + quarter + c) % static_cast<unsigned>(p.n_extra)) : 0;
           uint32_t r[RC];
           if constexpr (RC == 64) tmem_ld64(t_base + c * RC, r); else tmem_ld32(t_base + c * RC, r);
@@ -234,8 +242,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           }
           __syncwarp();
         }
+      } else if (p.c_tma) {
+        epilogue_rows_tma<TOut, PBN>(t_base, epi_stage + (warp - 2) * PEPI_STAGE_BYTES, &tmC,
+                                     mp * PBM + static_cast<int>(rank) * 128 + quarter * 32, static_cast<int>(col0), b, p,
+                                     alpha, bias, col_half, EPI_WARPS / 4, lane);
       } else {
-        epilogue_row<TOut, PBN>(t_base, crow, row < p.M, col0, p, alpha, bias);
+        epilogue_row<TOut, PBN>(t_base, crow, row < p.M, col0, p, alpha, bias, col_half, EPI_WARPS / 4);
       }
       tc_fence_before();
       __syncwarp();
@@ -246,6 +258,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       *p.status = KCG_ERR_TIMEOUT;
       __threadfence_system();
     }
+    if (p.c_tma && lane == 0) tma_store_wait_all<0>();   // this lane's TMA stores have been written
   }
 
   // Neither CTA may leave (or free tensor memory) while the other can still signal it.

@@ -6,14 +6,14 @@
 // register/shared double buffer.  The Blackwell design keeps the same roles — stage
 // operand tiles in shared memory, accumulate a C tile on chip, write it once — but maps
 // them to the hardware units that exist for it:
-//   warp 0      TMA producer: cp.async.bulk.tensor loads of 128-byte-swizzled A and B
-//               tiles into a 4-stage ring, completion counted on mbarriers;
-//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=32 bytes) from
-//               shared-memory descriptors into one of two 128x256 fp32 accumulators in
-//               tensor memory, and releases ring stages with tcgen05.commit;
-//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (one TMEM lane quarter per
-//               warp), scale, convert and store, while the MMA warp already fills the
-//               other accumulator with the next tile.
+//   warp 0      TMA producer (one thread): cp.async.bulk.tensor loads of 128-byte-swizzled A
+//               and B tiles into a ring, completion counted on mbarriers;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256/128/64, K=32 bytes) from
+//               shared-memory descriptors into one of two fp32 accumulators in tensor memory,
+//               and releases ring entries with tcgen05.commit;
+//   warps 2-9   epilogue: tcgen05.ld the finished accumulator (two warps per TMEM lane quarter,
+//               each half of the columns), scale, convert and store, while the MMA warp already
+//               fills the other accumulator with the next tile.
 // CTAs are persistent (one per SM) and walk the tile list in an M-grouped order so that
 // the tiles in flight share A row-blocks and B column-blocks in L2 (the reference's
 // unused GROUP_SIZE_M, include/KernelCodeGen.h:36).
@@ -36,11 +36,14 @@ using namespace sm100;
 
 constexpr int BM = 128, BN = 256;
 constexpr int A_BYTES = BM * 128;
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;                     // two per tensor-memory lane quarter
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int GROUP_M = 16;
 #define KCG_MAX_EXTRA_C 7
-constexpr int SMEM_BYTES = 4 * (A_BYTES + BN * 128) + 1024 + 256;   // = 6 * (A_BYTES + 128 * 128) + ... for the narrow tile
+constexpr int EPI_STAGE_BYTES = 32 * 128;            // per epilogue warp: 32 rows x 128 bytes of output on their way out
+constexpr int RING_BYTES = 4 * (A_BYTES + BN * 128);  // = 6 x 32 KB (128-wide tile) = 8 x 24 KB (64-wide tile)
+constexpr int SMEM_BYTES = RING_BYTES + EPI_WARPS * EPI_STAGE_BYTES + 1024 + 256;
 
 struct GemmParams {
   void* C;
@@ -63,6 +66,12 @@ struct GemmParams {
   // then stored once, to this address, instead of to C and every extra_c.
   void* mc_c;
   int group_m;   // row tiles (of 128) per group of the tile order
+  // An MN-major operand whose rows are whole 128-byte blocks is described by a rank-4 map
+  // {128 bytes, K, blocks, batch}: one TMA copy then brings all column blocks of a tile (the
+  // copy engine, not the issuing thread, pays a fixed price per copy: an MN-major B tile of 256
+  // columns in four copies held the 128x256 kernel at 650-700 clocks per k-block instead of 545).
+  int a_blocked, b_blocked;
+  int c_tma;     // C is written with TMA stores from a staged tile (needs c_vec_ok; see epilogue_rows_tma)
 };
 
 __device__ __forceinline__ void tile_coords(int64_t tile, const GemmParams& p, int& b, int& mt, int& nt) {
@@ -107,25 +116,29 @@ template <> __device__ __forceinline__ uint4 scale_pack16<__half>(const uint32_t
 // Epilogue of one thread for its row of a finished accumulator (kTileN columns starting at
 // col0): tensor memory is read 64 columns per round trip; full, aligned blocks without bias or
 // activation take the packed path above, everything else goes element by element.
-template <typename TOut, int kTileN>
+//
+// kChunk columns travel per round trip (64, or 32 for the 64-wide tile); a thread takes the chunks
+// first, first + step, ... so that two warps on the same lane quarter can share a row.
+template <typename TOut, int kTileN, int kChunk = 64>
 __device__ __forceinline__ void epilogue_row(uint32_t t_base, TOut* crow, bool row_ok, int64_t col0,
-                                             const GemmParams& p, float alpha, const TOut* bias) {
+                                             const GemmParams& p, float alpha, const TOut* bias,
+                                             int first = 0, int step = 1) {
   constexpr int VW = Vec16<TOut>::N;
   const bool plain = bias == nullptr && p.act == 0 && p.c_vec_ok != 0;
 #pragma unroll 1
-  for (int c = 0; c < kTileN / 64; ++c) {
-    uint32_t r[64];
-    tmem_ld64(t_base + c * 64, r);
+  for (int c = first; c < kTileN / kChunk; c += step) {
+    uint32_t r[kChunk];
+    if constexpr (kChunk == 64) tmem_ld64(t_base + c * kChunk, r); else tmem_ld32(t_base + c * kChunk, r);
     tmem_wait_ld();
     if (!row_ok) continue;
-    const int64_t cbase = col0 + c * 64;
-    if (plain && cbase + 64 <= p.N) {
+    const int64_t cbase = col0 + c * kChunk;
+    if (plain && cbase + kChunk <= p.N) {
 #pragma unroll
-      for (int g = 0; g < 64 / VW; ++g)
+      for (int g = 0; g < kChunk / VW; ++g)
         *reinterpret_cast<uint4*>(crow + cbase + g * VW) = scale_pack16<TOut>(&r[g * VW], alpha);
     } else {
 #pragma unroll
-      for (int g = 0; g < 64 / VW; ++g) {
+      for (int g = 0; g < kChunk / VW; ++g) {
         const int64_t col = cbase + g * VW;
         if (p.c_vec_ok && col + VW <= p.N) {
           Vec16<TOut> o;
@@ -142,17 +155,79 @@ __device__ __forceinline__ void epilogue_row(uint32_t t_base, TOut* crow, bool r
   }
 }
 
-// kBN: width of the CTA tile, 256 (4-stage ring of 48 KB) or 128 (6 stages of 32 KB).  The narrow
-// tile costs more shared-memory and L2 traffic per flop but quantises better: it is chosen when
-// the problem has too few 128x256 tiles to fill the SMs evenly (see pick_tiling()).
+// The same rows written through shared memory and TMA.  One thread per accumulator row is how
+// tensor memory hands the data out, but stored that way every warp instruction touches 32
+// different 128-byte lines with 16 bytes each — a 128x256 tile of 16-bit outputs is 4096 such
+// sector writes and took about 2 us, all of it exposed when a CTA has a single tile.  Here a warp
+// packs 128 bytes per row into a swizzled 4 KB staging tile of its own and one lane hands the
+// 32-row box to the copy engine, which writes whole lines and clips at M and N.
+template <typename TOut, int kTileN>
+__device__ __forceinline__ void epilogue_rows_tma(uint32_t t_base, uint8_t* stg, const CUtensorMap* tmC, int row0, int col0,
+                                                  int batch, const GemmParams& p, float alpha, const TOut* bias,
+                                                  int first, int step, int lane) {
+  constexpr int VW = Vec16<TOut>::N;
+  constexpr int RC = 128 / static_cast<int>(sizeof(TOut));   // columns per round: 128 bytes of output per row
+  const bool plain = bias == nullptr && p.act == 0;
+  bool pending = false;
+#pragma unroll 1
+  for (int c = first; c < kTileN / RC; c += step) {
+    uint32_t r[RC];
+    if constexpr (RC == 64) tmem_ld64(t_base + c * RC, r); else tmem_ld32(t_base + c * RC, r);
+    tmem_wait_ld();
+    const int cbase = col0 + c * RC;
+    if (cbase >= p.N || row0 >= p.M) continue;   // nothing of this box lies inside C
+    if (pending) {   // the copy engine has read the previous round out of the staging tile
+      if (lane == 0) tma_store_wait_read<0>();
+      __syncwarp();
+    }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      uint4 v;
+      if (plain) {
+        v = scale_pack16<TOut>(&r[g * VW], alpha);
+      } else {
+        Vec16<TOut> o;
+        const int64_t col = cbase + g * VW;
+#pragma unroll
+        for (int j = 0; j < VW; ++j)
+          o.v[j] = col + j < p.N ? gemm_epilogue_value<TOut>(__uint_as_float(r[g * VW + j]), alpha, bias, col + j, p.act)
+                                 : TOut(0.f);
+        v = *reinterpret_cast<const uint4*>(&o);
+      }
+      *reinterpret_cast<uint4*>(stg + lane * 128 + ((g ^ (lane & 7)) << 4)) = v;
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_3d(tmC, stg, cbase, row0, batch);
+      tma_store_commit();
+    }
+    pending = true;
+  }
+  // the staging tile is free again (and, for the kernel's last tile, the data on its way) before
+  // the warp moves on
+  if (pending && lane == 0) tma_store_wait_read<0>();
+  __syncwarp();
+}
+
+// kBN: width of the CTA tile, 256 (4-stage ring of 48 KB), 128 (6 stages of 32 KB) or 64 (8 stages
+// of 24 KB).  The narrower tiles cost more shared-memory and L2 traffic per flop but quantise
+// better: they are chosen when the problem has too few wide tiles to fill the SMs (see
+// pick_tiling()).  Eight epilogue warps, two per tensor-memory lane quarter, split a tile's columns:
+// small problems run one tile per CTA, so nothing hides the epilogue and its latency counts in full.
 template <Kind kKind, int kElemBytes, bool kAMn, bool kBMn, typename TOut, int kBN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmParams p, const uint32_t idesc) {
+                    const __grid_constant__ CUtensorMap tmC, const GemmParams p, const uint32_t idesc) {
   constexpr int BN = kBN;
   constexpr int B_BYTES = BN * 128;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int STAGES = kBN == 256 ? 4 : 6;
+  constexpr int STAGES = kBN == 256 ? 4 : (kBN == 128 ? 6 : 8);
+  // Ring entries ("units") of kSub stages share one pair of barriers: the MMA thread's cost per
+  // k-block, not the tensor pipe, bounds the narrow tiles, and a commit per 64 of K is a large
+  // part of it.  The wide tile is pipe-bound and keeps the finer ring.
+  constexpr int kSub = kBN == 256 ? 1 : 2;
+  constexpr int UNITS = STAGES / kSub;
   constexpr int BK = 128 / kElemBytes;             // elements per k-block (128 bytes of K)
   constexpr int UMMA_K = 32 / kElemBytes;          // elements per MMA (32 bytes of K)
   constexpr int MN_BOX = 128 / kElemBytes;         // inner extent of an MN-major TMA box
@@ -162,7 +237,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  static_assert(STAGES * STAGE_BYTES == RING_BYTES, "every tile width uses the whole ring");
+  uint8_t* epi_stage = smem + RING_BYTES;    // [EPI_WARPS] x 4 KB, 1024-byte aligned like the ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + EPI_WARPS * EPI_STAGE_BYTES);
   uint64_t* full_bar = bars;                 // [STAGES]
   uint64_t* empty_bar = bars + STAGES;       // [STAGES]
   uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]
@@ -176,13 +253,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
-    for (int s = 0; s < STAGES; ++s) {
+    if (p.c_tma) prefetch_tmap(&tmC);
+    for (int s = 0; s < UNITS; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], EPI_WARPS);
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -206,32 +284,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, s = 0, ph = 0;   // it: ring units filled so far; s, ph: unit and its phase
       bool ok = true;
       for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
         int b, mt, nt;
         tile_coords(tile, p, b, mt, nt);
         const int m0 = mt * BM, n0 = nt * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-          uint8_t* a_dst = smem + s * STAGE_BYTES;
-          uint8_t* b_dst = a_dst + A_BYTES;
-          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          const int k0 = kb * BK;
-          if constexpr (!kAMn) {
-            tma_load_3d(a_dst, &tmA, &full_bar[s], k0, m0, b);
-          } else {
+        for (int kb = 0; kb < p.k_blocks; kb += kSub, ++it, ph ^= (s + 1 == UNITS), s = (s + 1 == UNITS ? 0 : s + 1)) {
+          // the first pass over the ring finds every unit free without asking
+          if (it >= UNITS && !mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          const int nsub = min(kSub, p.k_blocks - kb);
+          mbar_expect_tx(&full_bar[s], nsub * STAGE_BYTES);
 #pragma unroll
-            for (int j = 0; j < A_BYTES / MN_BOX_BYTES; ++j)
-              tma_load_3d(a_dst + j * MN_BOX_BYTES, &tmA, &full_bar[s], m0 + j * MN_BOX, k0, b);
-          }
-          if constexpr (!kBMn) {
-            tma_load_3d(b_dst, &tmB, &full_bar[s], k0, n0, b);
-          } else {
+          for (int u = 0; u < kSub; ++u) {
+            if (u >= nsub) break;
+            uint8_t* a_dst = smem + (s * kSub + u) * STAGE_BYTES;
+            uint8_t* b_dst = a_dst + A_BYTES;
+            const int k0 = (kb + u) * BK;
+            if constexpr (!kAMn) {
+              tma_load_3d(a_dst, &tmA, &full_bar[s], k0, m0, b);
+            } else if (p.a_blocked && A_BYTES / MN_BOX_BYTES > 1) {
+              tma_load_4d(a_dst, &tmA, &full_bar[s], 0, k0, m0 / MN_BOX, b);   // all 128-byte column blocks in one copy
+            } else {
 #pragma unroll
-            for (int j = 0; j < B_BYTES / MN_BOX_BYTES; ++j)
-              tma_load_3d(b_dst + j * MN_BOX_BYTES, &tmB, &full_bar[s], n0 + j * MN_BOX, k0, b);
+              for (int j = 0; j < A_BYTES / MN_BOX_BYTES; ++j)
+                tma_load_3d(a_dst + j * MN_BOX_BYTES, &tmA, &full_bar[s], m0 + j * MN_BOX, k0, b);
+            }
+            if constexpr (!kBMn) {
+              tma_load_3d(b_dst, &tmB, &full_bar[s], k0, n0, b);
+            } else if (p.b_blocked && B_BYTES / MN_BOX_BYTES > 1) {
+              tma_load_4d(b_dst, &tmB, &full_bar[s], 0, k0, n0 / MN_BOX, b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < B_BYTES / MN_BOX_BYTES; ++j)
+                tma_load_3d(b_dst + j * MN_BOX_BYTES, &tmB, &full_bar[s], n0 + j * MN_BOX, k0, b);
+            }
           }
         }
       }
@@ -239,9 +326,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!*abort_flag) { *abort_flag = 1; *p.status = KCG_ERR_TIMEOUT; __threadfence_system(); }
         // Let the copies that were already issued land before the CTA goes away.
         int zero = 0;
-        const uint32_t first = it > STAGES ? it - STAGES : 0;
+        const uint32_t first = it > UNITS ? it - UNITS : 0;
         for (uint32_t j = first; j < it; ++j)
-          mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1u, &zero, 2000000ull);
+          mbar_wait(&full_bar[j % UNITS], (j / UNITS) & 1u, &zero, 2000000ull);
       }
     }
   } else if (warp == 1) {
@@ -251,7 +338,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // of a stage are derived from one precomputed base by integer adds, and no other lane
     // takes part (no reconvergence after the barrier waits).
     if (lane == 0) {
-      uint32_t it = 0, tile_iter = 0;
+      uint32_t tile_iter = 0;
       bool ok = true;
       const uint32_t smem_base = smem_u32(smem);
       // Descriptors of k-step 0 in stage 0; later k-steps / stages differ only in the address
@@ -261,20 +348,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                    : make_smem_desc(smem_base + A_BYTES, 16, 1024);
       constexpr uint32_t kStageStep = STAGE_BYTES >> 4;
       constexpr uint32_t kAStep = (kAMn ? MN_KSTEP : 32) >> 4, kBStep = (kBMn ? MN_KSTEP : 32) >> 4;
+      static_assert(BK / UMMA_K == 4, "mma_kblock issues four k-steps");
+      const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+      // s / ph walk the ring of units; `ready` says that the unit about to be used was already
+      // seen full by the test that rode along with the previous unit's last MMAs.
+      uint32_t s = 0, ph = 0;
+      bool ready = false;
       for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tile_iter) {
         const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1u, abort_flag)) { ok = false; break; }
-        tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-          if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+        for (int kb = 0; kb < p.k_blocks; kb += kSub) {
+          if (!ready && !mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t adesc = adesc0 + s * kStageStep, bdesc = bdesc0 + s * kStageStep;
+          const uint32_t s1 = s + 1 == UNITS ? 0u : s + 1, ph1 = s + 1 == UNITS ? ph ^ 1u : ph;
+          uint32_t slot = s * kSub;
+          if constexpr (kSub > 1) {
+            // all but the last k-block of the unit: MMAs only
+            for (int u = 0; u + 1 < kSub && kb + u + 1 < p.k_blocks; ++u, ++slot) {
+              const uint64_t adesc = adesc0 + slot * kStageStep, bdesc = bdesc0 + slot * kStageStep;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            mma_ss<kKind>(d_tmem, adesc + k * kAStep, bdesc + k * kBStep, idesc, (kb | k) != 0 ? 1u : 0u);
-          mma_commit(&empty_bar[s]);
+              for (int k = 0; k < 4; ++k)
+                mma_ss<kKind>(d_tmem, adesc + k * kAStep, bdesc + k * kBStep, idesc, (kb | u | k) != 0 ? 1u : 0u);
+            }
+          }
+          ready = mma_kblock<kKind, false>(d_tmem, adesc0 + slot * kStageStep, bdesc0 + slot * kStageStep, kAStep, kBStep,
+                                           idesc, (kb != 0 || slot != s * kSub) ? 1u : 0u, empty0 + s * 8, 0,
+                                           full0 + s1 * 8, ph1);
+          s = s1; ph = ph1;
         }
         if (ok) mma_commit(&tfull_bar[acc]);
       }
@@ -288,7 +389,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int quarter = warp & 3;
+    const int quarter = warp & 3, col_half = (warp - 2) >> 2;
     float alpha = 1.f;
     if (p.scale_a) alpha *= *p.scale_a;
     if (p.scale_b) alpha *= *p.scale_b;
@@ -305,7 +406,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int64_t col0 = static_cast<int64_t>(nt) * BN;
       TOut* crow = static_cast<TOut*>(p.C) + b * p.stride_c + row * p.ldc;
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-      epilogue_row<TOut, BN>(t_base, crow, row < p.M, col0, p, alpha, bias);
+      if (p.c_tma)
+        epilogue_rows_tma<TOut, BN>(t_base, epi_stage + (warp - 2) * EPI_STAGE_BYTES, &tmC, mt * BM + quarter * 32,
+                                    static_cast<int>(col0), b, p, alpha, bias, col_half, EPI_WARPS / 4, lane);
+      else
+        epilogue_row<TOut, BN, (BN >= 128 ? 64 : 32)>(t_base, crow, row < p.M, col0, p, alpha, bias, col_half, EPI_WARPS / 4);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
@@ -315,6 +420,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       *p.status = KCG_ERR_TIMEOUT;
       __threadfence_system();
     }
+    if (p.c_tma && lane == 0) tma_store_wait_all<0>();   // this lane's TMA stores have been written
   }
 
   tc_fence_before();
@@ -381,36 +487,56 @@ namespace {
 
 // Per calling thread, so that two host threads (two generators, or a generator and a direct
 // caller of the C ABI) never see each other's setting.
-thread_local int g_pair_mode = -1;  // -1: pick_tiling(); 0: 128x256 single CTA; 1: CTA pairs when M > 128; 2: 128x128 single CTA
+thread_local int g_pair_mode = -1;  // -1: pick_tiling(); 0: 128x256 single CTA; 1: CTA pairs when M > 128; 2: 128x128; 3: 128x64
 
-enum Tiling { kWide = 0, kPair = 1, kNarrow = 2 };
-struct Idescs { uint32_t wide, pair, narrow; };
+enum Tiling { kWide = 0, kPair = 1, kNarrow = 2, kSlim = 3 };
+struct Idescs { uint32_t wide, pair, narrow, slim; };
+struct BMaps { CUtensorMap wide, half, quarter; };   // B boxes of 256, 128 and 64 columns of the tile
 
 // Chooses the CTA tile from a small cost model fitted to measurements on a B200 (microseconds):
-// waves of tiles x time of one tile's main loop + a fixed cost per launch.  A 128x128 block of
-// output costs an SM about 2.1 ns per unit of K (64 clocks per 16 of K at ~1.9 GHz); the 256x256
-// pair tile and the 128x256 tile are two such blocks per SM, the latter ~4 % slower per flop;
-// the 128x128 tile is one block but runs at the shared-memory bandwidth limit (A and B tiles are
-// equally large), ~40 % slower per flop, and only pays when the wider shapes leave most SMs idle.
-// Fixed costs (launch, pipeline fill, the last tile's epilogue): 5.7 / 6.9 / 5.0 us measured for
-// wide / pair / narrow.
+// waves of tiles x time of one tile's main loop + a fixed cost per launch.  The unit is a 128x128
+// block of output at the tensor pipe's full rate, 2.2 ns per element of K (four MMAs of
+// 128x128x16 per 64 of K, 67.7 clocks each, at ~1.92 GHz).  The 256x256 pair tile and the 128x256
+// tile are two such blocks per SM at that rate (the latter moves twice the operand bytes per SM
+// and settles ~5 % lower under the power cap); the 128x128 and 128x64 tiles are bound by what one
+// thread can issue, 377 and 365 clocks per k-block instead of 271 and 135, and pay only when the
+// wider shapes would leave most SMs idle.  Fixed costs (launch, pipeline fill, the last tile's
+// epilogue): 4.4 / 4.9 / 3.7 / 3.4 us measured for 128x256 / pair / 128x128 / 128x64.
 Tiling pick_tiling(int64_t M, int64_t N, int64_t K, int64_t batch, int elem_bytes, int sms) {
   auto cdiv = [](int64_t a, int64_t b) { return (a + b - 1) / b; };
   // 8-bit inputs run at twice, tf32 at half the 16-bit rate
-  const double unit = 2.1e-3 * static_cast<double>(K) * (elem_bytes == 1 ? 0.5 : (elem_bytes == 4 ? 2.0 : 1.0));
-  const int64_t wide = cdiv(M, 128) * cdiv(N, 256) * batch, narrow = cdiv(M, 128) * cdiv(N, 128) * batch;
+  const double unit = 2.2e-3 * static_cast<double>(K) * (elem_bytes == 1 ? 0.5 : (elem_bytes == 4 ? 2.0 : 1.0));
+  const int64_t mt = cdiv(M, 128);
+  const int64_t wide = mt * cdiv(N, 256) * batch, narrow = mt * cdiv(N, 128) * batch, slim = mt * cdiv(N, 64) * batch;
   const int64_t pairs = cdiv(M, 256) * cdiv(N, 256) * batch;
-  const double c_wide = static_cast<double>(cdiv(wide, sms)) * 2 * 1.04 * unit + 5.7;
-  const double c_narrow = static_cast<double>(cdiv(narrow, sms)) * 1.40 * unit + 5.0;
-  const double c_pair = M >= 2 * BM ? static_cast<double>(cdiv(pairs, sms / 2)) * 2 * unit + 6.9 : 1e30;
-  if (c_pair <= c_wide && c_pair <= c_narrow) return kPair;
-  return c_narrow < c_wide ? kNarrow : kWide;
+  const double c_wide = static_cast<double>(cdiv(wide, sms)) * 2 * 1.05 * unit + 4.4;
+  const double c_narrow = static_cast<double>(cdiv(narrow, sms)) * 1.39 * unit + 3.7;
+  const double c_slim = elem_bytes == 2 ? static_cast<double>(cdiv(slim, sms)) * 1.35 * unit + 3.4 : 1e30;
+  const double c_pair = M >= 2 * BM ? static_cast<double>(cdiv(pairs, sms / 2)) * 2 * unit + 4.9 : 1e30;
+  if (c_pair <= c_wide && c_pair <= c_narrow && c_pair <= c_slim) return kPair;
+  if (c_wide <= c_narrow && c_wide <= c_slim) return kWide;
+  return c_slim < c_narrow ? kSlim : kNarrow;
 }
 
 template <Kind kKind, int kElemBytes, bool kAMn, bool kBMn, typename TOut>
-int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB_pair, const GemmParams& p,
+int launch_variant(const CUtensorMap& tmA, const BMaps& bm, const CUtensorMap& tmC, const GemmParams& p,
                    const Idescs& idescs, Tiling tiling, cudaStream_t stream) {
   const int sms = sm_count();
+  const CUtensorMap &tmB = bm.wide, &tmB_pair = bm.half;
+  if constexpr (kElemBytes == 2) {
+    if (tiling == kSlim) {
+      GemmParams q = p;
+      q.n_tiles = static_cast<int>((p.N + 63) / 64);
+      q.total_tiles = static_cast<int64_t>(q.m_tiles) * q.n_tiles * (p.total_tiles / (static_cast<int64_t>(p.m_tiles) * p.n_tiles));
+      auto kern = gemm_tcgen05_kernel<kKind, kElemBytes, kAMn, kBMn, TOut, 64>;
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+      if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      const int grid = static_cast<int>(q.total_tiles < sms ? q.total_tiles : sms);
+      launch_overlapped(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tmA, bm.quarter, tmC, q, idescs.slim);
+      return check_launch("gemm_tcgen05_kernel (128x64)");
+    }
+  }
+  if (tiling == kSlim) tiling = kNarrow;   // the 64-wide tile exists for 16-bit inputs only
   if (tiling == kPair) {
     auto kern = gemm_tcgen05_pair_kernel<kKind, kElemBytes, kAMn, kBMn, TOut>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PSMEM_BYTES);
@@ -418,7 +544,7 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
     const int64_t batch = p.total_tiles / (static_cast<int64_t>(p.m_tiles) * p.n_tiles);
     const int64_t pair_tiles = static_cast<int64_t>((p.m_tiles + 1) / 2) * p.n_tiles * batch;
     const int64_t clusters = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
-    launch_overlapped(kern, dim3(static_cast<unsigned>(clusters * 2)), dim3(NUM_THREADS), PSMEM_BYTES, stream, tmA, tmB_pair, p, idescs.pair);
+    launch_overlapped(kern, dim3(static_cast<unsigned>(clusters * 2)), dim3(NUM_THREADS), PSMEM_BYTES, stream, tmA, tmB_pair, tmC, p, idescs.pair);
     return check_launch("gemm_tcgen05_pair_kernel");
   }
   if (tiling == kNarrow) {
@@ -430,34 +556,35 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     const int grid = static_cast<int>(q.total_tiles < sms ? q.total_tiles : sms);
-    launch_overlapped(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tmA, tmB_pair, q, idescs.narrow);
+    launch_overlapped(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tmA, tmB_pair, tmC, q, idescs.narrow);
     return check_launch("gemm_tcgen05_kernel (128x128)");
   }
   auto kern = gemm_tcgen05_kernel<kKind, kElemBytes, kAMn, kBMn, TOut, 256>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return fail(KCG_ERR_CUDA, "gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   const int grid = static_cast<int>(p.total_tiles < sms ? p.total_tiles : sms);
-  launch_overlapped(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tmA, tmB, p, idescs.wide);
+  launch_overlapped(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tmA, tmB, tmC, p, idescs.wide);
   return check_launch("gemm_tcgen05_kernel");
 }
 
 template <Kind kKind, int kElemBytes, typename TOut>
-int launch_layout(int trans_a, int trans_b, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmBp,
+int launch_layout(int trans_a, int trans_b, const CUtensorMap& tmA, const BMaps& bm, const CUtensorMap& tmC,
                   const GemmParams& p, const Idescs& idescs, Tiling tiling, cudaStream_t s) {
   // trans_a != 0: A is [K, M] row-major -> MN-major operand; trans_b == 0: B is [K, N] -> MN-major.
   if (!trans_a && trans_b)
-    return launch_variant<kKind, kElemBytes, false, false, TOut>(tmA, tmB, tmBp, p, idescs, tiling, s);
+    return launch_variant<kKind, kElemBytes, false, false, TOut>(tmA, bm, tmC, p, idescs, tiling, s);
   if (!trans_a && !trans_b)
-    return launch_variant<kKind, kElemBytes, false, true, TOut>(tmA, tmB, tmBp, p, idescs, tiling, s);
+    return launch_variant<kKind, kElemBytes, false, true, TOut>(tmA, bm, tmC, p, idescs, tiling, s);
   if (trans_a && trans_b)
-    return launch_variant<kKind, kElemBytes, true, false, TOut>(tmA, tmB, tmBp, p, idescs, tiling, s);
-  return launch_variant<kKind, kElemBytes, true, true, TOut>(tmA, tmB, tmBp, p, idescs, tiling, s);
+    return launch_variant<kKind, kElemBytes, true, false, TOut>(tmA, bm, tmC, p, idescs, tiling, s);
+  return launch_variant<kKind, kElemBytes, true, true, TOut>(tmA, bm, tmC, p, idescs, tiling, s);
 }
 
 }  // namespace
 
 // -1 (default): tile shape chosen by pick_tiling(); 0: 128x256 single-CTA tiles; 1: CTA pairs
-// (cta_group::2, 256x256) whenever M > 128; 2: 128x128 single-CTA tiles.
+// (cta_group::2, 256x256) whenever M > 128; 2: 128x128 single-CTA tiles; 3: 128x64 single-CTA tiles
+// (16-bit inputs; 128x128 otherwise).
 extern "C" __attribute__((visibility("default"))) void kcg_gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
 
 int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, int64_t batch, int trans_a,
@@ -479,6 +606,7 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
   const uint32_t mn_box = 128 / es;
   Tiling tiling = g_pair_mode == 0 ? kWide
                   : g_pair_mode == 2 ? kNarrow
+                  : g_pair_mode == 3 ? (es == 2 ? kSlim : kNarrow)
                   : g_pair_mode == 1 ? (M > BM ? kPair : kWide)
                                      : pick_tiling(M, N, K, batch, es, sm_count());
   if (n_extra > 0 || mc_c) {
@@ -487,7 +615,9 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
     if (M <= BM) return fail(KCG_ERR_UNSUPPORTED, "gemm: extra outputs need M > 128 (got %lld)", static_cast<long long>(M));
     tiling = kPair;
   }
-  CUtensorMap tmA, tmB, tmBp;
+  CUtensorMap tmA;
+  BMaps bm;
+  int a_blocked = 0, b_blocked = 0;
   {
     const uint64_t a_rows = trans_a ? K : M, a_cols = trans_a ? M : K;
     uint64_t dims[3] = {a_cols, a_rows, static_cast<uint64_t>(batch)};
@@ -496,7 +626,16 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
     uint32_t box[3];
     if (!trans_a) { box[0] = BK; box[1] = BM; } else { box[0] = mn_box; box[1] = BK; }
     box[2] = 1;
-    int rc = encode_tmap_sw128(&tmA, dtype_in, A, 3, dims, strides, box);
+    a_blocked = trans_a && (M * es) % 128 == 0 && BM / mn_box > 1;
+    int rc;
+    if (a_blocked) {
+      uint64_t d4[4] = {mn_box, a_rows, a_cols / mn_box, static_cast<uint64_t>(batch)};
+      uint64_t s4[3] = {strides[0], 128, strides[1]};
+      uint32_t b4[4] = {mn_box, static_cast<uint32_t>(BK), BM / mn_box, 1};
+      rc = encode_tmap_sw128(&tmA, dtype_in, A, 4, d4, s4, b4);
+    } else {
+      rc = encode_tmap_sw128(&tmA, dtype_in, A, 3, dims, strides, box);
+    }
     if (rc) return rc;
   }
   {
@@ -507,12 +646,35 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
     uint32_t box[3];
     if (trans_b) { box[0] = BK; box[1] = BN; } else { box[0] = mn_box; box[1] = BK; }
     box[2] = 1;
-    int rc = encode_tmap_sw128(&tmB, dtype_in, B, 3, dims, strides, box);
+    b_blocked = !trans_b && (N * es) % 128 == 0;
+    int rc;
+    if (b_blocked) {
+      uint64_t d4[4] = {mn_box, b_rows, b_cols / mn_box, static_cast<uint64_t>(batch)};
+      uint64_t s4[3] = {strides[0], 128, strides[1]};
+      uint32_t b4[4] = {mn_box, static_cast<uint32_t>(BK), BN / mn_box, 1};
+      rc = encode_tmap_sw128(&bm.wide, dtype_in, B, 4, d4, s4, b4);
+      if (rc) return rc;
+      if (BN / 2 / mn_box > 1) {
+        b4[2] = BN / 2 / mn_box;
+        rc = encode_tmap_sw128(&bm.half, dtype_in, B, 4, d4, s4, b4);
+      } else {
+        rc = encode_tmap_sw128(&bm.half, dtype_in, B, 3, dims, strides, box);   // one block: the plain box
+      }
+      if (rc) return rc;
+      rc = encode_tmap_sw128(&bm.quarter, dtype_in, B, 3, dims, strides, box);
+      if (rc) return rc;
+    } else {
+    rc = encode_tmap_sw128(&bm.wide, dtype_in, B, 3, dims, strides, box);
     if (rc) return rc;
-    // the CTA-pair kernel loads half of the B tile (128 of its 256 columns) per CTA
+    // the CTA-pair kernel loads half of the B tile (128 of its 256 columns) per CTA; the 128- and
+    // 64-wide single-CTA tiles use the same narrower boxes (an MN-major box is 128 bytes wide anyway)
     if (trans_b) box[1] = BN / 2;
-    rc = encode_tmap_sw128(&tmBp, dtype_in, B, 3, dims, strides, box);
+    rc = encode_tmap_sw128(&bm.half, dtype_in, B, 3, dims, strides, box);
     if (rc) return rc;
+    if (trans_b) box[1] = BN / 4;
+    rc = encode_tmap_sw128(&bm.quarter, dtype_in, B, 3, dims, strides, box);
+    if (rc) return rc;
+    }
   }
 
   GemmParams p;
@@ -529,6 +691,21 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
   p.c_vec_ok = aligned16(C) && (ldc * out_es) % 16 == 0 && (stride_c * out_es) % 16 == 0;
   p.n_extra = n_extra;
   p.mc_c = mc_c;
+  p.a_blocked = a_blocked; p.b_blocked = b_blocked;
+  // C through TMA stores (boxes of 32 rows x 128 bytes) when its layout allows a tensor map
+  CUtensorMap tmC;
+  p.c_tma = 0;
+  if (p.c_vec_ok && n_extra == 0 && !mc_c) {
+    uint64_t dims[3] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M), static_cast<uint64_t>(batch)};
+    uint64_t strides[2] = {static_cast<uint64_t>(ldc) * out_es,
+                           batch > 1 ? static_cast<uint64_t>(stride_c) * out_es : static_cast<uint64_t>(M) * ldc * out_es};
+    uint32_t box[3] = {static_cast<uint32_t>(128 / out_es), 32, 1};
+    int rc = encode_tmap_sw128(&tmC, dtype_out, C, 3, dims, strides, box);
+    if (rc) return rc;
+    p.c_tma = 1;
+  } else {
+    tmC = tmA;   // never read
+  }
   p.group_m = GROUP_M;   // 8, 32 and 64 were measured at 4096..16384: no better than 16
   for (int i = 0; i < KCG_MAX_EXTRA_C; ++i) p.extra_c[i] = i < n_extra ? extra_c[i] : nullptr;
   if (n_extra > 0 || mc_c) {
@@ -541,28 +718,28 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
   const uint32_t a_mn = trans_a ? 1u : 0u, b_mn = trans_b ? 0u : 1u;
   if (dtype_in == KCG_F8E4M3) {
     const Idescs ids = {make_idesc(0, 0, a_mn, b_mn, BM, BN), make_idesc(0, 0, a_mn, b_mn, 2 * BM, BN),
-                        make_idesc(0, 0, a_mn, b_mn, BM, 128)};
+                        make_idesc(0, 0, a_mn, b_mn, BM, 128), 0u};
     if (dtype_out == KCG_BF16)
-      return launch_layout<Kind::F8F6F4, 1, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, tmBp, p, ids, tiling, stream);
+      return launch_layout<Kind::F8F6F4, 1, __nv_bfloat16>(trans_a, trans_b, tmA, bm, tmC, p, ids, tiling, stream);
     if (dtype_out == KCG_F32)
-      return launch_layout<Kind::F8F6F4, 1, float>(trans_a, trans_b, tmA, tmB, tmBp, p, ids, tiling, stream);
+      return launch_layout<Kind::F8F6F4, 1, float>(trans_a, trans_b, tmA, bm, tmC, p, ids, tiling, stream);
     return fail(KCG_ERR_UNSUPPORTED, "gemm: float8_e4m3 inputs produce bfloat16 or float32 (got dtype %d)", dtype_out);
   }
   if (dtype_in == KCG_F32) {
     // tf32 operands (both K-major: the caller has laid them out that way), fp32 result
     if (trans_a || !trans_b || dtype_out != KCG_F32)
       return fail(KCG_ERR_UNSUPPORTED, "gemm: the tf32 path takes K-major operands and produces float32");
-    const Idescs ids = {make_idesc(2, 2, 0, 0, BM, BN), make_idesc(2, 2, 0, 0, 2 * BM, BN), make_idesc(2, 2, 0, 0, BM, 128)};
-    return launch_variant<Kind::TF32, 4, false, false, float>(tmA, tmB, tmBp, p, ids, tiling, stream);
+    const Idescs ids = {make_idesc(2, 2, 0, 0, BM, BN), make_idesc(2, 2, 0, 0, 2 * BM, BN), make_idesc(2, 2, 0, 0, BM, 128), 0u};
+    return launch_variant<Kind::TF32, 4, false, false, float>(tmA, bm, tmC, p, ids, tiling, stream);
   }
   const uint32_t fmt = dtype_in == KCG_BF16 ? 1u : 0u;
   const Idescs ids = {make_idesc(fmt, fmt, a_mn, b_mn, BM, BN), make_idesc(fmt, fmt, a_mn, b_mn, 2 * BM, BN),
-                      make_idesc(fmt, fmt, a_mn, b_mn, BM, 128)};
-  if (dtype_out == KCG_F32) return launch_layout<Kind::F16, 2, float>(trans_a, trans_b, tmA, tmB, tmBp, p, ids, tiling, stream);
+                      make_idesc(fmt, fmt, a_mn, b_mn, BM, 128), make_idesc(fmt, fmt, a_mn, b_mn, BM, 64)};
+  if (dtype_out == KCG_F32) return launch_layout<Kind::F16, 2, float>(trans_a, trans_b, tmA, bm, tmC, p, ids, tiling, stream);
   if (dtype_in == KCG_BF16 && dtype_out == KCG_BF16)
-    return launch_layout<Kind::F16, 2, __nv_bfloat16>(trans_a, trans_b, tmA, tmB, tmBp, p, ids, tiling, stream);
+    return launch_layout<Kind::F16, 2, __nv_bfloat16>(trans_a, trans_b, tmA, bm, tmC, p, ids, tiling, stream);
   if (dtype_in == KCG_F16 && dtype_out == KCG_F16)
-    return launch_layout<Kind::F16, 2, __half>(trans_a, trans_b, tmA, tmB, tmBp, p, ids, tiling, stream);
+    return launch_layout<Kind::F16, 2, __half>(trans_a, trans_b, tmA, bm, tmC, p, ids, tiling, stream);
   return fail(KCG_ERR_UNSUPPORTED, "gemm: dtype combination %d -> %d has no kernel", dtype_in, dtype_out);
 }
 

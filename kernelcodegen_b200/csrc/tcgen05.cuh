@@ -373,6 +373,52 @@ __device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t cta_mask
                : "memory");
 }
 
+// One k-block (128 bytes of K = four MMAs) of a GEMM main loop as a single instruction group: the
+// four MMAs, the commit that hands the ring stage back, and in front of them a non-blocking test
+// of another barrier (the next stage's "full" barrier) whose answer is read only after the MMAs
+// have been handed to the tensor pipe.  The issuing thread is the bottleneck of narrow tiles: a
+// barrier test takes far longer to answer than an MMA takes to issue, and issued on its own it
+// would stand between two MMAs.  a_step / b_step: descriptor increments per k-step (16-byte units).
+// Returns whether the tested phase had completed.
+#define KCG_MMA_KBLOCK_ASM(GROUP, KIND, COMMIT)                                                        \
+  asm volatile(                                                                                        \
+      "{\n\t.reg .pred P, Q, T;\n\t"                                                                   \
+      "setp.ne.b32 P, %10, 0;\n\t"                                                                     \
+      "setp.eq.b32 T, %10, %10;\n\t"                                                                   \
+      "mbarrier.test_wait.parity.shared::cta.b64 Q, [%12], %13;\n\t"                                   \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %2, %6, %11, P;\n\t"                      \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %3, %7, %11, T;\n\t"                      \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %4, %8, %11, T;\n\t"                      \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%1], %5, %9, %11, T;\n\t" COMMIT                \
+      "selp.u32 %0, 1, 0, Q;\n\t}"                                                                     \
+      : "=r"(ok)                                                                                       \
+      : "r"(d_tmem), "l"(a0), "l"(a0 + a_step), "l"(a0 + 2 * a_step), "l"(a0 + 3 * a_step), "l"(b0),   \
+        "l"(b0 + b_step), "l"(b0 + 2 * b_step), "l"(b0 + 3 * b_step), "r"(acc_first), "r"(idesc),      \
+        "r"(peek_bar), "r"(peek_parity), "r"(commit_bar), "h"(cta_mask)                                \
+      : "memory")
+#define KCG_COMMIT_ONE "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%14];\n\t"
+#define KCG_COMMIT_PAIR \
+  "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%14], %15;\n\t"
+template <Kind kKind, bool kPair>
+__device__ __forceinline__ bool mma_kblock(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint32_t a_step, uint32_t b_step,
+                                           uint32_t idesc, uint32_t acc_first, uint32_t commit_bar, uint16_t cta_mask,
+                                           uint32_t peek_bar, uint32_t peek_parity) {
+  uint32_t ok;
+  if constexpr (!kPair) {
+    if constexpr (kKind == Kind::F16) KCG_MMA_KBLOCK_ASM("1", "f16", KCG_COMMIT_ONE);
+    else if constexpr (kKind == Kind::TF32) KCG_MMA_KBLOCK_ASM("1", "tf32", KCG_COMMIT_ONE);
+    else KCG_MMA_KBLOCK_ASM("1", "f8f6f4", KCG_COMMIT_ONE);
+  } else {
+    if constexpr (kKind == Kind::F16) KCG_MMA_KBLOCK_ASM("2", "f16", KCG_COMMIT_PAIR);
+    else if constexpr (kKind == Kind::TF32) KCG_MMA_KBLOCK_ASM("2", "tf32", KCG_COMMIT_PAIR);
+    else KCG_MMA_KBLOCK_ASM("2", "f8f6f4", KCG_COMMIT_PAIR);
+  }
+  return ok != 0;
+}
+#undef KCG_MMA_KBLOCK_ASM
+#undef KCG_COMMIT_ONE
+#undef KCG_COMMIT_PAIR
+
 // Shared-memory matrix descriptor for a 128-byte-swizzled operand tile whose base is
 // 1024-byte aligned.  Field positions: start address [0,14), leading byte offset [16,30),
 // stride byte offset [32,46) (all in 16-byte units), descriptor version 1 at [46,48),

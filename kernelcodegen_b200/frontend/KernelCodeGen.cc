@@ -80,7 +80,9 @@ KernelCodeGenerator::KernelCodeGenerator(const std::string& platform_) : platfor
                    {{"BLOCK_SIZE_M", 128}, {"BLOCK_SIZE_N", 256}, {"BLOCK_SIZE_K", 64}, {"GROUP_SIZE_M", 16},
                     {"STAGES", 4}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}, {"CTA_PAIR", 0}},
                    {{"BLOCK_SIZE_M", 128}, {"BLOCK_SIZE_N", 128}, {"BLOCK_SIZE_K", 64}, {"GROUP_SIZE_M", 16},
-                    {"STAGES", 6}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}, {"CTA_PAIR", 0}}};
+                    {"STAGES", 6}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}, {"CTA_PAIR", 0}},
+                   {{"BLOCK_SIZE_M", 128}, {"BLOCK_SIZE_N", 64}, {"BLOCK_SIZE_K", 64}, {"GROUP_SIZE_M", 16},
+                    {"STAGES", 8}, {"ACCUMULATORS", 2}, {"WARP_SIZE", 32}, {"CTA_PAIR", 0}}};
   batchMatmulConfigs = matmulConfigs;
   binaryConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
   elementWiseConfigs = {{{"BLOCK_SIZE", 256}, {"UNROLL", 4}, {"VECTORIZE_WIDTH", 16}}};
@@ -301,7 +303,7 @@ void apply_knobs(OpKind kind, const std::map<std::string, int>& cfg, bool restor
         int bn = 256;
         find("BLOCK_SIZE_N", bn);
         // CTA_PAIR=1: the library's own choice; 0: single-CTA tiles of the stated width
-        kcg_gemm_set_pair_mode(restore ? -1 : (v ? -1 : (bn == 128 ? 2 : 0)));
+        kcg_gemm_set_pair_mode(restore ? -1 : (v ? -1 : (bn == 128 ? 2 : (bn == 64 ? 3 : 0))));
       }
       break;
     case OpKind::LayerNorm: case OpKind::FusedLayerNormGeluAdd:

@@ -123,17 +123,18 @@ def test_alignment_is_reported():
 
 @pytest.mark.parametrize("m,n,k", [(512, 640, 256), (1024, 1024, 1024), (392, 264, 520)])
 def test_tile_shapes_give_identical_bits(m, n, k):
-    # 128x256, CTA-pair 256x256 and 128x128 tiles accumulate every output over k in the same order
+    # 128x256, CTA-pair 256x256, 128x128 and 128x64 tiles accumulate every output over k in the same order
     from kernelcodegen_b200 import _lib
     A = randn((m, k), torch.bfloat16, 580, std=1.0 / np.sqrt(k)).cuda()
     B = randn((k, n), torch.bfloat16, 581).cuda()
     Bt = B.t().contiguous()
     outs = []
     try:
-        for mode in (0, 1, 2, -1):
+        for mode in (0, 1, 2, 3, -1):
             _lib.load().kcg_gemm_set_pair_mode(mode)
             outs.append(ops().matmul(A, B))
             outs.append(ops().batched_matmul(A, Bt, False, True))
+            outs.append(ops().batched_matmul(A.t().contiguous(), Bt, True, True))
             sync_ok()
     finally:
         _lib.load().kcg_gemm_set_pair_mode(-1)
