@@ -699,11 +699,47 @@ __device__ __forceinline__ bool softmax_block_px(uint32_t s_addr, uint32_t o_add
 // Stores the calling thread's finished output row: O / l, rounded to T.  With extra outputs
 // (copies of O in other GPUs' memory) the warp's 32 rows are staged through `stg` (32 rows x D
 // elements of shared memory that is idle by now) and leave as whole rows to every destination.
+//
+// With a tensor map of O (tmO, the two-tile kernel) and no extra outputs, the rows of a tile
+// that had key blocks leave through the copy engine instead: the warp packs them into swizzled
+// boxes of 32 rows x 128 bytes in `stg` and one lane issues a TMA store per box, which writes
+// whole lines and clips at Sq.  Stored directly, every warp instruction touches 32 different
+// lines with 16 bytes each.
 template <typename T, int D>
 __device__ __forceinline__ void store_output(const FmhaParams& p, uint32_t o_addr, bool have_o, float l, int b, int h,
-                                             int row0, int lane, uint8_t* stg, int peer_seed) {
+                                             int row0, int lane, uint8_t* stg, int peer_seed,
+                                             const CUtensorMap* tmO = nullptr) {
   const int qi = row0 + lane;   // this thread's query row; row0 is the first row of the warp
   const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+  if (tmO != nullptr && have_o && p.n_extra == 0 && p.mc_o == nullptr) {
+    if (row0 >= p.Sq) return;
+#pragma unroll 1
+    for (int cc = 0; cc < D / 32; ++cc) {
+      uint32_t oreg[32];
+      tmem_ld32(o_addr + cc * 32, oreg);
+      tmem_wait_ld();
+      uint8_t* box = stg + (cc >> 1) * 4096 + lane * 128;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 o;
+        o.x = pack2<T>(__uint_as_float(oreg[g * 8 + 0]) * inv_l, __uint_as_float(oreg[g * 8 + 1]) * inv_l);
+        o.y = pack2<T>(__uint_as_float(oreg[g * 8 + 2]) * inv_l, __uint_as_float(oreg[g * 8 + 3]) * inv_l);
+        o.z = pack2<T>(__uint_as_float(oreg[g * 8 + 4]) * inv_l, __uint_as_float(oreg[g * 8 + 5]) * inv_l);
+        o.w = pack2<T>(__uint_as_float(oreg[g * 8 + 6]) * inv_l, __uint_as_float(oreg[g * 8 + 7]) * inv_l);
+        const int gc = (cc & 1) * 4 + g;   // 16-byte chunk within the box's 128-byte row
+        *reinterpret_cast<uint4*>(box + ((gc ^ (lane & 7)) << 4)) = o;
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+      for (int d = 0; d < D / 64; ++d) tma_store_4d(tmO, stg + d * 4096, d * 64, row0, h, b);
+      tma_store_commit();
+      tma_store_wait_read<0>();   // the CTA's shared memory must outlive the copy engine's reads
+    }
+    return;
+  }
   T* orow = static_cast<T*>(p.O) + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh +
             static_cast<int64_t>(qi) * p.o_ss;
   if (p.n_extra > 0 || p.mc_o != nullptr) {
@@ -782,6 +818,86 @@ __device__ __forceinline__ void store_output(const FmhaParams& p, uint32_t o_add
   }
 }
 
+// ---- MMA groups of the two-tile kernel's issuing thread ------------------------------------
+// The issuing thread is one of the kernel's two bottlenecks: an MMA of 128x128x16 takes the thread
+// about as long to issue (65-75 clocks) as the tensor pipe needs to run it (68), and a barrier
+// test needs ~140 clocks to answer.  Tested on its own in front of a batch of MMAs, every barrier
+// would idle the pipe for that long, five times per key block.  So each batch is one asm block
+// that first issues a non-blocking test of the barrier(s) needed *after* it, then the MMAs (and
+// the commit), and reads the answers last; only a barrier that was not complete yet is waited
+// for in the ordinary way.
+//
+// Four PV k-steps: O (+)= P[:, 16 kk .. 16 kk + 16) V[16 kk .., :], kk = kk0 .. kk0 + 3.  a_p / vd address
+// k-step kk0 (P advances 8 tensor-memory columns, the V descriptor 2048 bytes per k-step).
+__device__ __forceinline__ bool pv4_peek(uint32_t d_o, uint32_t a_p, uint64_t vd, uint32_t idesc, uint32_t acc_first,
+                                         uint32_t peek_bar, uint32_t peek_par) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P, Q, T;\n\t.reg .b32 a1, a2, a3;\n\t.reg .b64 v1, v2, v3;\n\t"
+      "setp.ne.b32 P, %5, 0;\n\t"
+      "setp.eq.b32 T, %5, %5;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 Q, [%6], %7;\n\t"
+      "add.u32 a1, %2, 8;\n\tadd.u32 a2, %2, 16;\n\tadd.u32 a3, %2, 24;\n\t"
+      "add.s64 v1, %3, 128;\n\tadd.s64 v2, %3, 256;\n\tadd.s64 v3, %3, 384;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], %3, %4, P;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a1], v1, %4, T;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a2], v2, %4, T;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a3], v3, %4, T;\n\t"
+      "selp.u32 %0, 1, 0, Q;\n\t}"
+      : "=r"(ok)
+      : "r"(d_o), "r"(a_p), "l"(vd), "r"(idesc), "r"(acc_first), "r"(peek_bar), "r"(peek_par)
+      : "memory");
+  return ok != 0;
+}
+// Four PV k-steps (always accumulating), then — if kWithS — the next score tile S = Q K^T (D / 16
+// k-steps, the first one overwriting), then the commit on `commit_bar`; two barriers are tested.
+// qd / kd: descriptors of k-step 0 (k-steps advance 32 bytes, the second 64-element half of the
+// head dimension lies one 16 KB block further).
+#define KCG_SS_STEP(OFF, PRED)                                                            \
+  "add.s64 qx, %7, " #OFF ";\n\tadd.s64 kx, %8, " #OFF ";\n\t"                             \
+  "tcgen05.mma.cta_group::1.kind::f16 [%6], qx, kx, %9, " #PRED ";\n\t"
+template <int D, bool kWithS>
+__device__ __forceinline__ void pv4_s_commit_peek2(uint32_t d_o, uint32_t a_p, uint64_t vd, uint32_t idesc_pv, uint32_t d_s,
+                                                   uint64_t qd, uint64_t kd, uint32_t idesc_qk, uint32_t commit_bar,
+                                                   uint32_t peek1, uint32_t par1, uint32_t peek2, uint32_t par2,
+                                                   bool& ok1, bool& ok2) {
+  uint32_t r1, r2;
+#define KCG_PV4                                                                                    \
+  "{\n\t.reg .pred F, Q1, Q2, T;\n\t.reg .b32 a1, a2, a3;\n\t.reg .b64 v1, v2, v3, qx, kx;\n\t"     \
+  "setp.eq.b32 T, %2, %2;\n\t"                                                                     \
+  "setp.ne.b32 F, %2, %2;\n\t"                                                                     \
+  "mbarrier.test_wait.parity.shared::cta.b64 Q1, [%11], %12;\n\t"                                  \
+  "mbarrier.test_wait.parity.shared::cta.b64 Q2, [%13], %14;\n\t"                                  \
+  "add.u32 a1, %3, 8;\n\tadd.u32 a2, %3, 16;\n\tadd.u32 a3, %3, 24;\n\t"                           \
+  "add.s64 v1, %4, 128;\n\tadd.s64 v2, %4, 256;\n\tadd.s64 v3, %4, 384;\n\t"                       \
+  "tcgen05.mma.cta_group::1.kind::f16 [%2], [%3], %4, %5, T;\n\t"                                  \
+  "tcgen05.mma.cta_group::1.kind::f16 [%2], [a1], v1, %5, T;\n\t"                                  \
+  "tcgen05.mma.cta_group::1.kind::f16 [%2], [a2], v2, %5, T;\n\t"                                  \
+  "tcgen05.mma.cta_group::1.kind::f16 [%2], [a3], v3, %5, T;\n\t"
+#define KCG_TAIL                                                                                   \
+  "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%10];\n\t"               \
+  "selp.u32 %0, 1, 0, Q1;\n\tselp.u32 %1, 1, 0, Q2;\n\t}"
+#define KCG_OPERANDS                                                                               \
+  : "=r"(r1), "=r"(r2)                                                                             \
+  : "r"(d_o), "r"(a_p), "l"(vd), "r"(idesc_pv), "r"(d_s), "l"(qd), "l"(kd), "r"(idesc_qk),         \
+    "r"(commit_bar), "r"(peek1), "r"(par1), "r"(peek2), "r"(par2)                                  \
+  : "memory"
+  if constexpr (!kWithS) {
+    asm volatile(KCG_PV4 KCG_TAIL KCG_OPERANDS);
+  } else if constexpr (D == 128) {
+    asm volatile(KCG_PV4 KCG_SS_STEP(0, F) KCG_SS_STEP(2, T) KCG_SS_STEP(4, T) KCG_SS_STEP(6, T) KCG_SS_STEP(1024, T)
+                     KCG_SS_STEP(1026, T) KCG_SS_STEP(1028, T) KCG_SS_STEP(1030, T) KCG_TAIL KCG_OPERANDS);
+  } else {
+    asm volatile(KCG_PV4 KCG_SS_STEP(0, F) KCG_SS_STEP(2, T) KCG_SS_STEP(4, T) KCG_SS_STEP(6, T) KCG_TAIL KCG_OPERANDS);
+  }
+#undef KCG_PV4
+#undef KCG_TAIL
+#undef KCG_OPERANDS
+  ok1 = r1 != 0;
+  ok2 = r2 != 0;
+}
+#undef KCG_SS_STEP
+
 // ---------------------------------------------------------------------------------------------
 // Version 2: two 128-query tiles per CTA.
 //
@@ -806,7 +922,7 @@ constexpr int V2_REGS_SOFTMAX = 208, V2_REGS_SERVICE = 88;   // 2*128*208 + 128*
 
 template <typename T, int D, int NSLOT>
 __global__ void __launch_bounds__(V2_THREADS, 1)
-fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FmhaParams p, const uint32_t idesc_qk,
                  const uint32_t idesc_pv) {
   constexpr int DB = D / 64;
@@ -845,6 +961,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
+    prefetch_tmap(&tmO);
     mbar_init(q_full, 1);
     for (int s = 0; s < NSLOT; ++s) {
       mbar_init(&kv_full[s], 1);
@@ -929,13 +1046,6 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           mma_ss<Kind::F16>(tmem_base + i * BN, qd + ((d * TILE16K + k * 32) >> 4), kd + ((d * TILE16K + k * 32) >> 4),
                             idesc_qk, (d | k) != 0 ? 1u : 0u);
     };
-    auto issue_pv = [&](int i, int j, int half) {  // O_i += P_i(j)[:, half] V_j[half, :]
-      const uint64_t vd = v_desc0 + static_cast<uint64_t>((2 * (j & 1) * TILE) >> 4);
-#pragma unroll
-      for (int kk = half * 4; kk < half * 4 + 4; ++kk)
-        mma_ts_f16(tmem_base + 256 + i * BN, tmem_base + i * BN + kk * 8, vd + ((kk * 2048) >> 4), idesc_pv,
-                   (j | kk) != 0 ? 1u : 0u);
-    };
     // One thread runs the whole issue loop: nothing here needs the other lanes, and a single
     // thread has no reconvergence points between a barrier wait and the MMAs that follow it.
     // (An MMA is accepted only when the tensor pipe has room, so issuing blocks for about as
@@ -951,22 +1061,51 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             mma_commit(&s_full[i]);
           }
       }
+      // Barriers already seen complete by a test that rode along with an earlier MMA batch
+      bool r_kv = false, r_p00 = false, r_p01 = false, r_p10 = false, r_p11 = false;
+      const uint32_t kvf0 = smem_u32(kv_full), pf0 = smem_u32(p_full), sf0 = smem_u32(s_full);
       for (int j = 0; j < n_max && ok; ++j) {
-        if (!mbar_wait(&kv_full[j & 1], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (!r_kv && !mbar_wait(&kv_full[j & 1], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+        r_kv = false;
+        const uint32_t pj = j & 1u;
+        const uint64_t vd = v_desc0 + static_cast<uint64_t>((2 * (j & 1) * TILE) >> 4);
+        const uint64_t kd_next = kv_desc0 + static_cast<uint64_t>(((2 * (j & 1) + 1) * TILE) >> 4);   // K_{j+1}
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           const int n_i = i == 0 ? n_blk0 : n_blk1;
           if (j >= n_i) continue;
+          bool& r_h0 = i == 0 ? r_p00 : r_p10;
+          bool& r_h1 = i == 0 ? r_p01 : r_p11;
           // P arrives in two column halves; the first four k-steps of PV start on the first
-          if (!mbar_wait(&p_full[2 * i], j & 1u, abort_flag)) { ok = false; break; }
+          if (!r_h0 && !mbar_wait(&p_full[2 * i], pj, abort_flag)) { ok = false; break; }
+          r_h0 = false;
           tc_fence_after();
-          issue_pv(i, j, 0);
-          if (!mbar_wait(&p_full[2 * i + 1], j & 1u, abort_flag)) { ok = false; break; }
+          const uint32_t d_o = tmem_base + 256 + i * BN, a_p = tmem_base + i * BN;
+          r_h1 = pv4_peek(d_o, a_p, vd, idesc_pv, j != 0 ? 1u : 0u, pf0 + (2 * i + 1) * 8, pj);
+          if (!r_h1 && !mbar_wait(&p_full[2 * i + 1], pj, abort_flag)) { ok = false; break; }
+          r_h1 = false;
           tc_fence_after();
-          issue_pv(i, j, 1);
-          if (j + 1 < n_i) issue_s(i, j + 1);
-          // one commit covers both: the next score tile, or the finished output, is ready
-          mma_commit(&s_full[i]);
+          // Second half of PV, the next score tile behind it, one commit for both (the next score
+          // tile, or the finished output, is ready); tested meanwhile: what the thread needs next —
+          // after tile 0 the first P half of tile 1, after tile 1 the next K/V ring entry and the
+          // first P half of tile 0 for the next key block.
+          const uint32_t peek1 = i == 0 ? pf0 + 2 * 8 : kvf0 + ((j + 1) & 1) * 8;
+          const uint32_t par1 = i == 0 ? pj : static_cast<uint32_t>(((j + 1) >> 1) & 1);
+          const uint32_t peek2 = pf0, par2 = pj ^ 1u;   // p_full[0] of key block j + 1 (used after tile 1 only)
+          const uint64_t qd = q_desc0 + static_cast<uint64_t>((i * TILE) >> 4);
+          bool t1, t2;
+          if (j + 1 < n_i)
+            pv4_s_commit_peek2<D, true>(d_o, a_p + 32, vd + 512, idesc_pv, tmem_base + i * BN, qd, kd_next, idesc_qk,
+                                        sf0 + i * 8, peek1, par1, peek2, par2, t1, t2);
+          else
+            pv4_s_commit_peek2<D, false>(d_o, a_p + 32, vd + 512, idesc_pv, tmem_base + i * BN, qd, kd_next, idesc_qk,
+                                         sf0 + i * 8, peek1, par1, peek2, par2, t1, t2);
+          if (i == 0) {
+            r_p10 = t1 && j < n_blk1;
+          } else {
+            r_kv = t1 && j + 1 < n_max;
+            r_p00 = t2 && j + 1 < n_blk0;
+          }
         }
         if (ok) mma_commit(&kv_empty[j & 1]);
       }
@@ -1006,7 +1145,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       store_output<T, D>(p, o_addr, n_mine > 0, l, b, h, q0 + i * BM + quarter * 32, lane,
                          q_smem + i * TILE + quarter * (32 * D * 2),
-                         static_cast<int>(blockIdx.x + blockIdx.y) + warp);
+                         static_cast<int>(blockIdx.x + blockIdx.y) + warp, &tmO);
     } else if (lane == 0 && !*abort_flag) {
       *abort_flag = 1;
       *p.status = KCG_ERR_TIMEOUT;
@@ -1028,7 +1167,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #include "fmha_split_kernel.cuh"
 
 template <typename T, int D>
-int launch_fmha2(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FmhaParams& p,
+int launch_fmha2(const CUtensorMap& tmO, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FmhaParams& p,
                  uint32_t fmt, cudaStream_t stream) {
   constexpr int DB = D / 64;
   constexpr int TILE = DB * TILE16K;
@@ -1040,7 +1179,7 @@ int launch_fmha2(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorM
   const uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, BM, BN);
   const uint32_t idesc_pv = make_idesc(fmt, fmt, 0, 1, BM, D);
   dim3 grid((p.q_tiles + 1) / 2, p.B * p.H);
-  launch_overlapped(kern, grid, dim3(V2_THREADS), SMEM, stream, tmQ, tmK, tmV, p, idesc_qk, idesc_pv);
+  launch_overlapped(kern, grid, dim3(V2_THREADS), SMEM, stream, tmO, tmQ, tmK, tmV, p, idesc_qk, idesc_pv);
   return check_launch("fmha_fwd_kernel2");
 }
 
@@ -1155,15 +1294,15 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
         return fail(KCG_ERR_ALIGNMENT, "fmha: strides must be positive multiples of 8 elements (tensor %d stride %d = %lld)",
                     t, i, static_cast<long long>(strides[t][i]));
   }
-  CUtensorMap tm[4];   // Q, K, V with 128-row boxes; K again with 64-row boxes (the CTA-pair kernel's halves)
-  const int64_t seq[4] = {Sq, Skv, Skv, Skv};
-  const int src[4] = {0, 1, 2, 1};
-  for (int t = 0; t < 4; ++t) {
+  CUtensorMap tm[5];   // Q, K, V with 128-row boxes; K again with 64-row boxes (the CTA-pair kernel's halves); O, 32-row boxes
+  const int64_t seq[5] = {Sq, Skv, Skv, Skv, Sq};
+  const int src[5] = {0, 1, 2, 1, 3};
+  for (int t = 0; t < 5; ++t) {
     uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(seq[t]), static_cast<uint64_t>(H),
                         static_cast<uint64_t>(B)};
     uint64_t st[3] = {static_cast<uint64_t>(strides[src[t]][2]) * 2, static_cast<uint64_t>(strides[src[t]][1]) * 2,
                       static_cast<uint64_t>(strides[src[t]][0]) * 2};
-    uint32_t box[4] = {64, t == 3 ? 64u : 128u, 1, 1};
+    uint32_t box[4] = {64, t == 3 ? 64u : (t == 4 ? 32u : 128u), 1, 1};
     int rc = encode_tmap_sw128(&tm[t], dtype, ptrs[src[t]], 4, dims, st, box);
     if (rc) return rc;
   }
@@ -1196,7 +1335,7 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
     return dtype == KCG_BF16 ? launch_fmha_pair<__nv_bfloat16>(tm[0], tm[3], tm[2], p, fmt, s)
                              : launch_fmha_pair<__half>(tm[0], tm[3], tm[2], p, fmt, s);
 #define KCG_FMHA(TT, DD)                                                                      \
-  (variant == 2   ? launch_fmha2<TT, DD>(tm[0], tm[1], tm[2], p, fmt, s)                      \
+  (variant == 2   ? launch_fmha2<TT, DD>(tm[4], tm[0], tm[1], tm[2], p, fmt, s)               \
    : variant == 1 ? launch_fmha<TT, DD, true>(tm[0], tm[1], tm[2], p, fmt, s)                 \
                   : launch_fmha<TT, DD, false>(tm[0], tm[1], tm[2], p, fmt, s))
   if (dtype == KCG_BF16) return D == 128 ? KCG_FMHA(__nv_bfloat16, 128) : KCG_FMHA(__nv_bfloat16, 64);

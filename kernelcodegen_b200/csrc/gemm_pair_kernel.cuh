@@ -258,7 +258,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       *p.status = KCG_ERR_TIMEOUT;
       __threadfence_system();
     }
-    if (p.c_tma && lane == 0) tma_store_wait_all<0>();   // this lane's TMA stores have been written
   }
 
   // Neither CTA may leave (or free tensor memory) while the other can still signal it.

@@ -204,8 +204,9 @@ __device__ __forceinline__ void epilogue_rows_tma(uint32_t t_base, uint8_t* stg,
     }
     pending = true;
   }
-  // the staging tile is free again (and, for the kernel's last tile, the data on its way) before
-  // the warp moves on
+  // The staging tile must have been read before the warp reuses it or the CTA exits and its
+  // shared memory goes away; that the bytes have reached global memory is the kernel boundary's
+  // business, as for any other store.
   if (pending && lane == 0) tma_store_wait_read<0>();
   __syncwarp();
 }
@@ -420,7 +421,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       *p.status = KCG_ERR_TIMEOUT;
       __threadfence_system();
     }
-    if (p.c_tma && lane == 0) tma_store_wait_all<0>();   // this lane's TMA stores have been written
   }
 
   tc_fence_before();
