@@ -245,7 +245,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       } else if (p.c_tma) {
         epilogue_rows_tma<TOut, PBN>(t_base, epi_stage + (warp - 2) * PEPI_STAGE_BYTES, &tmC,
                                      mp * PBM + static_cast<int>(rank) * 128 + quarter * 32, static_cast<int>(col0), b, p,
-                                     alpha, bias, col_half, EPI_WARPS / 4, lane);
+                                     alpha, bias, col_half, EPI_WARPS / 4, lane,
+                                     // after the pair's last tile the operand ring is idle: 16 KB of it per warp
+                                     tile + n_clusters >= total ? smem + (warp - 2) * 16384 : nullptr);
       } else {
         epilogue_row<TOut, PBN>(t_base, crow, row < p.M, col0, p, alpha, bias, col_half, EPI_WARPS / 4);
       }

@@ -161,10 +161,13 @@ __device__ __forceinline__ void epilogue_row(uint32_t t_base, TOut* crow, bool r
 // sector writes and took about 2 us, all of it exposed when a CTA has a single tile.  Here a warp
 // packs 128 bytes per row into a swizzled 4 KB staging tile of its own and one lane hands the
 // 32-row box to the copy engine, which writes whole lines and clips at M and N.
+// `spare`, when not null, is shared memory nobody else uses any more (the operand ring after the
+// CTA's last tile) with room for every round of this warp: the rounds then need not wait for
+// one another's staging tile, which matters when nothing else hides the epilogue.
 template <typename TOut, int kTileN>
 __device__ __forceinline__ void epilogue_rows_tma(uint32_t t_base, uint8_t* stg, const CUtensorMap* tmC, int row0, int col0,
                                                   int batch, const GemmParams& p, float alpha, const TOut* bias,
-                                                  int first, int step, int lane) {
+                                                  int first, int step, int lane, uint8_t* spare = nullptr) {
   constexpr int VW = Vec16<TOut>::N;
   constexpr int RC = 128 / static_cast<int>(sizeof(TOut));   // columns per round: 128 bytes of output per row
   const bool plain = bias == nullptr && p.act == 0;
@@ -176,7 +179,10 @@ __device__ __forceinline__ void epilogue_rows_tma(uint32_t t_base, uint8_t* stg,
     tmem_wait_ld();
     const int cbase = col0 + c * RC;
     if (cbase >= p.N || row0 >= p.M) continue;   // nothing of this box lies inside C
-    if (pending) {   // the copy engine has read the previous round out of the staging tile
+    if (spare != nullptr) {
+      stg = spare;
+      spare += EPI_STAGE_BYTES;
+    } else if (pending) {   // the copy engine has read the previous round out of the staging tile
       if (lane == 0) tma_store_wait_read<0>();
       __syncwarp();
     }
@@ -411,7 +417,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // than the scattered stores: 6.15 against 6.45 us at 1024^3)
       if (p.c_tma && BN >= 128)
         epilogue_rows_tma<TOut, BN>(t_base, epi_stage + (warp - 2) * EPI_STAGE_BYTES, &tmC, mt * BM + quarter * 32,
-                                    static_cast<int>(col0), b, p, alpha, bias, col_half, EPI_WARPS / 4, lane);
+                                    static_cast<int>(col0), b, p, alpha, bias, col_half, EPI_WARPS / 4, lane,
+                                    // after the CTA's last tile the operand ring is idle: 16 KB of it per warp
+                                    tile + gridDim.x >= p.total_tiles ? smem + (warp - 2) * 16384 : nullptr);
       else
         epilogue_row<TOut, BN, (BN >= 128 ? 64 : 32)>(t_base, crow, row < p.M, col0, p, alpha, bias, col_half, EPI_WARPS / 4);
       tc_fence_before();
