@@ -818,6 +818,39 @@ __device__ __forceinline__ void store_output(const FmhaParams& p, uint32_t o_add
   }
 }
 
+// The calling thread's finished output row, read out of tensor memory in one go and stored straight
+// from registers (no shared memory).  `released` runs as soon as the accumulator has been read, before
+// the conversion and the stores: the persistent kernel lets the next item's first PV overwrite it then.
+template <typename T, int D, typename Released>
+__device__ __forceinline__ void store_output_direct(const FmhaParams& p, uint32_t o_addr, bool have_o, float l, int b, int h,
+                                                    int row0, int lane, Released released) {
+  const int qi = row0 + lane;
+  const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+  T* orow = static_cast<T*>(p.O) + static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(h) * p.o_sh +
+            static_cast<int64_t>(qi) * p.o_ss;
+  uint32_t oreg[D];
+  if (have_o) {
+#pragma unroll
+    for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(o_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&oreg[cc * 32]));
+    tmem_wait_ld();
+    released();
+  } else {
+#pragma unroll
+    for (int k = 0; k < D; ++k) oreg[k] = 0u;
+  }
+  if (qi < p.Sq) {
+#pragma unroll
+    for (int g = 0; g < D / 8; ++g) {
+      uint4 o;
+      o.x = pack2<T>(__uint_as_float(oreg[g * 8 + 0]) * inv_l, __uint_as_float(oreg[g * 8 + 1]) * inv_l);
+      o.y = pack2<T>(__uint_as_float(oreg[g * 8 + 2]) * inv_l, __uint_as_float(oreg[g * 8 + 3]) * inv_l);
+      o.z = pack2<T>(__uint_as_float(oreg[g * 8 + 4]) * inv_l, __uint_as_float(oreg[g * 8 + 5]) * inv_l);
+      o.w = pack2<T>(__uint_as_float(oreg[g * 8 + 6]) * inv_l, __uint_as_float(oreg[g * 8 + 7]) * inv_l);
+      *reinterpret_cast<uint4*>(orow + g * 8) = o;
+    }
+  }
+}
+
 // ---- MMA groups of the two-tile kernel's issuing thread ------------------------------------
 // The issuing thread is one of the kernel's two bottlenecks: an MMA of 128x128x16 takes the thread
 // about as long to issue (65-75 clocks) as the tensor pipe needs to run it (68), and a barrier
@@ -1165,6 +1198,7 @@ fmha_fwd_kernel2(const __grid_constant__ CUtensorMap tmO, const __grid_constant_
 
 #include "fmha_pair_kernel.cuh"
 #include "fmha_split_kernel.cuh"
+#include "fmha_persist_kernel.cuh"
 
 template <typename T, int D>
 int launch_fmha2(const CUtensorMap& tmO, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FmhaParams& p,
@@ -1326,8 +1360,16 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
   // (The CTA-pair kernels, variants 3 and 4, are correct on every test shape but measured slower
   // than the two-tile kernel; they stay selectable.)  Extra outputs are written by variants 2 and 3.
   int variant = g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? 2 : 1);
-  if (variant >= 3 && D != 128) variant = 2;
-  if ((n_extra > 0 || mc_o) && (variant < 2 || variant == 4)) variant = 2;
+  if ((variant == 3 || variant == 4) && D != 128) variant = 2;
+  if ((n_extra > 0 || mc_o) && (variant < 2 || variant >= 4)) variant = 2;
+  if (variant == 5 && Sq <= BM) variant = 1;
+  if (variant == 5) {
+    if (dtype == KCG_BF16)
+      return D == 128 ? launch_fmha2p<__nv_bfloat16, 128>(tm[0], tm[1], tm[2], p, fmt, s)
+                      : launch_fmha2p<__nv_bfloat16, 64>(tm[0], tm[1], tm[2], p, fmt, s);
+    return D == 128 ? launch_fmha2p<__half, 128>(tm[0], tm[1], tm[2], p, fmt, s)
+                    : launch_fmha2p<__half, 64>(tm[0], tm[1], tm[2], p, fmt, s);
+  }
   if (variant == 4)
     return dtype == KCG_BF16 ? launch_fmha_split<__nv_bfloat16>(tm[0], tm[3], tm[2], p, fmt, s)
                              : launch_fmha_split<__half>(tm[0], tm[3], tm[2], p, fmt, s);

@@ -97,6 +97,7 @@ KernelCodeGenerator::KernelCodeGenerator(const std::string& platform_) : platfor
   fusionConfigs = {{{"EPILOGUE", 1}}};
   // VARIANT -1: the library picks the attention kernel by shape (CTA pair, two tiles, one tile)
   fmhaConfigs = {{{"BLOCK_SIZE", 384}, {"Br", 512}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}, {"VARIANT", -1}},
+                 {{"BLOCK_SIZE", 384}, {"Br", 256}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}, {"VARIANT", 5}},
                  {{"BLOCK_SIZE", 384}, {"Br", 512}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}, {"VARIANT", 3}},
                  {{"BLOCK_SIZE", 384}, {"Br", 256}, {"Bc", 128}, {"KV_STAGES", 3}, {"WARP_SIZE", 32}, {"VARIANT", 4}},
                  {{"BLOCK_SIZE", 384}, {"Br", 256}, {"Bc", 128}, {"KV_STAGES", 2}, {"WARP_SIZE", 32}, {"VARIANT", 2}},

@@ -58,8 +58,9 @@ def variant(request):
 # picks for a shape: 0 / 1 = one query tile per CTA with P through shared / tensor memory (also
 # for long sequences), 2 = two query tiles per CTA (also for a single, partly empty tile pair),
 # 3 = a CTA pair on four query tiles (also when most of the four are empty), 4 = a CTA pair with one
-# tile per CTA whose warpgroups take alternate key blocks (D = 64 runs variant 2 for both).
-@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4], indirect=True)
+# tile per CTA whose warpgroups take alternate key blocks (D = 64 runs variant 2 for both), 5 = the
+# two-tile kernel as a persistent grid.
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4, 5], indirect=True)
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("B,H,Sq,Skv,D", CASES)
@@ -149,3 +150,22 @@ def test_fmha_rejects_unsupported():
     Q32 = torch.zeros((1, 1, 128, 128), dtype=torch.float32, device="cuda")
     with pytest.raises(_lib.KcgError):
         ops().fmha(Q32, Q32, Q32)
+
+
+# The persistent kernel with more work items than SMs, so that every CTA walks over several items:
+# ragged last tile pair (one tile and an empty one), Sq != Skv, both masks, both head dimensions.
+@pytest.mark.parametrize("variant", [5], indirect=True)
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,H,Sq,Skv,D", [(3, 20, 640, 896, 128), (2, 40, 512, 512, 64), (5, 32, 300, 260, 128)])
+def test_fmha_persistent_many_items(B, H, Sq, Skv, D, causal, variant):
+    dtype = torch.bfloat16
+    Q = randn((B, H, Sq, D), dtype, 610)
+    K = randn((B, H, Skv, D), dtype, 611)
+    V = randn((B, H, Skv, D), dtype, 612)
+    scale = 1.0 / np.sqrt(D)
+    out = ops().fmha(Q.cuda(), K.cuda(), V.cuda(), scale, causal)
+    again = ops().fmha(Q.cuda(), K.cuda(), V.cuda(), scale, causal)
+    sync_ok()
+    want = O.attention_f64(f64(Q), f64(K), f64(V), scale, causal)
+    assert rel_fro(out, want) <= 1e-2
+    assert torch.equal(out, again)
