@@ -458,7 +458,7 @@ def main() -> None:
     def want(name):
         return not args.no_extras and (not only or name in only)
 
-    def time_op(fn, iters, replays=1, warm=3, idle=0.25):
+    def time_op(fn, iters, replays=1, warm=10, idle=0.25):
         """Device time of one call of `fn`: `iters` calls captured in a CUDA graph that is replayed
         `replays` times, each replay between its own pair of events on the launching stream.
         Returns a dict with the median, best and mean time per call over the replays
