@@ -716,7 +716,9 @@ int gemm_tcgen05(int dtype_in, int dtype_out, int64_t M, int64_t N, int64_t K, i
   } else {
     tmC = tmA;   // never read
   }
-  p.group_m = GROUP_M;   // 8, 32 and 64 were measured at 4096..16384: no better than 16
+  // 8, 32 and 64 were measured at 4096..16384: no better than 16 up to 8192^3; at 16384^3, where the
+  // kernel is held back by DRAM traffic (22-34 GB per launch depending on the group), 32 reads the least
+  p.group_m = static_cast<int64_t>(K) * es >= 32768 ? 2 * GROUP_M : GROUP_M;
   for (int i = 0; i < KCG_MAX_EXTRA_C; ++i) p.extra_c[i] = i < n_extra ? extra_c[i] : nullptr;
   if (n_extra > 0 || mc_c) {
     bool ok = p.c_vec_ok && (N * out_es) % 16 == 0 && aligned16(mc_c);
