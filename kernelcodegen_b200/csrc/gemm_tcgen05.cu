@@ -232,9 +232,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int STAGES = kBN == 256 ? 4 : (kBN == 128 ? 6 : 8);
   // Ring entries ("units") of kSub stages share one pair of barriers: the MMA thread's cost per
   // k-block, not the tensor pipe, bounds the narrow tiles, and a commit per 64 of K is a large
-  // part of it (two k-blocks per unit for the 128-wide tile, four for the 64-wide one, whose ring
-  // is still two units deep beyond the one in use).  The wide tile is pipe-bound and keeps the
-  // finer ring.
+  // part of it: two k-blocks per unit for the 128-wide tile (three units), four for the 64-wide
+  // one (two units, one in use and one loading).  The wide tile is pipe-bound and keeps the finer
+  // ring.
   constexpr int kSub = kBN == 256 ? 1 : (kBN == 128 ? 2 : 4);
   constexpr int UNITS = STAGES / kSub;
   constexpr int BK = 128 / kElemBytes;             // elements per k-block (128 bytes of K)
