@@ -504,6 +504,18 @@ def main() -> None:
         t = time_op(lambda: torch.matmul(A, B, out=C), iters, replays)
         return t
 
+    def cublaslt_fp8_tflops(A8, B8, one, C, iters, replays, flops):
+        """cuBLASLt's FP8 GEMM (torch._scaled_mm) on the same values: the library wants B column-major,
+        so it gets the transpose of a row-major [N, K] copy.  None when this torch build has no such call."""
+        try:
+            Bt = B8.t().contiguous()
+            fn = lambda: torch._scaled_mm(A8, Bt.t(), scale_a=one, scale_b=one, out_dtype=C.dtype, out=C)
+            fn()
+            t = time_op(fn, iters, replays)
+            return flops / (t["ms"] * 1e-3) / 1e12
+        except Exception:   # noqa: BLE001 - the comparison is optional
+            return None
+
     for op_name in ("layernorm", "gelu", "add"):
         # per-op split of the headline step, from the same buffers
         def one(i=[0]):
@@ -593,9 +605,10 @@ def main() -> None:
         one = torch.ones(1, device="cuda")
         e = entry(time_op(lambda: ops.matmul(A8, B8, out_dtype=dt, scale_a=one, scale_b=one, out=C), 10, 6), fl, "TFLOP/s")
         e["frac_of_nominal_4500"] = e["value"] / world / NOMINAL_FP8_TFLOPS
+        e["cublas_tflops"] = cublaslt_fp8_tflops(A8, B8, one, C, 10, 6, fl)
         workloads["gemm_fp8_8192"] = e
         tensor_entry("gemm_fp8_8192", "gemm_tcgen05_pair_kernel<f8f6f4 kind, e4m3 -> bf16>", e, fl, NOMINAL_FP8_TFLOPS,
-                     "gemm_tcgen05_pair_fp8_8192")
+                     "gemm_tcgen05_pair_fp8_8192", e["cublas_tflops"])
         del A, B, C, A8, B8
         torch.cuda.empty_cache()
 
@@ -714,8 +727,10 @@ def main() -> None:
             e = entry(time_op(lambda: ops.matmul(A8, B8, out_dtype=dt, scale_a=one, scale_b=one, out=C), iters, reps),
                       2 * n ** 3, "TFLOP/s")
             e["frac_of_nominal_4500"] = e["value"] / world / NOMINAL_FP8_TFLOPS
+            e["cublas_tflops"] = cublaslt_fp8_tflops(A8, B8, one, C, iters, reps, 2 * n ** 3)
             workloads[f"gemm_fp8_{n}"] = e
-            sweep[f"gemm_fp8_{n}"] = [round(e["value"] / world, 1), round(e["best"] / world, 1), None]
+            sweep[f"gemm_fp8_{n}"] = [round(e["value"] / world, 1), round(e["best"] / world, 1),
+                                      None if e["cublas_tflops"] is None else round(e["cublas_tflops"], 1)]
             del A8, B8, C
             torch.cuda.empty_cache()
     if world > 1 and not args.no_extras:
