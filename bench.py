@@ -516,6 +516,18 @@ def main() -> None:
         except Exception:   # noqa: BLE001 - the comparison is optional
             return None
 
+    def sdpa_tflops(Q, K, V, causal, iters, replays, flops):
+        """torch's fused attention (whichever library backend it picks for these tensors) on the same
+        operands, same timing: the library figure beside ours.  None when it cannot run."""
+        try:
+            F = torch.nn.functional
+            fn = lambda: F.scaled_dot_product_attention(Q, K, V, is_causal=causal)
+            fn()
+            t = time_op(fn, iters, replays)
+            return flops / (t["ms"] * 1e-3) / 1e12
+        except Exception:   # noqa: BLE001 - the comparison is optional
+            return None
+
     for op_name in ("layernorm", "gelu", "add"):
         # per-op split of the headline step, from the same buffers
         def one(i=[0]):
@@ -637,9 +649,12 @@ def main() -> None:
             e["frac_of_measured_bf16_peak"] = e["value"] / world / peaks["bf16_tflops"]
             e["frac_of_nominal_2250"] = e["value"] / world / NOMINAL_BF16_TFLOPS
             key = f"fmha_bf16_s4096_{'causal' if causal else 'full'}"
+            e["torch_sdpa_tflops"] = sdpa_tflops(Q, K, V, causal, 10, 5, fl)
             workloads[key] = e
             tensor_entry(key, "fmha_fwd_kernel2<bf16, D=128>", e, fl, NOMINAL_BF16_TFLOPS,
                          "fmha_fwd_bf16_b8_h32_s4096_d128" + ("_causal" if causal else ""))
+            if e["torch_sdpa_tflops"] is not None:
+                tensor[key]["torch_sdpa_tflops"] = e["torch_sdpa_tflops"]
         del Q, K, V, Oo
         torch.cuda.empty_cache()
     if want("bw2"):
@@ -687,7 +702,7 @@ def main() -> None:
         workloads["transpose_bf16_4x8192x8192"] = e
         del x, y
         torch.cuda.empty_cache()
-    sweep = {}    # compact copy kept inside "roofline": name -> [median, best, cuBLAS median] TFLOP/s per GPU
+    sweep = {}    # compact copy kept inside "roofline": name -> [median, best, library median] TFLOP/s per GPU
     if want("sweep"):
         # the other sizes of the GEMM and FMHA configurations (per GPU; N ranks run N copies)
         Bq, H, D = 8, 32, 128
@@ -699,8 +714,10 @@ def main() -> None:
                 e = entry(time_op(lambda: ops.fmha(Q, K, V, D ** -0.5, causal, out=Oo), 20, 3), fl, "TFLOP/s")
                 e["frac_of_nominal_2250"] = e["value"] / world / NOMINAL_BF16_TFLOPS
                 key = f"fmha_bf16_s{S}_{'causal' if causal else 'full'}"
+                lib = sdpa_tflops(Q, K, V, causal, 20, 3, fl)
+                e["torch_sdpa_tflops"] = lib
                 workloads[key] = e
-                sweep[key] = [round(e["value"] / world, 1), round(e["best"] / world, 1), None]
+                sweep[key] = [round(e["value"] / world, 1), round(e["best"] / world, 1), None if lib is None else round(lib, 1)]
             del Q, K, V, Oo
         torch.cuda.empty_cache()
         for n in (1024, 2048, 4096, 16384):
@@ -1022,7 +1039,7 @@ def main() -> None:
     if tensor:
         roofline["tensor"] = tensor
     if sweep:
-        roofline["sweep"] = {"columns": ["median TFLOP/s", "best TFLOP/s", "cuBLAS median TFLOP/s"], **sweep}
+        roofline["sweep"] = {"columns": ["median TFLOP/s", "best TFLOP/s", "library median TFLOP/s (cuBLAS / cuBLASLt for GEMM, torch SDPA for attention)"], **sweep}
     if sharded:
         roofline["sharded"] = sharded
     if rank == 0:
