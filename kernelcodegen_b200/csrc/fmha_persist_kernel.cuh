@@ -11,9 +11,9 @@
 //     item has completed (q_empty), i.e. under the current item's last softmax and PV;
 //   - the MMA thread issues the next item's first QK^T right behind the current item's last
 //     PV, so those scores are ready when the softmax warps return from storing the output;
-//   - the softmax warps store the output straight from registers (no staging: all shared
-//     memory is spoken for) and release the output accumulator (o_free) as soon as they have
-//     read it, before the stores are issued;
+//   - the softmax warps release the output accumulator (o_free) as soon as they have read it and
+//     send the rows out through TMA stores, staged in the K / V ring entry that is idle at the
+//     end of an item; the loader refills that entry only when all eight warps are done (stage_done);
 //   - every barrier keeps running across items: phases are counted, not derived from the
 //     key-block index.
 // Items are numbered head-major (the pairs of one head are adjacent, so CTAs working on the same
@@ -28,7 +28,7 @@ constexpr int V2P_REGS_SOFTMAX = 200, V2P_REGS_SERVICE = 104;   // 2*128*200 + 1
 
 template <typename T, int D>
 __global__ void __launch_bounds__(V2_THREADS, 1)
-fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FmhaParams p, const uint32_t idesc_qk,
                   const uint32_t idesc_pv) {
   constexpr int DB = D / 64;
@@ -52,7 +52,10 @@ fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   // s_full; here the next item's first score tile may complete right behind it, and a waiter
   // that has not yet looked at a barrier must never fall two phases behind it.)
   uint64_t* o_full = o_free + 2;
-  uint64_t* drain_bar = o_full + 2;
+  // [1]  all eight softmax warps have stored the item's output: the ring entry they staged it in
+  // (the one the item's second-to-last key block used) may receive the next item's first K / V
+  uint64_t* stage_done = o_full + 2;
+  uint64_t* drain_bar = stage_done + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -81,6 +84,7 @@ fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
+    prefetch_tmap(&tmO);
     mbar_init(q_full, 1);
     mbar_init(q_empty, 1);
     for (int s = 0; s < 2; ++s) {
@@ -94,6 +98,7 @@ fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_init(&o_free[i], 4);
       mbar_init(&o_full[i], 1);
     }
+    mbar_init(stage_done, 8);
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -134,6 +139,8 @@ fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int j = 0; j < it.nmax; ++j, ++g) {
           const uint32_t r = g & 1u, ph = (g >> 1) & 1u;
           if (g >= 2 && !mbar_wait(&kv_empty[r], ph ^ 1u, abort_flag)) { ok = false; break; }
+          // the previous item's output was staged in this ring entry on its way to global memory
+          if (j == 0 && n_item > 1 && !mbar_wait(stage_done, (n_item - 2) & 1u, abort_flag)) { ok = false; break; }
           const bool more = j + 1 < it.nmax;
           mbar_expect_tx(&kv_full[r], more ? 2 * TILE : TILE);
 #pragma unroll
@@ -264,6 +271,7 @@ fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t o_addr = tmem_base + lane_base + 256 + i * BN;
     uint32_t cs = 0;   // completions of s_full[i] consumed so far
     uint32_t cf = 0;   // completions of o_full[i] consumed so far
+    int g0 = 0;        // ring entries used by the items before this one
     bool ok = true;
     for (int k = blockIdx.x; k < items && ok; k += gridDim.x) {
       const Item it = decode(k);
@@ -285,12 +293,27 @@ fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         ++cf;
         tc_fence_after();
       }
-      store_output_direct<T, D>(p, o_addr, n_mine > 0, l, it.b, it.h, it.q0 + i * BM + quarter * 32, lane,
-                                [&]() {   // the accumulator has been read: the next item's first PV may overwrite it
-                                  tc_fence_before();
-                                  __syncwarp();
-                                  if (lane == 0) mbar_arrive(&o_free[i]);
-                                });
+      auto released = [&]() {   // the accumulator has been read: the next item's first PV may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&o_free[i]);
+      };
+      if (n_mine > 0) {
+        // Staging space: the ring entry of the item's second-to-last key block (the one that will
+        // next receive the following item's first K / V).  The longer tile's last block has left it
+        // by the time either tile gets here, except that the shorter tile of a causal pair finishes
+        // one block early and has to wait for the other tile to leave that block.
+        const int G = g0 + it.nmax - 2;   // global index of that key block; negative: the entry was never used
+        if (G >= 0 && !mbar_wait(&kv_empty[G & 1], (G >> 1) & 1u, abort_flag)) { ok = false; break; }
+        uint8_t* stg = kv_smem + (2 * (G >= 0 ? (G & 1) : 1)) * TILE + warp * (32 * D * 2);
+        store_output_tma<T, D>(p, o_addr, l, it.b, it.h, it.q0 + i * BM + quarter * 32, lane, stg, &tmO, released);
+      } else {
+        store_output_direct<T, D>(p, o_addr, false, l, it.b, it.h, it.q0 + i * BM + quarter * 32, lane, released);
+      }
+      if (it.nmax > 0) {
+        if (lane == 0) mbar_arrive(stage_done);
+        g0 += it.nmax;
+      }
     }
     if (!ok && lane == 0 && !*abort_flag) {
       *abort_flag = 1;
@@ -320,8 +343,8 @@ inline int persist_grid(int items, int pairs, int limit) {
 }
 
 template <typename T, int D>
-int launch_fmha2p(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FmhaParams& p, uint32_t fmt,
-                  cudaStream_t stream) {
+int launch_fmha2p(const CUtensorMap& tmO, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                  const FmhaParams& p, uint32_t fmt, cudaStream_t stream) {
   constexpr int DB = D / 64;
   constexpr int TILE = DB * TILE16K;
   constexpr int SMEM = 7 * TILE + 1024 + 256;
@@ -334,6 +357,6 @@ int launch_fmha2p(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensor
   const int64_t items64 = static_cast<int64_t>(pairs) * p.B * p.H;
   if (items64 > INT32_MAX) return fail(KCG_ERR_UNSUPPORTED, "fmha: too many work items for the persistent kernel");
   const int grid = persist_grid(static_cast<int>(items64), pairs, sm_count());
-  launch_overlapped(kern, dim3(static_cast<unsigned>(grid)), dim3(V2_THREADS), SMEM, stream, tmQ, tmK, tmV, p, idesc_qk, idesc_pv);
+  launch_overlapped(kern, dim3(static_cast<unsigned>(grid)), dim3(V2_THREADS), SMEM, stream, tmO, tmQ, tmK, tmV, p, idesc_qk, idesc_pv);
   return check_launch("fmha_fwd_kernel2p");
 }

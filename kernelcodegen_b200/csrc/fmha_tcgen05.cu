@@ -851,6 +851,42 @@ __device__ __forceinline__ void store_output_direct(const FmhaParams& p, uint32_
   }
 }
 
+// The warp's 32 finished output rows through the copy engine: read out of tensor memory in one go
+// (`released` runs right after, the accumulator may be overwritten from then on), packed into
+// swizzled boxes of 32 rows x 128 bytes in `stg` (D * 64 bytes of shared memory nobody else uses
+// at this moment) and handed to TMA stores, which write whole lines and clip at Sq.  Returns when
+// the copy engine has read the staging tile.
+template <typename T, int D, typename Released>
+__device__ __forceinline__ void store_output_tma(const FmhaParams& p, uint32_t o_addr, float l, int b, int h, int row0,
+                                                 int lane, uint8_t* stg, const CUtensorMap* tmO, Released released) {
+  const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+  uint32_t oreg[D];
+#pragma unroll
+  for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(o_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&oreg[cc * 32]));
+  tmem_wait_ld();
+  released();
+  if (row0 >= p.Sq) return;
+#pragma unroll
+  for (int g = 0; g < D / 8; ++g) {
+    uint4 o;
+    o.x = pack2<T>(__uint_as_float(oreg[g * 8 + 0]) * inv_l, __uint_as_float(oreg[g * 8 + 1]) * inv_l);
+    o.y = pack2<T>(__uint_as_float(oreg[g * 8 + 2]) * inv_l, __uint_as_float(oreg[g * 8 + 3]) * inv_l);
+    o.z = pack2<T>(__uint_as_float(oreg[g * 8 + 4]) * inv_l, __uint_as_float(oreg[g * 8 + 5]) * inv_l);
+    o.w = pack2<T>(__uint_as_float(oreg[g * 8 + 6]) * inv_l, __uint_as_float(oreg[g * 8 + 7]) * inv_l);
+    // box g / 8 (64 columns = 128 bytes per row), 16-byte chunk g % 8 within the row
+    *reinterpret_cast<uint4*>(stg + (g >> 3) * 4096 + lane * 128 + (((g & 7) ^ (lane & 7)) << 4)) = o;
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+#pragma unroll
+    for (int d = 0; d < D / 64; ++d) tma_store_4d(tmO, stg + d * 4096, d * 64, row0, h, b);
+    tma_store_commit();
+    tma_store_wait_read<0>();
+  }
+  __syncwarp();
+}
+
 // ---- MMA groups of the two-tile kernel's issuing thread ------------------------------------
 // The issuing thread is one of the kernel's two bottlenecks: an MMA of 128x128x16 takes the thread
 // about as long to issue (65-75 clocks) as the tensor pipe needs to run it (68), and a barrier
@@ -1356,19 +1392,20 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
     if (!extra_o[i] || !aligned16(extra_o[i])) return fail(KCG_ERR_ALIGNMENT, "fmha: extra output %d is null or not 16-byte aligned", i);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const uint32_t fmt = dtype == KCG_BF16 ? 1u : 0u;
-  // By shape: two query tiles per CTA when there is more than one tile of queries, else one tile.
-  // (The CTA-pair kernels, variants 3 and 4, are correct on every test shape but measured slower
-  // than the two-tile kernel; they stay selectable.)  Extra outputs are written by variants 2 and 3.
-  int variant = g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? 2 : 1);
+  // By shape: the persistent two-tile kernel when there is more than one tile of queries, else one
+  // tile per CTA.  (The CTA-pair kernels, variants 3 and 4, are correct on every test shape but
+  // measured slower; they and the one-shot two-tile kernel stay selectable.)  Extra outputs (the
+  // gather epilogues) are written by variants 2 and 3.
+  int variant = g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? 5 : 1);
   if ((variant == 3 || variant == 4) && D != 128) variant = 2;
   if ((n_extra > 0 || mc_o) && (variant < 2 || variant >= 4)) variant = 2;
   if (variant == 5 && Sq <= BM) variant = 1;
   if (variant == 5) {
     if (dtype == KCG_BF16)
-      return D == 128 ? launch_fmha2p<__nv_bfloat16, 128>(tm[0], tm[1], tm[2], p, fmt, s)
-                      : launch_fmha2p<__nv_bfloat16, 64>(tm[0], tm[1], tm[2], p, fmt, s);
-    return D == 128 ? launch_fmha2p<__half, 128>(tm[0], tm[1], tm[2], p, fmt, s)
-                    : launch_fmha2p<__half, 64>(tm[0], tm[1], tm[2], p, fmt, s);
+      return D == 128 ? launch_fmha2p<__nv_bfloat16, 128>(tm[4], tm[0], tm[1], tm[2], p, fmt, s)
+                      : launch_fmha2p<__nv_bfloat16, 64>(tm[4], tm[0], tm[1], tm[2], p, fmt, s);
+    return D == 128 ? launch_fmha2p<__half, 128>(tm[4], tm[0], tm[1], tm[2], p, fmt, s)
+                    : launch_fmha2p<__half, 64>(tm[4], tm[0], tm[1], tm[2], p, fmt, s);
   }
   if (variant == 4)
     return dtype == KCG_BF16 ? launch_fmha_split<__nv_bfloat16>(tm[0], tm[3], tm[2], p, fmt, s)
