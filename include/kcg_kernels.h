@@ -339,7 +339,8 @@ KCG_API int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Sk
 
 /*
  * Tuning switch with no counterpart in the reference: which attention kernel runs.
- *   -1 (default)  chosen by shape: variant 5 when Sq > 128 (variant 2 for the gather epilogues), else 1;
+ *   -1 (default)  chosen by shape: variant 5 when Sq > 128 (variant 2 for the gather epilogues and for a
+ *                 causal mask over 32 or more query tiles), else 1;
  *    5            the two-tile kernel as a persistent grid: a CTA stays resident and walks over
  *                 (tile pair, batch x head) work items, loading the next item's Q and K_0 and issuing
  *                 its first QK^T under the current item's last key block, the output leaving through

@@ -1396,7 +1396,11 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
   // tile per CTA.  (The CTA-pair kernels, variants 3 and 4, are correct on every test shape but
   // measured slower; they and the one-shot two-tile kernel stay selectable.)  Extra outputs (the
   // gather epilogues) are written by variants 2 and 3.
-  int variant = g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? 5 : 1);
+  // A causal mask over many tile pairs (S >= 4096) makes the items very unequal (3 to 63 key-block
+  // units at S = 4096); the persistent grid deals items out statically and its last CTAs then finish
+  // up to one long item apart (-5 % sustained), where the one-shot kernel's CTAs are scheduled as
+  // SMs fall free; that shape keeps the one-shot kernel.
+  int variant = g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? ((causal && p.q_tiles >= 32) ? 2 : 5) : 1);
   if ((variant == 3 || variant == 4) && D != 128) variant = 2;
   if ((n_extra > 0 || mc_o) && (variant < 2 || variant >= 4)) variant = 2;
   if (variant == 5 && Sq <= BM) variant = 1;
