@@ -651,8 +651,7 @@ def main() -> None:
             key = f"fmha_bf16_s4096_{'causal' if causal else 'full'}"
             e["torch_sdpa_tflops"] = sdpa_tflops(Q, K, V, causal, 10, 5, fl)
             workloads[key] = e
-            tensor_entry(key, "fmha_fwd_kernel2<bf16, D=128> (two-tile kernel)" if causal else
-                         "fmha_fwd_kernel2p<bf16, D=128> (persistent two-tile kernel)", e, fl, NOMINAL_BF16_TFLOPS,
+            tensor_entry(key, "fmha_fwd_kernel2p<bf16, D=128> (persistent two-tile kernel)", e, fl, NOMINAL_BF16_TFLOPS,
                          "fmha_fwd_bf16_b8_h32_s4096_d128" + ("_causal" if causal else ""))
             if e["torch_sdpa_tflops"] is not None:
                 tensor[key]["torch_sdpa_tflops"] = e["torch_sdpa_tflops"]

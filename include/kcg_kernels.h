@@ -339,13 +339,13 @@ KCG_API int kcg_fmha_fwd(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Sk
 
 /*
  * Tuning switch with no counterpart in the reference: which attention kernel runs.
- *   -1 (default)  chosen by shape: variant 5 when Sq > 128 (variant 2 for the gather epilogues and for a
- *                 causal mask over 32 or more query tiles), else 1;
+ *   -1 (default)  chosen by shape: variant 5 when Sq > 128 (variant 2 for the gather epilogues), else 1;
  *    5            the two-tile kernel as a persistent grid: a CTA stays resident and walks over
  *                 (tile pair, batch x head) work items, loading the next item's Q and K_0 and issuing
  *                 its first QK^T under the current item's last key block, the output leaving through
- *                 TMA stores staged in the idle K / V ring entry (no gather epilogue; Sq <= 128 runs
- *                 variant 1);
+ *                 TMA stores staged in the idle K / V ring entry; with a causal mask the items are dealt
+ *                 so that every CTA gets long and short tile pairs alike (no gather epilogue; Sq <= 128
+ *                 runs variant 1);
  *    4            CTA pair with one query tile per CTA, two score buffers and P in tensor-memory
  *                 columns of its own; the two softmax warpgroups take alternate key blocks and
  *                 two threads issue the MMAs (D = 128 only, no gather epilogue);

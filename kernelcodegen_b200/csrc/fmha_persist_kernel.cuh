@@ -18,19 +18,22 @@
 //     key-block index.
 // Items are numbered head-major (the pairs of one head are adjacent, so CTAs working on the same
 // head at the same time share its K / V through L2); for a causal mask the pairs of a head run
-// longest first, and the grid size is chosen coprime to the pairs per head so that every CTA
-// meets all pair lengths in turn.
+// longest first, and grid size and dealing order are chosen so that every CTA gets a fair mix
+// of pair lengths (persist_plan).
 #pragma once
 
 // The issuing thread carries more state across items than in the one-item kernel (phase counters of
 // every barrier, the item's coordinates): 104 registers for the service warps, 200 for the softmax warps.
-constexpr int V2P_REGS_SOFTMAX = 200, V2P_REGS_SERVICE = 104;   // 2*128*200 + 128*104 = 64512 <= 65536
+// setmaxnreg only redistributes the registers the CTA was launched with (384 threads x 168): a split
+// that adds up to more makes the raising warps wait for registers that never come.
+constexpr int V2P_REGS_SOFTMAX = 200, V2P_REGS_SERVICE = 104;
+static_assert(2 * 128 * V2P_REGS_SOFTMAX + 128 * V2P_REGS_SERVICE <= V2_THREADS * 168, "register split exceeds the CTA's allocation");
 
 template <typename T, int D>
 __global__ void __launch_bounds__(V2_THREADS, 1)
 fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FmhaParams p, const uint32_t idesc_qk,
-                  const uint32_t idesc_pv) {
+                  const uint32_t idesc_pv, const int snake) {
   constexpr int DB = D / 64;
   constexpr int TILE = DB * TILE16K;   // bytes of one Q, K or V tile
   constexpr int NSLOT = 5;             // two (V, K) ring entries plus the slot of K_0
@@ -80,6 +83,15 @@ fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmO, const __grid_constant
     return it;
   };
 
+  // This CTA's item of round r (items are dealt in rounds of gridDim.x): in the plain order CTA c
+  // takes item r * G + c; in the snake order every second round runs backwards, so that with a
+  // grid that is a multiple of the pairs per head a CTA alternates between a pair position and its
+  // mirror image (the longest and the shortest pair of a causal head, and so on).
+  auto item_of_round = [&](int r) {
+    const int c = (snake && (r & 1)) ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+    return r * static_cast<int>(gridDim.x) + c;
+  };
+
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
@@ -121,7 +133,9 @@ fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmO, const __grid_constant
       bool ok = true;
       uint32_t n_item = 0;   // items with key blocks loaded so far
       uint32_t g = 0;        // ring entries filled so far
-      for (int k = blockIdx.x; k < items && ok; k += gridDim.x) {
+      for (int rd = 0; rd * static_cast<int>(gridDim.x) < items && ok; ++rd) {
+        const int k = item_of_round(rd);
+        if (k >= items) continue;
         const Item it = decode(k);
         if (it.nmax == 0) continue;
         // Q of both tiles and K_0: free once the previous item's last QK^T has completed
@@ -187,7 +201,9 @@ fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmO, const __grid_constant
       uint32_t co0 = 0, co1 = 0;      // items whose output accumulator this tile has produced (o_free phases)
       // Barriers already seen complete by a test that rode along with an earlier MMA batch
       bool r_kv = false, r_p00 = false, r_p01 = false, r_p10 = false, r_p11 = false;
-      for (int k = blockIdx.x; k < items && ok; k += gridDim.x) {
+      for (int rd = 0; rd * static_cast<int>(gridDim.x) < items && ok; ++rd) {
+        const int k = item_of_round(rd);
+        if (k >= items) continue;
         const Item it = decode(k);
         if (it.nmax == 0) continue;
         if (!mbar_wait(q_full, n_item & 1u, abort_flag)) { ok = false; break; }
@@ -273,7 +289,9 @@ fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmO, const __grid_constant
     uint32_t cf = 0;   // completions of o_full[i] consumed so far
     int g0 = 0;        // ring entries used by the items before this one
     bool ok = true;
-    for (int k = blockIdx.x; k < items && ok; k += gridDim.x) {
+    for (int rd = 0; rd * static_cast<int>(gridDim.x) < items && ok; ++rd) {
+      const int k = item_of_round(rd);
+      if (k >= items) continue;
       const Item it = decode(k);
       const int n_mine = i == 0 ? it.n0 : it.n1;
       const int qi = it.q0 + i * BM + r;
@@ -332,14 +350,49 @@ fmha_fwd_kernel2p(const __grid_constant__ CUtensorMap tmO, const __grid_constant
   }
 }
 
-// Largest grid <= limit that is coprime to `pairs`, so that a CTA striding over head-major items
-// visits every pair position of a head in turn.
-inline int persist_grid(int items, int pairs, int limit) {
+// Grid size and dealing order of the persistent kernel.  Items are head-major; with a causal mask
+// the pairs of a head cost from 3 to 4 * pairs - 1 key-block units, and what matters is the most
+// loaded CTA.  Two schemes are compared on the item costs themselves: every SM with the snake order
+// (balanced when the SM count is a multiple of the pairs per head and the number of rounds is
+// even), or the largest grid coprime to the pairs per head with the plain order (every CTA meets
+// all pair positions in turn).  Without a mask all items are equal and every SM is used.
+struct PersistPlan { int grid; int snake; };
+inline PersistPlan persist_plan(const FmhaParams& p, int items, int pairs, int sms) {
+  if (items <= sms) return {items, 0};
+  if (!p.causal) return {sms, 0};
   auto gcd = [](int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; };
-  int g = items < limit ? items : limit;
-  if (g == items) return g;   // one item per CTA at most
-  while (g > 1 && gcd(g, pairs) != 1) --g;
-  return g;
+  int g_plain = sms;
+  while (g_plain > 1 && gcd(g_plain, pairs) != 1) --g_plain;
+  const int off = p.Skv - p.Sq;
+  auto cost = [&](int pos) {   // key blocks of both tiles of the pair at position `pos` of a head, plus a fixed part
+    const int pr = pairs - 1 - pos;
+    const int q0 = pr * 2 * BM;
+    const int e0 = std::min(p.Skv, q0 + BM + off), e1 = std::min(p.Skv, q0 + 2 * BM + off);
+    const int n0 = e0 > 0 ? (e0 + BN - 1) / BN : 0, n1 = e1 > 0 ? (e1 + BN - 1) / BN : 0;
+    return n0 + n1 + 3;
+  };
+  std::vector<int> pos_cost(pairs);
+  for (int i = 0; i < pairs; ++i) pos_cost[i] = cost(i);
+  auto max_load = [&](int grid, int snake) {
+    std::vector<int64_t> load(grid, 0);
+    for (int k = 0; k < items; ++k) {
+      const int r = k / grid;
+      int c = k % grid;
+      if (snake && (r & 1)) c = grid - 1 - c;
+      load[c] += pos_cost[k % pairs];
+    }
+    int64_t m = 0;
+    for (int64_t v : load) m = std::max(m, v);
+    return m;
+  };
+  // the decision depends on (items, pairs, mask geometry) only: remember the last one per thread
+  thread_local int key[4] = {-1, -1, -1, -1};
+  thread_local PersistPlan last = {0, 0};
+  if (key[0] == items && key[1] == pairs && key[2] == p.Sq && key[3] == p.Skv) return last;
+  const int64_t a = max_load(sms, 1), b = max_load(g_plain, 0);
+  last = a <= b ? PersistPlan{sms, 1} : PersistPlan{g_plain, 0};
+  key[0] = items; key[1] = pairs; key[2] = p.Sq; key[3] = p.Skv;
+  return last;
 }
 
 template <typename T, int D>
@@ -356,7 +409,8 @@ int launch_fmha2p(const CUtensorMap& tmO, const CUtensorMap& tmQ, const CUtensor
   const int pairs = (p.q_tiles + 1) / 2;
   const int64_t items64 = static_cast<int64_t>(pairs) * p.B * p.H;
   if (items64 > INT32_MAX) return fail(KCG_ERR_UNSUPPORTED, "fmha: too many work items for the persistent kernel");
-  const int grid = persist_grid(static_cast<int>(items64), pairs, sm_count());
-  launch_overlapped(kern, dim3(static_cast<unsigned>(grid)), dim3(V2_THREADS), SMEM, stream, tmO, tmQ, tmK, tmV, p, idesc_qk, idesc_pv);
+  const PersistPlan plan = persist_plan(p, static_cast<int>(items64), pairs, sm_count());
+  launch_overlapped(kern, dim3(static_cast<unsigned>(plan.grid)), dim3(V2_THREADS), SMEM, stream, tmO, tmQ, tmK, tmV, p, idesc_qk,
+                    idesc_pv, plan.snake);
   return check_launch("fmha_fwd_kernel2p");
 }

@@ -23,6 +23,9 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
+#include <algorithm>
+#include <vector>
+
 
 // Pairs of exponentials whose index has all bits of this mask set are computed on the FMA pipe
 // (exp2_pair_fma) instead of the special-function unit: 0 none, 7 one in eight, 3 one in four.
@@ -987,7 +990,8 @@ __device__ __forceinline__ void pv4_s_commit_peek2(uint32_t d_o, uint32_t a_p, u
 // gives most of its registers to the softmax warpgroups (setmaxnreg), whose 128-element score
 // rows otherwise spill at the 168 registers a 384-thread CTA gets per thread.
 constexpr int V2_THREADS = 384;
-constexpr int V2_REGS_SOFTMAX = 208, V2_REGS_SERVICE = 88;   // 2*128*208 + 128*88 = 64512 <= 65536
+constexpr int V2_REGS_SOFTMAX = 208, V2_REGS_SERVICE = 88;   // 2*128*208 + 128*88 = 64512 = 384 x 168, what the CTA is launched with
+static_assert(2 * 128 * V2_REGS_SOFTMAX + 128 * V2_REGS_SERVICE <= V2_THREADS * 168, "register split exceeds the CTA's allocation");
 
 template <typename T, int D, int NSLOT>
 __global__ void __launch_bounds__(V2_THREADS, 1)
@@ -1396,11 +1400,7 @@ int fmha_fwd_impl(int dtype, int64_t B, int64_t H, int64_t Sq, int64_t Skv, int6
   // tile per CTA.  (The CTA-pair kernels, variants 3 and 4, are correct on every test shape but
   // measured slower; they and the one-shot two-tile kernel stay selectable.)  Extra outputs (the
   // gather epilogues) are written by variants 2 and 3.
-  // A causal mask over many tile pairs (S >= 4096) makes the items very unequal (3 to 63 key-block
-  // units at S = 4096); the persistent grid deals items out statically and its last CTAs then finish
-  // up to one long item apart (-5 % sustained), where the one-shot kernel's CTAs are scheduled as
-  // SMs fall free; that shape keeps the one-shot kernel.
-  int variant = g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? ((causal && p.q_tiles >= 32) ? 2 : 5) : 1);
+  int variant = g_p_in_tmem >= 0 ? g_p_in_tmem : (Sq > BM ? 5 : 1);
   if ((variant == 3 || variant == 4) && D != 128) variant = 2;
   if ((n_extra > 0 || mc_o) && (variant < 2 || variant >= 4)) variant = 2;
   if (variant == 5 && Sq <= BM) variant = 1;
