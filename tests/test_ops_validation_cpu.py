@@ -70,3 +70,25 @@ def test_out_dtype_and_layout_checked():
 def test_cpu_tensors_still_refused():
     with pytest.raises(ValueError, match="CUDA tensors"):
         ops.matmul(t(64, 32), t(32, 16))
+
+
+class _FakeBuffers:
+    """Stands in for shard.MulticastBuffers: only the fields the argument checks read."""
+    def __init__(self, total_rows, cols, dtype, mc_ptr, world=2, rank=0):
+        self.total_rows, self.cols, self.dtype, self.mc_ptr = total_rows, cols, dtype, mc_ptr
+        self.world, self.rank, self.group, self.local = world, rank, None, None
+
+
+def test_layernorm_allgather_arguments_checked():
+    # every mismatch that would make the kernel write outside the gathered tensor raises before any launch
+    from kernelcodegen_b200 import shard
+    x = torch.zeros(8, 64, dtype=torch.bfloat16)
+    g = torch.ones(64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="multicast"):
+        shard.layernorm_allgather(x, g, g, _FakeBuffers(16, 64, torch.bfloat16, 0))
+    with pytest.raises(ValueError, match="width"):
+        shard.layernorm_allgather(x, g, g, _FakeBuffers(16, 128, torch.bfloat16, 1 << 20))
+    with pytest.raises(ValueError, match="dtype"):
+        shard.layernorm_allgather(x.float(), g, g, _FakeBuffers(16, 64, torch.bfloat16, 1 << 20))
+    with pytest.raises(ValueError, match="CUDA"):
+        shard.layernorm_allgather(x, g, g, _FakeBuffers(16, 64, torch.bfloat16, 1 << 20))
