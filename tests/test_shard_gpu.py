@@ -76,15 +76,14 @@ def _worker(rank, world, port, results):
                 print(f"rank {rank}: multicast gather used: {bool(mb.mc_ptr)}", flush=True)
             finally:
                 mb.close()
-            if True:
-                ml = shard.MulticastBuffers(4096, 2048, torch.bfloat16)
-                try:
-                    if ml.mc_ptr:
-                        yl = shard.layernorm_allgather(shard.shard_rows(x).contiguous(), gm, gm, ml, 1e-5)
-                        torch.cuda.synchronize()
-                        ok = ok and torch.equal(yl, ops.layernorm(x, gm, gm, 1, 1e-5))
-                finally:
-                    ml.close()
+            ml = shard.MulticastBuffers(4096, 2048, torch.bfloat16)
+            try:
+                if ml.mc_ptr:
+                    yl = shard.layernorm_allgather(shard.shard_rows(x).contiguous(), gm, gm, ml, 1e-5)
+                    torch.cuda.synchronize()
+                    ok = ok and torch.equal(yl, ops.layernorm(x, gm, gm, 1, 1e-5))
+            finally:
+                ml.close()
             mf = shard.MulticastBuffers(6 * 2 * 256, 128, torch.bfloat16)
             try:
                 out = shard.fmha_allgather(shard.shard_rows(Q).contiguous(), shard.shard_rows(K).contiguous(),
